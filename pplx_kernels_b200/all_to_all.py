@@ -1,0 +1,312 @@
+"""Python face of the dispatch/combine all-to-all.
+
+Role parity: src/pplx_kernels/all_to_all.py:11-164 of the reference.  The class
+name, the two constructors, the ``dispatch``/``combine``/``destroy`` methods and
+all argument names and orders are the same, so code written against the
+reference runs unchanged.  Additions: ``check_status`` (a wait that ran out is
+reported instead of hanging), tunables, and ``local_world`` / ``dispatch_group``
+/ ``combine_group`` which run several ranks on one GPU inside a single
+cooperative launch.  The reference's requirement of more than one DP group is
+dropped: ``world_size == dp_size`` (including a single GPU) is accepted.
+"""
+
+from __future__ import annotations
+
+from collections.abc import Callable, Sequence
+from typing import Any
+
+import torch
+
+from .ops import _ops
+
+
+def _resolve_group_name(group_name: str) -> str:
+    """Returns a name that the C++ side can resolve to a ProcessGroup."""
+    c10d = torch._C._distributed_c10d
+    try:
+        c10d._resolve_process_group(group_name)
+        return group_name
+    except Exception:
+        pass
+    import torch.distributed as dist
+
+    if not dist.is_initialized():
+        raise RuntimeError(
+            f"process group {group_name!r} is not registered and torch.distributed is not initialised"
+        )
+    world = dist.group.WORLD
+    try:
+        c10d._register_process_group(group_name, world)
+        return group_name
+    except Exception:
+        return world.group_name
+
+
+class AllToAll:
+    def __init__(
+        self,
+        ptr: Any,
+        combine_fn: Callable,
+        dispatch_fn: Callable,
+        has_scales: bool,
+    ) -> None:
+        self._ptr = ptr
+        self._combine_fn = combine_fn
+        self._dispatch_fn = dispatch_fn
+        self._has_scales = has_scales
+
+    def __del__(self) -> None:
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------ operations --
+
+    def dispatch(
+        self,
+        out_expert_num_tokens: torch.Tensor,
+        out_expert_x: torch.Tensor,
+        out_expert_x_scale: torch.Tensor | None,
+        dp_x: torch.Tensor,
+        dp_x_scale: torch.Tensor | None,
+        indices: torch.Tensor,
+        bound_m: torch.Tensor | None,
+        do_send: bool = True,
+        do_recv: bool = True,
+    ) -> None:
+        assert self._ptr is not None
+        if self._has_scales:
+            assert out_expert_x_scale is not None
+            assert dp_x_scale is not None
+        else:
+            assert out_expert_x_scale is None
+            assert dp_x_scale is None
+        self._dispatch_fn(
+            self._ptr,
+            out_expert_num_tokens,
+            out_expert_x,
+            out_expert_x_scale,
+            dp_x,
+            dp_x_scale,
+            indices,
+            bound_m,
+            do_send,
+            do_recv,
+        )
+
+    def combine(
+        self,
+        out_tokens: torch.Tensor,
+        indices: torch.Tensor,
+        weights: torch.Tensor,
+        expert_y: torch.Tensor,
+        bound_m: torch.Tensor | None,
+        do_send: bool = True,
+        do_recv: bool = True,
+    ) -> None:
+        assert self._ptr is not None
+        self._combine_fn(
+            self._ptr,
+            out_tokens,
+            indices,
+            weights,
+            expert_y,
+            bound_m,
+            do_send,
+            do_recv,
+        )
+
+    def destroy(self) -> None:
+        if self._ptr is not None:
+            _ops.all_to_all_destroy(self._ptr)
+            self._ptr = None
+
+    # ---------------------------------------------------- status and tunables --
+
+    def status(self) -> dict[str, int]:
+        """Failure record of this object; ``code == 0`` means healthy.  Synchronises."""
+        keys = ("code", "phase", "peer", "expected", "observed", "block", "rank", "count")
+        return dict(zip(keys, _ops.all_to_all_status(self._ptr), strict=True))
+
+    def check_status(self) -> None:
+        """Raises RuntimeError if a device-side wait ran out or a bounds check failed."""
+        _ops.all_to_all_check_status(self._ptr)
+
+    def set_timeout_ms(self, ms: float) -> None:
+        _ops.all_to_all_set_timeout_ms(self._ptr, float(ms))
+
+    def set_debug_checks(self, on: bool) -> None:
+        _ops.all_to_all_set_debug_checks(self._ptr, bool(on))
+
+    def set_max_blocks(self, n: int) -> None:
+        _ops.all_to_all_set_max_blocks(self._ptr, int(n))
+
+    def layout(self) -> dict[str, int]:
+        keys = ("num_local_experts", "num_dp_groups", "rows_per_expert", "region_slots",
+                "slot_bytes", "arena_bytes")
+        return dict(zip(keys, _ops.all_to_all_layout(self._ptr), strict=True))
+
+    # ------------------------------------------------------------ constructors --
+
+    @classmethod
+    def intranode(
+        cls,
+        max_num_tokens: int,
+        num_experts: int,
+        experts_per_token: int,
+        rank: int,
+        world_size: int,
+        dp_size: int,
+        hidden_dim: int,
+        hidden_dim_bytes: int,
+        hidden_dim_scale_bytes: int,
+        group_name: str = "default",
+    ) -> "AllToAll":
+        assert world_size % dp_size == 0
+        has_scales = hidden_dim_scale_bytes > 0
+        if world_size > 1:
+            group_name = _resolve_group_name(group_name)
+        ptr = _ops.all_to_all_intranode_create(
+            max_num_tokens,
+            num_experts,
+            experts_per_token,
+            rank,
+            world_size,
+            dp_size,
+            hidden_dim,
+            hidden_dim_bytes,
+            hidden_dim_scale_bytes,
+            group_name,
+        )
+        assert ptr != 0
+        return cls(
+            ptr,
+            _ops.all_to_all_intranode_combine,
+            _ops.all_to_all_intranode_dispatch,
+            has_scales,
+        )
+
+    @classmethod
+    def internode(
+        cls,
+        max_num_tokens: int,
+        num_experts: int,
+        experts_per_token: int,
+        rank: int,
+        world_size: int,
+        dp_size: int,
+        hidden_dim: int,
+        hidden_dim_bytes: int,
+        hidden_dim_scale_bytes: int,
+    ) -> "AllToAll":
+        assert world_size % dp_size == 0
+        has_scales = hidden_dim_scale_bytes > 0
+        ptr = _ops.all_to_all_internode_create(
+            max_num_tokens,
+            num_experts,
+            experts_per_token,
+            rank,
+            world_size,
+            dp_size,
+            hidden_dim,
+            hidden_dim_bytes,
+            hidden_dim_scale_bytes,
+        )
+        assert ptr != 0
+        return cls(
+            ptr,
+            _ops.all_to_all_internode_combine,
+            _ops.all_to_all_internode_dispatch,
+            has_scales,
+        )
+
+    @classmethod
+    def local_world(
+        cls,
+        max_num_tokens: int,
+        num_experts: int,
+        experts_per_token: int,
+        world_size: int,
+        dp_size: int,
+        hidden_dim: int,
+        hidden_dim_bytes: int,
+        hidden_dim_scale_bytes: int,
+    ) -> list["AllToAll"]:
+        """``world_size`` ranks that all live on the current GPU of this process.
+
+        They must be driven together with ``dispatch_group`` / ``combine_group``:
+        ranks wait on one another, so they have to run inside one launch.
+        """
+        assert world_size % dp_size == 0
+        ptrs = _ops.all_to_all_local_world_create(
+            max_num_tokens,
+            num_experts,
+            experts_per_token,
+            world_size,
+            dp_size,
+            hidden_dim,
+            hidden_dim_bytes,
+            hidden_dim_scale_bytes,
+        )
+        has_scales = hidden_dim_scale_bytes > 0
+        return [
+            cls(p, _ops.all_to_all_intranode_combine, _ops.all_to_all_intranode_dispatch, has_scales)
+            for p in ptrs
+        ]
+
+
+def _or_empty(t: torch.Tensor | None, device: torch.device) -> torch.Tensor:
+    return t if t is not None else torch.empty(0, device=device)
+
+
+def dispatch_group(
+    ranks: Sequence[AllToAll],
+    out_expert_num_tokens: Sequence[torch.Tensor],
+    out_expert_x: Sequence[torch.Tensor],
+    out_expert_x_scale: Sequence[torch.Tensor | None],
+    dp_x: Sequence[torch.Tensor],
+    dp_x_scale: Sequence[torch.Tensor | None],
+    indices: Sequence[torch.Tensor],
+    bound_m: Sequence[torch.Tensor | None],
+    do_send: bool = True,
+    do_recv: bool = True,
+) -> None:
+    """One dispatch of every rank of a local world, as a single cooperative launch."""
+    dev = dp_x[0].device
+    _ops.all_to_all_dispatch_group(
+        [r._ptr for r in ranks],
+        list(out_expert_num_tokens),
+        list(out_expert_x),
+        [_or_empty(t, dev) for t in out_expert_x_scale],
+        list(dp_x),
+        [_or_empty(t, dev) for t in dp_x_scale],
+        list(indices),
+        [_or_empty(t, dev) for t in bound_m],
+        do_send,
+        do_recv,
+    )
+
+
+def combine_group(
+    ranks: Sequence[AllToAll],
+    out_tokens: Sequence[torch.Tensor],
+    indices: Sequence[torch.Tensor],
+    weights: Sequence[torch.Tensor],
+    expert_y: Sequence[torch.Tensor],
+    bound_m: Sequence[torch.Tensor | None],
+    do_send: bool = True,
+    do_recv: bool = True,
+) -> None:
+    """One combine of every rank of a local world, as a single cooperative launch."""
+    dev = expert_y[0].device
+    _ops.all_to_all_combine_group(
+        [r._ptr for r in ranks],
+        list(out_tokens),
+        list(indices),
+        list(weights),
+        list(expert_y),
+        [_or_empty(t, dev) for t in bound_m],
+        do_send,
+        do_recv,
+    )

@@ -1,0 +1,114 @@
+// Plain-data description of one rank's all-to-all state, shared by host and device.
+//
+// Role parity: the reference's device-side `BufferWrapper` (intranode.cuh:10-64)
+// and the buffer tables of AllToAllIntraNode / AllToAllInterNode
+// (intranode.h:66-88, internode.h:111-132).  The design differs:
+//
+//  * One symmetric arena per rank holds every region that peers touch, at the
+//    same offsets on every rank, so the kernels need a single table of peer base
+//    pointers.
+//  * Dispatch staging is keyed by SOURCE RANK only.  A sender sorts its rows by
+//    destination-local expert with a prefix sum it computes from `indices`, so
+//    the region holds at most `ceil(max_tokens/dp_size) * min(topk, nle)` slots
+//    instead of `nle * max_tokens`.
+//  * Combine staging is keyed by (token, k): each token's top-k expert outputs
+//    sit side by side at its home rank, `max_tokens * topk` rows in total rather
+//    than `max_tokens * num_experts`.
+//  * Counts and arrival counters exist twice, selected by the parity of a
+//    device-side iteration counter.  No flag handshake is needed before a send:
+//    a rank can be at most one dispatch ahead of any peer, because every rank
+//    posts counts to every rank in every dispatch.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+#include "../core/status.h"
+
+namespace pplx {
+
+constexpr int kMaxWorld = 16;
+
+struct A2AParams {
+  // geometry
+  int rank;
+  int world;
+  int dp_size;
+  int num_dp_groups;
+  int num_experts;
+  int nle;           // experts owned by each rank
+  int topk;
+  int max_tokens;    // per DP group and step
+  int hidden_dim;    // elements
+  int hidden_bytes;  // dispatch payload bytes per token (multiple of 16)
+  int scale_bytes;   // fp32 scale bytes per token (multiple of 16, may be 0)
+  int slot_bytes;    // hidden_bytes + scale_bytes + 16 (trailer)
+  int region_slots;  // dispatch staging slots per source rank
+  int cap;           // rows per local expert in out_expert_x / expert_y
+  int debug_checks;  // non-zero: bounds checks that record instead of corrupting
+
+  // offsets into the symmetric arena (bytes, 256-aligned)
+  size_t off_counts;        // u32 [2][world][nle]   value = count + 1, 0 = not posted
+  size_t off_arrived;       // u32 [2][world]        rows landed from each source
+  size_t off_comb_arrived;  // u32 [max_tokens]      expert outputs landed per token
+  size_t off_disp_stage;    // u8  [world][region_slots][slot_bytes]
+  size_t off_comb_stage;    // u8  [max_tokens*topk][hidden_dim*4]
+  size_t arena_bytes;
+
+  uint8_t* peer[kMaxWorld];  // arena base of every rank as mapped in this process
+
+  // rank-local state (plain device memory)
+  uint32_t* iter;         // dispatch iteration counter; its parity selects the flag set
+  uint32_t* ticket;       // [2] finished-block tickets: dispatch, combine
+  uint32_t* recv_count;   // [nle] rows received per local expert by the last dispatch
+  uint2* row_src;         // [nle][cap] {src_rank | k << 16, src_token} per received row
+  Status* status;
+  uint64_t timeout_ns;
+};
+
+struct DispatchArgs {
+  A2AParams p;
+  int32_t* out_num_tokens;   // [nle]
+  uint8_t* out_x;            // [nle][cap][hidden_bytes]
+  int64_t out_x_stride_e;    // bytes
+  int64_t out_x_stride_row;  // bytes
+  float* out_scale;          // optional, element strides below
+  int64_t out_scale_stride_e;
+  int64_t out_scale_stride_row;
+  int64_t out_scale_stride_col;
+  const uint8_t* x;          // [m][hidden_bytes]
+  int64_t x_stride_row;      // bytes
+  const float* x_scale;      // optional
+  int64_t x_scale_stride_row;
+  int64_t x_scale_stride_col;
+  const uint32_t* indices;   // [m][topk]
+  const uint32_t* bound_m;   // optional device scalar
+  int num_tokens;            // indices.size(0)
+};
+
+struct CombineArgs {
+  A2AParams p;
+  void* out_tokens;          // [max_tokens][hidden_dim] of U
+  int64_t out_stride_row;    // elements
+  const float* weights;      // [m][topk]
+  int64_t w_stride_row;
+  const void* expert_y;      // [nle][cap][hidden_dim] of T
+  int64_t y_stride_e;        // elements
+  int64_t y_stride_row;      // elements
+  const uint32_t* bound_m;
+  int num_tokens;
+};
+
+// Trailer written after payload + scales in every dispatch slot.
+struct SlotTrailer {
+  uint32_t token;
+  uint32_t k;
+  uint32_t local_expert;
+  uint32_t reserved;
+};
+
+__host__ __device__ inline size_t a2a_counts_index(const A2AParams& p, int parity, int src, int le) {
+  return (static_cast<size_t>(parity) * p.world + src) * p.nle + le;
+}
+
+}  // namespace pplx

@@ -1,0 +1,332 @@
+// Combine: every expert output row travels back to the rank(s) that own the
+// token, and each token's top-k rows are reduced with the router weights.
+//
+// Capability parity: intranode_combine.cu:16-187 and internode_combine.cu:11-147
+// of the reference (fused / send-only / recv-only; expert_y in f32, f16 or bf16;
+// out_tokens in f16 or bf16; results replicated to every rank of the token's DP
+// group; fp32 accumulation in k order with one final cast).  What differs:
+//
+//  * Staging at the token's home rank is indexed by (token, k), where k came
+//    with the dispatch trailer, so the reduction reads top-k consecutive rows
+//    and never looks at `indices`.
+//  * A sender is one warp per received row: batched 16-byte P2P stores, then a
+//    single red.release.sys on the token's arrival counter.  No flag handshake
+//    precedes the stores (see a2a_params.h for why a rank cannot run ahead).
+//  * The reduction is spread over (token, 256-element chunk) warp units so that a
+//    single token still uses many warps, and a unit starts as soon as its own
+//    token is complete.
+//  * The last block to finish clears the arrival counters; nothing else is
+//    reset.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "../core/device_utils.cuh"
+#include "../core/ptx.cuh"
+#include "../core/utils.h"
+#include "../core/wait.cuh"
+#include "a2a_kernels.h"
+#include "a2a_params.h"
+
+namespace pplx {
+namespace {
+
+constexpr int kCombineThreads = 512;
+
+struct CombineSmem {
+  uint32_t* estart;  // [nle + 1]
+  uint32_t* tmp;     // [kScanTmpWords]
+  uint32_t* misc;    // [4]
+};
+
+__device__ __forceinline__ CombineSmem carve(uint32_t* s, int nle) {
+  CombineSmem m;
+  m.estart = s;
+  m.tmp = m.estart + nle + 1;
+  m.misc = m.tmp + kScanTmpWords;
+  return m;
+}
+
+// ---- 8-element vector helpers ------------------------------------------------
+
+template <typename T>
+struct Vec8;
+
+template <>
+struct Vec8<float> {
+  int4 a, b;
+  __device__ __forceinline__ void load_cg(const void* p) {
+    a = ptx::ld_cg_v4(p);
+    b = ptx::ld_cg_v4(static_cast<const uint8_t*>(p) + 16);
+  }
+  __device__ __forceinline__ void fma_into(float (&acc)[8], float w) const {
+    acc[0] = fmaf(w, __int_as_float(a.x), acc[0]);
+    acc[1] = fmaf(w, __int_as_float(a.y), acc[1]);
+    acc[2] = fmaf(w, __int_as_float(a.z), acc[2]);
+    acc[3] = fmaf(w, __int_as_float(a.w), acc[3]);
+    acc[4] = fmaf(w, __int_as_float(b.x), acc[4]);
+    acc[5] = fmaf(w, __int_as_float(b.y), acc[5]);
+    acc[6] = fmaf(w, __int_as_float(b.z), acc[6]);
+    acc[7] = fmaf(w, __int_as_float(b.w), acc[7]);
+  }
+};
+
+__device__ __forceinline__ float2 unpack2(__half2 h) { return __half22float2(h); }
+__device__ __forceinline__ float2 unpack2(__nv_bfloat162 h) { return __bfloat1622float2(h); }
+
+template <typename T2>
+struct Vec8Half {
+  int4 a;
+  __device__ __forceinline__ void load_cg(const void* p) { a = ptx::ld_cg_v4(p); }
+  __device__ __forceinline__ void fma_into(float (&acc)[8], float w) const {
+    const T2* h = reinterpret_cast<const T2*>(&a);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack2(h[j]);
+      acc[2 * j] = fmaf(w, f.x, acc[2 * j]);
+      acc[2 * j + 1] = fmaf(w, f.y, acc[2 * j + 1]);
+    }
+  }
+};
+template <>
+struct Vec8<__half> : Vec8Half<__half2> {};
+template <>
+struct Vec8<__nv_bfloat16> : Vec8Half<__nv_bfloat162> {};
+
+__device__ __forceinline__ int4 pack8(const float (&acc)[8], __half*) {
+  int4 r;
+  __half2* h = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+  return r;
+}
+__device__ __forceinline__ int4 pack8(const float (&acc)[8], __nv_bfloat16*) {
+  int4 r;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) h[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+  return r;
+}
+
+// ---- phases --------------------------------------------------------------------
+
+template <typename T>
+__device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSmem& sm) {
+  const A2AParams& p = a.p;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int nwarps = blockDim.x >> 5;
+
+  for (int le = tid; le < p.nle; le += blockDim.x) sm.estart[le] = p.recv_count[le];
+  __syncthreads();
+  block_exclusive_scan(sm.estart, p.nle, sm.tmp);
+  const uint32_t total_rows = sm.estart[p.nle];
+
+  const int row_bytes = p.hidden_dim * static_cast<int>(sizeof(T));
+  const int nvec = row_bytes >> 4;
+  const T* y = static_cast<const T*>(a.expert_y);
+  const uint32_t gwarp = blockIdx.x * nwarps + warp;
+  const uint32_t gwarps = gridDim.x * nwarps;
+
+  for (uint32_t f = gwarp; f < total_rows; f += gwarps) {
+    const int le = find_group(sm.estart, p.nle, f);
+    const uint32_t row = f - sm.estart[le];
+    const uint2 rs = p.row_src[static_cast<size_t>(le) * p.cap + row];
+    const int src_rank = static_cast<int>(rs.x & 0xffffu);
+    const uint32_t k = rs.x >> 16;
+    const uint32_t token = rs.y;
+    if (p.debug_checks && (token >= static_cast<uint32_t>(p.max_tokens) ||
+                           k >= static_cast<uint32_t>(p.topk) || src_rank >= p.world)) {
+      if (lane == 0)
+        report_failure(p.status, kBadToken, kPhaseCombinePayload, src_rank, p.max_tokens, token,
+                       p.rank);
+      continue;
+    }
+    const T* src = y + le * a.y_stride_e + static_cast<int64_t>(row) * a.y_stride_row;
+    const int group_first = (src_rank / p.dp_size) * p.dp_size;
+    for (int r = 0; r < p.dp_size; ++r) {
+      const int dst = group_first + r;
+      uint8_t* slot = p.peer[dst] + p.off_comb_stage +
+                      (static_cast<size_t>(token) * p.topk + k) * row_bytes;
+      ptx::warp_copy_v4<ptx::LoadKind::kNonCoherent>(slot, src, nvec, lane);
+      __syncwarp();
+      if (lane == 0) {
+        ptx::red_add_release_sys(
+            reinterpret_cast<uint32_t*>(p.peer[dst] + p.off_comb_arrived) + token, 1u);
+      }
+    }
+  }
+}
+
+template <typename T, typename U>
+__device__ __forceinline__ void recv_phase(const CombineArgs& a, const CombineSmem& sm, int m) {
+  const A2AParams& p = a.p;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const WaitCtx w{p.status, p.timeout_ns, static_cast<uint32_t>(p.rank)};
+
+  const int topk = p.topk;
+  const int nvec8 = p.hidden_dim >> 3;          // 8-element vectors per row
+  const int chunks = ceil_div<int>(nvec8, 32);  // warp units per token
+  const int row_bytes = p.hidden_dim * static_cast<int>(sizeof(T));
+  const uint8_t* stage = p.peer[p.rank] + p.off_comb_stage;
+  uint32_t* arrived = reinterpret_cast<uint32_t*>(p.peer[p.rank] + p.off_comb_arrived);
+  U* out = static_cast<U*>(a.out_tokens);
+
+  const uint32_t units = static_cast<uint32_t>(m) * chunks;
+  const uint32_t gwarp = blockIdx.x * nwarps + warp;
+  const uint32_t gwarps = gridDim.x * nwarps;
+  for (uint32_t u = gwarp; u < units; u += gwarps) {
+    const int i = u / chunks;
+    const int c = u - i * chunks;
+    bool ok = true;
+    if (lane == 0) {
+      uint32_t seen;
+      ok = wait_until(arrived + i, PredGe{static_cast<uint32_t>(topk)}, seen, w,
+                      kPhaseCombinePayload, i, topk);
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();
+    if (!ok) continue;
+    const int v = c * 32 + lane;
+    if (v >= nvec8) continue;
+
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    const uint8_t* base = stage + static_cast<size_t>(i) * topk * row_bytes +
+                          static_cast<size_t>(v) * 8 * sizeof(T);
+    const float* wrow = a.weights + static_cast<int64_t>(i) * a.w_stride_row;
+    constexpr int kBatch = 4;
+    for (int k0 = 0; k0 < topk; k0 += kBatch) {
+      Vec8<T> x[kBatch];
+      float wk[kBatch];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        if (k0 + j < topk) {
+          x[j].load_cg(base + static_cast<size_t>(k0 + j) * row_bytes);
+          wk[j] = __ldg(wrow + k0 + j);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        if (k0 + j < topk) x[j].fma_into(acc, wk[j]);
+      }
+    }
+    const int4 packed = pack8(acc, static_cast<U*>(nullptr));
+    ptx::st_v4(out + static_cast<int64_t>(i) * a.out_stride_row + static_cast<int64_t>(v) * 8,
+               packed);
+  }
+
+  __syncthreads();
+  if (tid == 0) {
+    ptx::fence_acq_rel_gpu();
+    const uint32_t t = ptx::atom_add_acq_rel_gpu(p.ticket + 1, 1u);
+    sm.misc[0] = (t == gridDim.x - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (sm.misc[0]) {
+    for (int i = tid; i < m; i += blockDim.x) arrived[i] = 0;
+    if (tid == 0) p.ticket[1] = 0;
+  }
+}
+
+template <typename T, typename U, bool SEND, bool RECV>
+__device__ __forceinline__ void combine_body(const CombineArgs& a, uint32_t* smem) {
+  const A2AParams& p = a.p;
+  const CombineSmem sm = carve(smem, p.nle);
+  int m = a.num_tokens;
+  if (a.bound_m != nullptr) m = min(m, static_cast<int>(__ldg(a.bound_m)));
+  m = min(m, p.max_tokens);
+  if constexpr (SEND) send_phase<T>(a, sm);
+  if constexpr (SEND && RECV) __syncthreads();
+  if constexpr (RECV) recv_phase<T, U>(a, sm, m);
+}
+
+template <typename T, typename U, bool SEND, bool RECV>
+__global__ void __launch_bounds__(kCombineThreads, 1)
+    combine_kernel(const __grid_constant__ CombineArgs a) {
+  extern __shared__ __align__(16) uint32_t dyn_smem[];
+  combine_body<T, U, SEND, RECV>(a, dyn_smem);
+}
+
+template <typename T, typename U, bool SEND, bool RECV>
+__global__ void __launch_bounds__(kCombineThreads, 1)
+    combine_kernel_multi(const CombineArgs* __restrict__ args) {
+  extern __shared__ __align__(16) uint32_t dyn_smem[];
+  combine_body<T, U, SEND, RECV>(args[blockIdx.y], dyn_smem);
+}
+
+template <typename T, typename U>
+cudaError_t launch_typed(const CombineArgs& a, bool send, bool recv, int grid, size_t smem,
+                         cudaStream_t stream) {
+  if (send && recv) {
+    combine_kernel<T, U, true, true><<<grid, kCombineThreads, smem, stream>>>(a);
+  } else if (send) {
+    combine_kernel<T, U, true, false><<<grid, kCombineThreads, smem, stream>>>(a);
+  } else {
+    combine_kernel<T, U, false, true><<<grid, kCombineThreads, smem, stream>>>(a);
+  }
+  return cudaGetLastError();
+}
+
+template <typename T, typename U>
+cudaError_t launch_typed_multi(const CombineArgs* dev_args, int nranks, bool send, bool recv,
+                               int grid, size_t smem, cudaStream_t stream) {
+  void* params[] = {const_cast<CombineArgs**>(&dev_args)};
+  const void* fn = nullptr;
+  if (send && recv) fn = reinterpret_cast<const void*>(&combine_kernel_multi<T, U, true, true>);
+  else if (send) fn = reinterpret_cast<const void*>(&combine_kernel_multi<T, U, true, false>);
+  else fn = reinterpret_cast<const void*>(&combine_kernel_multi<T, U, false, true>);
+  return cudaLaunchCooperativeKernel(fn, dim3(grid, nranks), dim3(kCombineThreads), params, smem,
+                                     stream);
+}
+
+// Calls fn.template operator()<T, U>() for the (in, out) dtype pair.
+template <typename F>
+cudaError_t dispatch_types(DType in, DType out, F&& fn) {
+  const bool out_bf16 = out == DType::kBF16;
+  if (out != DType::kBF16 && out != DType::kF16) return cudaErrorInvalidValue;
+  switch (in) {
+    case DType::kF32:
+      return out_bf16 ? fn.template operator()<float, __nv_bfloat16>()
+                      : fn.template operator()<float, __half>();
+    case DType::kF16:
+      return out_bf16 ? fn.template operator()<__half, __nv_bfloat16>()
+                      : fn.template operator()<__half, __half>();
+    case DType::kBF16:
+      return out_bf16 ? fn.template operator()<__nv_bfloat16, __nv_bfloat16>()
+                      : fn.template operator()<__nv_bfloat16, __half>();
+  }
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+size_t combine_smem_bytes(const A2AParams& p) {
+  return sizeof(uint32_t) * (static_cast<size_t>(p.nle) + 1 + kScanTmpWords + 4);
+}
+
+int combine_threads() { return kCombineThreads; }
+
+cudaError_t launch_combine(const CombineArgs& a, DType in, DType out, bool send, bool recv,
+                           int grid, cudaStream_t stream) {
+  const size_t smem = combine_smem_bytes(a.p);
+  return dispatch_types(in, out, [&]<typename T, typename U>() {
+    return launch_typed<T, U>(a, send, recv, grid, smem, stream);
+  });
+}
+
+cudaError_t launch_combine_multi(const CombineArgs* dev_args, int nranks, const A2AParams& p,
+                                 DType in, DType out, bool send, bool recv, int grid,
+                                 cudaStream_t stream) {
+  const size_t smem = combine_smem_bytes(p);
+  return dispatch_types(in, out, [&]<typename T, typename U>() {
+    return launch_typed_multi<T, U>(dev_args, nranks, send, recv, grid, smem, stream);
+  });
+}
+
+}  // namespace pplx

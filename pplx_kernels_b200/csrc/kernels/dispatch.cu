@@ -1,0 +1,367 @@
+// Token dispatch: every rank scatters its tokens to the ranks that own the
+// tokens' experts, with P2P stores over NVLink, and gathers what it receives
+// into the caller's per-expert buffers.
+//
+// Capability parity: intranode_dispatch.cu:15-284 and internode_dispatch.cu:14-250
+// of the reference (fused / send-only / recv-only, fp8 payload with strided fp32
+// scales, device-side bound_m, DP-group work split).  The protocol is new:
+//
+//  SEND  1. Every block histograms `indices` in shared memory, which yields both
+//           the per-expert counts and, for the block's own token range, the
+//           number of earlier rows per expert.  No global atomics, no grid sync.
+//        2. Block 0 posts the counts (value + 1) to every peer straight away, so
+//           receivers can lay out their output while payload is in flight.
+//        3. One warp per (token, k) copies payload + scales + trailer into the
+//           destination's staging region for this source, at a slot that keeps
+//           the region sorted by destination-local expert.
+//        4. After a block barrier, one thread per destination adds the number of
+//           rows the block stored to the destination's arrival counter with a
+//           release at system scope.
+//  RECV  1. Every block reads all (source, expert) counts (bounded wait) and
+//           derives row offsets with a block scan; block 0 writes the per-expert
+//           totals.
+//        2. One warp per received row waits (bounded) until its source's arrival
+//           counter is complete, then copies slot -> out_expert_x / scale and
+//           records (source rank, token, k) for combine.
+//        3. The last block to finish clears this parity's counters and bumps the
+//           iteration counter.
+//
+// Blocks never wait on other blocks of the same rank, and the send phase never
+// waits at all, so the kernel needs no cooperative launch.  In fused mode a
+// block may sit in a receive wait while a peer still has blocks to schedule, so
+// the host keeps the grid within what is resident at once.
+#include <cuda_runtime.h>
+
+#include "../core/device_utils.cuh"
+#include "../core/ptx.cuh"
+#include "../core/utils.h"
+#include "../core/wait.cuh"
+#include "a2a_kernels.h"
+#include "a2a_params.h"
+
+namespace pplx {
+namespace {
+
+constexpr int kDispatchThreads = 512;
+
+struct DispatchSmem {
+  uint32_t* hist;    // [E]
+  uint32_t* base;    // [E]
+  uint32_t* fstart;  // [P + 1]  counts, then their exclusive scan
+  uint32_t* rbase;   // [P]
+  uint32_t* sent;    // [kMaxWorld]
+  uint32_t* tmp;     // [kScanTmpWords]
+  uint32_t* misc;    // [4]: 0 = last-block flag
+};
+
+__device__ __forceinline__ DispatchSmem carve(uint32_t* s, int E, int P) {
+  DispatchSmem m;
+  m.hist = s;
+  m.base = m.hist + E;
+  m.fstart = m.base + E;
+  m.rbase = m.fstart + P + 1;
+  m.sent = m.rbase + P;
+  m.tmp = m.sent + kMaxWorld;
+  m.misc = m.tmp + kScanTmpWords;
+  return m;
+}
+
+__device__ __forceinline__ uint32_t* counts_ptr(const A2AParams& p, int dst, int parity, int src,
+                                                int le) {
+  return reinterpret_cast<uint32_t*>(p.peer[dst] + p.off_counts) +
+         a2a_counts_index(p, parity, src, le);
+}
+
+__device__ __forceinline__ uint32_t* arrived_ptr(const A2AParams& p, int dst, int parity, int src) {
+  return reinterpret_cast<uint32_t*>(p.peer[dst] + p.off_arrived) + parity * p.world + src;
+}
+
+__device__ __forceinline__ void send_phase(const DispatchArgs& a, const DispatchSmem& sm,
+                                           int parity, int m) {
+  const A2AParams& p = a.p;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int E = p.num_experts;
+  const int topk = p.topk;
+  const int dp_rank = p.rank % p.dp_size;
+
+  // Tokens this rank sends: i = o * dp_size + dp_rank.  Blocks own contiguous
+  // ranges of the ordinal o.
+  const int n_own = (m > dp_rank) ? (m - dp_rank + p.dp_size - 1) / p.dp_size : 0;
+  const int per_block = ceil_div<int>(n_own, gridDim.x);
+  const int o_begin = min(static_cast<int>(blockIdx.x) * per_block, n_own);
+  const int o_end = min(o_begin + per_block, n_own);
+
+  for (int e = tid; e < E; e += blockDim.x) {
+    sm.hist[e] = 0;
+    sm.base[e] = 0;
+  }
+  if (tid < kMaxWorld) sm.sent[tid] = 0;
+  __syncthreads();
+
+  const int n_entries = n_own * topk;
+  for (int idx = tid; idx < n_entries; idx += blockDim.x) {
+    const int o = idx / topk;
+    const int k = idx - o * topk;
+    const int i = o * p.dp_size + dp_rank;
+    const uint32_t e = __ldg(a.indices + static_cast<size_t>(i) * topk + k);
+    if (e < static_cast<uint32_t>(E)) {
+      atomicAdd(&sm.hist[e], 1u);
+      if (o < o_begin) atomicAdd(&sm.base[e], 1u);
+    } else if (p.debug_checks) {
+      report_failure(p.status, kBadExpert, kPhaseDispatchCounts, i, E, e, p.rank);
+    }
+  }
+  __syncthreads();
+
+  if (blockIdx.x == 0) {
+    for (int e = tid; e < E; e += blockDim.x) {
+      const int dst = e / p.nle;
+      const int le = e - dst * p.nle;
+      ptx::st_relaxed_sys(counts_ptr(p, dst, parity, p.rank, le), sm.hist[e] + 1u);
+    }
+  }
+
+  // Slot of the first row this block stores for expert e: rows for lower local
+  // experts of the same destination come first, then earlier blocks' rows.
+  for (int e = tid; e < E; e += blockDim.x) {
+    const int le = e % p.nle;
+    uint32_t before = sm.base[e];
+    for (int j = 1; j <= le; ++j) before += sm.hist[e - j];
+    sm.base[e] = before;
+  }
+  __syncthreads();
+
+  const int nvec = p.hidden_bytes >> 4;
+  const int nscale = p.scale_bytes >> 2;
+  const int u_end = o_end * topk;
+  for (int u = o_begin * topk + warp; u < u_end; u += nwarps) {
+    const int o = u / topk;
+    const int k = u - o * topk;
+    const int i = o * p.dp_size + dp_rank;
+    const uint32_t e = __ldg(a.indices + static_cast<size_t>(i) * topk + k);
+    if (e >= static_cast<uint32_t>(E)) continue;
+    const int dst = e / p.nle;
+    const int le = e - dst * p.nle;
+    uint32_t pos = 0;
+    if (lane == 0) pos = atomicAdd(&sm.base[e], 1u);
+    pos = __shfl_sync(0xffffffffu, pos, 0);
+    if (p.debug_checks && pos >= static_cast<uint32_t>(p.region_slots)) {
+      if (lane == 0)
+        report_failure(p.status, kSlotOverflow, kPhaseDispatchPayload, dst, p.region_slots, pos,
+                       p.rank);
+      continue;
+    }
+    if (lane == 0) atomicAdd(&sm.sent[dst], 1u);
+
+    uint8_t* slot = p.peer[dst] + p.off_disp_stage +
+                    (static_cast<size_t>(p.rank) * p.region_slots + pos) * p.slot_bytes;
+    const uint8_t* src = a.x + static_cast<int64_t>(i) * a.x_stride_row;
+    ptx::warp_copy_v4<ptx::LoadKind::kNonCoherent>(slot, src, nvec, lane);
+    if (nscale > 0) {
+      float* sdst = reinterpret_cast<float*>(slot + p.hidden_bytes);
+      const float* ssrc = a.x_scale + static_cast<int64_t>(i) * a.x_scale_stride_row;
+      for (int j = lane; j < nscale; j += 32) sdst[j] = __ldg(ssrc + j * a.x_scale_stride_col);
+    }
+    if (lane == 0) {
+      int4 t;
+      t.x = i;
+      t.y = k;
+      t.z = le;
+      t.w = 0;
+      ptx::st_v4(slot + p.hidden_bytes + p.scale_bytes, t);
+    }
+  }
+  __syncthreads();
+  if (tid < p.world && sm.sent[tid] > 0) {
+    ptx::red_add_release_sys(arrived_ptr(p, tid, parity, p.rank), sm.sent[tid]);
+  }
+}
+
+__device__ __forceinline__ void recv_phase(const DispatchArgs& a, const DispatchSmem& sm,
+                                           int parity) {
+  const A2AParams& p = a.p;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int P = p.world * p.nle;
+  const WaitCtx w{p.status, p.timeout_ns, static_cast<uint32_t>(p.rank)};
+
+  uint32_t* counts = reinterpret_cast<uint32_t*>(p.peer[p.rank] + p.off_counts) +
+                     a2a_counts_index(p, parity, 0, 0);
+  uint32_t* arrived =
+      reinterpret_cast<uint32_t*>(p.peer[p.rank] + p.off_arrived) + parity * p.world;
+
+  for (int q = tid; q < P; q += blockDim.x) {
+    uint32_t v = 0;
+    const bool ok =
+        wait_until(counts + q, PredNonZero{}, v, w, kPhaseDispatchCounts, q / p.nle, 1u);
+    sm.fstart[q] = ok ? v - 1u : 0u;
+  }
+  __syncthreads();
+  // Row offset of (source s, expert le) inside the expert's output: sources in
+  // rank order.
+  for (int q = tid; q < P; q += blockDim.x) {
+    const int s = q / p.nle;
+    const int le = q - s * p.nle;
+    uint32_t before = 0;
+    for (int s2 = 0; s2 < s; ++s2) before += sm.fstart[s2 * p.nle + le];
+    sm.rbase[q] = before;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int le = tid; le < p.nle; le += blockDim.x) {
+      const int q = (p.world - 1) * p.nle + le;
+      const uint32_t total = sm.rbase[q] + sm.fstart[q];
+      a.out_num_tokens[le] = static_cast<int32_t>(total);
+      p.recv_count[le] = min(total, static_cast<uint32_t>(p.cap));
+    }
+  }
+  block_exclusive_scan(sm.fstart, P, sm.tmp);  // fstart[q] = first flat row of group q
+
+  const uint32_t total_rows = sm.fstart[P];
+  const int nvec = p.hidden_bytes >> 4;
+  const int nscale = p.scale_bytes >> 2;
+  const uint8_t* stage = p.peer[p.rank] + p.off_disp_stage;
+  const uint32_t gwarp = blockIdx.x * nwarps + warp;
+  const uint32_t gwarps = gridDim.x * nwarps;
+
+  uint32_t acquired = 0;  // sources whose arrival counter this warp has acquired
+  for (uint32_t f = gwarp; f < total_rows; f += gwarps) {
+    const int q = find_group(sm.fstart, P, f);
+    const int s = q / p.nle;
+    const int le = q - s * p.nle;
+    const uint32_t src_first = sm.fstart[s * p.nle];
+    const uint32_t src_total = sm.fstart[(s + 1) * p.nle] - src_first;
+    const uint32_t slot_idx = f - src_first;
+    const uint32_t row = sm.rbase[q] + (f - sm.fstart[q]);
+
+    // Each warp acquires a source's counter itself once; a flag set by another
+    // warp would not order this warp's loads after the peer's stores.
+    bool ok = true;
+    if (!((acquired >> s) & 1u)) {
+      if (lane == 0) {
+        uint32_t seen;
+        ok = wait_until(arrived + s, PredGe{src_total}, seen, w, kPhaseDispatchPayload, s,
+                        src_total);
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      __syncwarp();
+      if (!ok) continue;
+      acquired |= 1u << s;
+    }
+    if (p.debug_checks &&
+        (row >= static_cast<uint32_t>(p.cap) || slot_idx >= static_cast<uint32_t>(p.region_slots))) {
+      if (lane == 0)
+        report_failure(p.status, kRowOverflow, kPhaseDispatchPayload, s, p.cap, row, p.rank);
+      continue;
+    }
+
+    const uint8_t* slot =
+        stage + (static_cast<size_t>(s) * p.region_slots + slot_idx) * p.slot_bytes;
+    uint8_t* dst = a.out_x + le * a.out_x_stride_e + static_cast<int64_t>(row) * a.out_x_stride_row;
+    ptx::warp_copy_v4<ptx::LoadKind::kL2Only>(dst, slot, nvec, lane);
+    if (nscale > 0) {
+      const float* ssrc = reinterpret_cast<const float*>(slot + p.hidden_bytes);
+      float* sdst = a.out_scale + le * a.out_scale_stride_e +
+                    static_cast<int64_t>(row) * a.out_scale_stride_row;
+      for (int j = lane; j < nscale; j += 32) sdst[j * a.out_scale_stride_col] = __ldcg(ssrc + j);
+    }
+    if (lane == 0) {
+      const int4 t = ptx::ld_cg_v4(slot + p.hidden_bytes + p.scale_bytes);
+      if (p.debug_checks && static_cast<uint32_t>(t.x) >= static_cast<uint32_t>(p.max_tokens)) {
+        report_failure(p.status, kBadToken, kPhaseDispatchPayload, s, p.max_tokens, t.x, p.rank);
+      }
+      uint2 rs;
+      rs.x = static_cast<uint32_t>(s) | (static_cast<uint32_t>(t.y) << 16);
+      rs.y = static_cast<uint32_t>(t.x);
+      p.row_src[static_cast<size_t>(le) * p.cap + row] = rs;
+    }
+  }
+
+  // Last block out clears this parity's flags and opens the next iteration.
+  __syncthreads();
+  if (tid == 0) {
+    ptx::fence_acq_rel_gpu();
+    const uint32_t t = ptx::atom_add_acq_rel_gpu(p.ticket + 0, 1u);
+    sm.misc[0] = (t == gridDim.x - 1) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (sm.misc[0]) {
+    for (int q = tid; q < P; q += blockDim.x) counts[q] = 0;
+    if (tid < p.world) arrived[tid] = 0;
+    if (tid == 0) {
+      p.ticket[0] = 0;
+      *p.iter = *p.iter + 1u;
+    }
+  }
+}
+
+template <bool SEND, bool RECV>
+__device__ __forceinline__ void dispatch_body(const DispatchArgs& a, uint32_t* smem) {
+  const A2AParams& p = a.p;
+  const DispatchSmem sm = carve(smem, p.num_experts, p.world * p.nle);
+  const int parity = static_cast<int>(ptx::ld_volatile(p.iter) & 1u);
+  int m = a.num_tokens;
+  if (a.bound_m != nullptr) m = min(m, static_cast<int>(__ldg(a.bound_m)));
+  m = min(m, p.max_tokens);
+  if constexpr (SEND) send_phase(a, sm, parity, m);
+  if constexpr (SEND && RECV) __syncthreads();
+  if constexpr (RECV) recv_phase(a, sm, parity);
+}
+
+template <bool SEND, bool RECV>
+__global__ void __launch_bounds__(kDispatchThreads, 1)
+    dispatch_kernel(const __grid_constant__ DispatchArgs a) {
+  extern __shared__ __align__(16) uint32_t dyn_smem[];
+  dispatch_body<SEND, RECV>(a, dyn_smem);
+}
+
+// Several ranks that live on one device, run as one grid: blockIdx.y picks the
+// rank.  Blocks of different ranks wait on one another, so the launch is
+// cooperative to have them all resident.
+template <bool SEND, bool RECV>
+__global__ void __launch_bounds__(kDispatchThreads, 1)
+    dispatch_kernel_multi(const DispatchArgs* __restrict__ args) {
+  extern __shared__ __align__(16) uint32_t dyn_smem[];
+  dispatch_body<SEND, RECV>(args[blockIdx.y], dyn_smem);
+}
+
+}  // namespace
+
+size_t dispatch_smem_bytes(const A2AParams& p) {
+  const size_t E = p.num_experts, P = static_cast<size_t>(p.world) * p.nle;
+  return sizeof(uint32_t) * (2 * E + (P + 1) + P + kMaxWorld + kScanTmpWords + 4);
+}
+
+int dispatch_threads() { return kDispatchThreads; }
+
+cudaError_t launch_dispatch(const DispatchArgs& a, bool send, bool recv, int grid,
+                            cudaStream_t stream) {
+  const size_t smem = dispatch_smem_bytes(a.p);
+  if (send && recv) {
+    dispatch_kernel<true, true><<<grid, kDispatchThreads, smem, stream>>>(a);
+  } else if (send) {
+    dispatch_kernel<true, false><<<grid, kDispatchThreads, smem, stream>>>(a);
+  } else {
+    dispatch_kernel<false, true><<<grid, kDispatchThreads, smem, stream>>>(a);
+  }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dispatch_multi(const DispatchArgs* dev_args, int nranks, const A2AParams& p,
+                                  bool send, bool recv, int grid, cudaStream_t stream) {
+  const size_t smem = dispatch_smem_bytes(p);
+  void* params[] = {const_cast<DispatchArgs**>(&dev_args)};
+  const dim3 g(grid, nranks);
+  const void* fn = nullptr;
+  if (send && recv) fn = reinterpret_cast<const void*>(&dispatch_kernel_multi<true, true>);
+  else if (send) fn = reinterpret_cast<const void*>(&dispatch_kernel_multi<true, false>);
+  else fn = reinterpret_cast<const void*>(&dispatch_kernel_multi<false, true>);
+  return cudaLaunchCooperativeKernel(fn, g, dim3(kDispatchThreads), params, smem, stream);
+}
+
+}  // namespace pplx

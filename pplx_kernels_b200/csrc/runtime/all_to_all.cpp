@@ -1,0 +1,335 @@
+#include "all_to_all.h"
+
+#include <algorithm>
+#include <sstream>
+
+#include <nvtx3/nvToolsExt.h>
+
+namespace pplx {
+
+namespace {
+
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+};
+
+size_t align256(size_t x) { return round_up<size_t>(x, 256); }
+
+const char* phase_name(uint32_t phase) {
+  switch (phase) {
+    case kPhaseDispatchCounts: return "dispatch: waiting for a peer's per-expert counts";
+    case kPhaseDispatchPayload: return "dispatch: waiting for a peer's token payload";
+    case kPhaseCombinePayload: return "combine: waiting for a token's expert outputs";
+    case kPhaseBarrier: return "barrier";
+    case kPhaseTest: return "wait probe";
+    case kPhaseFusedGemm: return "fused expert GEMM: waiting for rows";
+    default: return "unknown phase";
+  }
+}
+
+const char* code_name(uint32_t code) {
+  switch (code) {
+    case kTimeout: return "wait timed out";
+    case kBadExpert: return "expert index out of range";
+    case kSlotOverflow: return "staging slot out of range";
+    case kRowOverflow: return "output row out of range";
+    case kBadToken: return "token index out of range";
+    default: return "unknown failure";
+  }
+}
+
+}  // namespace
+
+std::string describe_status(const Status& s) {
+  std::ostringstream os;
+  os << code_name(s.code) << " on rank " << s.rank << " (" << phase_name(s.phase)
+     << "; peer/token " << s.peer << ", expected " << s.expected << ", observed " << s.observed
+     << ", block " << s.block << ", " << s.count << " failure(s) in total)";
+  return os.str();
+}
+
+void AllToAll::validate(const A2AConfig& c) {
+  PPLX_CHECK(c.world_size >= 1 && c.world_size <= kMaxWorld,
+             "world_size " << c.world_size << " not in [1, " << kMaxWorld << "]");
+  PPLX_CHECK(c.rank >= 0 && c.rank < c.world_size, "rank out of range");
+  PPLX_CHECK(c.dp_size >= 1 && c.world_size % c.dp_size == 0, "dp_size must divide world_size");
+  PPLX_CHECK(c.max_num_tokens > 0, "max_num_tokens must be positive");
+  PPLX_CHECK(c.num_experts > 0 && c.num_experts % c.world_size == 0,
+             "num_experts (" << c.num_experts << ") must be a positive multiple of world_size ("
+                             << c.world_size << ")");
+  PPLX_CHECK(c.experts_per_token > 0 && c.experts_per_token <= c.num_experts,
+             "experts_per_token out of range");
+  PPLX_CHECK(c.experts_per_token < (1 << 16), "experts_per_token too large");
+  PPLX_CHECK(c.hidden_dim > 0, "hidden_dim must be positive");
+  PPLX_CHECK(c.hidden_dim_bytes > 0 && c.hidden_dim_bytes % 16 == 0,
+             "hidden_dim_bytes must be a positive multiple of 16");
+  PPLX_CHECK(c.hidden_dim_scale_bytes >= 0 && c.hidden_dim_scale_bytes % 16 == 0,
+             "hidden_dim_scale_bytes must be a multiple of 16");
+  PPLX_CHECK(c.hidden_dim_scale_bytes <= c.hidden_dim_bytes, "scales larger than the payload");
+}
+
+namespace {
+
+// Fills geometry and arena offsets; pointers stay null.
+A2AParams make_layout(const A2AConfig& c) {
+  A2AParams p{};
+  p.rank = c.rank;
+  p.world = c.world_size;
+  p.dp_size = c.dp_size;
+  p.num_dp_groups = c.world_size / c.dp_size;
+  p.num_experts = c.num_experts;
+  p.nle = c.num_experts / c.world_size;
+  p.topk = c.experts_per_token;
+  p.max_tokens = c.max_num_tokens;
+  p.hidden_dim = c.hidden_dim;
+  p.hidden_bytes = c.hidden_dim_bytes;
+  p.scale_bytes = c.hidden_dim_scale_bytes;
+  p.slot_bytes = c.hidden_dim_bytes + c.hidden_dim_scale_bytes + 16;
+  const int tokens_per_sender = ceil_div(c.max_num_tokens, c.dp_size);
+  p.region_slots = tokens_per_sender * std::min(c.experts_per_token, p.nle);
+  p.cap = c.max_num_tokens * p.num_dp_groups;
+
+  size_t off = 0;
+  p.off_counts = off;
+  off = align256(off + sizeof(uint32_t) * 2 * p.world * p.nle);
+  p.off_arrived = off;
+  off = align256(off + sizeof(uint32_t) * 2 * p.world);
+  p.off_comb_arrived = off;
+  off = align256(off + sizeof(uint32_t) * p.max_tokens);
+  p.off_disp_stage = off;
+  off = align256(off + static_cast<size_t>(p.world) * p.region_slots * p.slot_bytes);
+  p.off_comb_stage = off;
+  off = align256(off + static_cast<size_t>(p.max_tokens) * p.topk * p.hidden_dim * 4);
+  p.arena_bytes = off;
+  return p;
+}
+
+}  // namespace
+
+size_t AllToAll::arena_bytes(const A2AConfig& cfg) {
+  validate(cfg);
+  return make_layout(cfg).arena_bytes;
+}
+
+AllToAll::AllToAll(const A2AConfig& cfg, std::shared_ptr<SymmetricAllocation> arena)
+    : cfg_(cfg), arena_(std::move(arena)) {
+  validate(cfg_);
+  params_ = make_layout(cfg_);
+  PPLX_CHECK(arena_ && arena_->world() == cfg_.world_size && arena_->rank() == cfg_.rank,
+             "arena does not match the configuration");
+  PPLX_CHECK(arena_->bytes() >= params_.arena_bytes, "arena too small");
+  for (int r = 0; r < cfg_.world_size; ++r) params_.peer[r] = static_cast<uint8_t*>(arena_->peer(r));
+
+  iter_ = DeviceBuffer<uint32_t>(1);
+  ticket_ = DeviceBuffer<uint32_t>(2);
+  recv_count_ = DeviceBuffer<uint32_t>(params_.nle);
+  row_src_ = DeviceBuffer<uint2>(static_cast<size_t>(params_.nle) * params_.cap);
+  status_ = DeviceBuffer<Status>(1);
+  params_.iter = iter_.get();
+  params_.ticket = ticket_.get();
+  params_.recv_count = recv_count_.get();
+  params_.row_src = row_src_.get();
+  params_.status = status_.get();
+  params_.timeout_ns = static_cast<uint64_t>(env_long("PPLX_B200_TIMEOUT_MS", 10000)) * 1000000ull;
+  params_.debug_checks = env_long("PPLX_B200_DEBUG_CHECKS", 0) != 0 ? 1 : 0;
+  num_sms_ = get_sm_count();
+  max_blocks_ = static_cast<int>(env_long("PPLX_B200_NUM_SMS", 0));
+  CUDA_CHECK(cudaDeviceSynchronize());
+}
+
+AllToAll::~AllToAll() {
+  // Kernels of this object may still be in flight on some stream.
+  cudaDeviceSynchronize();
+}
+
+std::unique_ptr<AllToAll> AllToAll::create(const A2AConfig& cfg, Bootstrap& bs) {
+  validate(cfg);
+  PPLX_CHECK(bs.world() == cfg.world_size && bs.rank() == cfg.rank,
+             "bootstrap rank/world (" << bs.rank() << "/" << bs.world()
+                                      << ") differ from the configuration (" << cfg.rank << "/"
+                                      << cfg.world_size << ")");
+  auto arena = SymmetricAllocation::create(bs, arena_bytes(cfg));
+  auto obj = std::make_unique<AllToAll>(cfg, std::move(arena));
+  bs.barrier();
+  return obj;
+}
+
+std::vector<std::unique_ptr<AllToAll>> AllToAll::create_local_world(const A2AConfig& cfg_in) {
+  A2AConfig cfg = cfg_in;
+  cfg.rank = 0;
+  validate(cfg);
+  auto arenas = SymmetricAllocation::create_local_world(cfg.world_size, arena_bytes(cfg));
+  std::vector<std::unique_ptr<AllToAll>> out;
+  for (int r = 0; r < cfg.world_size; ++r) {
+    cfg.rank = r;
+    out.push_back(std::make_unique<AllToAll>(cfg, arenas[r]));
+  }
+  return out;
+}
+
+void AllToAll::set_timeout_ms(double ms) {
+  PPLX_CHECK(ms > 0, "timeout must be positive");
+  params_.timeout_ns = static_cast<uint64_t>(ms * 1e6);
+}
+
+int AllToAll::dispatch_grid(int num_tokens) const {
+  const int limit = max_blocks_ > 0 ? std::min(max_blocks_, num_sms_) : num_sms_;
+  const int units = std::max(1, num_tokens) * cfg_.experts_per_token;
+  return std::clamp(ceil_div(units, 4), std::min(4, limit), limit);
+}
+
+int AllToAll::combine_grid(int num_tokens) const {
+  const int limit = max_blocks_ > 0 ? std::min(max_blocks_, num_sms_) : num_sms_;
+  const int warps = combine_threads() / 32;
+  const int chunks = ceil_div(cfg_.hidden_dim / 8, 32);
+  const int units = std::max(1, num_tokens) * std::max(cfg_.experts_per_token, chunks);
+  return std::clamp(ceil_div(units, warps), std::min(4, limit), limit);
+}
+
+DispatchArgs AllToAll::make_dispatch_args(const DispatchCall& c) const {
+  const A2AParams& p = params_;
+  PPLX_CHECK(c.out_num_tokens != nullptr && c.out_x.data != nullptr && c.x.data != nullptr &&
+                 c.indices != nullptr,
+             "dispatch: missing tensor");
+  PPLX_CHECK(c.num_tokens >= 0 && c.num_tokens <= p.max_tokens,
+             "dispatch: " << c.num_tokens << " tokens exceed max_num_tokens " << p.max_tokens);
+  PPLX_CHECK(c.out_rows >= p.cap, "dispatch: out_expert_x holds "
+                                      << c.out_rows << " rows per expert, need " << p.cap);
+  const bool has_scale = p.scale_bytes > 0;
+  PPLX_CHECK(has_scale == (c.out_scale.data != nullptr) && has_scale == (c.x_scale.data != nullptr),
+             "dispatch: scale tensors must be given exactly when hidden_dim_scale_bytes > 0");
+  PPLX_CHECK(reinterpret_cast<uintptr_t>(c.out_x.data) % 16 == 0 &&
+                 reinterpret_cast<uintptr_t>(c.x.data) % 16 == 0 && c.out_x.stride_row % 16 == 0 &&
+                 c.out_x.stride_outer % 16 == 0 && c.x.stride_row % 16 == 0,
+             "dispatch: token buffers must be 16-byte aligned");
+  DispatchArgs a{};
+  a.p = p;
+  a.out_num_tokens = c.out_num_tokens;
+  a.out_x = c.out_x.data;
+  a.out_x_stride_e = c.out_x.stride_outer;
+  a.out_x_stride_row = c.out_x.stride_row;
+  a.out_scale = c.out_scale.data;
+  a.out_scale_stride_e = c.out_scale.stride_outer;
+  a.out_scale_stride_row = c.out_scale.stride_row;
+  a.out_scale_stride_col = c.out_scale.stride_col;
+  a.x = c.x.data;
+  a.x_stride_row = c.x.stride_row;
+  a.x_scale = c.x_scale.data;
+  a.x_scale_stride_row = c.x_scale.stride_row;
+  a.x_scale_stride_col = c.x_scale.stride_col;
+  a.indices = c.indices;
+  a.bound_m = c.bound_m;
+  a.num_tokens = c.num_tokens;
+  return a;
+}
+
+CombineArgs AllToAll::make_combine_args(const CombineCall& c) const {
+  const A2AParams& p = params_;
+  PPLX_CHECK(c.out_tokens != nullptr && c.weights != nullptr && c.expert_y != nullptr,
+             "combine: missing tensor");
+  PPLX_CHECK(c.num_tokens >= 0 && c.num_tokens <= p.max_tokens,
+             "combine: " << c.num_tokens << " tokens exceed max_num_tokens " << p.max_tokens);
+  PPLX_CHECK(p.hidden_dim % 8 == 0, "combine: hidden_dim must be a multiple of 8");
+  const int64_t in_sz = static_cast<int64_t>(dtype_size(c.in));
+  PPLX_CHECK(reinterpret_cast<uintptr_t>(c.expert_y) % 16 == 0 &&
+                 (c.y_stride_row * in_sz) % 16 == 0 && (c.y_stride_e * in_sz) % 16 == 0 &&
+                 reinterpret_cast<uintptr_t>(c.out_tokens) % 16 == 0 &&
+                 (c.out_stride_row * 2) % 16 == 0,
+             "combine: buffers must be 16-byte aligned");
+  CombineArgs a{};
+  a.p = p;
+  a.out_tokens = c.out_tokens;
+  a.out_stride_row = c.out_stride_row;
+  a.weights = c.weights;
+  a.w_stride_row = c.w_stride_row;
+  a.expert_y = c.expert_y;
+  a.y_stride_e = c.y_stride_e;
+  a.y_stride_row = c.y_stride_row;
+  a.bound_m = c.bound_m;
+  a.num_tokens = c.num_tokens;
+  return a;
+}
+
+void AllToAll::dispatch(const DispatchCall& call, SplitMode mode, cudaStream_t stream) {
+  NvtxRange range("dispatch");
+  const DispatchArgs a = make_dispatch_args(call);
+  const bool send = mode != SplitMode::kRecv, recv = mode != SplitMode::kSend;
+  CUDA_CHECK(launch_dispatch(a, send, recv, dispatch_grid(call.num_tokens), stream));
+}
+
+void AllToAll::combine(const CombineCall& call, SplitMode mode, cudaStream_t stream) {
+  NvtxRange range("combine");
+  const CombineArgs a = make_combine_args(call);
+  const bool send = mode != SplitMode::kRecv, recv = mode != SplitMode::kSend;
+  CUDA_CHECK(launch_combine(a, call.in, call.out, send, recv, combine_grid(call.num_tokens),
+                            stream));
+}
+
+namespace {
+
+template <typename Args>
+struct StagedArgs {
+  Args* dev = nullptr;
+  explicit StagedArgs(const std::vector<Args>& host) {
+    CUDA_CHECK(cudaMalloc(&dev, host.size() * sizeof(Args)));
+    CUDA_CHECK(cudaMemcpy(dev, host.data(), host.size() * sizeof(Args), cudaMemcpyHostToDevice));
+  }
+  ~StagedArgs() { cudaFree(dev); }
+};
+
+}  // namespace
+
+void AllToAll::dispatch_group(const std::vector<AllToAll*>& ranks,
+                              const std::vector<DispatchCall>& calls, SplitMode mode,
+                              cudaStream_t stream) {
+  PPLX_CHECK(!ranks.empty() && ranks.size() == calls.size(), "dispatch_group: size mismatch");
+  std::vector<DispatchArgs> args;
+  int grid = 1, max_tokens = 0;
+  for (size_t r = 0; r < ranks.size(); ++r) {
+    args.push_back(ranks[r]->make_dispatch_args(calls[r]));
+    max_tokens = std::max(max_tokens, calls[r].num_tokens);
+  }
+  const int n = static_cast<int>(ranks.size());
+  const int per_rank_limit = std::max(1, ranks[0]->num_sms_ / n);
+  grid = std::min(ranks[0]->dispatch_grid(max_tokens), per_rank_limit);
+  StagedArgs<DispatchArgs> staged(args);
+  const bool send = mode != SplitMode::kRecv, recv = mode != SplitMode::kSend;
+  CUDA_CHECK(launch_dispatch_multi(staged.dev, n, ranks[0]->params_, send, recv, grid, stream));
+  CUDA_CHECK(cudaStreamSynchronize(stream));
+}
+
+void AllToAll::combine_group(const std::vector<AllToAll*>& ranks,
+                             const std::vector<CombineCall>& calls, SplitMode mode,
+                             cudaStream_t stream) {
+  PPLX_CHECK(!ranks.empty() && ranks.size() == calls.size(), "combine_group: size mismatch");
+  std::vector<CombineArgs> args;
+  int max_tokens = 0;
+  for (size_t r = 0; r < ranks.size(); ++r) {
+    args.push_back(ranks[r]->make_combine_args(calls[r]));
+    max_tokens = std::max(max_tokens, calls[r].num_tokens);
+    PPLX_CHECK(calls[r].in == calls[0].in && calls[r].out == calls[0].out,
+               "combine_group: all ranks must use the same dtypes");
+  }
+  const int n = static_cast<int>(ranks.size());
+  const int per_rank_limit = std::max(1, ranks[0]->num_sms_ / n);
+  const int grid = std::min(ranks[0]->combine_grid(max_tokens), per_rank_limit);
+  StagedArgs<CombineArgs> staged(args);
+  const bool send = mode != SplitMode::kRecv, recv = mode != SplitMode::kSend;
+  CUDA_CHECK(launch_combine_multi(staged.dev, n, ranks[0]->params_, calls[0].in, calls[0].out,
+                                  send, recv, grid, stream));
+  CUDA_CHECK(cudaStreamSynchronize(stream));
+}
+
+Status AllToAll::read_status() const {
+  Status s{};
+  CUDA_CHECK(cudaMemcpy(&s, status_.get(), sizeof(Status), cudaMemcpyDeviceToHost));
+  return s;
+}
+
+void AllToAll::check_status() const {
+  const Status s = read_status();
+  if (s.code != kOk) throw Error("pplx_kernels_b200: " + describe_status(s));
+}
+
+}  // namespace pplx

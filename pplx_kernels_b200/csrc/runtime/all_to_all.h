@@ -1,0 +1,139 @@
+// Host side of the dispatch/combine all-to-all.
+//
+// Role parity: `SplitMode` + `AllToAll` (csrc/all_to_all/all_to_all.h:9-71),
+// `AllToAllIntraNode` (intranode.h:21-89) and `AllToAllInterNode`
+// (internode.h:16-133).  One class serves both API flavours: inside one NVSwitch
+// box every peer is reachable by load/store, so "internode" differs only in how
+// the ranks find one another.  Relaxations against the reference: a single DP
+// group (including world_size 1) is accepted, and num_experts must divide evenly
+// over the ranks (the reference mixes ceil and floor there).
+#pragma once
+
+#include <memory>
+#include <string>
+#include <vector>
+
+#include <cuda_runtime.h>
+
+#include "../core/buffer.h"
+#include "../core/status.h"
+#include "../kernels/a2a_kernels.h"
+#include "../kernels/a2a_params.h"
+#include "symm_heap.h"
+
+namespace pplx {
+
+enum class SplitMode { kNone = 0, kSend = 1, kRecv = 2 };
+
+inline SplitMode split_mode(bool do_send, bool do_recv) {
+  if (do_send && do_recv) return SplitMode::kNone;
+  if (do_send) return SplitMode::kSend;
+  if (do_recv) return SplitMode::kRecv;
+  throw Error("dispatch/combine called with do_send = do_recv = false");
+}
+
+// Human-readable rendering of a failure record.
+std::string describe_status(const Status& s);
+
+struct A2AConfig {
+  int max_num_tokens = 0;
+  int num_experts = 0;
+  int experts_per_token = 0;
+  int rank = 0;
+  int world_size = 1;
+  int dp_size = 1;
+  int hidden_dim = 0;
+  int hidden_dim_bytes = 0;
+  int hidden_dim_scale_bytes = 0;
+};
+
+// Tensor arguments of one dispatch call (everything except the object itself).
+struct DispatchCall {
+  int32_t* out_num_tokens = nullptr;
+  Strided3D<uint8_t> out_x;   // strides in bytes; stride_col unused
+  Strided3D<float> out_scale; // optional (data == nullptr), strides in elements
+  Strided2D<const uint8_t> x; // row stride in bytes
+  Strided2D<const float> x_scale;
+  const uint32_t* indices = nullptr;
+  const uint32_t* bound_m = nullptr;
+  int num_tokens = 0;
+  // Capacity checks (rows per expert the caller's buffers can hold).
+  int64_t out_rows = 0;
+};
+
+struct CombineCall {
+  void* out_tokens = nullptr;
+  int64_t out_stride_row = 0;  // elements
+  const float* weights = nullptr;
+  int64_t w_stride_row = 0;
+  const void* expert_y = nullptr;
+  int64_t y_stride_e = 0;      // elements
+  int64_t y_stride_row = 0;
+  const uint32_t* bound_m = nullptr;
+  int num_tokens = 0;
+  DType in = DType::kBF16;
+  DType out = DType::kBF16;
+};
+
+class AllToAll {
+ public:
+  AllToAll(const A2AConfig& cfg, std::shared_ptr<SymmetricAllocation> arena);
+  ~AllToAll();
+  AllToAll(const AllToAll&) = delete;
+  AllToAll& operator=(const AllToAll&) = delete;
+
+  // Bytes of symmetric memory one rank needs for `cfg`.
+  static size_t arena_bytes(const A2AConfig& cfg);
+  static void validate(const A2AConfig& cfg);
+
+  // Collective: allocates the arena through `bs` and builds the object.
+  static std::unique_ptr<AllToAll> create(const A2AConfig& cfg, Bootstrap& bs);
+
+  // `cfg.world_size` ranks on the current device; cfg.rank is ignored.
+  static std::vector<std::unique_ptr<AllToAll>> create_local_world(const A2AConfig& cfg);
+
+  void dispatch(const DispatchCall& call, SplitMode mode, cudaStream_t stream);
+  void combine(const CombineCall& call, SplitMode mode, cudaStream_t stream);
+
+  // All ranks of a local world in one cooperative launch per operation.
+  static void dispatch_group(const std::vector<AllToAll*>& ranks,
+                             const std::vector<DispatchCall>& calls, SplitMode mode,
+                             cudaStream_t stream);
+  static void combine_group(const std::vector<AllToAll*>& ranks,
+                            const std::vector<CombineCall>& calls, SplitMode mode,
+                            cudaStream_t stream);
+
+  // Reads the device status block (synchronises the device); throws on failure.
+  Status read_status() const;
+  void check_status() const;
+
+  // Tunables (also settable through PPLX_B200_* environment variables at creation).
+  void set_timeout_ms(double ms);
+  void set_debug_checks(bool on) { params_.debug_checks = on ? 1 : 0; }
+  void set_max_blocks(int n) { max_blocks_ = n; }
+
+  const A2AParams& params() const { return params_; }
+  const A2AConfig& config() const { return cfg_; }
+  int num_local_experts() const { return params_.nle; }
+  int num_dp_groups() const { return params_.num_dp_groups; }
+  int experts_per_token() const { return cfg_.experts_per_token; }
+
+  DispatchArgs make_dispatch_args(const DispatchCall& call) const;
+  CombineArgs make_combine_args(const CombineCall& call) const;
+  int dispatch_grid(int num_tokens) const;
+  int combine_grid(int num_tokens) const;
+
+ private:
+  A2AConfig cfg_;
+  A2AParams params_{};
+  std::shared_ptr<SymmetricAllocation> arena_;
+  DeviceBuffer<uint32_t> iter_;
+  DeviceBuffer<uint32_t> ticket_;
+  DeviceBuffer<uint32_t> recv_count_;
+  DeviceBuffer<uint2> row_src_;
+  DeviceBuffer<Status> status_;
+  int num_sms_ = 0;
+  int max_blocks_ = 0;
+};
+
+}  // namespace pplx

@@ -1,0 +1,109 @@
+"""CPU tests of the host side: operator surface, configuration checks and the
+socket bootstrap (spawned processes, no GPU)."""
+
+import multiprocessing as mp
+
+import pytest
+import torch
+
+import pplx_kernels_b200 as pk
+from pplx_kernels_b200.ops import _ops
+
+
+def test_operator_surface_matches_reference_names():
+    names = [
+        "all_to_all_intranode_create", "all_to_all_internode_create", "all_to_all_destroy",
+        "all_to_all_intranode_dispatch", "all_to_all_intranode_combine",
+        "all_to_all_internode_dispatch", "all_to_all_internode_combine",
+        "nvshmem_get_unique_id", "nvshmem_unique_id_size", "nvshmem_init", "nvshmem_finalize",
+        "nvshmem_my_pe", "nvshmem_n_pes", "nvshmem_malloc", "nvshmem_barrier_all",
+        "nvshmem_barrier_all_on_current_stream", "nvshmem_alltoall",
+    ]
+    for n in names:
+        assert hasattr(_ops, n), n
+
+
+def test_dispatch_schema_marks_outputs_mutable():
+    schema = str(_ops.all_to_all_intranode_dispatch.default._schema)
+    assert "Tensor($0! -> ) out_expert_num_tokens" in schema
+    assert "Tensor($2! -> )? out_expert_x_scale" in schema
+    assert "Tensor? bound_m" in schema
+    schema = str(_ops.all_to_all_internode_combine.default._schema)
+    assert "Tensor($0! -> ) out_tokens" in schema
+
+
+def test_unique_id_is_128_bytes():
+    assert pk.nvshmem_unique_id_size() == 128
+    uid = pk.nvshmem_get_unique_id()
+    assert uid.dtype == torch.uint8 and uid.device.type == "cpu" and uid.numel() == 128
+    assert pk.nvshmem_alloc_empty_unique_id().sum() == 0
+    assert not torch.equal(uid, pk.nvshmem_get_unique_id())
+
+
+@pytest.mark.parametrize(
+    "kwargs, message",
+    [
+        (dict(hidden_dim_bytes=1000), "multiple of 16"),
+        (dict(hidden_dim_scale_bytes=8), "multiple of 16"),
+        (dict(num_experts=0), "multiple of world_size"),
+        (dict(experts_per_token=0), "experts_per_token"),
+        (dict(max_num_tokens=0), "max_num_tokens"),
+    ],
+)
+def test_bad_configuration_is_rejected_before_touching_the_gpu(kwargs, message):
+    base = dict(max_num_tokens=8, num_experts=8, experts_per_token=2, rank=0, world_size=1,
+                dp_size=1, hidden_dim=512, hidden_dim_bytes=1024, hidden_dim_scale_bytes=0)
+    base.update(kwargs)
+    with pytest.raises(RuntimeError, match=message):
+        pk.AllToAll.intranode(**base)
+
+
+def test_send_and_recv_both_false_is_an_error_name():
+    # The op must exist with both flags in its schema (the failure itself needs a GPU object).
+    schema = str(_ops.all_to_all_intranode_combine.default._schema)
+    assert "bool do_send, bool do_recv" in schema
+
+
+def _bootstrap_rank(uid_bytes: bytes, rank: int, world: int, q) -> None:
+    import torch as t
+
+    from pplx_kernels_b200.ops import _ops as ops
+
+    uid = t.tensor(list(uid_bytes), dtype=t.uint8)
+    q.put((rank, ops.bootstrap_selftest(uid, rank, world, 20000).tolist()))
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_socket_bootstrap_gathers_and_exchanges(world):
+    uid = pk.nvshmem_get_unique_id()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_bootstrap_rank, args=(bytes(uid.tolist()), r, world, q))
+             for r in range(1, world)]
+    for p in procs:
+        p.start()
+    mine = _ops.bootstrap_selftest(uid, 0, world, 20000).tolist()
+    results = {0: mine}
+    for _ in procs:
+        r, out = q.get(timeout=60)
+        results[r] = out
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for r in range(world):
+        assert results[r][:world] == [1000 + i for i in range(world)]
+        assert results[r][world:] == [src * 100 + r for src in range(world)]
+
+
+def test_socket_bootstrap_reports_a_missing_peer():
+    # A world of two in which rank 1 never shows up: rank 0 gives up with an error.
+    uid = pk.nvshmem_get_unique_id()
+    with pytest.raises(RuntimeError, match="peers connected"):
+        _ops.bootstrap_selftest(uid, 0, 2, 300)
+
+
+def test_socket_bootstrap_reports_an_unreachable_hub():
+    uid = pk.nvshmem_get_unique_id().clone()
+    uid[20:40] = 65  # a socket name nobody listens on
+    with pytest.raises(RuntimeError, match="could not reach rank 0"):
+        _ops.bootstrap_selftest(uid, 1, 2, 300)
