@@ -1,0 +1,352 @@
+"""Headline benchmark: MoE dispatch + combine all-to-all, DeepSeek-V3 shape.
+
+One step = one ``AllToAll.dispatch`` (fp8 e4m3 payload + fp32 scale per 128
+columns, 256 experts, top-8, hidden 7168, 128 tokens per GPU) followed by one
+``AllToAll.combine`` (bf16 expert outputs -> bf16 tokens), the pair the
+reference's own benchmark times (tests/bench_all_to_all.py:144-210).  Routing,
+tokens and weights are synthetic.
+
+    python bench.py --gpus 1 --steps 200 --warmup 20
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 \
+        --master-addr 127.0.0.1 --master-port 29501 bench.py --gpus 8
+
+Timing: every step is bracketed by CUDA events on the launching stream, after a
+write of a 256 MiB buffer that flushes the 126 MB L2 and (for N > 1) a device
+barrier across ranks so that all ranks start together; per step the maximum over
+ranks is taken, then the mean over the K timed steps gives ``ms_per_step`` and
+the aggregate tokens/s; p50 values are reported next to it.  Rank 0 prints one
+JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# Published EP8 NVLink numbers of the reference (its README.md:60-81), in microseconds.
+PUBLISHED_US = {1: {"dispatch": 41.6, "combine": 41.7}, 128: {"dispatch": 83.6, "combine": 102.3}}
+NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction on this pool
+
+
+def _peaks() -> dict:
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return json.load(f)
+    except OSError:
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "fallback": True}
+
+
+def reference_arm(args: argparse.Namespace) -> None:
+    """Runs the unmodified reference if it could be installed under baseline/_ref."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    lib = os.path.join(ref_dir, "pplx_kernels", "libpplx_kernels.so")
+    if not os.path.exists(lib):
+        print(json.dumps({
+            "impl": "reference",
+            "unavailable": "offline install failed: the reference's setup.py passes "
+                           "'-WITH_TESTS=OFF' to cmake, which cmake 3.x+ rejects, and its "
+                           "CMakeLists needs find_package(NVSHMEM) + MPI, neither of which "
+                           "has a CMake package in this image",
+        }))
+        return
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "reference library present but no runner is wired up"}))
+
+
+class Bench:
+    def __init__(self, tokens: int) -> None:
+        import pplx_kernels_b200 as pk
+        from pplx_kernels_b200.utils.testing import MoEConfig, as_index_tensor, make_rank_inputs
+
+        self.pk = pk
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+        self.cfg = MoEConfig(num_experts=256, experts_per_token=8, hidden_dim=7168,
+                             max_num_tokens=tokens, in_dtype=torch.float8_e4m3fn,
+                             out_dtype=torch.bfloat16)
+        cfg = self.cfg
+        self.tokens = tokens
+        nle = cfg.num_experts // self.world
+        gen = torch.Generator().manual_seed(1000 + self.rank)
+        inp = make_rank_inputs(cfg, gen, num_tokens=tokens, softmax_weights=True)
+        # Host copies in pinned memory (the end-to-end path uploads them every step).
+        self.h_x = inp.x.view(torch.uint8).pin_memory()
+        self.h_scale = inp.x_scale.pin_memory()
+        self.h_idx = inp.indices.pin_memory()
+        self.h_w = inp.weights.pin_memory()
+        dev = self.device
+        self.x = inp.x.to(dev)
+        self.x_scale = inp.x_scale.to(dev)
+        self.indices = as_index_tensor(inp.indices, dev)
+        self.weights = inp.weights.to(dev)
+        self.bound_m = torch.tensor([tokens], dtype=torch.int32, device=dev).view(torch.uint32)
+        rows = tokens * self.world
+        self.counts = torch.zeros(nle, dtype=torch.int32, device=dev)
+        self.expert_x = torch.zeros(nle, rows, cfg.hidden_dim, dtype=torch.uint8,
+                                    device=dev).view(cfg.in_dtype)
+        self.expert_scale = torch.zeros(nle, rows, cfg.hidden_dim_scale, device=dev)
+        self.expert_y = torch.randn(nle, rows, cfg.hidden_dim, device=dev).to(cfg.out_dtype)
+        self.out = torch.zeros(tokens, cfg.hidden_dim, dtype=cfg.out_dtype, device=dev)
+        self.h_out = torch.empty(tokens, cfg.hidden_dim, dtype=cfg.out_dtype).pin_memory()
+        self.ata = pk.AllToAll.intranode(
+            cfg.max_num_tokens, cfg.num_experts, cfg.experts_per_token, self.rank, self.world, 1,
+            cfg.hidden_dim, cfg.hidden_dim_bytes, cfg.hidden_dim_scale_bytes)
+
+    def dispatch(self) -> None:
+        self.ata.dispatch(self.counts, self.expert_x, self.expert_scale, self.x, self.x_scale,
+                          self.indices, self.bound_m)
+
+    def combine(self) -> None:
+        self.ata.combine(self.out, self.indices, self.weights, self.expert_y, self.bound_m)
+
+    def upload(self) -> None:
+        self.x.view(torch.uint8).copy_(self.h_x, non_blocking=True)
+        self.x_scale.copy_(self.h_scale, non_blocking=True)
+        self.indices.view(torch.int32).copy_(self.h_idx, non_blocking=True)
+        self.weights.copy_(self.h_w, non_blocking=True)
+
+    def download(self) -> None:
+        self.h_out.copy_(self.out, non_blocking=True)
+
+    def h2d_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.h_x, self.h_scale, self.h_idx, self.h_w))
+
+    def d2h_bytes(self) -> int:
+        return self.h_out.numel() * self.h_out.element_size()
+
+    def close(self) -> None:
+        self.ata.check_status()
+        self.ata.destroy()
+
+
+def _rank_barrier(world: int) -> None:
+    if world > 1:
+        from pplx_kernels_b200 import nvshmem_barrier_all_on_current_stream
+
+        nvshmem_barrier_all_on_current_stream()
+
+
+def _max_over_ranks(t: torch.Tensor, world: int) -> torch.Tensor:
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t
+
+
+def time_steps(b: Bench, steps: int, warmup: int, flush: torch.Tensor, e2e: bool) -> torch.Tensor:
+    """Returns [steps, 3] microseconds (dispatch, combine, whole step), max over ranks."""
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    for i in range(warmup + steps):
+        flush.add_(1)
+        _rank_barrier(b.world)
+        e = evs[i - warmup] if i >= warmup else None
+        if e:
+            e[0].record()
+        if e2e:
+            b.upload()
+        b.dispatch()
+        if e:
+            e[1].record()
+        b.combine()
+        if e2e:
+            b.download()
+        if e:
+            e[2].record()
+    torch.cuda.synchronize()
+    t = torch.tensor(
+        [[e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2]), e[0].elapsed_time(e[2])] for e in evs],
+        dtype=torch.float64, device=b.device) * 1e3
+    return _max_over_ranks(t, b.world).cpu()
+
+
+def nccl_baseline(b: Bench, steps: int, warmup: int, flush: torch.Tensor) -> float | None:
+    """p50 microseconds of torch all_to_all_single on the reference's dense shape."""
+    if b.world == 1:
+        return None
+    import torch.distributed as dist
+
+    cfg = b.cfg
+    per_token = cfg.hidden_dim_bytes + cfg.hidden_dim_scale_bytes
+    shape = (b.world, cfg.num_experts // b.world, b.tokens * per_token)
+    src = torch.zeros(shape, dtype=torch.uint8, device=b.device)
+    dst = torch.empty_like(src)
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(steps)]
+    for i in range(warmup + steps):
+        flush.add_(1)
+        _rank_barrier(b.world)
+        if i >= warmup:
+            evs[i - warmup][0].record()
+        dist.all_to_all_single(dst, src)
+        if i >= warmup:
+            evs[i - warmup][1].record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e[0].elapsed_time(e[1]) for e in evs], dtype=torch.float64,
+                     device=b.device) * 1e3
+    return float(_max_over_ranks(t, b.world).median())
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--tokens", type=int, default=128, help="tokens per GPU of the headline run")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        if int(os.environ.get("RANK", "0")) == 0:
+            reference_arm(args)
+        return
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        import torch.distributed as dist
+
+        import pplx_kernels_b200 as pk
+
+        dist.init_process_group(backend="cpu:gloo,cuda:nccl",
+                                device_id=torch.device("cuda", local_rank))
+        uid = pk.nvshmem_get_unique_id() if rank == 0 else pk.nvshmem_alloc_empty_unique_id()
+        dist.broadcast(uid, src=0)
+        pk.nvshmem_init(uid, rank, world)
+
+    from pplx_kernels_b200.utils.clocks import ClockSampler
+
+    steps, warmup = args.steps, max(args.warmup, 3)
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
+    peaks = _peaks()
+
+    results: dict[int, dict] = {}
+    e2e_us = None
+    bench_main = Bench(args.tokens)
+    with ClockSampler(local_rank) as sampler:
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        wall0 = time.perf_counter()
+        t_main = time_steps(bench_main, steps, warmup, flush, e2e=False)
+        torch.cuda.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+        wall1 = time.perf_counter()
+    clocks = sampler.summary()
+    t_e2e = time_steps(bench_main, steps, warmup, flush, e2e=True)
+    e2e_us = float(t_e2e[:, 2].mean())
+    nccl_us = nccl_baseline(bench_main, min(steps, 50), 5, flush)
+    h2d, d2h = bench_main.h2d_bytes(), bench_main.d2h_bytes()
+    bench_main.close()
+    results[args.tokens] = {
+        "dispatch_us_p50": float(t_main[:, 0].median()),
+        "combine_us_p50": float(t_main[:, 1].median()),
+        "step_us_p50": float(t_main[:, 2].median()),
+        "step_us_mean": float(t_main[:, 2].mean()),
+        "nccl_all_to_all_single_us_p50": nccl_us,
+    }
+    for extra_tokens in ([1] if args.tokens != 1 else []):
+        b = Bench(extra_tokens)
+        t = time_steps(b, min(steps, 100), warmup, flush, e2e=False)
+        b.close()
+        results[extra_tokens] = {
+            "dispatch_us_p50": float(t[:, 0].median()),
+            "combine_us_p50": float(t[:, 1].median()),
+            "step_us_p50": float(t[:, 2].median()),
+        }
+
+    # Roofline of the headline step: bytes that must move over the slower path.
+    cfg = bench_main.cfg
+    slot = cfg.hidden_dim_bytes + cfg.hidden_dim_scale_bytes + 16
+    rows = args.tokens * cfg.experts_per_token
+    disp_bytes = rows * slot
+    comb_bytes = rows * cfg.hidden_dim * 2
+    if world > 1:
+        remote = (world - 1) / world
+        floor_us = {"dispatch": disp_bytes * remote / NVLINK_GBS / 1e3,
+                    "combine": comb_bytes * remote / NVLINK_GBS / 1e3}
+        bound = f"NVLink {NVLINK_GBS:.0f} GB/s per direction (measured peer copy)"
+    else:
+        # single GPU: staging write + staging read + output write per row (dispatch);
+        # staging write + staging read per row plus the token write (combine)
+        hbm = float(peaks["hbm_gbs"])
+        floor_us = {"dispatch": 3 * disp_bytes / hbm / 1e3, "combine": 2.125 * comb_bytes / hbm / 1e3}
+        bound = f"HBM {hbm:.0f} GB/s of measured copy bandwidth"
+    main_res = results[args.tokens]
+    roofline = {
+        "bound": bound,
+        "dispatch_floor_us": floor_us["dispatch"],
+        "combine_floor_us": floor_us["combine"],
+        "dispatch_frac": floor_us["dispatch"] / main_res["dispatch_us_p50"],
+        "combine_frac": floor_us["combine"] / main_res["combine_us_p50"],
+    }
+
+    step_s = main_res["step_us_mean"] * 1e-6
+    value = world * args.tokens / step_s
+    pub = PUBLISHED_US.get(args.tokens)
+    vs = None
+    if pub:
+        # the published numbers are per-rank latencies at EP8; same tokens per GPU
+        vs = value / (world * args.tokens / ((pub["dispatch"] + pub["combine"]) * 1e-6))
+    line = {
+        "metric": "MoE dispatch+combine tokens/s (DeepSeek-V3 shape: 256 experts, top-8, hidden "
+                  "7168, fp8 dispatch + bf16 combine)",
+        "value": value,
+        "unit": "tokens/s",
+        "n_gpus": world,
+        "steps": steps,
+        "warmup": warmup,
+        "ms_per_step": main_res["step_us_mean"] / 1e3,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": vs,
+        "dtype": "fp8_e4m3 dispatch (fp32 scale per 128) / bf16 combine",
+        "data": "synthetic (uniform random distinct top-8 routing, random tokens, softmax weights)",
+        "config": {
+            "model": "DeepSeek-V3 MoE layer all-to-all",
+            "global_batch": world * args.tokens,
+            "seq_len": 1,
+            "tokens_per_gpu": args.tokens,
+            "parallelism": f"ep{world}",
+            "l2": "flushed between steps (256 MiB write)",
+            "timing": "CUDA events per step, max over ranks, mean over steps",
+        },
+        "latency_us": {str(k): v for k, v in results.items()},
+        "published_reference_us": {str(k): v for k, v in PUBLISHED_US.items()},
+        "roofline": roofline,
+        "clocks": clocks,
+        "wall_ms_per_step_incl_flush_and_barrier": (wall1 - wall0) * 1e3 / (steps + warmup),
+        "e2e": {
+            "value": world * args.tokens / (e2e_us * 1e-6),
+            "unit": "tokens/s",
+            "us_per_step": e2e_us,
+            "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h,
+        },
+        "gpu_launches": 2 * steps,
+        "impl": "ours",
+    }
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        import pplx_kernels_b200 as pk
+
+        torch.distributed.barrier()
+        pk.nvshmem_finalize()
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -142,6 +142,21 @@ class AllToAll:
     def set_max_blocks(self, n: int) -> None:
         _ops.all_to_all_set_max_blocks(self._ptr, int(n))
 
+    def set_trace(self, on: bool) -> None:
+        """Turns the per-phase device time stamps of block 0 on or off."""
+        _ops.all_to_all_set_trace(self._ptr, bool(on))
+
+    def read_trace(self) -> dict[str, int]:
+        """Last recorded %globaltimer stamps in nanoseconds, by phase name.  Synchronises."""
+        t = _ops.all_to_all_read_trace(self._ptr)
+        names = {
+            0: "dispatch_start", 1: "dispatch_hist", 2: "dispatch_posted", 3: "dispatch_stored",
+            4: "dispatch_signalled", 5: "dispatch_counts", 6: "dispatch_layout",
+            7: "dispatch_copied", 8: "dispatch_end", 16: "combine_start", 17: "combine_layout",
+            18: "combine_sent", 19: "combine_reduced", 20: "combine_end",
+        }
+        return {name: t[i] for i, name in names.items()}
+
     def layout(self) -> dict[str, int]:
         keys = ("num_local_experts", "num_dp_groups", "rows_per_expert", "region_slots",
                 "slot_bytes", "arena_bytes")

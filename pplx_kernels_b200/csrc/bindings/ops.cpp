@@ -390,6 +390,13 @@ void set_debug_checks_op(int64_t ptr, bool on) { lookup(ptr)->set_debug_checks(o
 
 void set_max_blocks_op(int64_t ptr, int64_t n) { lookup(ptr)->set_max_blocks(static_cast<int>(n)); }
 
+void set_trace_op(int64_t ptr, bool on) { lookup(ptr)->set_trace(on); }
+
+std::vector<int64_t> read_trace_op(int64_t ptr) {
+  const std::vector<uint64_t> t = guarded([&] { return lookup(ptr)->read_trace(); });
+  return std::vector<int64_t>(t.begin(), t.end());
+}
+
 std::vector<int64_t> layout_op(int64_t ptr) {
   const A2AParams& p = lookup(ptr)->params();
   return {p.nle, p.num_dp_groups, p.cap, p.region_slots, p.slot_bytes,
@@ -566,6 +573,8 @@ void register_all_to_all_ops(torch::Library& m) {
   m.def("all_to_all_set_debug_checks(int ptr, bool on) -> ()", &set_debug_checks_op);
   m.def("all_to_all_set_max_blocks(int ptr, int n) -> ()", &set_max_blocks_op);
   m.def("all_to_all_layout(int ptr) -> int[]", &layout_op);
+  m.def("all_to_all_set_trace(int ptr, bool on) -> ()", &set_trace_op);
+  m.def("all_to_all_read_trace(int ptr) -> int[]", &read_trace_op);
 }
 
 void register_symmetric_memory_ops(torch::Library& m) {

@@ -69,6 +69,28 @@ __device__ inline void block_exclusive_scan(uint32_t* data, int n, uint32_t* war
 }
 constexpr int kScanTmpWords = 34;
 
+// Exclusive scan of data[0..n) in shared memory by ONE warp (all 32 lanes call
+// it); data[n] receives the total when `write_total`.  Each lane owns a
+// contiguous run, so n up to a few thousand costs a handful of steps and no
+// block barrier.  The caller synchronises the block afterwards.
+__device__ __forceinline__ void warp_exclusive_scan_smem(uint32_t* data, int n, int lane,
+                                                         bool write_total) {
+  const int per = (n + 31) >> 5;
+  const int begin = min(lane * per, n);
+  const int end = min(begin + per, n);
+  uint32_t sum = 0;
+  for (int i = begin; i < end; ++i) sum += data[i];
+  const uint32_t inc = warp_inclusive_scan(sum, lane);
+  uint32_t run = inc - sum;
+  for (int i = begin; i < end; ++i) {
+    const uint32_t v = data[i];
+    data[i] = run;
+    run += v;
+  }
+  if (write_total && lane == 31) data[n] = inc;
+  __syncwarp();
+}
+
 // Largest p in [0, n) with prefix[p] <= x, given prefix[0] = 0 and x < prefix[n].
 // Entries with equal prefix (empty groups) are skipped in favour of the last one.
 __device__ __forceinline__ int find_group(const uint32_t* prefix, int n, uint32_t x) {

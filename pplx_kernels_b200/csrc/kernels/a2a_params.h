@@ -41,8 +41,9 @@ struct A2AParams {
   int max_tokens;    // per DP group and step
   int hidden_dim;    // elements
   int hidden_bytes;  // dispatch payload bytes per token (multiple of 16)
-  int scale_bytes;   // fp32 scale bytes per token (multiple of 16, may be 0)
-  int slot_bytes;    // hidden_bytes + scale_bytes + 16 (trailer)
+  int scale_bytes;   // fp32 scale bytes per token (multiple of 4, may be 0)
+  int trailer_off;   // round_up(hidden_bytes + scale_bytes, 16): where the trailer sits
+  int slot_bytes;    // trailer_off + 16
   int region_slots;  // dispatch staging slots per source rank
   int cap;           // rows per local expert in out_expert_x / expert_y
   int debug_checks;  // non-zero: bounds checks that record instead of corrupting
@@ -64,6 +65,26 @@ struct A2AParams {
   uint2* row_src;         // [nle][cap] {src_rank | k << 16, src_token} per received row
   Status* status;
   uint64_t timeout_ns;
+  uint64_t* trace;        // optional [kTraceSlots] %globaltimer stamps of block 0, or null
+};
+
+// Trace slots (block 0, thread 0).  Dispatch uses 0..15, combine 16..31.
+constexpr int kTraceSlots = 32;
+enum TraceSlot : int {
+  kTrDispatchStart = 0,
+  kTrDispatchHist = 1,      // histogram of indices done
+  kTrDispatchPosted = 2,    // counts posted, slot bases ready
+  kTrDispatchStored = 3,    // this block's payload stores issued
+  kTrDispatchSignalled = 4, // arrival counters bumped (end of send)
+  kTrDispatchCounts = 5,    // all peers' counts seen
+  kTrDispatchLayout = 6,    // row offsets ready
+  kTrDispatchCopied = 7,    // this block's rows copied out
+  kTrDispatchEnd = 8,
+  kTrCombineStart = 16,
+  kTrCombineLayout = 17,
+  kTrCombineSent = 18,
+  kTrCombineReduced = 19,
+  kTrCombineEnd = 20,
 };
 
 struct DispatchArgs {

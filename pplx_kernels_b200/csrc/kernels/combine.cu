@@ -47,6 +47,10 @@ __device__ __forceinline__ CombineSmem carve(uint32_t* s, int nle) {
   return m;
 }
 
+__device__ __forceinline__ void trace(const A2AParams& p, int slot) {
+  if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.trace[slot] = ptx::globaltimer_ns();
+}
+
 // ---- 8-element vector helpers ------------------------------------------------
 
 template <typename T>
@@ -120,7 +124,9 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
 
   for (int le = tid; le < p.nle; le += blockDim.x) sm.estart[le] = p.recv_count[le];
   __syncthreads();
-  block_exclusive_scan(sm.estart, p.nle, sm.tmp);
+  if (warp == 0) warp_exclusive_scan_smem(sm.estart, p.nle, lane, true);
+  __syncthreads();
+  trace(p, kTrCombineLayout);
   const uint32_t total_rows = sm.estart[p.nle];
 
   const int row_bytes = p.hidden_dim * static_cast<int>(sizeof(T));
@@ -221,6 +227,7 @@ __device__ __forceinline__ void recv_phase(const CombineArgs& a, const CombineSm
                packed);
   }
 
+  trace(p, kTrCombineReduced);
   __syncthreads();
   if (tid == 0) {
     ptx::fence_acq_rel_gpu();
@@ -241,9 +248,12 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a, uint32_t* sme
   int m = a.num_tokens;
   if (a.bound_m != nullptr) m = min(m, static_cast<int>(__ldg(a.bound_m)));
   m = min(m, p.max_tokens);
+  trace(p, kTrCombineStart);
   if constexpr (SEND) send_phase<T>(a, sm);
+  trace(p, kTrCombineSent);
   if constexpr (SEND && RECV) __syncthreads();
   if constexpr (RECV) recv_phase<T, U>(a, sm, m);
+  trace(p, kTrCombineEnd);
 }
 
 template <typename T, typename U, bool SEND, bool RECV>

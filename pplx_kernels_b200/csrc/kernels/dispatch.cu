@@ -47,6 +47,7 @@ constexpr int kDispatchThreads = 512;
 struct DispatchSmem {
   uint32_t* hist;    // [E]
   uint32_t* base;    // [E]
+  uint32_t* off;     // [E]  rows for lower local experts of the same destination
   uint32_t* fstart;  // [P + 1]  counts, then their exclusive scan
   uint32_t* rbase;   // [P]
   uint32_t* sent;    // [kMaxWorld]
@@ -58,12 +59,17 @@ __device__ __forceinline__ DispatchSmem carve(uint32_t* s, int E, int P) {
   DispatchSmem m;
   m.hist = s;
   m.base = m.hist + E;
-  m.fstart = m.base + E;
+  m.off = m.base + E;
+  m.fstart = m.off + E;
   m.rbase = m.fstart + P + 1;
   m.sent = m.rbase + P;
   m.tmp = m.sent + kMaxWorld;
   m.misc = m.tmp + kScanTmpWords;
   return m;
+}
+
+__device__ __forceinline__ void trace(const A2AParams& p, int slot) {
+  if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.trace[slot] = ptx::globaltimer_ns();
 }
 
 __device__ __forceinline__ uint32_t* counts_ptr(const A2AParams& p, int dst, int parity, int src,
@@ -115,6 +121,7 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
     }
   }
   __syncthreads();
+  trace(p, kTrDispatchHist);
 
   if (blockIdx.x == 0) {
     for (int e = tid; e < E; e += blockDim.x) {
@@ -126,13 +133,16 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
 
   // Slot of the first row this block stores for expert e: rows for lower local
   // experts of the same destination come first, then earlier blocks' rows.
-  for (int e = tid; e < E; e += blockDim.x) {
-    const int le = e % p.nle;
-    uint32_t before = sm.base[e];
-    for (int j = 1; j <= le; ++j) before += sm.hist[e - j];
-    sm.base[e] = before;
+  // One warp per destination scans that destination's experts.
+  for (int e = tid; e < E; e += blockDim.x) sm.off[e] = sm.hist[e];
+  __syncthreads();
+  for (int dst = warp; dst < p.world; dst += nwarps) {
+    warp_exclusive_scan_smem(sm.off + dst * p.nle, p.nle, lane, false);
   }
   __syncthreads();
+  for (int e = tid; e < E; e += blockDim.x) sm.base[e] += sm.off[e];
+  __syncthreads();
+  trace(p, kTrDispatchPosted);
 
   const int nvec = p.hidden_bytes >> 4;
   const int nscale = p.scale_bytes >> 2;
@@ -171,13 +181,15 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
       t.y = k;
       t.z = le;
       t.w = 0;
-      ptx::st_v4(slot + p.hidden_bytes + p.scale_bytes, t);
+      ptx::st_v4(slot + p.trailer_off, t);
     }
   }
+  trace(p, kTrDispatchStored);
   __syncthreads();
   if (tid < p.world && sm.sent[tid] > 0) {
     ptx::red_add_release_sys(arrived_ptr(p, tid, parity, p.rank), sm.sent[tid]);
   }
+  trace(p, kTrDispatchSignalled);
 }
 
 __device__ __forceinline__ void recv_phase(const DispatchArgs& a, const DispatchSmem& sm,
@@ -202,6 +214,7 @@ __device__ __forceinline__ void recv_phase(const DispatchArgs& a, const Dispatch
     sm.fstart[q] = ok ? v - 1u : 0u;
   }
   __syncthreads();
+  trace(p, kTrDispatchCounts);
   // Row offset of (source s, expert le) inside the expert's output: sources in
   // rank order.
   for (int q = tid; q < P; q += blockDim.x) {
@@ -220,7 +233,10 @@ __device__ __forceinline__ void recv_phase(const DispatchArgs& a, const Dispatch
       p.recv_count[le] = min(total, static_cast<uint32_t>(p.cap));
     }
   }
-  block_exclusive_scan(sm.fstart, P, sm.tmp);  // fstart[q] = first flat row of group q
+  __syncthreads();
+  if (warp == 0) warp_exclusive_scan_smem(sm.fstart, P, lane, true);  // first flat row of group q
+  __syncthreads();
+  trace(p, kTrDispatchLayout);
 
   const uint32_t total_rows = sm.fstart[P];
   const int nvec = p.hidden_bytes >> 4;
@@ -271,7 +287,7 @@ __device__ __forceinline__ void recv_phase(const DispatchArgs& a, const Dispatch
       for (int j = lane; j < nscale; j += 32) sdst[j * a.out_scale_stride_col] = __ldcg(ssrc + j);
     }
     if (lane == 0) {
-      const int4 t = ptx::ld_cg_v4(slot + p.hidden_bytes + p.scale_bytes);
+      const int4 t = ptx::ld_cg_v4(slot + p.trailer_off);
       if (p.debug_checks && static_cast<uint32_t>(t.x) >= static_cast<uint32_t>(p.max_tokens)) {
         report_failure(p.status, kBadToken, kPhaseDispatchPayload, s, p.max_tokens, t.x, p.rank);
       }
@@ -282,6 +298,7 @@ __device__ __forceinline__ void recv_phase(const DispatchArgs& a, const Dispatch
     }
   }
 
+  trace(p, kTrDispatchCopied);
   // Last block out clears this parity's flags and opens the next iteration.
   __syncthreads();
   if (tid == 0) {
@@ -298,6 +315,7 @@ __device__ __forceinline__ void recv_phase(const DispatchArgs& a, const Dispatch
       *p.iter = *p.iter + 1u;
     }
   }
+  trace(p, kTrDispatchEnd);
 }
 
 template <bool SEND, bool RECV>
@@ -308,6 +326,7 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a, uint32_t* s
   int m = a.num_tokens;
   if (a.bound_m != nullptr) m = min(m, static_cast<int>(__ldg(a.bound_m)));
   m = min(m, p.max_tokens);
+  trace(p, kTrDispatchStart);
   if constexpr (SEND) send_phase(a, sm, parity, m);
   if constexpr (SEND && RECV) __syncthreads();
   if constexpr (RECV) recv_phase(a, sm, parity);
@@ -334,7 +353,7 @@ __global__ void __launch_bounds__(kDispatchThreads, 1)
 
 size_t dispatch_smem_bytes(const A2AParams& p) {
   const size_t E = p.num_experts, P = static_cast<size_t>(p.world) * p.nle;
-  return sizeof(uint32_t) * (2 * E + (P + 1) + P + kMaxWorld + kScanTmpWords + 4);
+  return sizeof(uint32_t) * (3 * E + (P + 1) + P + kMaxWorld + kScanTmpWords + 4);
 }
 
 int dispatch_threads() { return kDispatchThreads; }

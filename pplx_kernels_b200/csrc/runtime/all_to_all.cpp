@@ -64,8 +64,8 @@ void AllToAll::validate(const A2AConfig& c) {
   PPLX_CHECK(c.hidden_dim > 0, "hidden_dim must be positive");
   PPLX_CHECK(c.hidden_dim_bytes > 0 && c.hidden_dim_bytes % 16 == 0,
              "hidden_dim_bytes must be a positive multiple of 16");
-  PPLX_CHECK(c.hidden_dim_scale_bytes >= 0 && c.hidden_dim_scale_bytes % 16 == 0,
-             "hidden_dim_scale_bytes must be a multiple of 16");
+  PPLX_CHECK(c.hidden_dim_scale_bytes >= 0 && c.hidden_dim_scale_bytes % 4 == 0,
+             "hidden_dim_scale_bytes must be a multiple of 4");
   PPLX_CHECK(c.hidden_dim_scale_bytes <= c.hidden_dim_bytes, "scales larger than the payload");
 }
 
@@ -85,7 +85,8 @@ A2AParams make_layout(const A2AConfig& c) {
   p.hidden_dim = c.hidden_dim;
   p.hidden_bytes = c.hidden_dim_bytes;
   p.scale_bytes = c.hidden_dim_scale_bytes;
-  p.slot_bytes = c.hidden_dim_bytes + c.hidden_dim_scale_bytes + 16;
+  p.trailer_off = round_up(c.hidden_dim_bytes + c.hidden_dim_scale_bytes, 16);
+  p.slot_bytes = p.trailer_off + 16;
   const int tokens_per_sender = ceil_div(c.max_num_tokens, c.dp_size);
   p.region_slots = tokens_per_sender * std::min(c.experts_per_token, p.nle);
   p.cap = c.max_num_tokens * p.num_dp_groups;
@@ -126,6 +127,8 @@ AllToAll::AllToAll(const A2AConfig& cfg, std::shared_ptr<SymmetricAllocation> ar
   recv_count_ = DeviceBuffer<uint32_t>(params_.nle);
   row_src_ = DeviceBuffer<uint2>(static_cast<size_t>(params_.nle) * params_.cap);
   status_ = DeviceBuffer<Status>(1);
+  trace_ = DeviceBuffer<uint64_t>(kTraceSlots);
+  params_.trace = nullptr;
   params_.iter = iter_.get();
   params_.ticket = ticket_.get();
   params_.recv_count = recv_count_.get();
@@ -167,6 +170,10 @@ std::vector<std::unique_ptr<AllToAll>> AllToAll::create_local_world(const A2ACon
   }
   return out;
 }
+
+void AllToAll::set_trace(bool on) { params_.trace = on ? trace_.get() : nullptr; }
+
+std::vector<uint64_t> AllToAll::read_trace() const { return trace_.to_host(); }
 
 void AllToAll::set_timeout_ms(double ms) {
   PPLX_CHECK(ms > 0, "timeout must be positive");

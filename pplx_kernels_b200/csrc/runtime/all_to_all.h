@@ -111,6 +111,9 @@ class AllToAll {
   void set_timeout_ms(double ms);
   void set_debug_checks(bool on) { params_.debug_checks = on ? 1 : 0; }
   void set_max_blocks(int n) { max_blocks_ = n; }
+  // Per-phase %globaltimer stamps of block 0 (see TraceSlot); synchronises on read.
+  void set_trace(bool on);
+  std::vector<uint64_t> read_trace() const;
 
   const A2AParams& params() const { return params_; }
   const A2AConfig& config() const { return cfg_; }
@@ -132,6 +135,7 @@ class AllToAll {
   DeviceBuffer<uint32_t> recv_count_;
   DeviceBuffer<uint2> row_src_;
   DeviceBuffer<Status> status_;
+  DeviceBuffer<uint64_t> trace_;
   int num_sms_ = 0;
   int max_blocks_ = 0;
 };

@@ -1,0 +1,98 @@
+"""Single-GPU profiling driver for the dispatch and combine kernels.
+
+    python -m pplx_kernels_b200.utils.profile_a2a --tokens 128 --iters 20 --trace
+
+runs the DeepSeek-V3 shape (256 experts, top-8, hidden 7168, fp8 + scales in,
+bf16 out) as one rank, prints CUDA-event latencies and, with ``--trace``, the
+per-phase breakdown that block 0 stamps with %globaltimer.  With few iterations
+it is also the command to put under ``ncu`` (one kernel, a few launches).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+
+import torch
+
+import pplx_kernels_b200 as pk
+from pplx_kernels_b200.utils.testing import MoEConfig, as_index_tensor, make_rank_inputs
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=128)
+    ap.add_argument("--experts", type=int, default=256)
+    ap.add_argument("--topk", type=int, default=8)
+    ap.add_argument("--hidden", type=int, default=7168)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--trace", action="store_true")
+    ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--max-blocks", type=int, default=0)
+    args = ap.parse_args()
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    cfg = MoEConfig(args.experts, args.topk, args.hidden, args.tokens,
+                    in_dtype=torch.float8_e4m3fn, out_dtype=torch.bfloat16)
+    inp = make_rank_inputs(cfg, torch.Generator().manual_seed(1), num_tokens=args.tokens,
+                           softmax_weights=True)
+    ata = pk.AllToAll.intranode(cfg.max_num_tokens, cfg.num_experts, cfg.experts_per_token, 0, 1,
+                                1, cfg.hidden_dim, cfg.hidden_dim_bytes,
+                                cfg.hidden_dim_scale_bytes)
+    if args.max_blocks:
+        ata.set_max_blocks(args.max_blocks)
+    ata.set_trace(args.trace)
+    x, xs = inp.x.to(dev), inp.x_scale.to(dev)
+    idx, w = as_index_tensor(inp.indices, dev), inp.weights.to(dev)
+    bound_m = torch.tensor([args.tokens], dtype=torch.int32, device=dev).view(torch.uint32)
+    counts = torch.zeros(cfg.num_experts, dtype=torch.int32, device=dev)
+    ex = torch.zeros(cfg.num_experts, args.tokens, cfg.hidden_dim, dtype=torch.uint8,
+                     device=dev).view(cfg.in_dtype)
+    es = torch.zeros(cfg.num_experts, args.tokens, cfg.hidden_dim_scale, device=dev)
+    ey = torch.randn(cfg.num_experts, args.tokens, cfg.hidden_dim, device=dev).to(cfg.out_dtype)
+    out = torch.zeros(args.tokens, cfg.hidden_dim, dtype=cfg.out_dtype, device=dev)
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+
+    lat = {"dispatch": [], "combine": []}
+    phases: dict[str, list[float]] = {}
+    for it in range(args.warmup + args.iters):
+        if not args.no_flush:
+            flush.add_(1)
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        ata.dispatch(counts, ex, es, x, xs, idx, bound_m)
+        e[1].record()
+        ata.combine(out, idx, w, ey, bound_m)
+        e[2].record()
+        torch.cuda.synchronize()
+        if it < args.warmup:
+            continue
+        lat["dispatch"].append(e[0].elapsed_time(e[1]) * 1e3)
+        lat["combine"].append(e[1].elapsed_time(e[2]) * 1e3)
+        if args.trace:
+            t = ata.read_trace()
+            order = ["dispatch_start", "dispatch_hist", "dispatch_posted", "dispatch_stored",
+                     "dispatch_signalled", "dispatch_counts", "dispatch_layout",
+                     "dispatch_copied", "dispatch_end"]
+            for a, b in zip(order, order[1:], strict=False):
+                phases.setdefault(f"{a}->{b}", []).append((t[b] - t[a]) / 1e3)
+            order = ["combine_start", "combine_layout", "combine_sent", "combine_reduced",
+                     "combine_end"]
+            for a, b in zip(order, order[1:], strict=False):
+                phases.setdefault(f"{a}->{b}", []).append((t[b] - t[a]) / 1e3)
+    ata.check_status()
+    ata.destroy()
+    report = {
+        "tokens": args.tokens,
+        "dispatch_us_p50": statistics.median(lat["dispatch"]),
+        "combine_us_p50": statistics.median(lat["combine"]),
+        "phases_us_p50": {k: statistics.median(v) for k, v in phases.items()},
+    }
+    print(json.dumps(report, indent=1))
+
+
+if __name__ == "__main__":
+    main()

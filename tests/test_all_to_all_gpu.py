@@ -1,0 +1,292 @@
+"""GPU tests of dispatch/combine.
+
+Single-GPU coverage of the multi-rank protocol comes from local worlds: all
+ranks live on GPU 0 and run inside one cooperative launch per operation, with
+the same device code as the one-rank-per-GPU path.  The matrix mirrors the
+reference's `test_all_to_all_4_gpu` (tests/test_all_to_all.py:313-332: world 4,
+dp 2, 8 experts, top-3, hidden 512, three input dtypes x two output dtypes) and
+adds what the reference leaves untested: split send/recv, bound_m absent,
+strided scales, repeated iterations on one object, EP 1/2/4/8, skewed routing,
+CUDA-graph replay and time-outs.
+"""
+
+import pytest
+import torch
+
+import pplx_kernels_b200 as pk
+from pplx_kernels_b200.ops import _ops
+from pplx_kernels_b200.utils.testing import MoEConfig, as_index_tensor
+
+from .a2a_harness import (
+    RankBuffers,
+    run_local_world,
+    verify_combine,
+    verify_dispatch,
+    world_inputs,
+)
+
+pytestmark = pytest.mark.gpu
+
+
+def small(in_dtype=torch.bfloat16, out_dtype=torch.bfloat16, **kw) -> MoEConfig:
+    base = dict(num_experts=8, experts_per_token=3, hidden_dim=512, max_num_tokens=10)
+    base.update(kw)
+    return MoEConfig(in_dtype=in_dtype, out_dtype=out_dtype, **base)
+
+
+@pytest.mark.parametrize("in_dtype", [torch.bfloat16, torch.float8_e4m3fn, torch.float16])
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.bfloat16])
+def test_world4_dp2_dtype_matrix(in_dtype, out_dtype):
+    run_local_world(small(in_dtype, out_dtype), world=4, dp_size=2, seed=123)
+
+
+@pytest.mark.parametrize("world,dp_size", [(1, 1), (2, 1), (2, 2), (4, 1), (4, 4), (8, 1), (8, 2)])
+def test_expert_parallel_sizes(world, dp_size):
+    cfg = small(torch.float8_e4m3fn, num_experts=16, experts_per_token=4, hidden_dim=256,
+                max_num_tokens=12)
+    run_local_world(cfg, world=world, dp_size=dp_size, seed=5)
+
+
+def test_float32_expert_outputs():
+    run_local_world(small(), world=2, dp_size=1, seed=3, y_dtype=torch.float32)
+
+
+def test_float32_payload():
+    cfg = small(torch.float32, torch.bfloat16, hidden_dim=64)
+    run_local_world(cfg, world=2, dp_size=1, seed=4)
+
+
+def test_tiny_hidden_dim():
+    # The reference's C++ test shape: hidden 16, top-3, 8 experts, <= 10 tokens, dp 2.
+    cfg = small(torch.bfloat16, torch.bfloat16, hidden_dim=16)
+    run_local_world(cfg, world=4, dp_size=2, seed=0xBEEF)
+
+
+@pytest.mark.parametrize("in_dtype", [torch.bfloat16, torch.float8_e4m3fn])
+def test_split_send_recv(in_dtype):
+    run_local_world(small(in_dtype), world=4, dp_size=2, seed=11, split=True, iterations=2)
+
+
+def test_without_bound_m():
+    run_local_world(small(torch.float8_e4m3fn), world=4, dp_size=1, seed=12, use_bound_m=False)
+
+
+def test_strided_scales():
+    run_local_world(small(torch.float8_e4m3fn), world=2, dp_size=1, seed=13, strided_scale=True)
+
+
+def test_many_iterations_on_one_object():
+    # Exercises both parities of the flag sets and the self-reset of all counters.
+    run_local_world(small(torch.float8_e4m3fn), world=4, dp_size=2, seed=21, iterations=7)
+
+
+def test_more_tokens_than_blocks():
+    # Several tokens per block and several rows per warp.
+    cfg = small(torch.bfloat16, num_experts=32, experts_per_token=4, hidden_dim=128,
+                max_num_tokens=300)
+    run_local_world(cfg, world=4, dp_size=1, seed=31, num_tokens=300, max_blocks=3)
+
+
+def test_zipf_skewed_routing():
+    cfg = small(torch.float8_e4m3fn, num_experts=64, experts_per_token=8, hidden_dim=256,
+                max_num_tokens=64)
+    run_local_world(cfg, world=8, dp_size=1, seed=41, num_tokens=64, zipf=1.2)
+
+
+def test_deepseek_shape_world8_emulated():
+    cfg = MoEConfig(num_experts=256, experts_per_token=8, hidden_dim=7168, max_num_tokens=16,
+                    in_dtype=torch.float8_e4m3fn)
+    run_local_world(cfg, world=8, dp_size=1, seed=51, num_tokens=16)
+
+
+# ---------------------------------------------------------------- single rank ----
+
+
+def _single_rank(cfg: MoEConfig, seed: int):
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    inputs = world_inputs(cfg, 1, 1, seed)
+    ata = pk.AllToAll.intranode(
+        cfg.max_num_tokens, cfg.num_experts, cfg.experts_per_token, 0, 1, 1, cfg.hidden_dim,
+        cfg.hidden_dim_bytes, cfg.hidden_dim_scale_bytes)
+    ata.set_debug_checks(True)
+    ata.set_timeout_ms(3000)
+    buf = RankBuffers(cfg, 1, 1, inputs[0], device)
+    return ata, inputs, buf
+
+
+def _dispatch(ata, buf, **kw):
+    ata.dispatch(buf.counts, buf.expert_x, buf.expert_scale, buf.x, buf.x_scale, buf.indices,
+                 buf.bound_m, **kw)
+
+
+def _combine(ata, buf, **kw):
+    ata.combine(buf.out, buf.indices, buf.weights, buf.expert_y, buf.bound_m, **kw)
+
+
+@pytest.mark.parametrize("in_dtype", [torch.bfloat16, torch.float8_e4m3fn])
+def test_single_gpu_world_through_public_api(in_dtype):
+    cfg = small(in_dtype)
+    ata, inputs, buf = _single_rank(cfg, seed=61)
+    _dispatch(ata, buf)
+    torch.cuda.synchronize()
+    verify_dispatch(cfg, inputs, 1, 0, buf)
+    buf.make_expert_y()
+    _combine(ata, buf)
+    torch.cuda.synchronize()
+    ata.check_status()
+    verify_combine(cfg, inputs, 0, buf)
+    ata.destroy()
+    ata.destroy()  # idempotent
+
+
+def test_single_gpu_split_mode_with_work_in_between():
+    cfg = small(torch.float8_e4m3fn)
+    ata, inputs, buf = _single_rank(cfg, seed=62)
+    _dispatch(ata, buf, do_send=True, do_recv=False)
+    filler = torch.randn(512, 512, device="cuda") @ torch.randn(512, 512, device="cuda")
+    _dispatch(ata, buf, do_send=False, do_recv=True)
+    torch.cuda.synchronize()
+    verify_dispatch(cfg, inputs, 1, 0, buf)
+    buf.make_expert_y()
+    _combine(ata, buf, do_send=True, do_recv=False)
+    filler = filler @ filler
+    _combine(ata, buf, do_send=False, do_recv=True)
+    torch.cuda.synchronize()
+    ata.check_status()
+    verify_combine(cfg, inputs, 0, buf)
+    ata.destroy()
+
+
+def test_send_and_recv_false_is_rejected():
+    cfg = small()
+    ata, _, buf = _single_rank(cfg, seed=63)
+    with pytest.raises(RuntimeError, match="do_send = do_recv = false"):
+        _dispatch(ata, buf, do_send=False, do_recv=False)
+    ata.destroy()
+
+
+def test_argument_checks():
+    cfg = small(torch.float8_e4m3fn)
+    ata, _, buf = _single_rank(cfg, seed=64)
+    with pytest.raises(AssertionError):
+        ata.dispatch(buf.counts, buf.expert_x, None, buf.x, buf.x_scale, buf.indices, buf.bound_m)
+    with pytest.raises(RuntimeError, match="out_expert_num_tokens"):
+        ata.dispatch(buf.counts.to(torch.int64), buf.expert_x, buf.expert_scale, buf.x,
+                     buf.x_scale, buf.indices, buf.bound_m)
+    with pytest.raises(RuntimeError, match="rows per expert"):
+        ata.dispatch(buf.counts, buf.expert_x[:, :2].contiguous(), buf.expert_scale[:, :2].contiguous(),
+                     buf.x, buf.x_scale, buf.indices, buf.bound_m)
+    ata.destroy()
+    with pytest.raises(AssertionError):
+        _dispatch(ata, buf)
+
+
+def test_cuda_graph_replay():
+    cfg = small(torch.float8_e4m3fn, num_experts=16, experts_per_token=4, hidden_dim=1024,
+                max_num_tokens=32)
+    ata, inputs, buf = _single_rank(cfg, seed=65)
+    # Warm up outside capture, then capture one dispatch + expert + combine round.
+    _dispatch(ata, buf)
+    buf.make_expert_y()
+    _combine(ata, buf)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            _dispatch(ata, buf)
+            buf.expert_y.copy_((buf.expert_x.to(torch.float32) * 1.5).to(cfg.out_dtype))
+            _combine(ata, buf)
+    for n in (3, 1000):
+        buf.out.fill_(float("nan"))
+        buf.counts.fill_(-1)
+        for _ in range(n):
+            graph.replay()
+        torch.cuda.synchronize()
+        ata.check_status()
+        verify_dispatch(cfg, inputs, 1, 0, buf)
+        verify_combine(cfg, inputs, 0, buf)
+    # bound_m is read on the device: shrinking it changes the replayed work.
+    new_m = max(1, inputs[0].num_tokens // 2)
+    buf.bound_m.view(torch.int32).fill_(new_m)
+    inputs[0].num_tokens = new_m
+    buf.out.fill_(float("nan"))
+    graph.replay()
+    torch.cuda.synchronize()
+    verify_dispatch(cfg, inputs, 1, 0, buf)
+    verify_combine(cfg, inputs, 0, buf)
+    ata.destroy()
+
+
+def test_torch_compile_wraps_the_ops():
+    cfg = small(torch.bfloat16)
+    ata, inputs, buf = _single_rank(cfg, seed=66)
+    dispatch = torch.compile(ata.dispatch)
+    combine = torch.compile(ata.combine)
+    dispatch(buf.counts, buf.expert_x, buf.expert_scale, buf.x, buf.x_scale, buf.indices,
+             buf.bound_m)
+    torch.cuda.synchronize()
+    verify_dispatch(cfg, inputs, 1, 0, buf)
+    buf.make_expert_y()
+    combine(buf.out, buf.indices, buf.weights, buf.expert_y, buf.bound_m)
+    torch.cuda.synchronize()
+    verify_combine(cfg, inputs, 0, buf)
+    ata.destroy()
+
+
+# -------------------------------------------------------------------- time-outs ----
+
+
+def test_wait_helper_gives_up_and_reports():
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    code, phase, peer, expected, observed = _ops.wait_probe(flag, 20.0)
+    assert (code, phase, expected, observed) == (1, 5, 1, 0)
+    flag.fill_(7)
+    code, *_ = _ops.wait_probe(flag, 20.0)
+    assert code == 0
+    # the context is still usable
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0
+
+
+def test_missing_peer_times_out_instead_of_hanging():
+    cfg = small(torch.bfloat16, hidden_dim=64)
+    device = torch.device("cuda", 0)
+    ranks = pk.AllToAll.local_world(cfg.max_num_tokens, cfg.num_experts, cfg.experts_per_token,
+                                    2, 1, cfg.hidden_dim, cfg.hidden_dim_bytes, 0)
+    inputs = world_inputs(cfg, 2, 1, seed=71)
+    buf = RankBuffers(cfg, 2, 1, inputs[0], device)
+    ranks[0].set_timeout_ms(100)
+    # Only rank 0 runs: the counts of rank 1 never arrive.
+    pk.dispatch_group([ranks[0]], [buf.counts], [buf.expert_x], [None], [buf.x], [None],
+                      [buf.indices], [buf.bound_m])
+    torch.cuda.synchronize()
+    st = ranks[0].status()
+    assert st["code"] == 1 and st["phase"] == 1 and st["peer"] == 1 and st["rank"] == 0
+    with pytest.raises(RuntimeError, match="wait timed out"):
+        ranks[0].check_status()
+    for r in ranks:
+        r.destroy()
+    # A fresh object works after the failure.
+    run_local_world(cfg, world=2, dp_size=1, seed=72)
+
+
+def test_bad_expert_index_is_reported_with_debug_checks():
+    cfg = small(torch.bfloat16, hidden_dim=64)
+    ata, inputs, buf = _single_rank(cfg, seed=73)
+    bad = buf.indices.view(torch.int32).clone()
+    bad[0, 0] = cfg.num_experts + 5
+    ata.dispatch(buf.counts, buf.expert_x, None, buf.x, None, bad.view(torch.uint32), buf.bound_m)
+    torch.cuda.synchronize()
+    st = ata.status()
+    assert st["code"] == 2 and st["observed"] == cfg.num_experts + 5
+    ata.destroy()
+
+
+def test_sleep_on_stream_takes_about_that_long():
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    _ops.sleep_on_stream(0.002)
+    end.record()
+    torch.cuda.synchronize()
+    assert 1.5 <= start.elapsed_time(end) <= 50.0
