@@ -155,7 +155,18 @@ class AllToAll:
             7: "dispatch_copied", 8: "dispatch_end", 16: "combine_start", 17: "combine_layout",
             18: "combine_sent", 19: "combine_reduced", 20: "combine_end",
         }
-        return {name: t[i] for i, name in names.items()}
+        out = {name: t[i] for i, name in names.items()}
+        # Per-block stamps: earliest start and latest end over the blocks that ran.
+        nb = 256
+        for j, key in enumerate(("dispatch_blocks", "combine_blocks")):
+            starts = [v for v in t[32 + 2 * j * nb: 32 + (2 * j + 1) * nb] if v]
+            ends = [v for v in t[32 + (2 * j + 1) * nb: 32 + (2 * j + 2) * nb] if v]
+            if starts and ends:
+                out[key + "_first_start"] = min(starts)
+                out[key + "_last_start"] = max(starts)
+                out[key + "_first_end"] = min(ends)
+                out[key + "_last_end"] = max(ends)
+        return out
 
     def layout(self) -> dict[str, int]:
         keys = ("num_local_experts", "num_dp_groups", "rows_per_expert", "region_slots",

@@ -47,6 +47,13 @@ struct PredEq {
   uint32_t want;
   __device__ __forceinline__ bool operator()(uint32_t v) const { return v == want; }
 };
+// v has reached `want` on a counter that only grows, compared modulo 2^32.
+struct PredReached {
+  uint32_t want;
+  __device__ __forceinline__ bool operator()(uint32_t v) const {
+    return static_cast<int32_t>(v - want) >= 0;
+  }
+};
 struct PredGe {
   uint32_t want;
   __device__ __forceinline__ bool operator()(uint32_t v) const { return v >= want; }

@@ -18,6 +18,12 @@
 //    device-side iteration counter.  No flag handshake is needed before a send:
 //    a rank can be at most one dispatch ahead of any peer, because every rank
 //    posts counts to every rank in every dispatch.
+//  * Resets ride on the strict dispatch/combine alternation: a combine clears the
+//    flag set of the dispatch before it and bumps the iteration counter.  The
+//    combine's per-token arrival counters are never cleared: every combine adds
+//    16 * topk to each of them (peers for live tokens, the owner itself for
+//    tokens at or beyond bound_m), so the n-th combine waits for n * 16 * topk
+//    modulo 2^32.
 #pragma once
 
 #include <cstddef>
@@ -51,7 +57,7 @@ struct A2AParams {
   // offsets into the symmetric arena (bytes, 256-aligned)
   size_t off_counts;        // u32 [2][world][nle]   value = count + 1, 0 = not posted
   size_t off_arrived;       // u32 [2][world]        rows landed from each source
-  size_t off_comb_arrived;  // u32 [max_tokens]      expert outputs landed per token
+  size_t off_comb_arrived;  // u32 [max_tokens]      running total, 16 units per expert output
   size_t off_disp_stage;    // u8  [world][region_slots][slot_bytes]
   size_t off_comb_stage;    // u8  [max_tokens*topk][hidden_dim*4]
   size_t arena_bytes;
@@ -60,7 +66,7 @@ struct A2AParams {
 
   // rank-local state (plain device memory)
   uint32_t* iter;         // dispatch iteration counter; its parity selects the flag set
-  uint32_t* ticket;       // [2] finished-block tickets: dispatch, combine
+  uint32_t* comb_iter;    // number of dispatches started = ordinal of the coming combine
   uint32_t* recv_count;   // [nle] rows received per local expert by the last dispatch
   uint2* row_src;         // [nle][cap] {src_rank | k << 16, src_token} per received row
   Status* status;
@@ -68,8 +74,15 @@ struct A2AParams {
   uint64_t* trace;        // optional [kTraceSlots] %globaltimer stamps of block 0, or null
 };
 
-// Trace slots (block 0, thread 0).  Dispatch uses 0..15, combine 16..31.
-constexpr int kTraceSlots = 32;
+// Trace slots.  0..31: phase stamps of block 0, thread 0 (dispatch 0..15, combine
+// 16..31).  Then four arrays of kTraceBlocks stamps taken by thread 0 of every
+// block: dispatch start, dispatch end, combine start, combine end.
+constexpr int kTraceBlocks = 256;
+constexpr int kTraceSlots = 32 + 4 * kTraceBlocks;
+constexpr int kTrBlockDispatchStart = 32;
+constexpr int kTrBlockDispatchEnd = 32 + kTraceBlocks;
+constexpr int kTrBlockCombineStart = 32 + 2 * kTraceBlocks;
+constexpr int kTrBlockCombineEnd = 32 + 3 * kTraceBlocks;
 enum TraceSlot : int {
   kTrDispatchStart = 0,
   kTrDispatchHist = 1,      // histogram of indices done

@@ -15,8 +15,16 @@
 //  * The reduction is spread over (token, 256-element chunk) warp units so that a
 //    single token still uses many warps, and a unit starts as soon as its own
 //    token is complete.
-//  * The last block to finish clears the arrival counters; nothing else is
-//    reset.
+//  * A row is split over several warps when there are fewer rows than warps.
+//    Each part adds 16/parts to the token's arrival counter, so a token is
+//    complete at 16 * top-k whatever split the senders chose.
+//  * Signals are issued once per block and round: all warps store their parts,
+//    the block synchronises, and one warp executes a single system-scope fence
+//    followed by relaxed adds.  (A fence per warp serialises inside an SM and
+//    was the largest item of the first version's latency.)
+//  * Block 0 of the send phase clears the counters of the dispatch that just
+//    ended and bumps the iteration counter.  The per-token counters used here
+//    are never cleared; see a2a_params.h.  Nothing waits on a last block.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -32,23 +40,41 @@ namespace pplx {
 namespace {
 
 constexpr int kCombineThreads = 512;
+constexpr uint32_t kArrivalUnitsPerRow = 16;
+
+__device__ __forceinline__ int split_factor(uint32_t rows, uint32_t warps, int nvec) {
+  if (rows == 0 || rows >= warps) return 1;
+  uint32_t s = warps / rows;
+  s = 1u << (31 - __clz(s));
+  const uint32_t by_size = max(1, nvec >> 5);
+  s = min(s, min(kArrivalUnitsPerRow, 1u << (31 - __clz(by_size))));
+  return static_cast<int>(s);
+}
 
 struct CombineSmem {
-  uint32_t* estart;  // [nle + 1]
-  uint32_t* tmp;     // [kScanTmpWords]
-  uint32_t* misc;    // [4]
+  uint32_t* estart;   // [nle + 1]
+  uint32_t* tmp;      // [kScanTmpWords]
+  uint32_t* sig_tok;  // [nwarps] token whose part a warp stored this round, or kNoSignal
+  uint32_t* sig_grp;  // [nwarps] first rank of the token's DP group
 };
+constexpr uint32_t kNoSignal = 0xffffffffu;
 
 __device__ __forceinline__ CombineSmem carve(uint32_t* s, int nle) {
   CombineSmem m;
   m.estart = s;
   m.tmp = m.estart + nle + 1;
-  m.misc = m.tmp + kScanTmpWords;
+  m.sig_tok = m.tmp + kScanTmpWords;
+  m.sig_grp = m.sig_tok + kCombineThreads / 32;
   return m;
 }
 
 __device__ __forceinline__ void trace(const A2AParams& p, int slot) {
   if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.trace[slot] = ptx::globaltimer_ns();
+}
+
+__device__ __forceinline__ void trace_block(const A2AParams& p, int first_slot) {
+  if (p.trace != nullptr && threadIdx.x == 0 && blockIdx.x < kTraceBlocks)
+    p.trace[first_slot + blockIdx.x] = ptx::globaltimer_ns();
 }
 
 // ---- 8-element vector helpers ------------------------------------------------
@@ -122,6 +148,21 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
   const int warp = tid >> 5;
   const int nwarps = blockDim.x >> 5;
 
+  if (blockIdx.x == 0) {
+    // The dispatch that produced these rows has finished on this rank: clear the
+    // flag set it used and move on to the other one.  No peer can write this set
+    // again before it has seen counts of this rank's next dispatch.
+    const int parity = static_cast<int>(ptx::ld_volatile(p.iter) & 1u);
+    uint32_t* counts = reinterpret_cast<uint32_t*>(p.peer[p.rank] + p.off_counts) +
+                       a2a_counts_index(p, parity, 0, 0);
+    uint32_t* arrived =
+        reinterpret_cast<uint32_t*>(p.peer[p.rank] + p.off_arrived) + parity * p.world;
+    const int P = p.world * p.nle;
+    for (int q = tid; q < P; q += blockDim.x) counts[q] = 0;
+    if (tid < p.world) arrived[tid] = 0;
+    __syncthreads();
+    if (tid == 0) *p.iter = *p.iter + 1u;
+  }
   for (int le = tid; le < p.nle; le += blockDim.x) sm.estart[le] = p.recv_count[le];
   __syncthreads();
   if (warp == 0) warp_exclusive_scan_smem(sm.estart, p.nle, lane, true);
@@ -134,34 +175,65 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
   const T* y = static_cast<const T*>(a.expert_y);
   const uint32_t gwarp = blockIdx.x * nwarps + warp;
   const uint32_t gwarps = gridDim.x * nwarps;
+  const int split = split_factor(total_rows, gwarps, nvec);
+  const uint32_t n_units = total_rows * split;
+  const uint32_t arrival_units = kArrivalUnitsPerRow / split;
 
-  for (uint32_t f = gwarp; f < total_rows; f += gwarps) {
-    const int le = find_group(sm.estart, p.nle, f);
-    const uint32_t row = f - sm.estart[le];
-    const uint2 rs = p.row_src[static_cast<size_t>(le) * p.cap + row];
-    const int src_rank = static_cast<int>(rs.x & 0xffffu);
-    const uint32_t k = rs.x >> 16;
-    const uint32_t token = rs.y;
-    if (p.debug_checks && (token >= static_cast<uint32_t>(p.max_tokens) ||
-                           k >= static_cast<uint32_t>(p.topk) || src_rank >= p.world)) {
-      if (lane == 0)
-        report_failure(p.status, kBadToken, kPhaseCombinePayload, src_rank, p.max_tokens, token,
-                       p.rank);
-      continue;
-    }
-    const T* src = y + le * a.y_stride_e + static_cast<int64_t>(row) * a.y_stride_row;
-    const int group_first = (src_rank / p.dp_size) * p.dp_size;
-    for (int r = 0; r < p.dp_size; ++r) {
-      const int dst = group_first + r;
-      uint8_t* slot = p.peer[dst] + p.off_comb_stage +
-                      (static_cast<size_t>(token) * p.topk + k) * row_bytes;
-      ptx::warp_copy_v4<ptx::LoadKind::kNonCoherent>(slot, src, nvec, lane);
-      __syncwarp();
-      if (lane == 0) {
-        ptx::red_add_release_sys(
-            reinterpret_cast<uint32_t*>(p.peer[dst] + p.off_comb_arrived) + token, 1u);
+  // Rounds: in each, every warp stores at most one part; then one fence and the
+  // adds for the whole block.  All warps take part in every round's barriers.
+  const uint32_t rounds = ceil_div<uint32_t>(n_units, gwarps);
+  for (uint32_t round = 0; round < rounds; ++round) {
+    const uint32_t unit = round * gwarps + gwarp;
+    uint32_t sig_token = kNoSignal;
+    uint32_t sig_group = 0;
+    if (unit < n_units) {
+      const uint32_t f = unit / split;
+      const int c = static_cast<int>(unit - f * split);
+      const int le = find_group(sm.estart, p.nle, f);
+      const uint32_t row = f - sm.estart[le];
+      const uint2 rs = p.row_src[static_cast<size_t>(le) * p.cap + row];
+      const int src_rank = static_cast<int>(rs.x & 0xffffu);
+      const uint32_t k = rs.x >> 16;
+      const uint32_t token = rs.y;
+      if (p.debug_checks && (token >= static_cast<uint32_t>(p.max_tokens) ||
+                             k >= static_cast<uint32_t>(p.topk) || src_rank >= p.world)) {
+        if (lane == 0)
+          report_failure(p.status, kBadToken, kPhaseCombinePayload, src_rank, p.max_tokens,
+                         token, p.rank);
+      } else {
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(
+            y + le * a.y_stride_e + static_cast<int64_t>(row) * a.y_stride_row);
+        const size_t v0 = static_cast<size_t>((c * nvec) / split);
+        const int nv = ((c + 1) * nvec) / split - static_cast<int>(v0);
+        const int group_first = (src_rank / p.dp_size) * p.dp_size;
+        for (int r = 0; r < p.dp_size; ++r) {
+          uint8_t* slot = p.peer[group_first + r] + p.off_comb_stage +
+                          (static_cast<size_t>(token) * p.topk + k) * row_bytes;
+          ptx::warp_copy_v4<ptx::LoadKind::kNonCoherent>(slot + (v0 << 4), src + (v0 << 4), nv,
+                                                         lane);
+        }
+        sig_token = token;
+        sig_group = static_cast<uint32_t>(group_first);
       }
     }
+    if (lane == 0) {
+      sm.sig_tok[warp] = sig_token;
+      sm.sig_grp[warp] = sig_group;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      const uint32_t tok = lane < nwarps ? sm.sig_tok[lane] : kNoSignal;
+      const uint32_t grp = lane < nwarps ? sm.sig_grp[lane] : 0u;
+      if (__any_sync(0xffffffffu, tok != kNoSignal)) ptx::fence_acq_rel_sys();
+      if (tok != kNoSignal) {
+        for (int r = 0; r < p.dp_size; ++r) {
+          ptx::red_add_relaxed_sys(
+              reinterpret_cast<uint32_t*>(p.peer[grp + r] + p.off_comb_arrived) + tok,
+              arrival_units);
+        }
+      }
+    }
+    __syncthreads();
   }
 }
 
@@ -183,6 +255,13 @@ __device__ __forceinline__ void recv_phase(const CombineArgs& a, const CombineSm
   U* out = static_cast<U*>(a.out_tokens);
 
   const uint32_t units = static_cast<uint32_t>(m) * chunks;
+  const uint32_t per_round = static_cast<uint32_t>(topk) * kArrivalUnitsPerRow;
+  const uint32_t complete = ptx::ld_volatile(p.comb_iter) * per_round;
+  if (blockIdx.x == 0) {
+    // Tokens beyond bound_m receive nothing in this round; advance their counters
+    // here so that every counter grows by the same amount per combine.
+    for (int i = m + tid; i < p.max_tokens; i += blockDim.x) atomicAdd(arrived + i, per_round);
+  }
   const uint32_t gwarp = blockIdx.x * nwarps + warp;
   const uint32_t gwarps = gridDim.x * nwarps;
   for (uint32_t u = gwarp; u < units; u += gwarps) {
@@ -191,8 +270,8 @@ __device__ __forceinline__ void recv_phase(const CombineArgs& a, const CombineSm
     bool ok = true;
     if (lane == 0) {
       uint32_t seen;
-      ok = wait_until(arrived + i, PredGe{static_cast<uint32_t>(topk)}, seen, w,
-                      kPhaseCombinePayload, i, topk);
+      ok = wait_until(arrived + i, PredReached{complete}, seen, w, kPhaseCombinePayload, i,
+                      complete);
     }
     ok = __shfl_sync(0xffffffffu, ok, 0);
     __syncwarp();
@@ -206,7 +285,7 @@ __device__ __forceinline__ void recv_phase(const CombineArgs& a, const CombineSm
     const uint8_t* base = stage + static_cast<size_t>(i) * topk * row_bytes +
                           static_cast<size_t>(v) * 8 * sizeof(T);
     const float* wrow = a.weights + static_cast<int64_t>(i) * a.w_stride_row;
-    constexpr int kBatch = 4;
+    constexpr int kBatch = 8;
     for (int k0 = 0; k0 < topk; k0 += kBatch) {
       Vec8<T> x[kBatch];
       float wk[kBatch];
@@ -228,17 +307,6 @@ __device__ __forceinline__ void recv_phase(const CombineArgs& a, const CombineSm
   }
 
   trace(p, kTrCombineReduced);
-  __syncthreads();
-  if (tid == 0) {
-    ptx::fence_acq_rel_gpu();
-    const uint32_t t = ptx::atom_add_acq_rel_gpu(p.ticket + 1, 1u);
-    sm.misc[0] = (t == gridDim.x - 1) ? 1u : 0u;
-  }
-  __syncthreads();
-  if (sm.misc[0]) {
-    for (int i = tid; i < m; i += blockDim.x) arrived[i] = 0;
-    if (tid == 0) p.ticket[1] = 0;
-  }
 }
 
 template <typename T, typename U, bool SEND, bool RECV>
@@ -249,11 +317,14 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a, uint32_t* sme
   if (a.bound_m != nullptr) m = min(m, static_cast<int>(__ldg(a.bound_m)));
   m = min(m, p.max_tokens);
   trace(p, kTrCombineStart);
+  trace_block(p, kTrBlockCombineStart);
   if constexpr (SEND) send_phase<T>(a, sm);
   trace(p, kTrCombineSent);
   if constexpr (SEND && RECV) __syncthreads();
   if constexpr (RECV) recv_phase<T, U>(a, sm, m);
   trace(p, kTrCombineEnd);
+  __syncthreads();
+  trace_block(p, kTrBlockCombineEnd);
 }
 
 template <typename T, typename U, bool SEND, bool RECV>
@@ -317,7 +388,7 @@ cudaError_t dispatch_types(DType in, DType out, F&& fn) {
 }  // namespace
 
 size_t combine_smem_bytes(const A2AParams& p) {
-  return sizeof(uint32_t) * (static_cast<size_t>(p.nle) + 1 + kScanTmpWords + 4);
+  return sizeof(uint32_t) * (static_cast<size_t>(p.nle) + 1 + kScanTmpWords + 2 * (kCombineThreads / 32));
 }
 
 int combine_threads() { return kCombineThreads; }

@@ -23,8 +23,12 @@
 //        2. One warp per received row waits (bounded) until its source's arrival
 //           counter is complete, then copies slot -> out_expert_x / scale and
 //           records (source rank, token, k) for combine.
-//        3. The last block to finish clears this parity's counters and bumps the
-//           iteration counter.
+//        3. Nothing is reset here: the combine that follows clears this parity's
+//           counters and bumps the iteration counter (dispatch and combine must
+//           alternate, as in the reference).
+//
+// Rows are split over several warps whenever there are fewer rows than warps, so
+// that a single token still moves with the whole block's memory parallelism.
 //
 // Blocks never wait on other blocks of the same rank, and the send phase never
 // waits at all, so the kernel needs no cooperative launch.  In fused mode a
@@ -43,6 +47,19 @@ namespace pplx {
 namespace {
 
 constexpr int kDispatchThreads = 512;
+constexpr int kRowCap = 512;           // rows per block whose slots are precomputed
+constexpr uint32_t kNoSlot = 0xffffffffu;
+
+// Number of warps that share one row: the largest power of two that keeps every
+// warp busy, at most 16, and never so many that a warp gets under 32 vectors.
+__device__ __forceinline__ int split_factor(uint32_t rows, uint32_t warps, int nvec) {
+  if (rows == 0 || rows >= warps) return 1;
+  uint32_t s = warps / rows;
+  s = 1u << (31 - __clz(s));
+  const uint32_t by_size = max(1, nvec >> 5);
+  s = min(s, min(16u, 1u << (31 - __clz(by_size))));
+  return static_cast<int>(s);
+}
 
 struct DispatchSmem {
   uint32_t* hist;    // [E]
@@ -52,7 +69,7 @@ struct DispatchSmem {
   uint32_t* rbase;   // [P]
   uint32_t* sent;    // [kMaxWorld]
   uint32_t* tmp;     // [kScanTmpWords]
-  uint32_t* misc;    // [4]: 0 = last-block flag
+  uint32_t* rowpos;  // [kRowCap] staging slot of each row this block sends
 };
 
 __device__ __forceinline__ DispatchSmem carve(uint32_t* s, int E, int P) {
@@ -64,12 +81,17 @@ __device__ __forceinline__ DispatchSmem carve(uint32_t* s, int E, int P) {
   m.rbase = m.fstart + P + 1;
   m.sent = m.rbase + P;
   m.tmp = m.sent + kMaxWorld;
-  m.misc = m.tmp + kScanTmpWords;
+  m.rowpos = m.tmp + kScanTmpWords;
   return m;
 }
 
 __device__ __forceinline__ void trace(const A2AParams& p, int slot) {
   if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.trace[slot] = ptx::globaltimer_ns();
+}
+
+__device__ __forceinline__ void trace_block(const A2AParams& p, int first_slot) {
+  if (p.trace != nullptr && threadIdx.x == 0 && blockIdx.x < kTraceBlocks)
+    p.trace[first_slot + blockIdx.x] = ptx::globaltimer_ns();
 }
 
 __device__ __forceinline__ uint32_t* counts_ptr(const A2AParams& p, int dst, int parity, int src,
@@ -93,21 +115,23 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
   const int topk = p.topk;
   const int dp_rank = p.rank % p.dp_size;
 
-  // Tokens this rank sends: i = o * dp_size + dp_rank.  Blocks own contiguous
-  // ranges of the ordinal o.
+  // Rows this rank sends: entry u = o * topk + k of token i = o * dp_size + dp_rank.
+  // Blocks own contiguous ranges of u.
   const int n_own = (m > dp_rank) ? (m - dp_rank + p.dp_size - 1) / p.dp_size : 0;
-  const int per_block = ceil_div<int>(n_own, gridDim.x);
-  const int o_begin = min(static_cast<int>(blockIdx.x) * per_block, n_own);
-  const int o_end = min(o_begin + per_block, n_own);
+  const int n_entries = n_own * topk;
+  const int per_block = ceil_div<int>(n_entries, gridDim.x);
+  const int u_begin = min(static_cast<int>(blockIdx.x) * per_block, n_entries);
+  const int u_end = min(u_begin + per_block, n_entries);
 
   for (int e = tid; e < E; e += blockDim.x) {
     sm.hist[e] = 0;
     sm.base[e] = 0;
   }
   if (tid < kMaxWorld) sm.sent[tid] = 0;
+  // A new round begins: the combine that follows this dispatch is one further.
+  if (blockIdx.x == 0 && tid == 0) *p.comb_iter = *p.comb_iter + 1u;
   __syncthreads();
 
-  const int n_entries = n_own * topk;
   for (int idx = tid; idx < n_entries; idx += blockDim.x) {
     const int o = idx / topk;
     const int k = idx - o * topk;
@@ -115,7 +139,7 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
     const uint32_t e = __ldg(a.indices + static_cast<size_t>(i) * topk + k);
     if (e < static_cast<uint32_t>(E)) {
       atomicAdd(&sm.hist[e], 1u);
-      if (o < o_begin) atomicAdd(&sm.base[e], 1u);
+      if (idx < u_begin) atomicAdd(&sm.base[e], 1u);
     } else if (p.debug_checks) {
       report_failure(p.status, kBadExpert, kPhaseDispatchCounts, i, E, e, p.rank);
     }
@@ -142,12 +166,42 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
   __syncthreads();
   for (int e = tid; e < E; e += blockDim.x) sm.base[e] += sm.off[e];
   __syncthreads();
-  trace(p, kTrDispatchPosted);
 
   const int nvec = p.hidden_bytes >> 4;
   const int nscale = p.scale_bytes >> 2;
-  const int u_end = o_end * topk;
-  for (int u = o_begin * topk + warp; u < u_end; u += nwarps) {
+  const int rows_here = u_end - u_begin;
+  const bool precomputed = rows_here <= kRowCap;
+  int split = 1;
+  if (precomputed) {
+    // Reserve every row's slot up front so that several warps can share a row.
+    for (int r = tid; r < rows_here; r += blockDim.x) {
+      const int u = u_begin + r;
+      const int o = u / topk;
+      const int i = o * p.dp_size + dp_rank;
+      const uint32_t e = __ldg(a.indices + static_cast<size_t>(i) * topk + (u - o * topk));
+      uint32_t pos = kNoSlot;
+      if (e < static_cast<uint32_t>(E)) {
+        pos = atomicAdd(&sm.base[e], 1u);
+        if (p.debug_checks && pos >= static_cast<uint32_t>(p.region_slots)) {
+          report_failure(p.status, kSlotOverflow, kPhaseDispatchPayload, e / p.nle,
+                         p.region_slots, pos, p.rank);
+          pos = kNoSlot;
+        } else {
+          atomicAdd(&sm.sent[e / p.nle], 1u);
+        }
+      }
+      sm.rowpos[r] = pos;
+    }
+    __syncthreads();
+    split = split_factor(rows_here, nwarps, nvec);
+  }
+  trace(p, kTrDispatchPosted);
+
+  const int n_units = rows_here * split;
+  for (int unit = warp; unit < n_units; unit += nwarps) {
+    const int r = unit / split;
+    const int c = unit - r * split;
+    const int u = u_begin + r;
     const int o = u / topk;
     const int k = u - o * topk;
     const int i = o * p.dp_size + dp_rank;
@@ -155,33 +209,45 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
     if (e >= static_cast<uint32_t>(E)) continue;
     const int dst = e / p.nle;
     const int le = e - dst * p.nle;
-    uint32_t pos = 0;
-    if (lane == 0) pos = atomicAdd(&sm.base[e], 1u);
-    pos = __shfl_sync(0xffffffffu, pos, 0);
-    if (p.debug_checks && pos >= static_cast<uint32_t>(p.region_slots)) {
-      if (lane == 0)
-        report_failure(p.status, kSlotOverflow, kPhaseDispatchPayload, dst, p.region_slots, pos,
-                       p.rank);
-      continue;
+    uint32_t pos;
+    if (precomputed) {
+      pos = sm.rowpos[r];
+      if (pos == kNoSlot) continue;
+    } else {
+      pos = 0;
+      if (lane == 0) pos = atomicAdd(&sm.base[e], 1u);
+      pos = __shfl_sync(0xffffffffu, pos, 0);
+      if (p.debug_checks && pos >= static_cast<uint32_t>(p.region_slots)) {
+        if (lane == 0)
+          report_failure(p.status, kSlotOverflow, kPhaseDispatchPayload, dst, p.region_slots, pos,
+                         p.rank);
+        continue;
+      }
+      if (lane == 0) atomicAdd(&sm.sent[dst], 1u);
     }
-    if (lane == 0) atomicAdd(&sm.sent[dst], 1u);
 
     uint8_t* slot = p.peer[dst] + p.off_disp_stage +
                     (static_cast<size_t>(p.rank) * p.region_slots + pos) * p.slot_bytes;
     const uint8_t* src = a.x + static_cast<int64_t>(i) * a.x_stride_row;
-    ptx::warp_copy_v4<ptx::LoadKind::kNonCoherent>(slot, src, nvec, lane);
-    if (nscale > 0) {
-      float* sdst = reinterpret_cast<float*>(slot + p.hidden_bytes);
-      const float* ssrc = a.x_scale + static_cast<int64_t>(i) * a.x_scale_stride_row;
-      for (int j = lane; j < nscale; j += 32) sdst[j] = __ldg(ssrc + j * a.x_scale_stride_col);
-    }
-    if (lane == 0) {
-      int4 t;
-      t.x = i;
-      t.y = k;
-      t.z = le;
-      t.w = 0;
-      ptx::st_v4(slot + p.trailer_off, t);
+    const int v0 = (c * nvec) / split;
+    const int v1 = ((c + 1) * nvec) / split;
+    ptx::warp_copy_v4<ptx::LoadKind::kNonCoherent>(slot + (static_cast<size_t>(v0) << 4),
+                                                   src + (static_cast<size_t>(v0) << 4), v1 - v0,
+                                                   lane);
+    if (c == split - 1) {
+      if (nscale > 0) {
+        float* sdst = reinterpret_cast<float*>(slot + p.hidden_bytes);
+        const float* ssrc = a.x_scale + static_cast<int64_t>(i) * a.x_scale_stride_row;
+        for (int j = lane; j < nscale; j += 32) sdst[j] = __ldg(ssrc + j * a.x_scale_stride_col);
+      }
+      if (lane == 0) {
+        int4 t;
+        t.x = i;
+        t.y = k;
+        t.z = le;
+        t.w = 0;
+        ptx::st_v4(slot + p.trailer_off, t);
+      }
     }
   }
   trace(p, kTrDispatchStored);
@@ -245,8 +311,12 @@ __device__ __forceinline__ void recv_phase(const DispatchArgs& a, const Dispatch
   const uint32_t gwarp = blockIdx.x * nwarps + warp;
   const uint32_t gwarps = gridDim.x * nwarps;
 
+  const int split = split_factor(total_rows, gwarps, nvec);
+  const uint32_t n_units = total_rows * split;
   uint32_t acquired = 0;  // sources whose arrival counter this warp has acquired
-  for (uint32_t f = gwarp; f < total_rows; f += gwarps) {
+  for (uint32_t unit = gwarp; unit < n_units; unit += gwarps) {
+    const uint32_t f = unit / split;
+    const int c = static_cast<int>(unit - f * split);
     const int q = find_group(sm.fstart, P, f);
     const int s = q / p.nle;
     const int le = q - s * p.nle;
@@ -279,42 +349,30 @@ __device__ __forceinline__ void recv_phase(const DispatchArgs& a, const Dispatch
     const uint8_t* slot =
         stage + (static_cast<size_t>(s) * p.region_slots + slot_idx) * p.slot_bytes;
     uint8_t* dst = a.out_x + le * a.out_x_stride_e + static_cast<int64_t>(row) * a.out_x_stride_row;
-    ptx::warp_copy_v4<ptx::LoadKind::kL2Only>(dst, slot, nvec, lane);
-    if (nscale > 0) {
-      const float* ssrc = reinterpret_cast<const float*>(slot + p.hidden_bytes);
-      float* sdst = a.out_scale + le * a.out_scale_stride_e +
-                    static_cast<int64_t>(row) * a.out_scale_stride_row;
-      for (int j = lane; j < nscale; j += 32) sdst[j * a.out_scale_stride_col] = __ldcg(ssrc + j);
-    }
-    if (lane == 0) {
-      const int4 t = ptx::ld_cg_v4(slot + p.trailer_off);
-      if (p.debug_checks && static_cast<uint32_t>(t.x) >= static_cast<uint32_t>(p.max_tokens)) {
-        report_failure(p.status, kBadToken, kPhaseDispatchPayload, s, p.max_tokens, t.x, p.rank);
+    const int v0 = (c * nvec) / split;
+    const int v1 = ((c + 1) * nvec) / split;
+    ptx::warp_copy_v4<ptx::LoadKind::kL2Only>(dst + (static_cast<size_t>(v0) << 4),
+                                              slot + (static_cast<size_t>(v0) << 4), v1 - v0, lane);
+    if (c == split - 1) {
+      if (nscale > 0) {
+        const float* ssrc = reinterpret_cast<const float*>(slot + p.hidden_bytes);
+        float* sdst = a.out_scale + le * a.out_scale_stride_e +
+                      static_cast<int64_t>(row) * a.out_scale_stride_row;
+        for (int j = lane; j < nscale; j += 32) sdst[j * a.out_scale_stride_col] = __ldcg(ssrc + j);
       }
-      uint2 rs;
-      rs.x = static_cast<uint32_t>(s) | (static_cast<uint32_t>(t.y) << 16);
-      rs.y = static_cast<uint32_t>(t.x);
-      p.row_src[static_cast<size_t>(le) * p.cap + row] = rs;
+      if (lane == 0) {
+        const int4 t = ptx::ld_cg_v4(slot + p.trailer_off);
+        if (p.debug_checks && static_cast<uint32_t>(t.x) >= static_cast<uint32_t>(p.max_tokens)) {
+          report_failure(p.status, kBadToken, kPhaseDispatchPayload, s, p.max_tokens, t.x, p.rank);
+        }
+        uint2 rs;
+        rs.x = static_cast<uint32_t>(s) | (static_cast<uint32_t>(t.y) << 16);
+        rs.y = static_cast<uint32_t>(t.x);
+        p.row_src[static_cast<size_t>(le) * p.cap + row] = rs;
+      }
     }
   }
-
   trace(p, kTrDispatchCopied);
-  // Last block out clears this parity's flags and opens the next iteration.
-  __syncthreads();
-  if (tid == 0) {
-    ptx::fence_acq_rel_gpu();
-    const uint32_t t = ptx::atom_add_acq_rel_gpu(p.ticket + 0, 1u);
-    sm.misc[0] = (t == gridDim.x - 1) ? 1u : 0u;
-  }
-  __syncthreads();
-  if (sm.misc[0]) {
-    for (int q = tid; q < P; q += blockDim.x) counts[q] = 0;
-    if (tid < p.world) arrived[tid] = 0;
-    if (tid == 0) {
-      p.ticket[0] = 0;
-      *p.iter = *p.iter + 1u;
-    }
-  }
   trace(p, kTrDispatchEnd);
 }
 
@@ -327,9 +385,12 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a, uint32_t* s
   if (a.bound_m != nullptr) m = min(m, static_cast<int>(__ldg(a.bound_m)));
   m = min(m, p.max_tokens);
   trace(p, kTrDispatchStart);
+  trace_block(p, kTrBlockDispatchStart);
   if constexpr (SEND) send_phase(a, sm, parity, m);
   if constexpr (SEND && RECV) __syncthreads();
   if constexpr (RECV) recv_phase(a, sm, parity);
+  __syncthreads();
+  trace_block(p, kTrBlockDispatchEnd);
 }
 
 template <bool SEND, bool RECV>
@@ -353,7 +414,7 @@ __global__ void __launch_bounds__(kDispatchThreads, 1)
 
 size_t dispatch_smem_bytes(const A2AParams& p) {
   const size_t E = p.num_experts, P = static_cast<size_t>(p.world) * p.nle;
-  return sizeof(uint32_t) * (3 * E + (P + 1) + P + kMaxWorld + kScanTmpWords + 4);
+  return sizeof(uint32_t) * (3 * E + (P + 1) + P + kMaxWorld + kScanTmpWords + kRowCap);
 }
 
 int dispatch_threads() { return kDispatchThreads; }

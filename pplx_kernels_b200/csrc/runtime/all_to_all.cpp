@@ -122,15 +122,14 @@ AllToAll::AllToAll(const A2AConfig& cfg, std::shared_ptr<SymmetricAllocation> ar
   PPLX_CHECK(arena_->bytes() >= params_.arena_bytes, "arena too small");
   for (int r = 0; r < cfg_.world_size; ++r) params_.peer[r] = static_cast<uint8_t*>(arena_->peer(r));
 
-  iter_ = DeviceBuffer<uint32_t>(1);
-  ticket_ = DeviceBuffer<uint32_t>(2);
+  iter_ = DeviceBuffer<uint32_t>(2);
   recv_count_ = DeviceBuffer<uint32_t>(params_.nle);
   row_src_ = DeviceBuffer<uint2>(static_cast<size_t>(params_.nle) * params_.cap);
   status_ = DeviceBuffer<Status>(1);
   trace_ = DeviceBuffer<uint64_t>(kTraceSlots);
   params_.trace = nullptr;
   params_.iter = iter_.get();
-  params_.ticket = ticket_.get();
+  params_.comb_iter = iter_.get() + 1;
   params_.recv_count = recv_count_.get();
   params_.row_src = row_src_.get();
   params_.status = status_.get();

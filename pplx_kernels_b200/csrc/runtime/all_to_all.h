@@ -131,7 +131,6 @@ class AllToAll {
   A2AParams params_{};
   std::shared_ptr<SymmetricAllocation> arena_;
   DeviceBuffer<uint32_t> iter_;
-  DeviceBuffer<uint32_t> ticket_;
   DeviceBuffer<uint32_t> recv_count_;
   DeviceBuffer<uint2> row_src_;
   DeviceBuffer<Status> status_;

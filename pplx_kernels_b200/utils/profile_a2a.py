@@ -56,7 +56,9 @@ def main() -> None:
     out = torch.zeros(args.tokens, cfg.hidden_dim, dtype=cfg.out_dtype, device=dev)
     flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
 
-    lat = {"dispatch": [], "combine": []}
+    from pplx_kernels_b200.ops import _ops
+
+    lat = {"dispatch": [], "combine": [], "empty_kernel": []}
     phases: dict[str, list[float]] = {}
     for it in range(args.warmup + args.iters):
         if not args.no_flush:
@@ -68,8 +70,17 @@ def main() -> None:
         ata.combine(out, idx, w, ey, bound_m)
         e[2].record()
         torch.cuda.synchronize()
+        # Calibration: the same event bracket around a kernel that does nothing.
+        if not args.no_flush:
+            flush.add_(1)
+        c = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        c[0].record()
+        _ops.sleep_on_stream(0.0)
+        c[1].record()
+        torch.cuda.synchronize()
         if it < args.warmup:
             continue
+        lat["empty_kernel"].append(c[0].elapsed_time(c[1]) * 1e3)
         lat["dispatch"].append(e[0].elapsed_time(e[1]) * 1e3)
         lat["combine"].append(e[1].elapsed_time(e[2]) * 1e3)
         if args.trace:
@@ -83,12 +94,23 @@ def main() -> None:
                      "combine_end"]
             for a, b in zip(order, order[1:], strict=False):
                 phases.setdefault(f"{a}->{b}", []).append((t[b] - t[a]) / 1e3)
+            for op in ("dispatch", "combine"):
+                k = op + "_blocks"
+                phases.setdefault(f"{op}: first block start -> last block start", []).append(
+                    (t[k + "_last_start"] - t[k + "_first_start"]) / 1e3)
+                phases.setdefault(f"{op}: first block start -> first block end", []).append(
+                    (t[k + "_first_end"] - t[k + "_first_start"]) / 1e3)
+                phases.setdefault(f"{op}: first block start -> last block end", []).append(
+                    (t[k + "_last_end"] - t[k + "_first_start"]) / 1e3)
+            phases.setdefault("dispatch last end -> combine first start", []).append(
+                (t["combine_blocks_first_start"] - t["dispatch_blocks_last_end"]) / 1e3)
     ata.check_status()
     ata.destroy()
     report = {
         "tokens": args.tokens,
         "dispatch_us_p50": statistics.median(lat["dispatch"]),
         "combine_us_p50": statistics.median(lat["combine"]),
+        "empty_kernel_us_p50": statistics.median(lat["empty_kernel"]),
         "phases_us_p50": {k: statistics.median(v) for k, v in phases.items()},
     }
     print(json.dumps(report, indent=1))
