@@ -1,0 +1,50 @@
+// Grouped expert GEMM (tcgen05 / tensor memory / TMA) -- host interface.
+// No counterpart in the reference, which has no GEMM.
+#pragma once
+
+#include <cstdint>
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace pplx {
+
+// Device-side arguments (the tensor maps travel as separate kernel parameters).
+struct GroupedGemmArgs {
+  const int32_t* counts;   // [num_experts] valid rows per expert
+  __nv_bfloat16* out;      // [num_experts][rows_per_expert][n_out]
+  int64_t out_stride_e;    // elements
+  int64_t out_stride_row;  // elements
+  uint32_t* status;        // optional device word, set to 1 if a wait ran out
+  int num_experts;
+  int rows_per_expert;     // capacity of x / out per expert
+  int n_out;               // output columns (the intermediate size for SwiGLU)
+  int k;
+};
+
+// Host-side description of one launch.  Strides are in bf16 elements; the
+// innermost (K) stride of x and w is 1.
+struct GroupedGemmCall {
+  const void* x = nullptr;   // [num_experts][rows_per_expert][k]
+  int64_t x_stride_e = 0;
+  int64_t x_stride_row = 0;
+  const void* w = nullptr;   // [num_experts][n_out or 2 * n_out][k]
+  int64_t w_stride_e = 0;
+  int64_t w_stride_row = 0;
+  const int32_t* counts = nullptr;
+  void* out = nullptr;
+  int64_t out_stride_e = 0;
+  int64_t out_stride_row = 0;
+  uint32_t* status = nullptr;
+  int num_experts = 0;
+  int rows_per_expert = 0;
+  int n_out = 0;
+  int k = 0;
+  bool swiglu = false;
+  int num_sms = 0;           // 0 = all
+};
+
+// out[e, :counts[e]] = act(x[e, :counts[e]] @ w[e]^T); rows beyond counts[e] are untouched.
+void launch_grouped_gemm(const GroupedGemmCall& call, cudaStream_t stream);
+
+}  // namespace pplx
