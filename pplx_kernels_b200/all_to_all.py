@@ -142,6 +142,32 @@ class AllToAll:
     def set_max_blocks(self, n: int) -> None:
         _ops.all_to_all_set_max_blocks(self._ptr, int(n))
 
+    def set_combine_units(self, units: int) -> None:
+        """Arrival units a complete expert-output row is worth (multiple of 16, default 16).
+
+        Must be the same on all ranks.  The fused down projection needs a multiple of its
+        number of 256-column output blocks.
+        """
+        _ops.all_to_all_set_combine_units(self._ptr, int(units))
+
+    def fused_up(self, w13: torch.Tensor, h: torch.Tensor,
+                 out_expert_num_tokens: torch.Tensor | None = None,
+                 status: torch.Tensor | None = None) -> None:
+        """SwiGLU up projection that reads the dispatch staging arena as peers fill it.
+
+        Call after ``dispatch(..., do_send=True, do_recv=False)``; it replaces the receive
+        half.  ``h[le, :n] = silu(x @ gate.T) * (x @ up.T)`` for the rows of local expert le.
+        """
+        _ops.moe_fused_up(self._ptr, w13, h, out_expert_num_tokens, status)
+
+    def fused_down(self, h: torch.Tensor, w2: torch.Tensor,
+                   status: torch.Tensor | None = None) -> None:
+        """Down projection whose epilogue stores each row to its token's home rank(s).
+
+        Call before ``combine(..., do_send=False, do_recv=True)``; it replaces the send half.
+        """
+        _ops.moe_fused_down(self._ptr, h, w2, status)
+
     def set_trace(self, on: bool) -> None:
         """Turns the per-phase device time stamps of block 0 on or off."""
         _ops.all_to_all_set_trace(self._ptr, bool(on))

@@ -390,6 +390,82 @@ void set_debug_checks_op(int64_t ptr, bool on) { lookup(ptr)->set_debug_checks(o
 
 void set_max_blocks_op(int64_t ptr, int64_t n) { lookup(ptr)->set_max_blocks(static_cast<int>(n)); }
 
+void set_combine_units_op(int64_t ptr, int64_t units) {
+  guarded([&] { lookup(ptr)->set_combine_units(static_cast<int>(units)); });
+}
+
+uint32_t* status_word(const std::optional<at::Tensor>& status) {
+  if (!status.has_value()) return nullptr;
+  TORCH_CHECK(status->is_cuda() && status->element_size() == 4 && status->numel() >= 1,
+              "status must be a 32-bit CUDA tensor");
+  return static_cast<uint32_t*>(status->data_ptr());
+}
+
+void check_bf16_3d(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.dim() == 3 && t.scalar_type() == at::kBFloat16 && t.stride(2) == 1,
+              name, " must be a 3-D bfloat16 CUDA tensor with a contiguous last dimension");
+}
+
+// SwiGLU up projection fed from the dispatch staging arena (after dispatch with do_recv=False).
+void moe_fused_up_op(int64_t ptr, const at::Tensor& w13, at::Tensor& h,
+                     const std::optional<at::Tensor>& out_expert_num_tokens,
+                     const std::optional<at::Tensor>& status) {
+  AllToAll* ata = lookup(ptr);
+  check_bf16_3d(w13, "w13");
+  check_bf16_3d(h, "h");
+  const A2AParams& p = ata->params();
+  TORCH_CHECK(w13.size(0) == p.nle && w13.size(2) == p.hidden_dim && w13.size(1) == 2 * h.size(2),
+              "w13 must be [num_local_experts, 2 * intermediate, hidden]");
+  TORCH_CHECK(h.size(0) == p.nle && h.size(1) >= p.cap, "h must be [num_local_experts, rows, intermediate]");
+  FusedFfnCall f;
+  f.w = w13.data_ptr();
+  f.w_stride_e = w13.stride(0);
+  f.w_stride_row = w13.stride(1);
+  f.h = h.data_ptr();
+  f.h_stride_e = h.stride(0);
+  f.h_stride_row = h.stride(1);
+  f.rows_per_expert = static_cast<int>(h.size(1));
+  f.inter_dim = static_cast<int>(h.size(2));
+  if (out_expert_num_tokens.has_value()) {
+    TORCH_CHECK(out_expert_num_tokens->is_cuda() && out_expert_num_tokens->scalar_type() == at::kInt &&
+                    out_expert_num_tokens->numel() == p.nle && out_expert_num_tokens->is_contiguous(),
+                "out_expert_num_tokens must be a contiguous int32 CUDA tensor of [num_local_experts]");
+    f.out_num_tokens = out_expert_num_tokens->data_ptr<int32_t>();
+  }
+  f.status = status_word(status);
+  const c10::cuda::OptionalCUDAGuard guard(h.device());
+  guarded([&] { ata->fused_up(f, at::cuda::getCurrentCUDAStream()); });
+}
+
+// Down projection whose epilogue stores to the tokens' home ranks (before combine with do_send=False).
+void moe_fused_down_op(int64_t ptr, const at::Tensor& h, const at::Tensor& w2,
+                       const std::optional<at::Tensor>& status) {
+  AllToAll* ata = lookup(ptr);
+  check_bf16_3d(w2, "w2");
+  check_bf16_3d(h, "h");
+  const A2AParams& p = ata->params();
+  TORCH_CHECK(w2.size(0) == p.nle && w2.size(1) == p.hidden_dim && w2.size(2) == h.size(2),
+              "w2 must be [num_local_experts, hidden, intermediate]");
+  TORCH_CHECK(h.size(0) == p.nle && h.size(1) >= p.cap, "h must be [num_local_experts, rows, intermediate]");
+  FusedFfnCall f;
+  f.w = w2.data_ptr();
+  f.w_stride_e = w2.stride(0);
+  f.w_stride_row = w2.stride(1);
+  f.h = h.data_ptr();
+  f.h_stride_e = h.stride(0);
+  f.h_stride_row = h.stride(1);
+  f.rows_per_expert = static_cast<int>(h.size(1));
+  f.inter_dim = static_cast<int>(h.size(2));
+  f.status = status_word(status);
+  const c10::cuda::OptionalCUDAGuard guard(h.device());
+  guarded([&] { ata->fused_down(f, at::cuda::getCurrentCUDAStream()); });
+}
+
+void fake_moe_fused_up(int64_t, const at::Tensor&, at::Tensor&, const std::optional<at::Tensor>&,
+                       const std::optional<at::Tensor>&) {}
+void fake_moe_fused_down(int64_t, const at::Tensor&, const at::Tensor&,
+                         const std::optional<at::Tensor>&) {}
+
 void set_trace_op(int64_t ptr, bool on) { lookup(ptr)->set_trace(on); }
 
 std::vector<int64_t> read_trace_op(int64_t ptr) {
@@ -574,6 +650,14 @@ void register_all_to_all_ops(torch::Library& m) {
   m.def("all_to_all_set_max_blocks(int ptr, int n) -> ()", &set_max_blocks_op);
   m.def("all_to_all_layout(int ptr) -> int[]", &layout_op);
   m.def("all_to_all_set_trace(int ptr, bool on) -> ()", &set_trace_op);
+  m.def("all_to_all_set_combine_units(int ptr, int units) -> ()", &set_combine_units_op);
+  m.def("moe_fused_up(int ptr, Tensor w13, Tensor! h, Tensor!? out_expert_num_tokens, "
+        "Tensor!? status) -> ()");
+  m.impl("moe_fused_up", c10::kCUDA, &moe_fused_up_op);
+  m.impl("moe_fused_up", c10::kMeta, &fake_moe_fused_up);
+  m.def("moe_fused_down(int ptr, Tensor h, Tensor w2, Tensor!? status) -> ()");
+  m.impl("moe_fused_down", c10::kCUDA, &moe_fused_down_op);
+  m.impl("moe_fused_down", c10::kMeta, &fake_moe_fused_down);
   m.def("all_to_all_read_trace(int ptr) -> int[]", &read_trace_op);
 }
 

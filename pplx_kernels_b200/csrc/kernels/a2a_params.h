@@ -53,6 +53,7 @@ struct A2AParams {
   int region_slots;  // dispatch staging slots per source rank
   int cap;           // rows per local expert in out_expert_x / expert_y
   int debug_checks;  // non-zero: bounds checks that record instead of corrupting
+  int comb_units;    // arrival units one complete expert output row is worth (multiple of 16)
 
   // offsets into the symmetric arena (bytes, 256-aligned)
   size_t off_counts;        // u32 [2][world][nle]   value = count + 1, 0 = not posted

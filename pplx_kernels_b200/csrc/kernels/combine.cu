@@ -16,8 +16,9 @@
 //    single token still uses many warps, and a unit starts as soon as its own
 //    token is complete.
 //  * A row is split over several warps when there are fewer rows than warps.
-//    Each part adds 16/parts to the token's arrival counter, so a token is
-//    complete at 16 * top-k whatever split the senders chose.
+//    A complete row is worth `comb_units` arrival units (a multiple of 16) and
+//    each part adds comb_units/parts, so a token is complete at comb_units *
+//    top-k whatever split the senders chose.
 //  * Signals are issued once per block and round: all warps store their parts,
 //    the block synchronises, and one warp executes a single system-scope fence
 //    followed by relaxed adds.  (A fence per warp serialises inside an SM and
@@ -40,14 +41,14 @@ namespace pplx {
 namespace {
 
 constexpr int kCombineThreads = 512;
-constexpr uint32_t kArrivalUnitsPerRow = 16;
+constexpr uint32_t kMaxSplit = 16;
 
 __device__ __forceinline__ int split_factor(uint32_t rows, uint32_t warps, int nvec) {
   if (rows == 0 || rows >= warps) return 1;
   uint32_t s = warps / rows;
   s = 1u << (31 - __clz(s));
   const uint32_t by_size = max(1, nvec >> 5);
-  s = min(s, min(kArrivalUnitsPerRow, 1u << (31 - __clz(by_size))));
+  s = min(s, min(kMaxSplit, 1u << (31 - __clz(by_size))));
   return static_cast<int>(s);
 }
 
@@ -177,7 +178,7 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
   const uint32_t gwarps = gridDim.x * nwarps;
   const int split = split_factor(total_rows, gwarps, nvec);
   const uint32_t n_units = total_rows * split;
-  const uint32_t arrival_units = kArrivalUnitsPerRow / split;
+  const uint32_t arrival_units = static_cast<uint32_t>(p.comb_units) / split;
 
   // Rounds: in each, every warp stores at most one part; then one fence and the
   // adds for the whole block.  All warps take part in every round's barriers.
@@ -255,7 +256,7 @@ __device__ __forceinline__ void recv_phase(const CombineArgs& a, const CombineSm
   U* out = static_cast<U*>(a.out_tokens);
 
   const uint32_t units = static_cast<uint32_t>(m) * chunks;
-  const uint32_t per_round = static_cast<uint32_t>(topk) * kArrivalUnitsPerRow;
+  const uint32_t per_round = static_cast<uint32_t>(topk) * static_cast<uint32_t>(p.comb_units);
   const uint32_t complete = ptx::ld_volatile(p.comb_iter) * per_round;
   if (blockIdx.x == 0) {
     // Tokens beyond bound_m receive nothing in this round; advance their counters

@@ -7,6 +7,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include "a2a_params.h"
+
 namespace pplx {
 
 // Device-side arguments (the tensor maps travel as separate kernel parameters).
@@ -20,6 +22,10 @@ struct GroupedGemmArgs {
   int rows_per_expert;     // capacity of x / out per expert
   int n_out;               // output columns (the intermediate size for SwiGLU)
   int k;
+  // Only read by the kernels fused with the all-to-all:
+  int32_t* out_num_tokens;          // optional [nle]: per-expert totals for the caller
+  uint32_t arrival_units_per_tile;  // units added to a token's counter per column block
+  A2AParams a2a;
 };
 
 // Host-side description of one launch.  Strides are in bf16 elements; the
@@ -46,5 +52,20 @@ struct GroupedGemmCall {
 
 // out[e, :counts[e]] = act(x[e, :counts[e]] @ w[e]^T); rows beyond counts[e] are untouched.
 void launch_grouped_gemm(const GroupedGemmCall& call, cudaStream_t stream);
+
+// First expert GEMM of the fused MoE layer.  Takes the place of the dispatch
+// receive phase: A is read from the dispatch staging arena of `p` as peers fill
+// it (bf16 payload without scales), out[le] receives SwiGLU(x @ w[le]^T) for the
+// rows of local expert le, `out_num_tokens` (optional) the per-expert totals.
+// call.x / call.counts are ignored; call.k must equal the hidden size of `p`.
+void launch_gemm_from_staging(const GroupedGemmCall& call, const A2AParams& p,
+                              int32_t* out_num_tokens, cudaStream_t stream);
+
+// Second expert GEMM of the fused MoE layer.  Takes the place of the combine send
+// phase: every output row x[le, r] @ w[le]^T goes to the combine staging of the
+// token's home rank(s); call.out is ignored, call.counts must be p.recv_count and
+// call.n_out the hidden size of `p`.  p.comb_units must be a multiple of the
+// number of 256-column blocks of the output.
+void launch_gemm_to_peers(const GroupedGemmCall& call, const A2AParams& p, cudaStream_t stream);
 
 }  // namespace pplx

@@ -22,6 +22,23 @@
 // row counts are read on the device, so the launch is graph-capturable and does
 // no work for empty experts.
 //
+// Two template switches turn the same pipeline into the compute+collective
+// kernels of the fused MoE layer:
+//
+//   kFromStaging   the A operand is read by TMA straight out of the dispatch
+//                  staging arena that PEERS fill with P2P stores.  Groups are
+//                  (source rank, local expert) chunks; the producer warp waits on
+//                  the source's arrival counter (ld.acquire.sys, then
+//                  fence.proxy.async) before the first tile of that source, so the
+//                  expert GEMM starts tile by tile as tokens land and the
+//                  receive-side copy of dispatch disappears.  The epilogue also
+//                  records (source, token, k) of every row for combine.
+//   kToPeers       the epilogue does not write a local result: every output row
+//                  is stored into the combine staging of the token's home rank(s)
+//                  over NVLink, followed once per tile by one system-scope fence
+//                  and relaxed adds on the tokens' arrival counters.  The
+//                  combine send kernel and the expert_y round trip disappear.
+//
 // Every mbarrier wait is bounded: when one runs out the CTA raises a shared
 // abort flag, all roles leave their loops, in-flight TMA loads are drained,
 // tensor memory is freed and the kernel returns with *status = 1.
@@ -30,8 +47,10 @@
 #include <cuda_runtime.h>
 
 #include "../core/device_utils.cuh"
+#include "../core/ptx.cuh"
 #include "../core/tcgen05.cuh"
 #include "../core/utils.h"
+#include "../core/wait.cuh"
 #include "grouped_gemm.h"
 
 namespace pplx {
@@ -50,6 +69,8 @@ constexpr uint32_t kStageBytes = kABytes + kBBytes;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;     // 2 s per wait
 constexpr int kMaxExperts = 1024;
 
+constexpr uint32_t kNoSignal = 0xffffffffu;
+
 struct SharedControl {
   uint64_t full[kStages];
   uint64_t empty[kStages];
@@ -57,29 +78,56 @@ struct SharedControl {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   uint32_t abort_flag;
-  uint32_t total_tiles;
-  uint32_t pad;
+  uint32_t pad[2];
+  uint32_t src_total[kMaxWorld];   // kFromStaging: rows each source sends to this rank
+  uint32_t sig_token[2][kBlockM];  // kToPeers: token of each tile row, per accumulator
+  uint32_t sig_group[2][kBlockM];  //           first rank of the token's DP group
+};
+
+// Rows of A that share a weight matrix and an output base.  In the plain kernel a
+// group is an expert; with kFromStaging it is one (source rank, local expert) chunk.
+struct GroupTable {
+  uint32_t* tile_start;  // [G + 1] first tile of each group
+  uint32_t* rows;        // [G] valid rows
+  uint32_t* a_row0;      // [G] first row inside the A plane
+  uint32_t* out_row0;    // [G] first row inside the output plane
 };
 
 struct TileCoord {
-  int expert;
+  int group;
   int m_blk;
   int n_blk;
-  int rows;  // valid rows of the expert
+  int rows;      // valid rows of the group
+  int a_plane;   // dim-2 coordinate of A
+  int a_row0;
+  int w_plane;   // expert whose weights apply
+  int out_row0;
+  int src;       // source rank (kFromStaging), else -1
 };
 
-// tile_start[e] = first tile of expert e; tiles of one expert are ordered
-// (n_blk, m_blk) with m_blk fastest.
-__device__ __forceinline__ TileCoord locate_tile(const uint32_t* tile_start,
-                                                 const int32_t* __restrict__ counts, int E,
-                                                 int capacity, uint32_t t) {
+// Tiles of one group are ordered (n_blk, m_blk) with m_blk fastest.
+template <bool kFromStaging>
+__device__ __forceinline__ TileCoord locate_tile(const GroupTable& gt, int num_groups,
+                                                 const A2AParams& p, uint32_t t) {
   TileCoord c;
-  c.expert = find_group(tile_start, E, t);
-  c.rows = min(max(counts[c.expert], 0), capacity);
+  c.group = find_group(gt.tile_start, num_groups, t);
+  c.rows = static_cast<int>(gt.rows[c.group]);
   const int m_tiles = ceil_div<int>(c.rows, kBlockM);
-  const uint32_t rem = t - tile_start[c.expert];
+  const uint32_t rem = t - gt.tile_start[c.group];
   c.n_blk = static_cast<int>(rem / m_tiles);
   c.m_blk = static_cast<int>(rem - static_cast<uint32_t>(c.n_blk) * m_tiles);
+  c.a_row0 = static_cast<int>(gt.a_row0[c.group]);
+  c.out_row0 = static_cast<int>(gt.out_row0[c.group]);
+  if constexpr (kFromStaging) {
+    const int s_rot = c.group / p.nle;
+    c.w_plane = c.group - s_rot * p.nle;
+    c.src = (p.rank + s_rot) % p.world;
+    c.a_plane = c.src;
+  } else {
+    c.w_plane = c.group;
+    c.a_plane = c.group;
+    c.src = -1;
+  }
   return c;
 }
 
@@ -90,16 +138,23 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-template <bool SWIGLU>
+template <bool SWIGLU, bool kFromStaging, bool kToPeers>
 __global__ void __launch_bounds__(kThreads, 1)
     grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                        const __grid_constant__ CUtensorMap tmap_b, const GroupedGemmArgs g) {
+                        const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ GroupedGemmArgs g) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // Stage ring first (1024-byte aligned tiles), control block and tile table after.
   uint8_t* stages = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   SharedControl* ctl = reinterpret_cast<SharedControl*>(stages + kStages * kStageBytes);
-  uint32_t* tile_start = reinterpret_cast<uint32_t*>(ctl + 1);  // [E + 1]
+  const A2AParams& p = g.a2a;
+  const int num_groups = kFromStaging ? p.world * p.nle : g.num_experts;
+  GroupTable gt;
+  gt.tile_start = reinterpret_cast<uint32_t*>(ctl + 1);  // [G + 1]
+  gt.rows = gt.tile_start + num_groups + 1;
+  gt.a_row0 = gt.rows + num_groups;
+  gt.out_row0 = gt.a_row0 + num_groups;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -112,9 +167,74 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int num_kb = ceil_div<int>(g.k, kBlockK);
 
   // ---- set-up ---------------------------------------------------------------
-  for (int e = tid; e < g.num_experts; e += blockDim.x) {
-    const int rows = min(max(g.counts[e], 0), g.rows_per_expert);
-    tile_start[e] = static_cast<uint32_t>(ceil_div<int>(rows, kBlockM) * n_blocks);
+  if (tid == 0) ctl->abort_flag = 0;
+  int parity = 0;
+  if constexpr (kFromStaging || kToPeers) parity = static_cast<int>(ptx::ld_volatile(p.iter) & 1u);
+  if constexpr (kFromStaging) {
+    // Role of the dispatch receive phase: learn how many rows every source sends
+    // to every local expert, lay the rows out, publish the per-expert totals.
+    __syncthreads();
+    const WaitCtx w{p.status, p.timeout_ns, static_cast<uint32_t>(p.rank)};
+    const uint32_t* counts = reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.off_counts) +
+                             a2a_counts_index(p, parity, 0, 0);
+    for (int q = tid; q < num_groups; q += blockDim.x) {
+      const int s_rot = q / p.nle;
+      const int le = q - s_rot * p.nle;
+      const int src = (p.rank + s_rot) % p.world;
+      uint32_t v = 0;
+      const bool ok = wait_until(counts + src * p.nle + le, PredNonZero{}, v, w,
+                                 kPhaseDispatchCounts, src, 1u);
+      if (!ok) ctl->abort_flag = 1;
+      gt.rows[q] = ok ? min(v - 1u, static_cast<uint32_t>(p.region_slots)) : 0u;
+    }
+    __syncthreads();
+    for (int q = tid; q < num_groups; q += blockDim.x) {
+      const int s_rot = q / p.nle;
+      const int le = q - s_rot * p.nle;
+      uint32_t in_region = 0, in_output = 0;
+      for (int l2 = 0; l2 < le; ++l2) in_region += gt.rows[s_rot * p.nle + l2];
+      for (int r2 = 0; r2 < s_rot; ++r2) in_output += gt.rows[r2 * p.nle + le];
+      gt.a_row0[q] = in_region;
+      gt.out_row0[q] = in_output;
+      gt.tile_start[q] =
+          static_cast<uint32_t>(ceil_div<int>(static_cast<int>(gt.rows[q]), kBlockM) * n_blocks);
+    }
+    if (tid < p.world) {
+      uint32_t total = 0;
+      const int s_rot = tid;
+      for (int le = 0; le < p.nle; ++le) total += gt.rows[s_rot * p.nle + le];
+      ctl->src_total[(p.rank + s_rot) % p.world] = total;
+    }
+    if (blockIdx.x == 0) {
+      for (int le = tid; le < p.nle; le += blockDim.x) {
+        uint32_t total = 0;
+        for (int r2 = 0; r2 < p.world; ++r2) total += gt.rows[r2 * p.nle + le];
+        if (g.out_num_tokens != nullptr) g.out_num_tokens[le] = static_cast<int32_t>(total);
+        p.recv_count[le] = min(total, static_cast<uint32_t>(p.cap));
+      }
+    }
+  } else {
+    for (int e = tid; e < num_groups; e += blockDim.x) {
+      const int rows = min(max(g.counts[e], 0), g.rows_per_expert);
+      gt.rows[e] = static_cast<uint32_t>(rows);
+      gt.a_row0[e] = 0;
+      gt.out_row0[e] = 0;
+      gt.tile_start[e] = static_cast<uint32_t>(ceil_div<int>(rows, kBlockM) * n_blocks);
+    }
+  }
+  if constexpr (kToPeers) {
+    if (blockIdx.x == 0) {
+      // Role of the combine send phase's first block: the dispatch that produced
+      // these rows is over on this rank, so clear its flag set and move on.
+      uint32_t* counts = reinterpret_cast<uint32_t*>(p.peer[p.rank] + p.off_counts) +
+                         a2a_counts_index(p, parity, 0, 0);
+      uint32_t* arrived =
+          reinterpret_cast<uint32_t*>(p.peer[p.rank] + p.off_arrived) + parity * p.world;
+      for (int q = tid; q < p.world * p.nle; q += blockDim.x) counts[q] = 0;
+      if (tid < p.world) arrived[tid] = 0;
+      __syncthreads();
+      if (tid == 0) *p.iter = *p.iter + 1u;
+    }
   }
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -125,13 +245,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc::mbar_init(&ctl->tmem_full[b], 1);
       tc::mbar_init(&ctl->tmem_empty[b], 4);
     }
-    ctl->abort_flag = 0;
     tc::fence_mbar_init();
     tc::tma_prefetch_desc(&tmap_a);
     tc::tma_prefetch_desc(&tmap_b);
   }
   __syncthreads();
-  if (warp == 0) warp_exclusive_scan_smem(tile_start, g.num_experts, lane, true);
+  if (warp == 0) warp_exclusive_scan_smem(gt.tile_start, num_groups, lane, true);
   if (warp == 2) {
     tc::tmem_alloc(&ctl->tmem_base, kTmemCols);
     tc::tmem_relinquish();
@@ -140,7 +259,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
-  const uint32_t total_tiles = tile_start[g.num_experts];
+  const uint32_t total_tiles = gt.tile_start[num_groups];
 
   // ---- roles ----------------------------------------------------------------
   if (warp == 0) {
@@ -148,9 +267,30 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t stage = 0, phase = 0;
       uint32_t pending = 0;        // stages that have been filled at least once
       uint32_t pending_phase = 0;  // parity of the phase each stage was last filled in
-      bool ok = true;
+      bool ok = *abort_flag == 0u;
+      uint32_t acquired = 0;  // sources whose rows are known to have landed
       for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const TileCoord c = locate_tile(tile_start, g.counts, g.num_experts, g.rows_per_expert, t);
+        const TileCoord c = locate_tile<kFromStaging>(gt, num_groups, p, t);
+        if constexpr (kFromStaging) {
+          if (!((acquired >> c.src) & 1u)) {
+            // The tile's rows were stored by a peer: wait for that source's arrival
+            // counter, then order the peer's (generic-proxy) stores before the TMA
+            // (async-proxy) reads that follow.
+            const WaitCtx w{p.status, p.timeout_ns, static_cast<uint32_t>(p.rank)};
+            const uint32_t* arrived = reinterpret_cast<const uint32_t*>(
+                                          p.peer[p.rank] + p.off_arrived) +
+                                      parity * p.world + c.src;
+            uint32_t seen;
+            ok = wait_until(arrived, PredGe{ctl->src_total[c.src]}, seen, w, kPhaseFusedGemm,
+                            c.src, ctl->src_total[c.src]);
+            if (!ok) {
+              *abort_flag = 1u;
+              break;
+            }
+            ptx::fence_proxy_async();
+            acquired |= 1u << c.src;
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = tc::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, kWaitLimitNs);
           if (!ok) break;
@@ -159,18 +299,18 @@ __global__ void __launch_bounds__(kThreads, 1)
           tc::mbar_arrive_expect_tx(&ctl->full[stage], kStageBytes);
           pending |= 1u << stage;
           pending_phase = (pending_phase & ~(1u << stage)) | (phase << stage);
-          tc::tma_load_3d(a_dst, &tmap_a, &ctl->full[stage], kb * kBlockK, c.m_blk * kBlockM,
-                          c.expert);
+          tc::tma_load_3d(a_dst, &tmap_a, &ctl->full[stage], kb * kBlockK,
+                          c.a_row0 + c.m_blk * kBlockM, c.a_plane);
           if constexpr (SWIGLU) {
             const int row = c.n_blk * (kBlockN / 2);
-            tc::tma_load_3d(b_dst, &tmap_b, &ctl->full[stage], kb * kBlockK, row, c.expert);
+            tc::tma_load_3d(b_dst, &tmap_b, &ctl->full[stage], kb * kBlockK, row, c.w_plane);
             tc::tma_load_3d(b_dst + kBBytes / 2, &tmap_b, &ctl->full[stage], kb * kBlockK,
-                            g.n_out + row, c.expert);
+                            g.n_out + row, c.w_plane);
           } else {
             const int row = c.n_blk * kBlockN;
-            tc::tma_load_3d(b_dst, &tmap_b, &ctl->full[stage], kb * kBlockK, row, c.expert);
+            tc::tma_load_3d(b_dst, &tmap_b, &ctl->full[stage], kb * kBlockK, row, c.w_plane);
             tc::tma_load_3d(b_dst + kBBytes / 2, &tmap_b, &ctl->full[stage], kb * kBlockK,
-                            row + kBlockN / 2, c.expert);
+                            row + kBlockN / 2, c.w_plane);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -199,7 +339,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t idesc = tc::make_instr_desc(1u, kBlockM, kBlockN);
       uint32_t stage = 0, phase = 0;
       uint32_t local = 0;
-      bool ok = true;
+      bool ok = *abort_flag == 0u;
       for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
         const uint32_t buf = local & 1u;
         const uint32_t use = local >> 1;  // how often this accumulator was used before
@@ -233,19 +373,63 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else if (warp >= 4) {
     const int ew = warp - 4;  // lanes [32 * ew, 32 * ew + 32) of tensor memory
     uint32_t local = 0;
-    bool ok = true;
-    __nv_bfloat16* out = g.out;
+    bool ok = *abort_flag == 0u;
+    const int row_bytes_out = g.n_out * 2;
     for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
-      const TileCoord c = locate_tile(tile_start, g.counts, g.num_experts, g.rows_per_expert, t);
+      const TileCoord c = locate_tile<kFromStaging>(gt, num_groups, p, t);
       const uint32_t buf = local & 1u;
       const uint32_t use = local >> 1;
       ok = tc::mbar_wait(&ctl->tmem_full[buf], use & 1u, abort_flag, kWaitLimitNs);
       if (!ok) break;
       tc::tc_fence_after_sync();
-      const int row = c.m_blk * kBlockM + ew * 32 + lane;
+      const int tile_row = ew * 32 + lane;
+      const int row = c.m_blk * kBlockM + tile_row;  // row inside the group
       const bool row_ok = row < c.rows;
-      __nv_bfloat16* out_row = out + static_cast<int64_t>(c.expert) * g.out_stride_e +
-                               static_cast<int64_t>(row) * g.out_stride_row;
+      const int out_row = c.out_row0 + row;
+
+      // Where this thread's row goes.
+      __nv_bfloat16* local_row = nullptr;
+      uint8_t* peer_row[kToPeers ? 8 : 1];
+      int replicas = 0;
+      uint32_t sig_token = kNoSignal, sig_group = 0;
+      if constexpr (kToPeers) {
+        if (row_ok) {
+          const uint2 rs = p.row_src[static_cast<size_t>(c.w_plane) * p.cap + out_row];
+          const int src_rank = static_cast<int>(rs.x & 0xffffu);
+          const uint32_t k = rs.x >> 16;
+          const uint32_t token = rs.y;
+          if (token < static_cast<uint32_t>(p.max_tokens) && k < static_cast<uint32_t>(p.topk) &&
+              src_rank < p.world) {
+            sig_token = token;
+            sig_group = static_cast<uint32_t>((src_rank / p.dp_size) * p.dp_size);
+            replicas = min(p.dp_size, 8);
+            for (int r = 0; r < replicas; ++r) {
+              peer_row[r] = p.peer[sig_group + r] + p.off_comb_stage +
+                            (static_cast<size_t>(token) * p.topk + k) * row_bytes_out;
+            }
+          } else if (p.debug_checks) {
+            report_failure(p.status, kBadToken, kPhaseCombinePayload, src_rank, p.max_tokens,
+                           token, p.rank);
+          }
+        }
+      } else {
+        local_row = g.out + static_cast<int64_t>(c.w_plane) * g.out_stride_e +
+                    static_cast<int64_t>(out_row) * g.out_stride_row;
+      }
+      if constexpr (kFromStaging) {
+        // First column block of a row also records where the row came from.
+        if (row_ok && c.n_blk == 0) {
+          const uint8_t* slot = p.peer[p.rank] + p.off_disp_stage +
+                                (static_cast<size_t>(c.src) * p.region_slots + c.a_row0 + row) *
+                                    p.slot_bytes;
+          const int4 tr = ptx::ld_cg_v4(slot + p.trailer_off);
+          uint2 rs;
+          rs.x = static_cast<uint32_t>(c.src) | (static_cast<uint32_t>(tr.y) << 16);
+          rs.y = static_cast<uint32_t>(tr.x);
+          p.row_src[static_cast<size_t>(c.w_plane) * p.cap + out_row] = rs;
+        }
+      }
+
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + buf * kBlockN;
       const int col0 = c.n_blk * out_cols_per_tile;
 #pragma unroll 1
@@ -270,18 +454,21 @@ __global__ void __launch_bounds__(kThreads, 1)
             packed[j] = pack_bf16(__uint_as_float(acc[2 * j]), __uint_as_float(acc[2 * j + 1]));
           }
         }
-        if (row_ok) {
-          const int col = col0 + chunk * 32;
+        const int col = col0 + chunk * 32;
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            if (col + v * 8 + 8 <= g.n_out) {
-              int4 q;
-              q.x = packed[4 * v];
-              q.y = packed[4 * v + 1];
-              q.z = packed[4 * v + 2];
-              q.w = packed[4 * v + 3];
-              *reinterpret_cast<int4*>(out_row + col + v * 8) = q;
+        for (int v = 0; v < 4; ++v) {
+          if (col + v * 8 + 8 > g.n_out) continue;
+          int4 q;
+          q.x = packed[4 * v];
+          q.y = packed[4 * v + 1];
+          q.z = packed[4 * v + 2];
+          q.w = packed[4 * v + 3];
+          if constexpr (kToPeers) {
+            for (int r = 0; r < replicas; ++r) {
+              ptx::st_v4(peer_row[r] + static_cast<size_t>(col + v * 8) * 2, q);
             }
+          } else {
+            if (row_ok) *reinterpret_cast<int4*>(local_row + col + v * 8) = q;
           }
         }
       }
@@ -289,6 +476,28 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&ctl->tmem_empty[buf]);
+
+      if constexpr (kToPeers) {
+        // One fence for the whole tile, then the adds.  The sig arrays are double
+        // buffered by accumulator; the barrier below keeps the epilogue warps
+        // within one tile of each other.
+        ctl->sig_token[buf][tile_row] = sig_token;
+        ctl->sig_group[buf][tile_row] = sig_group;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ew == 0) {
+          ptx::fence_acq_rel_sys();
+          const uint32_t units = g.arrival_units_per_tile;
+          for (int j = lane; j < kBlockM; j += 32) {
+            const uint32_t tok = ctl->sig_token[buf][j];
+            if (tok == kNoSignal) continue;
+            const uint32_t grp = ctl->sig_group[buf][j];
+            for (int r = 0; r < min(p.dp_size, 8); ++r) {
+              ptx::red_add_relaxed_sys(
+                  reinterpret_cast<uint32_t*>(p.peer[grp + r] + p.off_comb_arrived) + tok, units);
+            }
+          }
+        }
+      }
     }
   }
 
@@ -300,6 +509,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc::tmem_dealloc(tmem_base, kTmemCols);
   }
   if (tid == 0 && ctl->abort_flag != 0u && g.status != nullptr) *g.status = 1u;
+  (void)parity;
 }
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -341,28 +551,30 @@ CUtensorMap make_operand_map(const void* base, int64_t experts, int64_t rows, in
   return map;
 }
 
-size_t smem_bytes(int num_experts) {
+size_t smem_bytes(int num_groups) {
   return 1024 + kStages * kStageBytes + sizeof(SharedControl) +
-         sizeof(uint32_t) * (static_cast<size_t>(num_experts) + 1);
+         sizeof(uint32_t) * (4 * static_cast<size_t>(num_groups) + 1);
 }
 
-}  // namespace
+template <bool SWIGLU, bool kFromStaging, bool kToPeers>
+void launch_variant(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
+                    const GroupedGemmArgs& g, int num_groups, int grid, cudaStream_t stream) {
+  auto* kernel = grouped_gemm_kernel<SWIGLU, kFromStaging, kToPeers>;
+  CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(smem_bytes(kMaxExperts))));
+  kernel<<<grid, kThreads, smem_bytes(num_groups), stream>>>(tmap_a, tmap_b, g);
+  CUDA_CHECK(cudaGetLastError());
+}
 
-void launch_grouped_gemm(const GroupedGemmCall& c, cudaStream_t stream) {
+void check_common(const GroupedGemmCall& c) {
   PPLX_CHECK(c.num_experts > 0 && c.num_experts <= kMaxExperts, "num_experts out of range");
   PPLX_CHECK(c.k > 0 && c.k % 8 == 0, "K must be a positive multiple of 8");
   PPLX_CHECK(c.n_out > 0 && c.n_out % 8 == 0, "the output width must be a positive multiple of 8");
   PPLX_CHECK(!c.swiglu || c.n_out % (kBlockN / 2) == 0,
              "SwiGLU needs an intermediate size that is a multiple of 128");
-  PPLX_CHECK(reinterpret_cast<uintptr_t>(c.out) % 16 == 0 && c.out_stride_row % 8 == 0 &&
-                 c.out_stride_e % 8 == 0,
-             "the output must be 16-byte aligned");
-  const int64_t w_rows = c.swiglu ? 2 * static_cast<int64_t>(c.n_out) : c.n_out;
-  const CUtensorMap tmap_a = make_operand_map(c.x, c.num_experts, c.rows_per_expert, c.k,
-                                              c.x_stride_row, c.x_stride_e);
-  const CUtensorMap tmap_b =
-      make_operand_map(c.w, c.num_experts, w_rows, c.k, c.w_stride_row, c.w_stride_e);
+}
 
+GroupedGemmArgs base_args(const GroupedGemmCall& c) {
   GroupedGemmArgs g{};
   g.counts = c.counts;
   g.out = static_cast<__nv_bfloat16*>(c.out);
@@ -373,21 +585,75 @@ void launch_grouped_gemm(const GroupedGemmCall& c, cudaStream_t stream) {
   g.rows_per_expert = c.rows_per_expert;
   g.n_out = c.n_out;
   g.k = c.k;
+  return g;
+}
 
-  const size_t smem = smem_bytes(c.num_experts);
+CUtensorMap weight_map(const GroupedGemmCall& c) {
+  const int64_t w_rows = c.swiglu ? 2 * static_cast<int64_t>(c.n_out) : c.n_out;
+  return make_operand_map(c.w, c.num_experts, w_rows, c.k, c.w_stride_row, c.w_stride_e);
+}
+
+}  // namespace
+
+void launch_grouped_gemm(const GroupedGemmCall& c, cudaStream_t stream) {
+  check_common(c);
+  PPLX_CHECK(reinterpret_cast<uintptr_t>(c.out) % 16 == 0 && c.out_stride_row % 8 == 0 &&
+                 c.out_stride_e % 8 == 0,
+             "the output must be 16-byte aligned");
+  const CUtensorMap tmap_a = make_operand_map(c.x, c.num_experts, c.rows_per_expert, c.k,
+                                              c.x_stride_row, c.x_stride_e);
+  const CUtensorMap tmap_b = weight_map(c);
+  const GroupedGemmArgs g = base_args(c);
   const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
-  if (c.swiglu) {
-    CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel<true>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(smem_bytes(kMaxExperts))));
-    grouped_gemm_kernel<true><<<grid, kThreads, smem, stream>>>(tmap_a, tmap_b, g);
-  } else {
-    CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_kernel<false>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(smem_bytes(kMaxExperts))));
-    grouped_gemm_kernel<false><<<grid, kThreads, smem, stream>>>(tmap_a, tmap_b, g);
-  }
-  CUDA_CHECK(cudaGetLastError());
+  if (c.swiglu) launch_variant<true, false, false>(tmap_a, tmap_b, g, c.num_experts, grid, stream);
+  else launch_variant<false, false, false>(tmap_a, tmap_b, g, c.num_experts, grid, stream);
+}
+
+void launch_gemm_from_staging(const GroupedGemmCall& c, const A2AParams& p,
+                              int32_t* out_num_tokens, cudaStream_t stream) {
+  check_common(c);
+  PPLX_CHECK(c.swiglu, "the staging-fed GEMM is the SwiGLU up projection");
+  PPLX_CHECK(p.scale_bytes == 0 && p.hidden_bytes == p.hidden_dim * 2,
+             "the staging-fed GEMM needs a bf16 dispatch payload without scales");
+  PPLX_CHECK(c.k == p.hidden_dim && c.num_experts == p.nle && c.rows_per_expert >= p.cap,
+             "shape mismatch between the GEMM and the all-to-all");
+  PPLX_CHECK(p.world * p.nle <= kMaxExperts && p.world <= kMaxWorld, "too many groups");
+  PPLX_CHECK(reinterpret_cast<uintptr_t>(c.out) % 16 == 0 && c.out_stride_row % 8 == 0 &&
+                 c.out_stride_e % 8 == 0,
+             "the output must be 16-byte aligned");
+  // A: [world][region_slots][hidden] bf16 view of this rank's staging regions.
+  const CUtensorMap tmap_a = make_operand_map(
+      p.peer[p.rank] + p.off_disp_stage, p.world, p.region_slots, p.hidden_dim, p.slot_bytes / 2,
+      static_cast<int64_t>(p.region_slots) * p.slot_bytes / 2);
+  const CUtensorMap tmap_b = weight_map(c);
+  GroupedGemmArgs g = base_args(c);
+  g.out_num_tokens = out_num_tokens;
+  g.a2a = p;
+  const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
+  launch_variant<true, true, false>(tmap_a, tmap_b, g, p.world * p.nle, grid, stream);
+}
+
+void launch_gemm_to_peers(const GroupedGemmCall& c, const A2AParams& p, cudaStream_t stream) {
+  check_common(c);
+  PPLX_CHECK(!c.swiglu, "the peer-storing GEMM is the plain down projection");
+  PPLX_CHECK(c.n_out == p.hidden_dim && c.num_experts == p.nle && c.rows_per_expert >= p.cap,
+             "shape mismatch between the GEMM and the all-to-all");
+  PPLX_CHECK(c.counts == reinterpret_cast<const int32_t*>(p.recv_count),
+             "counts must be the all-to-all's received-row counts");
+  const int n_blocks = ceil_div(c.n_out, kBlockN);
+  PPLX_CHECK(p.comb_units % n_blocks == 0,
+             "combine units (" << p.comb_units << ") must be a multiple of the "
+                               << n_blocks << " column blocks of the output");
+  PPLX_CHECK(p.dp_size <= 8, "at most 8 replicas per DP group");
+  const CUtensorMap tmap_a = make_operand_map(c.x, c.num_experts, c.rows_per_expert, c.k,
+                                              c.x_stride_row, c.x_stride_e);
+  const CUtensorMap tmap_b = weight_map(c);
+  GroupedGemmArgs g = base_args(c);
+  g.out = nullptr;
+  g.arrival_units_per_tile = static_cast<uint32_t>(p.comb_units / n_blocks);
+  g.a2a = p;
+  const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
+  launch_variant<false, false, true>(tmap_a, tmap_b, g, c.num_experts, grid, stream);
 }
 
 }  // namespace pplx

@@ -1,5 +1,7 @@
 #include "all_to_all.h"
 
+#include "../kernels/grouped_gemm.h"
+
 #include <algorithm>
 #include <sstream>
 
@@ -90,6 +92,7 @@ A2AParams make_layout(const A2AConfig& c) {
   const int tokens_per_sender = ceil_div(c.max_num_tokens, c.dp_size);
   p.region_slots = tokens_per_sender * std::min(c.experts_per_token, p.nle);
   p.cap = c.max_num_tokens * p.num_dp_groups;
+  p.comb_units = 16;
 
   size_t off = 0;
   p.off_counts = off;
@@ -168,6 +171,11 @@ std::vector<std::unique_ptr<AllToAll>> AllToAll::create_local_world(const A2ACon
     out.push_back(std::make_unique<AllToAll>(cfg, arenas[r]));
   }
   return out;
+}
+
+void AllToAll::set_combine_units(int units) {
+  PPLX_CHECK(units > 0 && units % 16 == 0, "combine units must be a positive multiple of 16");
+  params_.comb_units = units;
 }
 
 void AllToAll::set_trace(bool on) { params_.trace = on ? trace_.get() : nullptr; }
@@ -270,6 +278,45 @@ void AllToAll::combine(const CombineCall& call, SplitMode mode, cudaStream_t str
   const bool send = mode != SplitMode::kRecv, recv = mode != SplitMode::kSend;
   CUDA_CHECK(launch_combine(a, call.in, call.out, send, recv, combine_grid(call.num_tokens),
                             stream));
+}
+
+void AllToAll::fused_up(const FusedFfnCall& f, cudaStream_t stream) {
+  NvtxRange range("moe_fused_up");
+  GroupedGemmCall c;
+  c.w = f.w;
+  c.w_stride_e = f.w_stride_e;
+  c.w_stride_row = f.w_stride_row;
+  c.out = f.h;
+  c.out_stride_e = f.h_stride_e;
+  c.out_stride_row = f.h_stride_row;
+  c.status = f.status;
+  c.num_experts = params_.nle;
+  c.rows_per_expert = f.rows_per_expert;
+  c.n_out = f.inter_dim;
+  c.k = params_.hidden_dim;
+  c.swiglu = true;
+  c.num_sms = max_blocks_ > 0 ? std::min(max_blocks_, num_sms_) : num_sms_;
+  launch_gemm_from_staging(c, params_, f.out_num_tokens, stream);
+}
+
+void AllToAll::fused_down(const FusedFfnCall& f, cudaStream_t stream) {
+  NvtxRange range("moe_fused_down");
+  GroupedGemmCall c;
+  c.x = f.h;
+  c.x_stride_e = f.h_stride_e;
+  c.x_stride_row = f.h_stride_row;
+  c.w = f.w;
+  c.w_stride_e = f.w_stride_e;
+  c.w_stride_row = f.w_stride_row;
+  c.counts = reinterpret_cast<const int32_t*>(params_.recv_count);
+  c.status = f.status;
+  c.num_experts = params_.nle;
+  c.rows_per_expert = f.rows_per_expert;
+  c.n_out = params_.hidden_dim;
+  c.k = f.inter_dim;
+  c.swiglu = false;
+  c.num_sms = max_blocks_ > 0 ? std::min(max_blocks_, num_sms_) : num_sms_;
+  launch_gemm_to_peers(c, params_, stream);
 }
 
 namespace {

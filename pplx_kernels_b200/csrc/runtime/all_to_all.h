@@ -75,6 +75,20 @@ struct CombineCall {
   DType out = DType::kBF16;
 };
 
+// Weights and intermediate buffer of the fused expert FFN (bf16, strides in elements).
+struct FusedFfnCall {
+  const void* w = nullptr;   // up: [nle][2 * inter][hidden]; down: [nle][hidden][inter]
+  int64_t w_stride_e = 0;
+  int64_t w_stride_row = 0;
+  void* h = nullptr;         // [nle][rows_per_expert][inter]: written by up, read by down
+  int64_t h_stride_e = 0;
+  int64_t h_stride_row = 0;
+  int rows_per_expert = 0;
+  int inter_dim = 0;
+  int32_t* out_num_tokens = nullptr;  // up only, optional
+  uint32_t* status = nullptr;         // optional device word, 1 if a pipeline wait ran out
+};
+
 class AllToAll {
  public:
   AllToAll(const A2AConfig& cfg, std::shared_ptr<SymmetricAllocation> arena);
@@ -95,6 +109,13 @@ class AllToAll {
   void dispatch(const DispatchCall& call, SplitMode mode, cudaStream_t stream);
   void combine(const CombineCall& call, SplitMode mode, cudaStream_t stream);
 
+  // Fused MoE path: dispatch(kSend), fused_up, fused_down, combine(kRecv).
+  // fused_up takes the place of the dispatch receive phase (the tcgen05 GEMM reads
+  // the staging arena as peers fill it), fused_down that of the combine send phase
+  // (the GEMM epilogue stores to the tokens' home ranks).
+  void fused_up(const FusedFfnCall& call, cudaStream_t stream);
+  void fused_down(const FusedFfnCall& call, cudaStream_t stream);
+
   // All ranks of a local world in one cooperative launch per operation.
   static void dispatch_group(const std::vector<AllToAll*>& ranks,
                              const std::vector<DispatchCall>& calls, SplitMode mode,
@@ -111,6 +132,10 @@ class AllToAll {
   void set_timeout_ms(double ms);
   void set_debug_checks(bool on) { params_.debug_checks = on ? 1 : 0; }
   void set_max_blocks(int n) { max_blocks_ = n; }
+  // Arrival units one complete expert-output row is worth (default 16).  All ranks
+  // must agree; the GEMM whose epilogue stores to peers needs a multiple of its
+  // number of column blocks.  Change only between a combine and the next dispatch.
+  void set_combine_units(int units);
   // Per-phase %globaltimer stamps of block 0 (see TraceSlot); synchronises on read.
   void set_trace(bool on);
   std::vector<uint64_t> read_trace() const;

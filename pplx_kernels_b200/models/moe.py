@@ -1,0 +1,127 @@
+"""Expert-parallel MoE FFN layer: dispatch -> SwiGLU expert FFN -> combine.
+
+``MoELayer`` owns one rank's slice of the experts (``num_experts // world_size``
+experts, SwiGLU weights ``w13 = [gate; up]`` and ``w2``), an ``AllToAll`` and the
+intermediate buffers, and runs
+
+    tokens --dispatch--> per-expert rows --grouped GEMM + SwiGLU--> h
+           --grouped GEMM--> y --combine (top-k weighted sum)--> tokens
+
+on hand-written sm_100a kernels only: P2P dispatch/combine and the tcgen05
+grouped GEMM.  The reference library stops at dispatch/combine and leaves the
+expert computation to the caller (its tests fake it with ``x * 1.5``,
+tests/test_all_to_all.py:248-250); this layer is what a caller such as an
+inference engine builds on top.
+
+All buffers are allocated once, no host synchronisation happens in ``forward``,
+and the token count can be bounded on the device (``bound_m``), so a forward
+pass can be captured in a CUDA graph.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..all_to_all import AllToAll
+from ..ops.grouped_gemm import grouped_gemm
+from .configs import MoEModelConfig
+
+
+class MoELayer:
+    def __init__(self, cfg: MoEModelConfig, max_num_tokens: int, rank: int = 0,
+                 world_size: int = 1, dp_size: int = 1, device: torch.device | None = None,
+                 ata: AllToAll | None = None, seed: int = 0, group_name: str = "default",
+                 init_std: float = 0.02) -> None:
+        assert cfg.num_experts % world_size == 0
+        self.cfg = cfg
+        self.rank, self.world_size, self.dp_size = rank, world_size, dp_size
+        self.max_num_tokens = max_num_tokens
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.nle = cfg.num_experts // world_size
+        self.rows = max_num_tokens * (world_size // dp_size)
+        H, I = cfg.hidden_dim, cfg.intermediate_dim
+        self.ata = ata or AllToAll.intranode(
+            max_num_tokens, cfg.num_experts, cfg.experts_per_token, rank, world_size, dp_size,
+            H, H * 2, 0, group_name=group_name)
+        # Random-init weights of this rank's experts; every rank seeds by global expert id so
+        # that any world size holds the same model.
+        gen = torch.Generator(device="cpu")
+        w13, w2 = [], []
+        for le in range(self.nle):
+            gen.manual_seed(seed * 100003 + rank * self.nle + le)
+            w13.append(torch.randn(2 * I, H, generator=gen) * init_std)
+            w2.append(torch.randn(H, I, generator=gen) * init_std)
+        self.w13 = torch.stack(w13).to(torch.bfloat16).to(self.device)  # [nle, 2I, H]
+        self.w2 = torch.stack(w2).to(torch.bfloat16).to(self.device)    # [nle, H, I]
+        dev = self.device
+        self.counts = torch.zeros(self.nle, dtype=torch.int32, device=dev)
+        self.expert_x = torch.zeros(self.nle, self.rows, H, dtype=torch.bfloat16, device=dev)
+        self.h = torch.zeros(self.nle, self.rows, I, dtype=torch.bfloat16, device=dev)
+        self.expert_y = torch.zeros(self.nle, self.rows, H, dtype=torch.bfloat16, device=dev)
+        self.gemm_status = torch.zeros(1, dtype=torch.int32, device=dev)
+        # The fused down projection signals once per 256-column block of the output.
+        self.ata.set_combine_units(math.lcm(16, (H + 255) // 256))
+
+    def forward(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
+                out: torch.Tensor | None = None, bound_m: torch.Tensor | None = None,
+                fused: bool = True) -> torch.Tensor:
+        """x: [m, hidden] bf16; indices: [m, top-k] uint32; weights: [m, top-k] fp32.
+
+        ``fused=True`` runs four kernels: dispatch send, the up projection fed from the
+        staging arena as tokens land, the down projection whose epilogue stores to the
+        tokens' home ranks, and the combine reduction.  ``fused=False`` runs the plain
+        composition dispatch -> GEMM -> GEMM -> combine (six phases, two more passes over
+        the activations).
+        """
+        if out is None:
+            out = torch.empty(self.max_num_tokens, self.cfg.hidden_dim, dtype=torch.bfloat16,
+                              device=self.device)
+        if fused:
+            self.ata.dispatch(self.counts, self.expert_x, None, x, None, indices, bound_m,
+                              do_send=True, do_recv=False)
+            self.ata.fused_up(self.w13, self.h, self.counts, self.gemm_status)
+            self.ata.fused_down(self.h, self.w2, self.gemm_status)
+            self.ata.combine(out, indices, weights, self.expert_y, bound_m,
+                             do_send=False, do_recv=True)
+            return out
+        self.ata.dispatch(self.counts, self.expert_x, None, x, None, indices, bound_m)
+        grouped_gemm(self.expert_x, self.w13, self.counts, out=self.h, swiglu=True,
+                     status=self.gemm_status)
+        grouped_gemm(self.h, self.w2, self.counts, out=self.expert_y, swiglu=False,
+                     status=self.gemm_status)
+        self.ata.combine(out, indices, weights, self.expert_y, bound_m)
+        return out
+
+    __call__ = forward
+
+    def check_status(self) -> None:
+        self.ata.check_status()
+        if int(self.gemm_status.item()) != 0:
+            raise RuntimeError("pplx_kernels_b200: a grouped GEMM pipeline wait ran out")
+
+    def destroy(self) -> None:
+        self.ata.destroy()
+
+
+def moe_reference(x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
+                  w13: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+    """Plain PyTorch fp32 MoE FFN over ALL experts (w13: [E, 2I, H], w2: [E, H, I]).
+
+    Intermediate roundings follow the kernels: h and y are rounded to bf16 before
+    the next step, the top-k sum is accumulated in fp32.
+    """
+    m, _ = x.shape
+    I = w2.size(2)
+    out = torch.zeros(m, x.size(1), dtype=torch.float32, device=x.device)
+    xf = x.to(torch.float32)
+    idx = indices.to(torch.int64)
+    for k in range(idx.size(1)):
+        for e in idx[:, k].unique().tolist():
+            sel = (idx[:, k] == e).nonzero().flatten()
+            y = xf[sel] @ w13[e].to(torch.float32).t()
+            h = (torch.nn.functional.silu(y[:, :I]) * y[:, I:]).to(torch.bfloat16).to(torch.float32)
+            o = (h @ w2[e].to(torch.float32).t()).to(torch.bfloat16).to(torch.float32)
+            out[sel] += o * weights[sel, k : k + 1].to(torch.float32)
+    return out
