@@ -188,3 +188,41 @@ def test_lost_peer_is_reported_2_gpu():
     _need(2)
     cfg = MoEConfig(8, 2, 256, 8)
     parallel_launch(2, _worker_lost_peer, cfg)
+
+
+# ------------------------------------------------------------------ MoE layer ----
+
+
+def _worker_moe_layer(pgi: ProcessGroupInfo, model: str, tokens: int) -> None:
+    from pplx_kernels_b200.models.configs import CONFIGS
+    from pplx_kernels_b200.models.moe import MoELayer, moe_reference
+    from pplx_kernels_b200.utils.testing import as_index_tensor, routing
+
+    cfg = CONFIGS[model]
+    dev = pgi.device
+    layer = MoELayer(cfg, max_num_tokens=tokens, rank=pgi.rank, world_size=pgi.world_size,
+                     device=dev, init_std=0.05)
+    layer.ata.set_timeout_ms(5000)
+    gen = torch.Generator().manual_seed(50 + pgi.rank)
+    x = torch.randn(tokens, cfg.hidden_dim, generator=gen).to(torch.bfloat16).to(dev)
+    idx = routing(tokens, cfg.num_experts, cfg.experts_per_token, gen)
+    w = torch.softmax(torch.randn(tokens, cfg.experts_per_token, generator=gen), dim=-1).to(dev)
+    # The whole model's weights, for the reference: gather every rank's experts.
+    w13_all = [torch.empty_like(layer.w13) for _ in range(pgi.world_size)]
+    w2_all = [torch.empty_like(layer.w2) for _ in range(pgi.world_size)]
+    torch.distributed.all_gather(w13_all, layer.w13)
+    torch.distributed.all_gather(w2_all, layer.w2)
+    want = moe_reference(x, idx.to(dev), w, torch.cat(w13_all), torch.cat(w2_all))
+    for fused in (True, False, True):
+        out = layer(x, as_index_tensor(idx, dev), w, fused=fused)
+        torch.cuda.synchronize()
+        layer.check_status()
+        torch.testing.assert_close(out[:tokens].float(), want, rtol=3e-2, atol=3e-3)
+    torch.distributed.barrier()
+    layer.destroy()
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_moe_layer_fused_and_composed_multi_gpu(world):
+    _need(world)
+    parallel_launch(world, _worker_moe_layer, "tiny", 48)
