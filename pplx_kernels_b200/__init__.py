@@ -9,6 +9,7 @@ from .all_to_all import (
     AllToAll as AllToAll,
     combine_group as combine_group,
     dispatch_group as dispatch_group,
+    fused_dispatch_group as fused_dispatch_group,
 )
 from .nvshmem import (
     nvshmem_alloc_empty_unique_id as nvshmem_alloc_empty_unique_id,

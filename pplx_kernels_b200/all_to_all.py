@@ -150,13 +150,23 @@ class AllToAll:
         """
         _ops.all_to_all_set_combine_units(self._ptr, int(units))
 
+    def fused_dispatch(self, dp_x: torch.Tensor, indices: torch.Tensor,
+                       bound_m: torch.Tensor | None = None) -> None:
+        """Send half of the fused MoE dispatch (bf16 tokens, no scales).
+
+        Two-hop protocol: ranks first exchange their per-expert histograms, then store
+        every row at its final, expert-major position in the destination's staging, so
+        that ``fused_up`` can read dense 128-row tiles by TMA.  Follow it with
+        ``fused_up``, ``fused_down`` and ``combine(..., do_send=False)``.
+        """
+        _ops.moe_dispatch_send(self._ptr, dp_x, indices, bound_m)
+
     def fused_up(self, w13: torch.Tensor, h: torch.Tensor,
                  out_expert_num_tokens: torch.Tensor | None = None,
                  status: torch.Tensor | None = None) -> None:
         """SwiGLU up projection that reads the dispatch staging arena as peers fill it.
 
-        Call after ``dispatch(..., do_send=True, do_recv=False)``; it replaces the receive
-        half.  ``h[le, :n] = silu(x @ gate.T) * (x @ up.T)`` for the rows of local expert le.
+        Call after ``fused_dispatch``; it replaces the receive half of dispatch.  ``h[le, :n] = silu(x @ gate.T) * (x @ up.T)`` for the rows of local expert le.
         """
         _ops.moe_fused_up(self._ptr, w13, h, out_expert_num_tokens, status)
 
@@ -361,4 +371,17 @@ def combine_group(
         [_or_empty(t, dev) for t in bound_m],
         do_send,
         do_recv,
+    )
+
+
+def fused_dispatch_group(
+    ranks: Sequence[AllToAll],
+    dp_x: Sequence[torch.Tensor],
+    indices: Sequence[torch.Tensor],
+    bound_m: Sequence[torch.Tensor | None],
+) -> None:
+    """``fused_dispatch`` of every rank of a local world, as a single cooperative launch."""
+    dev = dp_x[0].device
+    _ops.moe_dispatch_send_group(
+        [r._ptr for r in ranks], list(dp_x), list(indices), [_or_empty(t, dev) for t in bound_m]
     )

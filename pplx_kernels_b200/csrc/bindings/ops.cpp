@@ -406,6 +406,61 @@ void check_bf16_3d(const at::Tensor& t, const char* name) {
               name, " must be a 3-D bfloat16 CUDA tensor with a contiguous last dimension");
 }
 
+DispatchCall make_packed_call(const AllToAll& ata, const at::Tensor& dp_x,
+                              const at::Tensor& indices,
+                              const std::optional<at::Tensor>& bound_m) {
+  const A2AParams& p = ata.params();
+  TORCH_CHECK(dp_x.is_cuda() && dp_x.dim() == 2 && dp_x.is_contiguous() &&
+                  dp_x.scalar_type() == at::kBFloat16 && dp_x.size(1) == p.hidden_dim,
+              "dp_x must be a contiguous bfloat16 CUDA tensor of [num_tokens, hidden_dim]");
+  TORCH_CHECK(indices.is_cuda() && indices.dim() == 2 && indices.is_contiguous() &&
+                  indices.element_size() == 4 && indices.size(1) == p.topk &&
+                  indices.size(0) == dp_x.size(0),
+              "indices must be a contiguous 32-bit CUDA tensor of [num_tokens, experts_per_token]");
+  DispatchCall c;
+  c.x.data = static_cast<const uint8_t*>(dp_x.data_ptr());
+  c.x.stride_row = dp_x.stride(0) * dp_x.element_size();
+  c.indices = static_cast<const uint32_t*>(indices.data_ptr());
+  if (bound_m.has_value()) {
+    TORCH_CHECK(bound_m->is_cuda() && bound_m->numel() == 1 && bound_m->element_size() == 4,
+                "bound_m must be a 32-bit CUDA scalar tensor");
+    c.bound_m = static_cast<const uint32_t*>(bound_m->data_ptr());
+  }
+  c.num_tokens = static_cast<int>(indices.size(0));
+  return c;
+}
+
+// Send half of the fused MoE dispatch: rows land in the peers' staging grouped by expert.
+void moe_dispatch_send_op(int64_t ptr, const at::Tensor& dp_x, const at::Tensor& indices,
+                          const std::optional<at::Tensor>& bound_m) {
+  AllToAll* ata = lookup(ptr);
+  const c10::cuda::OptionalCUDAGuard guard(dp_x.device());
+  guarded([&] {
+    ata->dispatch_send_packed(make_packed_call(*ata, dp_x, indices, bound_m),
+                              at::cuda::getCurrentCUDAStream());
+  });
+}
+
+void fake_moe_dispatch_send(int64_t, const at::Tensor&, const at::Tensor&,
+                            const std::optional<at::Tensor>&) {}
+
+void moe_dispatch_send_group_op(std::vector<int64_t> ptrs, std::vector<at::Tensor> dp_x,
+                                std::vector<at::Tensor> indices, std::vector<at::Tensor> bound_m) {
+  const size_t n = ptrs.size();
+  TORCH_CHECK(n > 0 && dp_x.size() == n && indices.size() == n && bound_m.size() == n,
+              "moe_dispatch_send_group: list lengths differ");
+  guarded([&] {
+    std::vector<AllToAll*> ranks;
+    std::vector<DispatchCall> calls;
+    for (size_t r = 0; r < n; ++r) {
+      ranks.push_back(lookup(ptrs[r]));
+      calls.push_back(make_packed_call(*ranks[r], dp_x[r], indices[r], opt(bound_m[r])));
+    }
+    const c10::cuda::OptionalCUDAGuard guard(dp_x[0].device());
+    AllToAll::dispatch_send_packed_group(ranks, calls, at::cuda::getCurrentCUDAStream());
+  });
+}
+
 // SwiGLU up projection fed from the dispatch staging arena (after dispatch with do_recv=False).
 void moe_fused_up_op(int64_t ptr, const at::Tensor& w13, at::Tensor& h,
                      const std::optional<at::Tensor>& out_expert_num_tokens,
@@ -651,6 +706,12 @@ void register_all_to_all_ops(torch::Library& m) {
   m.def("all_to_all_layout(int ptr) -> int[]", &layout_op);
   m.def("all_to_all_set_trace(int ptr, bool on) -> ()", &set_trace_op);
   m.def("all_to_all_set_combine_units(int ptr, int units) -> ()", &set_combine_units_op);
+  m.def("moe_dispatch_send(int ptr, Tensor dp_x, Tensor indices, Tensor? bound_m) -> ()");
+  m.impl("moe_dispatch_send", c10::kCUDA, &moe_dispatch_send_op);
+  m.impl("moe_dispatch_send", c10::kMeta, &fake_moe_dispatch_send);
+  m.def("moe_dispatch_send_group(int[] ptrs, Tensor[] dp_x, Tensor[] indices, "
+        "Tensor[] bound_m) -> ()",
+        &moe_dispatch_send_group_op);
   m.def("moe_fused_up(int ptr, Tensor w13, Tensor! h, Tensor!? out_expert_num_tokens, "
         "Tensor!? status) -> ()");
   m.impl("moe_fused_up", c10::kCUDA, &moe_fused_up_op);

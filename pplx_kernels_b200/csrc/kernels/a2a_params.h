@@ -18,6 +18,12 @@
 //    device-side iteration counter.  No flag handshake is needed before a send:
 //    a rank can be at most one dispatch ahead of any peer, because every rank
 //    posts counts to every rank in every dispatch.
+//  * A second, "packed" send mode serves the fused MoE layer: every rank first
+//    posts its whole per-expert histogram to every rank, waits for everyone's,
+//    and then stores each row at its final position in the destination's
+//    staging, grouped by local expert and then by source.  It costs one more
+//    flag round trip before the payload moves, and gives the expert GEMM dense
+//    128-row tiles that it can read with TMA without any receive-side copy.
 //  * Resets ride on the strict dispatch/combine alternation: a combine clears the
 //    flag set of the dispatch before it and bumps the iteration counter.  The
 //    combine's per-token arrival counters are never cleared: every combine adds
@@ -59,7 +65,12 @@ struct A2AParams {
   size_t off_counts;        // u32 [2][world][nle]   value = count + 1, 0 = not posted
   size_t off_arrived;       // u32 [2][world]        rows landed from each source
   size_t off_comb_arrived;  // u32 [max_tokens]      running total, 16 units per expert output
-  size_t off_disp_stage;    // u8  [world][region_slots][slot_bytes]
+  size_t off_counts_all;    // u32 [2][world][num_experts]  packed mode: every source's full
+                            //                       histogram, value = count + 1
+  size_t off_arrived_e;     // u32 [2][nle]          packed mode: rows landed per local expert
+  size_t off_disp_stage;    // u8  [world][region_slots][slot_bytes]; in packed mode the same
+                            //     memory is one array of world * region_slots slots with
+                            //     rows grouped by local expert, then by source rank
   size_t off_comb_stage;    // u8  [max_tokens*topk][hidden_dim*4]
   size_t arena_bytes;
 
@@ -119,6 +130,8 @@ struct DispatchArgs {
   const uint32_t* indices;   // [m][topk]
   const uint32_t* bound_m;   // optional device scalar
   int num_tokens;            // indices.size(0)
+  int packed;                // send only: two-hop protocol, rows land at their final,
+                             // expert-major position in the destination's staging
 };
 
 struct CombineArgs {

@@ -34,6 +34,7 @@
 #include "../core/ptx.cuh"
 #include "../core/utils.h"
 #include "../core/wait.cuh"
+#include "a2a_device.cuh"
 #include "a2a_kernels.h"
 #include "a2a_params.h"
 
@@ -161,6 +162,7 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
     const int P = p.world * p.nle;
     for (int q = tid; q < P; q += blockDim.x) counts[q] = 0;
     if (tid < p.world) arrived[tid] = 0;
+    reset_packed_flags(p, parity);
     __syncthreads();
     if (tid == 0) *p.iter = *p.iter + 1u;
   }

@@ -27,6 +27,12 @@
 //           counters and bumps the iteration counter (dispatch and combine must
 //           alternate, as in the reference).
 //
+// Packed send (a.packed, used by the fused MoE layer): step 2 posts the whole
+// histogram to every peer, every block then waits for all peers' histograms and
+// places each row at its final position in the destination's staging -- grouped
+// by local expert, then by source rank -- and step 4 signals per (destination,
+// expert) instead of per destination.
+//
 // Rows are split over several warps whenever there are fewer rows than warps, so
 // that a single token still moves with the whole block's memory parallelism.
 //
@@ -65,6 +71,7 @@ struct DispatchSmem {
   uint32_t* hist;    // [E]
   uint32_t* base;    // [E]
   uint32_t* off;     // [E]  rows for lower local experts of the same destination
+  uint32_t* bef;     // [E]  packed mode: rows that lower-ranked sources send to the expert
   uint32_t* fstart;  // [P + 1]  counts, then their exclusive scan
   uint32_t* rbase;   // [P]
   uint32_t* sent;    // [kMaxWorld]
@@ -77,7 +84,8 @@ __device__ __forceinline__ DispatchSmem carve(uint32_t* s, int E, int P) {
   m.hist = s;
   m.base = m.hist + E;
   m.off = m.base + E;
-  m.fstart = m.off + E;
+  m.bef = m.off + E;
+  m.fstart = m.bef + E;
   m.rbase = m.fstart + P + 1;
   m.sent = m.rbase + P;
   m.tmp = m.sent + kMaxWorld;
@@ -147,29 +155,68 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
   __syncthreads();
   trace(p, kTrDispatchHist);
 
-  if (blockIdx.x == 0) {
+  const bool packed = a.packed != 0;
+  if (!packed) {
+    if (blockIdx.x == 0) {
+      for (int e = tid; e < E; e += blockDim.x) {
+        const int dst = e / p.nle;
+        const int le = e - dst * p.nle;
+        ptx::st_relaxed_sys(counts_ptr(p, dst, parity, p.rank, le), sm.hist[e] + 1u);
+      }
+    }
+    for (int e = tid; e < E; e += blockDim.x) sm.off[e] = sm.hist[e];
+  } else {
+    // Hop 1: everybody learns everybody's histogram.
+    const int WE = p.world * E;
+    if (blockIdx.x == 0) {
+      for (int idx = tid; idx < WE; idx += blockDim.x) {
+        const int d = idx / E;
+        const int e = idx - d * E;
+        uint32_t* dstp = reinterpret_cast<uint32_t*>(p.peer[d] + p.off_counts_all) +
+                         (static_cast<size_t>(parity) * p.world + p.rank) * E + e;
+        ptx::st_relaxed_sys(dstp, sm.hist[e] + 1u);
+      }
+    }
     for (int e = tid; e < E; e += blockDim.x) {
-      const int dst = e / p.nle;
-      const int le = e - dst * p.nle;
-      ptx::st_relaxed_sys(counts_ptr(p, dst, parity, p.rank, le), sm.hist[e] + 1u);
+      sm.off[e] = 0;
+      sm.bef[e] = 0;
+    }
+    __syncthreads();
+    const WaitCtx w{p.status, p.timeout_ns, static_cast<uint32_t>(p.rank)};
+    const uint32_t* all = reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.off_counts_all) +
+                          static_cast<size_t>(parity) * p.world * E;
+    for (int idx = tid; idx < WE; idx += blockDim.x) {
+      const int src = idx / E;
+      const int e = idx - src * E;
+      uint32_t v = 0;
+      if (wait_until(all + idx, PredNonZero{}, v, w, kPhaseDispatchCounts, src, 1u) && v > 1u) {
+        atomicAdd(&sm.off[e], v - 1u);
+        if (src < p.rank) atomicAdd(&sm.bef[e], v - 1u);
+      }
     }
   }
 
   // Slot of the first row this block stores for expert e: rows for lower local
-  // experts of the same destination come first, then earlier blocks' rows.
-  // One warp per destination scans that destination's experts.
-  for (int e = tid; e < E; e += blockDim.x) sm.off[e] = sm.hist[e];
+  // experts of the same destination come first (all sources' rows in packed
+  // mode), then lower-ranked sources' rows for the expert (packed mode), then
+  // earlier blocks' rows.  One warp per destination scans that destination.
   __syncthreads();
   for (int dst = warp; dst < p.world; dst += nwarps) {
     warp_exclusive_scan_smem(sm.off + dst * p.nle, p.nle, lane, false);
   }
   __syncthreads();
-  for (int e = tid; e < E; e += blockDim.x) sm.base[e] += sm.off[e];
+  for (int e = tid; e < E; e += blockDim.x) {
+    sm.base[e] += sm.off[e] + (packed ? sm.bef[e] : 0u);
+    sm.hist[e] = 0;  // from here on: rows this block stored for expert e (packed mode)
+  }
   __syncthreads();
 
   const int nvec = p.hidden_bytes >> 4;
   const int nscale = p.scale_bytes >> 2;
   const int rows_here = u_end - u_begin;
+  const uint32_t slot_limit =
+      static_cast<uint32_t>(packed ? p.world * p.region_slots : p.region_slots);
+  const size_t region_first = packed ? 0 : static_cast<size_t>(p.rank) * p.region_slots;
   const bool precomputed = rows_here <= kRowCap;
   int split = 1;
   if (precomputed) {
@@ -182,12 +229,13 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
       uint32_t pos = kNoSlot;
       if (e < static_cast<uint32_t>(E)) {
         pos = atomicAdd(&sm.base[e], 1u);
-        if (p.debug_checks && pos >= static_cast<uint32_t>(p.region_slots)) {
-          report_failure(p.status, kSlotOverflow, kPhaseDispatchPayload, e / p.nle,
-                         p.region_slots, pos, p.rank);
+        if (p.debug_checks && pos >= slot_limit) {
+          report_failure(p.status, kSlotOverflow, kPhaseDispatchPayload, e / p.nle, slot_limit,
+                         pos, p.rank);
           pos = kNoSlot;
         } else {
           atomicAdd(&sm.sent[e / p.nle], 1u);
+          if (packed) atomicAdd(&sm.hist[e], 1u);
         }
       }
       sm.rowpos[r] = pos;
@@ -217,17 +265,19 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
       pos = 0;
       if (lane == 0) pos = atomicAdd(&sm.base[e], 1u);
       pos = __shfl_sync(0xffffffffu, pos, 0);
-      if (p.debug_checks && pos >= static_cast<uint32_t>(p.region_slots)) {
+      if (p.debug_checks && pos >= slot_limit) {
         if (lane == 0)
-          report_failure(p.status, kSlotOverflow, kPhaseDispatchPayload, dst, p.region_slots, pos,
+          report_failure(p.status, kSlotOverflow, kPhaseDispatchPayload, dst, slot_limit, pos,
                          p.rank);
         continue;
       }
-      if (lane == 0) atomicAdd(&sm.sent[dst], 1u);
+      if (lane == 0) {
+        atomicAdd(&sm.sent[dst], 1u);
+        if (packed) atomicAdd(&sm.hist[e], 1u);
+      }
     }
 
-    uint8_t* slot = p.peer[dst] + p.off_disp_stage +
-                    (static_cast<size_t>(p.rank) * p.region_slots + pos) * p.slot_bytes;
+    uint8_t* slot = p.peer[dst] + p.off_disp_stage + (region_first + pos) * p.slot_bytes;
     const uint8_t* src = a.x + static_cast<int64_t>(i) * a.x_stride_row;
     const int v0 = (c * nvec) / split;
     const int v1 = ((c + 1) * nvec) / split;
@@ -245,15 +295,32 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
         t.x = i;
         t.y = k;
         t.z = le;
-        t.w = 0;
+        t.w = p.rank;
         ptx::st_v4(slot + p.trailer_off, t);
       }
     }
   }
   trace(p, kTrDispatchStored);
   __syncthreads();
-  if (tid < p.world && sm.sent[tid] > 0) {
-    ptx::red_add_release_sys(arrived_ptr(p, tid, parity, p.rank), sm.sent[tid]);
+  if (!packed) {
+    if (tid < p.world && sm.sent[tid] > 0) {
+      ptx::red_add_release_sys(arrived_ptr(p, tid, parity, p.rank), sm.sent[tid]);
+    }
+  } else if (warp == 0) {
+    // One fence for the block, then one relaxed add per expert that got rows.
+    bool any = false;
+    for (int d = lane; d < p.world; d += 32) any |= sm.sent[d] > 0;
+    if (__any_sync(0xffffffffu, any)) {
+      ptx::fence_acq_rel_sys();
+      for (int e = lane; e < E; e += 32) {
+        const uint32_t n = sm.hist[e];
+        if (n == 0) continue;
+        const int dst = e / p.nle;
+        const int le = e - dst * p.nle;
+        ptx::red_add_relaxed_sys(
+            reinterpret_cast<uint32_t*>(p.peer[dst] + p.off_arrived_e) + parity * p.nle + le, n);
+      }
+    }
   }
   trace(p, kTrDispatchSignalled);
 }
@@ -414,7 +481,7 @@ __global__ void __launch_bounds__(kDispatchThreads, 1)
 
 size_t dispatch_smem_bytes(const A2AParams& p) {
   const size_t E = p.num_experts, P = static_cast<size_t>(p.world) * p.nle;
-  return sizeof(uint32_t) * (3 * E + (P + 1) + P + kMaxWorld + kScanTmpWords + kRowCap);
+  return sizeof(uint32_t) * (4 * E + (P + 1) + P + kMaxWorld + kScanTmpWords + kRowCap);
 }
 
 int dispatch_threads() { return kDispatchThreads; }

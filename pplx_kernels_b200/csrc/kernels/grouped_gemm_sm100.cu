@@ -26,11 +26,11 @@
 // kernels of the fused MoE layer:
 //
 //   kFromStaging   the A operand is read by TMA straight out of the dispatch
-//                  staging arena that PEERS fill with P2P stores.  Groups are
-//                  (source rank, local expert) chunks; the producer warp waits on
-//                  the source's arrival counter (ld.acquire.sys, then
-//                  fence.proxy.async) before the first tile of that source, so the
-//                  expert GEMM starts tile by tile as tokens land and the
+//                  staging arena that PEERS fill with P2P stores (packed send:
+//                  rows grouped by local expert, dense).  The producer warp waits
+//                  on the expert's arrival counter (ld.acquire.sys, then
+//                  fence.proxy.async) before the expert's first tile, so the
+//                  expert GEMM starts expert by expert as tokens land and the
 //                  receive-side copy of dispatch disappears.  The epilogue also
 //                  records (source, token, k) of every row for combine.
 //   kToPeers       the epilogue does not write a local result: every output row
@@ -51,6 +51,7 @@
 #include "../core/tcgen05.cuh"
 #include "../core/utils.h"
 #include "../core/wait.cuh"
+#include "a2a_device.cuh"
 #include "grouped_gemm.h"
 
 namespace pplx {
@@ -79,13 +80,13 @@ struct SharedControl {
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t pad[2];
-  uint32_t src_total[kMaxWorld];   // kFromStaging: rows each source sends to this rank
   uint32_t sig_token[2][kBlockM];  // kToPeers: token of each tile row, per accumulator
   uint32_t sig_group[2][kBlockM];  //           first rank of the token's DP group
 };
 
-// Rows of A that share a weight matrix and an output base.  In the plain kernel a
-// group is an expert; with kFromStaging it is one (source rank, local expert) chunk.
+// Rows of A that share a weight matrix: one group per local expert.  With
+// kFromStaging the rows of all experts sit back to back in one plane of A and
+// a_row0 is the expert's first row there.
 struct GroupTable {
   uint32_t* tile_start;  // [G + 1] first tile of each group
   uint32_t* rows;        // [G] valid rows
@@ -118,16 +119,10 @@ __device__ __forceinline__ TileCoord locate_tile(const GroupTable& gt, int num_g
   c.m_blk = static_cast<int>(rem - static_cast<uint32_t>(c.n_blk) * m_tiles);
   c.a_row0 = static_cast<int>(gt.a_row0[c.group]);
   c.out_row0 = static_cast<int>(gt.out_row0[c.group]);
-  if constexpr (kFromStaging) {
-    const int s_rot = c.group / p.nle;
-    c.w_plane = c.group - s_rot * p.nle;
-    c.src = (p.rank + s_rot) % p.world;
-    c.a_plane = c.src;
-  } else {
-    c.w_plane = c.group;
-    c.a_plane = c.group;
-    c.src = -1;
-  }
+  c.w_plane = c.group;
+  c.a_plane = kFromStaging ? 0 : c.group;
+  c.src = -1;
+  (void)p;
   return c;
 }
 
@@ -149,7 +144,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   SharedControl* ctl = reinterpret_cast<SharedControl*>(stages + kStages * kStageBytes);
   const A2AParams& p = g.a2a;
-  const int num_groups = kFromStaging ? p.world * p.nle : g.num_experts;
+  const int num_groups = g.num_experts;
   GroupTable gt;
   gt.tile_start = reinterpret_cast<uint32_t*>(ctl + 1);  // [G + 1]
   gt.rows = gt.tile_start + num_groups + 1;
@@ -173,46 +168,35 @@ __global__ void __launch_bounds__(kThreads, 1)
   if constexpr (kFromStaging) {
     // Role of the dispatch receive phase: learn how many rows every source sends
     // to every local expert, lay the rows out, publish the per-expert totals.
+    for (int le = tid; le < num_groups; le += blockDim.x) gt.rows[le] = 0;
     __syncthreads();
     const WaitCtx w{p.status, p.timeout_ns, static_cast<uint32_t>(p.rank)};
-    const uint32_t* counts = reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.off_counts) +
-                             a2a_counts_index(p, parity, 0, 0);
-    for (int q = tid; q < num_groups; q += blockDim.x) {
-      const int s_rot = q / p.nle;
-      const int le = q - s_rot * p.nle;
-      const int src = (p.rank + s_rot) % p.world;
+    const uint32_t* all = reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.off_counts_all) +
+                          static_cast<size_t>(parity) * p.world * p.num_experts;
+    for (int idx = tid; idx < p.world * p.nle; idx += blockDim.x) {
+      const int src = idx / p.nle;
+      const int le = idx - src * p.nle;
       uint32_t v = 0;
-      const bool ok = wait_until(counts + src * p.nle + le, PredNonZero{}, v, w,
-                                 kPhaseDispatchCounts, src, 1u);
+      const bool ok = wait_until(all + static_cast<size_t>(src) * p.num_experts + p.rank * p.nle + le,
+                                 PredNonZero{}, v, w, kPhaseDispatchCounts, src, 1u);
       if (!ok) ctl->abort_flag = 1;
-      gt.rows[q] = ok ? min(v - 1u, static_cast<uint32_t>(p.region_slots)) : 0u;
+      if (ok && v > 1u) atomicAdd(&gt.rows[le], v - 1u);
     }
     __syncthreads();
-    for (int q = tid; q < num_groups; q += blockDim.x) {
-      const int s_rot = q / p.nle;
-      const int le = q - s_rot * p.nle;
-      uint32_t in_region = 0, in_output = 0;
-      for (int l2 = 0; l2 < le; ++l2) in_region += gt.rows[s_rot * p.nle + l2];
-      for (int r2 = 0; r2 < s_rot; ++r2) in_output += gt.rows[r2 * p.nle + le];
-      gt.a_row0[q] = in_region;
-      gt.out_row0[q] = in_output;
-      gt.tile_start[q] =
-          static_cast<uint32_t>(ceil_div<int>(static_cast<int>(gt.rows[q]), kBlockM) * n_blocks);
-    }
-    if (tid < p.world) {
-      uint32_t total = 0;
-      const int s_rot = tid;
-      for (int le = 0; le < p.nle; ++le) total += gt.rows[s_rot * p.nle + le];
-      ctl->src_total[(p.rank + s_rot) % p.world] = total;
-    }
-    if (blockIdx.x == 0) {
-      for (int le = tid; le < p.nle; le += blockDim.x) {
-        uint32_t total = 0;
-        for (int r2 = 0; r2 < p.world; ++r2) total += gt.rows[r2 * p.nle + le];
-        if (g.out_num_tokens != nullptr) g.out_num_tokens[le] = static_cast<int32_t>(total);
-        p.recv_count[le] = min(total, static_cast<uint32_t>(p.cap));
+    for (int le = tid; le < num_groups; le += blockDim.x) {
+      uint32_t first = 0;
+      for (int l2 = 0; l2 < le; ++l2) first += gt.rows[l2];
+      gt.a_row0[le] = first;
+      gt.out_row0[le] = 0;
+      const uint32_t rows = min(gt.rows[le], static_cast<uint32_t>(p.cap));
+      gt.tile_start[le] = static_cast<uint32_t>(ceil_div<int>(static_cast<int>(rows), kBlockM) * n_blocks);
+      if (blockIdx.x == 0) {
+        if (g.out_num_tokens != nullptr) g.out_num_tokens[le] = static_cast<int32_t>(gt.rows[le]);
+        p.recv_count[le] = rows;
       }
     }
+    __syncthreads();
+    for (int le = tid; le < num_groups; le += blockDim.x) gt.rows[le] = min(gt.rows[le], static_cast<uint32_t>(p.cap));
   } else {
     for (int e = tid; e < num_groups; e += blockDim.x) {
       const int rows = min(max(g.counts[e], 0), g.rows_per_expert);
@@ -232,6 +216,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           reinterpret_cast<uint32_t*>(p.peer[p.rank] + p.off_arrived) + parity * p.world;
       for (int q = tid; q < p.world * p.nle; q += blockDim.x) counts[q] = 0;
       if (tid < p.world) arrived[tid] = 0;
+      reset_packed_flags(p, parity);
       __syncthreads();
       if (tid == 0) *p.iter = *p.iter + 1u;
     }
@@ -268,27 +253,27 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t pending = 0;        // stages that have been filled at least once
       uint32_t pending_phase = 0;  // parity of the phase each stage was last filled in
       bool ok = *abort_flag == 0u;
-      uint32_t acquired = 0;  // sources whose rows are known to have landed
+      int last_group = -1;  // expert whose rows are known to have landed
       for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         const TileCoord c = locate_tile<kFromStaging>(gt, num_groups, p, t);
         if constexpr (kFromStaging) {
-          if (!((acquired >> c.src) & 1u)) {
-            // The tile's rows were stored by a peer: wait for that source's arrival
-            // counter, then order the peer's (generic-proxy) stores before the TMA
+          if (c.group != last_group) {
+            // The expert's rows were stored by peers: wait for its arrival counter,
+            // then order the peers' (generic-proxy) stores before the TMA
             // (async-proxy) reads that follow.
             const WaitCtx w{p.status, p.timeout_ns, static_cast<uint32_t>(p.rank)};
-            const uint32_t* arrived = reinterpret_cast<const uint32_t*>(
-                                          p.peer[p.rank] + p.off_arrived) +
-                                      parity * p.world + c.src;
+            const uint32_t* arrived =
+                reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.off_arrived_e) +
+                parity * p.nle + c.group;
             uint32_t seen;
-            ok = wait_until(arrived, PredGe{ctl->src_total[c.src]}, seen, w, kPhaseFusedGemm,
-                            c.src, ctl->src_total[c.src]);
+            ok = wait_until(arrived, PredGe{static_cast<uint32_t>(c.rows)}, seen, w,
+                            kPhaseFusedGemm, c.group, c.rows);
             if (!ok) {
               *abort_flag = 1u;
               break;
             }
             ptx::fence_proxy_async();
-            acquired |= 1u << c.src;
+            last_group = c.group;
           }
         }
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -420,11 +405,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         // First column block of a row also records where the row came from.
         if (row_ok && c.n_blk == 0) {
           const uint8_t* slot = p.peer[p.rank] + p.off_disp_stage +
-                                (static_cast<size_t>(c.src) * p.region_slots + c.a_row0 + row) *
-                                    p.slot_bytes;
+                                static_cast<size_t>(c.a_row0 + row) * p.slot_bytes;
           const int4 tr = ptx::ld_cg_v4(slot + p.trailer_off);
           uint2 rs;
-          rs.x = static_cast<uint32_t>(c.src) | (static_cast<uint32_t>(tr.y) << 16);
+          rs.x = (static_cast<uint32_t>(tr.w) & 0xffffu) | (static_cast<uint32_t>(tr.y) << 16);
           rs.y = static_cast<uint32_t>(tr.x);
           p.row_src[static_cast<size_t>(c.w_plane) * p.cap + out_row] = rs;
         }
@@ -617,20 +601,20 @@ void launch_gemm_from_staging(const GroupedGemmCall& c, const A2AParams& p,
              "the staging-fed GEMM needs a bf16 dispatch payload without scales");
   PPLX_CHECK(c.k == p.hidden_dim && c.num_experts == p.nle && c.rows_per_expert >= p.cap,
              "shape mismatch between the GEMM and the all-to-all");
-  PPLX_CHECK(p.world * p.nle <= kMaxExperts && p.world <= kMaxWorld, "too many groups");
   PPLX_CHECK(reinterpret_cast<uintptr_t>(c.out) % 16 == 0 && c.out_stride_row % 8 == 0 &&
                  c.out_stride_e % 8 == 0,
              "the output must be 16-byte aligned");
-  // A: [world][region_slots][hidden] bf16 view of this rank's staging regions.
-  const CUtensorMap tmap_a = make_operand_map(
-      p.peer[p.rank] + p.off_disp_stage, p.world, p.region_slots, p.hidden_dim, p.slot_bytes / 2,
-      static_cast<int64_t>(p.region_slots) * p.slot_bytes / 2);
+  // A: [1][world * region_slots][hidden] bf16 view of this rank's packed staging.
+  const int64_t slots = static_cast<int64_t>(p.world) * p.region_slots;
+  const CUtensorMap tmap_a = make_operand_map(p.peer[p.rank] + p.off_disp_stage, 1, slots,
+                                              p.hidden_dim, p.slot_bytes / 2,
+                                              slots * p.slot_bytes / 2);
   const CUtensorMap tmap_b = weight_map(c);
   GroupedGemmArgs g = base_args(c);
   g.out_num_tokens = out_num_tokens;
   g.a2a = p;
   const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
-  launch_variant<true, true, false>(tmap_a, tmap_b, g, p.world * p.nle, grid, stream);
+  launch_variant<true, true, false>(tmap_a, tmap_b, g, p.nle, grid, stream);
 }
 
 void launch_gemm_to_peers(const GroupedGemmCall& c, const A2AParams& p, cudaStream_t stream) {

@@ -101,6 +101,10 @@ A2AParams make_layout(const A2AConfig& c) {
   off = align256(off + sizeof(uint32_t) * 2 * p.world);
   p.off_comb_arrived = off;
   off = align256(off + sizeof(uint32_t) * p.max_tokens);
+  p.off_counts_all = off;
+  off = align256(off + sizeof(uint32_t) * 2 * p.world * p.num_experts);
+  p.off_arrived_e = off;
+  off = align256(off + sizeof(uint32_t) * 2 * p.nle);
   p.off_disp_stage = off;
   off = align256(off + static_cast<size_t>(p.world) * p.region_slots * p.slot_bytes);
   p.off_comb_stage = off;
@@ -265,6 +269,64 @@ CombineArgs AllToAll::make_combine_args(const CombineCall& c) const {
   return a;
 }
 
+namespace {
+
+template <typename Args>
+struct StagedArgs {
+  Args* dev = nullptr;
+  explicit StagedArgs(const std::vector<Args>& host) {
+    CUDA_CHECK(cudaMalloc(&dev, host.size() * sizeof(Args)));
+    CUDA_CHECK(cudaMemcpy(dev, host.data(), host.size() * sizeof(Args), cudaMemcpyHostToDevice));
+  }
+  ~StagedArgs() { cudaFree(dev); }
+};
+
+}  // namespace
+
+void AllToAll::dispatch_send_packed(const DispatchCall& call, cudaStream_t stream) {
+  NvtxRange range("dispatch_send_packed");
+  const DispatchArgs a = make_packed_send_args(call);
+  CUDA_CHECK(launch_dispatch(a, true, false, dispatch_grid(call.num_tokens), stream));
+}
+
+DispatchArgs AllToAll::make_packed_send_args(const DispatchCall& c) const {
+  const A2AParams& p = params_;
+  PPLX_CHECK(c.x.data != nullptr && c.indices != nullptr, "packed dispatch: missing tensor");
+  PPLX_CHECK(p.scale_bytes == 0, "packed dispatch carries no scales");
+  PPLX_CHECK(c.num_tokens >= 0 && c.num_tokens <= p.max_tokens,
+             "dispatch: " << c.num_tokens << " tokens exceed max_num_tokens " << p.max_tokens);
+  PPLX_CHECK(reinterpret_cast<uintptr_t>(c.x.data) % 16 == 0 && c.x.stride_row % 16 == 0,
+             "dispatch: token buffers must be 16-byte aligned");
+  PPLX_CHECK(static_cast<size_t>(p.world) * p.num_experts <= 16384,
+             "packed dispatch supports world_size * num_experts up to 16384");
+  DispatchArgs a{};
+  a.p = p;
+  a.x = c.x.data;
+  a.x_stride_row = c.x.stride_row;
+  a.indices = c.indices;
+  a.bound_m = c.bound_m;
+  a.num_tokens = c.num_tokens;
+  a.packed = 1;
+  return a;
+}
+
+void AllToAll::dispatch_send_packed_group(const std::vector<AllToAll*>& ranks,
+                                          const std::vector<DispatchCall>& calls,
+                                          cudaStream_t stream) {
+  PPLX_CHECK(!ranks.empty() && ranks.size() == calls.size(), "dispatch group: size mismatch");
+  std::vector<DispatchArgs> args;
+  int max_tokens = 0;
+  for (size_t r = 0; r < ranks.size(); ++r) {
+    args.push_back(ranks[r]->make_packed_send_args(calls[r]));
+    max_tokens = std::max(max_tokens, calls[r].num_tokens);
+  }
+  const int n = static_cast<int>(ranks.size());
+  const int grid = std::min(ranks[0]->dispatch_grid(max_tokens), std::max(1, ranks[0]->num_sms_ / n));
+  StagedArgs<DispatchArgs> staged(args);
+  CUDA_CHECK(launch_dispatch_multi(staged.dev, n, ranks[0]->params_, true, false, grid, stream));
+  CUDA_CHECK(cudaStreamSynchronize(stream));
+}
+
 void AllToAll::dispatch(const DispatchCall& call, SplitMode mode, cudaStream_t stream) {
   NvtxRange range("dispatch");
   const DispatchArgs a = make_dispatch_args(call);
@@ -319,19 +381,6 @@ void AllToAll::fused_down(const FusedFfnCall& f, cudaStream_t stream) {
   launch_gemm_to_peers(c, params_, stream);
 }
 
-namespace {
-
-template <typename Args>
-struct StagedArgs {
-  Args* dev = nullptr;
-  explicit StagedArgs(const std::vector<Args>& host) {
-    CUDA_CHECK(cudaMalloc(&dev, host.size() * sizeof(Args)));
-    CUDA_CHECK(cudaMemcpy(dev, host.data(), host.size() * sizeof(Args), cudaMemcpyHostToDevice));
-  }
-  ~StagedArgs() { cudaFree(dev); }
-};
-
-}  // namespace
 
 void AllToAll::dispatch_group(const std::vector<AllToAll*>& ranks,
                               const std::vector<DispatchCall>& calls, SplitMode mode,

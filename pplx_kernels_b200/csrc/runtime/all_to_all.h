@@ -109,7 +109,16 @@ class AllToAll {
   void dispatch(const DispatchCall& call, SplitMode mode, cudaStream_t stream);
   void combine(const CombineCall& call, SplitMode mode, cudaStream_t stream);
 
-  // Fused MoE path: dispatch(kSend), fused_up, fused_down, combine(kRecv).
+  // Send half of the two-hop "packed" dispatch (bf16 payload, no scales): rows land
+  // in the destination's staging grouped by local expert, ready for fused_up.  Only
+  // x, indices, bound_m and num_tokens of the call are used.
+  void dispatch_send_packed(const DispatchCall& call, cudaStream_t stream);
+  static void dispatch_send_packed_group(const std::vector<AllToAll*>& ranks,
+                                         const std::vector<DispatchCall>& calls,
+                                         cudaStream_t stream);
+  DispatchArgs make_packed_send_args(const DispatchCall& call) const;
+
+  // Fused MoE path: dispatch_send_packed, fused_up, fused_down, combine(kRecv).
   // fused_up takes the place of the dispatch receive phase (the tcgen05 GEMM reads
   // the staging arena as peers fill it), fused_down that of the combine send phase
   // (the GEMM epilogue stores to the tokens' home ranks).

@@ -69,8 +69,8 @@ class MoELayer:
                 fused: bool = True) -> torch.Tensor:
         """x: [m, hidden] bf16; indices: [m, top-k] uint32; weights: [m, top-k] fp32.
 
-        ``fused=True`` runs four kernels: dispatch send, the up projection fed from the
-        staging arena as tokens land, the down projection whose epilogue stores to the
+        ``fused=True`` runs four kernels: the packed dispatch send, the up projection fed
+        from the staging arena as tokens land, the down projection whose epilogue stores to the
         tokens' home ranks, and the combine reduction.  ``fused=False`` runs the plain
         composition dispatch -> GEMM -> GEMM -> combine (six phases, two more passes over
         the activations).
@@ -79,8 +79,7 @@ class MoELayer:
             out = torch.empty(self.max_num_tokens, self.cfg.hidden_dim, dtype=torch.bfloat16,
                               device=self.device)
         if fused:
-            self.ata.dispatch(self.counts, self.expert_x, None, x, None, indices, bound_m,
-                              do_send=True, do_recv=False)
+            self.ata.fused_dispatch(x, indices, bound_m)
             self.ata.fused_up(self.w13, self.h, self.counts, self.gemm_status)
             self.ata.fused_down(self.h, self.w2, self.gemm_status)
             self.ata.combine(out, indices, weights, self.expert_y, bound_m,

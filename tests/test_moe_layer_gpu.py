@@ -90,9 +90,7 @@ def test_fused_layer_in_an_emulated_world(world, dp_size):
     for _ in range(3):  # several rounds on the same objects
         for o in outs:
             o.fill_(float("nan"))
-        pk.dispatch_group(atas, [l.counts for l in layers], [l.expert_x for l in layers],
-                          [None] * world, [d[0] for d in per_rank], [None] * world, idx_dev,
-                          [None] * world, do_send=True, do_recv=False)
+        pk.fused_dispatch_group(atas, [d[0] for d in per_rank], idx_dev, [None] * world)
         for l in layers:
             l.ata.fused_up(l.w13, l.h, l.counts, l.gemm_status)
         for l in layers:
