@@ -163,12 +163,12 @@ class AllToAll:
 
     def fused_up(self, w13: torch.Tensor, h: torch.Tensor,
                  out_expert_num_tokens: torch.Tensor | None = None,
-                 status: torch.Tensor | None = None) -> None:
+                 status: torch.Tensor | None = None, expected_rows: int = 0) -> None:
         """SwiGLU up projection that reads the dispatch staging arena as peers fill it.
 
         Call after ``fused_dispatch``; it replaces the receive half of dispatch.  ``h[le, :n] = silu(x @ gate.T) * (x @ up.T)`` for the rows of local expert le.
         """
-        _ops.moe_fused_up(self._ptr, w13, h, out_expert_num_tokens, status)
+        _ops.moe_fused_up(self._ptr, w13, h, out_expert_num_tokens, status, expected_rows)
 
     def fused_down(self, h: torch.Tensor, w2: torch.Tensor,
                    status: torch.Tensor | None = None) -> None:

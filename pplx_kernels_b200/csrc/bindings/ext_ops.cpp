@@ -13,7 +13,8 @@ namespace {
 
 // out[e, :counts[e]] = act(x[e, :counts[e]] @ w[e]^T), bf16 in / bf16 out.
 void grouped_gemm_op(const at::Tensor& x, const at::Tensor& w, const at::Tensor& counts,
-                     at::Tensor& out, bool swiglu, const std::optional<at::Tensor>& status) {
+                     at::Tensor& out, bool swiglu, const std::optional<at::Tensor>& status,
+                     int64_t expected_rows, int64_t half_n) {
   TORCH_CHECK(x.is_cuda() && w.is_cuda() && counts.is_cuda() && out.is_cuda(),
               "grouped_gemm: all tensors must be CUDA tensors");
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 &&
@@ -53,6 +54,8 @@ void grouped_gemm_op(const at::Tensor& x, const at::Tensor& w, const at::Tensor&
   c.n_out = static_cast<int>(n_out);
   c.k = static_cast<int>(K);
   c.swiglu = swiglu;
+  c.expected_total_rows = expected_rows;
+  c.half_n = static_cast<int>(half_n);
   try {
     launch_grouped_gemm(c, at::cuda::getCurrentCUDAStream());
   } catch (const Error& e) {
@@ -61,13 +64,13 @@ void grouped_gemm_op(const at::Tensor& x, const at::Tensor& w, const at::Tensor&
 }
 
 void fake_grouped_gemm(const at::Tensor&, const at::Tensor&, const at::Tensor&, at::Tensor&, bool,
-                       const std::optional<at::Tensor>&) {}
+                       const std::optional<at::Tensor>&, int64_t, int64_t) {}
 
 }  // namespace
 
 void register_extension_ops(torch::Library& m) {
   m.def("grouped_gemm(Tensor x, Tensor w, Tensor counts, Tensor! out, bool swiglu, "
-        "Tensor!? status) -> ()");
+        "Tensor!? status, int expected_rows=0, int half_n=0) -> ()");
   m.impl("grouped_gemm", c10::kCUDA, &grouped_gemm_op);
   m.impl("grouped_gemm", c10::kMeta, &fake_grouped_gemm);
 }

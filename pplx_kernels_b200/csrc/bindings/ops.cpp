@@ -464,7 +464,7 @@ void moe_dispatch_send_group_op(std::vector<int64_t> ptrs, std::vector<at::Tenso
 // SwiGLU up projection fed from the dispatch staging arena (after dispatch with do_recv=False).
 void moe_fused_up_op(int64_t ptr, const at::Tensor& w13, at::Tensor& h,
                      const std::optional<at::Tensor>& out_expert_num_tokens,
-                     const std::optional<at::Tensor>& status) {
+                     const std::optional<at::Tensor>& status, int64_t expected_rows) {
   AllToAll* ata = lookup(ptr);
   check_bf16_3d(w13, "w13");
   check_bf16_3d(h, "h");
@@ -488,6 +488,7 @@ void moe_fused_up_op(int64_t ptr, const at::Tensor& w13, at::Tensor& h,
     f.out_num_tokens = out_expert_num_tokens->data_ptr<int32_t>();
   }
   f.status = status_word(status);
+  f.expected_total_rows = expected_rows;
   const c10::cuda::OptionalCUDAGuard guard(h.device());
   guarded([&] { ata->fused_up(f, at::cuda::getCurrentCUDAStream()); });
 }
@@ -517,7 +518,7 @@ void moe_fused_down_op(int64_t ptr, const at::Tensor& h, const at::Tensor& w2,
 }
 
 void fake_moe_fused_up(int64_t, const at::Tensor&, at::Tensor&, const std::optional<at::Tensor>&,
-                       const std::optional<at::Tensor>&) {}
+                       const std::optional<at::Tensor>&, int64_t) {}
 void fake_moe_fused_down(int64_t, const at::Tensor&, const at::Tensor&,
                          const std::optional<at::Tensor>&) {}
 
@@ -713,7 +714,7 @@ void register_all_to_all_ops(torch::Library& m) {
         "Tensor[] bound_m) -> ()",
         &moe_dispatch_send_group_op);
   m.def("moe_fused_up(int ptr, Tensor w13, Tensor! h, Tensor!? out_expert_num_tokens, "
-        "Tensor!? status) -> ()");
+        "Tensor!? status, int expected_rows=0) -> ()");
   m.impl("moe_fused_up", c10::kCUDA, &moe_fused_up_op);
   m.impl("moe_fused_up", c10::kMeta, &fake_moe_fused_up);
   m.def("moe_fused_down(int ptr, Tensor h, Tensor w2, Tensor!? status) -> ()");

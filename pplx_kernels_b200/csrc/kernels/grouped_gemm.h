@@ -22,6 +22,7 @@ struct GroupedGemmArgs {
   int rows_per_expert;     // capacity of x / out per expert
   int n_out;               // output columns (the intermediate size for SwiGLU)
   int k;
+  int half_n;              // weight rows per B half; the tile is 2 * half_n columns wide
   // Only read by the kernels fused with the all-to-all:
   int32_t* out_num_tokens;          // optional [nle]: per-expert totals for the caller
   uint32_t arrival_units_per_tile;  // units added to a token's counter per column block
@@ -48,6 +49,8 @@ struct GroupedGemmCall {
   int k = 0;
   bool swiglu = false;
   int num_sms = 0;           // 0 = all
+  int half_n = 0;            // 0 = choose; else weight rows per B half (multiple of 8, 64..128)
+  int64_t expected_total_rows = 0;  // hint for the tile-width choice; 0 = capacity
 };
 
 // out[e, :counts[e]] = act(x[e, :counts[e]] @ w[e]^T); rows beyond counts[e] are untouched.

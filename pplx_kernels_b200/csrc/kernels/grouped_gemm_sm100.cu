@@ -42,6 +42,8 @@
 // Every mbarrier wait is bounded: when one runs out the CTA raises a shared
 // abort flag, all roles leave their loops, in-flight TMA loads are drained,
 // tensor memory is freed and the kernel returns with *status = 1.
+#include <algorithm>
+
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -156,8 +158,13 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int lane = tid & 31;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
 
-  // Output columns per tile and number of column blocks.
-  const int out_cols_per_tile = SWIGLU ? kBlockN / 2 : kBlockN;
+  // The B tile is two halves of g.half_n weight rows each (gate and up rows for
+  // SwiGLU, consecutive rows otherwise); the accumulator is 2 * half_n columns wide.
+  const int half_n = g.half_n;
+  const int tile_n = 2 * half_n;
+  const uint32_t b_half_bytes = static_cast<uint32_t>(half_n) * kBlockK * 2;
+  const uint32_t stage_tx_bytes = kABytes + 2 * b_half_bytes;
+  const int out_cols_per_tile = SWIGLU ? half_n : tile_n;
   const int n_blocks = ceil_div<int>(g.n_out, out_cols_per_tile);
   const int num_kb = ceil_div<int>(g.k, kBlockK);
 
@@ -281,21 +288,21 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (!ok) break;
           uint8_t* a_dst = stages + stage * kStageBytes;
           uint8_t* b_dst = a_dst + kABytes;
-          tc::mbar_arrive_expect_tx(&ctl->full[stage], kStageBytes);
+          tc::mbar_arrive_expect_tx(&ctl->full[stage], stage_tx_bytes);
           pending |= 1u << stage;
           pending_phase = (pending_phase & ~(1u << stage)) | (phase << stage);
           tc::tma_load_3d(a_dst, &tmap_a, &ctl->full[stage], kb * kBlockK,
                           c.a_row0 + c.m_blk * kBlockM, c.a_plane);
           if constexpr (SWIGLU) {
-            const int row = c.n_blk * (kBlockN / 2);
+            const int row = c.n_blk * half_n;
             tc::tma_load_3d(b_dst, &tmap_b, &ctl->full[stage], kb * kBlockK, row, c.w_plane);
-            tc::tma_load_3d(b_dst + kBBytes / 2, &tmap_b, &ctl->full[stage], kb * kBlockK,
+            tc::tma_load_3d(b_dst + b_half_bytes, &tmap_b, &ctl->full[stage], kb * kBlockK,
                             g.n_out + row, c.w_plane);
           } else {
-            const int row = c.n_blk * kBlockN;
+            const int row = c.n_blk * tile_n;
             tc::tma_load_3d(b_dst, &tmap_b, &ctl->full[stage], kb * kBlockK, row, c.w_plane);
-            tc::tma_load_3d(b_dst + kBBytes / 2, &tmap_b, &ctl->full[stage], kb * kBlockK,
-                            row + kBlockN / 2, c.w_plane);
+            tc::tma_load_3d(b_dst + b_half_bytes, &tmap_b, &ctl->full[stage], kb * kBlockK,
+                            row + half_n, c.w_plane);
           }
           if (++stage == kStages) {
             stage = 0;
@@ -321,7 +328,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     __syncwarp();
   } else if (warp == 1) {
     if (tc::elect_one()) {
-      const uint32_t idesc = tc::make_instr_desc(1u, kBlockM, kBlockN);
+      const uint32_t idesc = tc::make_instr_desc(1u, kBlockM, tile_n);
       uint32_t stage = 0, phase = 0;
       uint32_t local = 0;
       bool ok = *abort_flag == 0u;
@@ -417,13 +424,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + buf * kBlockN;
       const int col0 = c.n_blk * out_cols_per_tile;
 #pragma unroll 1
-      for (int chunk = 0; chunk < out_cols_per_tile / 32; ++chunk) {
+      for (int chunk = 0; chunk * 32 < out_cols_per_tile; ++chunk) {
         uint32_t acc[32];
         uint32_t packed[16];
         tc::tmem_ld_32x32(taddr + chunk * 32, acc);
         if constexpr (SWIGLU) {
           uint32_t up[32];
-          tc::tmem_ld_32x32(taddr + kBlockN / 2 + chunk * 32, up);
+          tc::tmem_ld_32x32(taddr + half_n + chunk * 32, up);
           tc::tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
@@ -441,7 +448,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int col = col0 + chunk * 32;
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
-          if (col + v * 8 + 8 > g.n_out) continue;
+          if (chunk * 32 + v * 8 + 8 > out_cols_per_tile || col + v * 8 + 8 > g.n_out) continue;
           int4 q;
           q.x = packed[4 * v];
           q.y = packed[4 * v + 1];
@@ -516,7 +523,8 @@ EncodeTiledFn encode_tiled() {
 // [experts, rows, k] bf16 with k contiguous; tiles of 64 x 128 x 1, 128-byte swizzle,
 // out-of-range elements read as zero.
 CUtensorMap make_operand_map(const void* base, int64_t experts, int64_t rows, int64_t k,
-                             int64_t stride_row_elems, int64_t stride_expert_elems) {
+                             int64_t stride_row_elems, int64_t stride_expert_elems,
+                             int box_rows = 128) {
   PPLX_CHECK(reinterpret_cast<uintptr_t>(base) % 16 == 0, "operand base must be 16-byte aligned");
   PPLX_CHECK((stride_row_elems * 2) % 16 == 0 && (stride_expert_elems * 2) % 16 == 0,
              "operand strides must be multiples of 16 bytes (8 bf16 elements)");
@@ -525,7 +533,7 @@ CUtensorMap make_operand_map(const void* base, int64_t experts, int64_t rows, in
                               static_cast<cuuint64_t>(experts)};
   const cuuint64_t strides[2] = {static_cast<cuuint64_t>(stride_row_elems) * 2,
                                  static_cast<cuuint64_t>(stride_expert_elems) * 2};
-  const cuuint32_t box[3] = {kBlockK, 128, 1};
+  const cuuint32_t box[3] = {kBlockK, static_cast<cuuint32_t>(box_rows), 1};
   const cuuint32_t elem_strides[3] = {1, 1, 1};
   const CUresult r = encode_tiled()(
       &map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
@@ -554,8 +562,18 @@ void check_common(const GroupedGemmCall& c) {
   PPLX_CHECK(c.num_experts > 0 && c.num_experts <= kMaxExperts, "num_experts out of range");
   PPLX_CHECK(c.k > 0 && c.k % 8 == 0, "K must be a positive multiple of 8");
   PPLX_CHECK(c.n_out > 0 && c.n_out % 8 == 0, "the output width must be a positive multiple of 8");
-  PPLX_CHECK(!c.swiglu || c.n_out % (kBlockN / 2) == 0,
-             "SwiGLU needs an intermediate size that is a multiple of 128");
+  PPLX_CHECK(c.half_n == 0 || (c.half_n % 8 == 0 && c.half_n >= 16 && c.half_n <= 128),
+             "half_n must be a multiple of 8 in [16, 128]");
+}
+
+// Without a device round trip the host only knows the capacity; callers that know
+// better pass an estimate of the total rows.
+int64_t expected_m_tiles(const GroupedGemmCall& c) {
+  const int64_t rows = c.expected_total_rows > 0
+                           ? c.expected_total_rows
+                           : static_cast<int64_t>(c.num_experts) * c.rows_per_expert;
+  return std::max<int64_t>(c.num_experts > 0 ? 1 : 0,
+                           ceil_div<int64_t>(rows, kBlockM));
 }
 
 GroupedGemmArgs base_args(const GroupedGemmCall& c) {
@@ -572,9 +590,31 @@ GroupedGemmArgs base_args(const GroupedGemmCall& c) {
   return g;
 }
 
-CUtensorMap weight_map(const GroupedGemmCall& c) {
+CUtensorMap weight_map(const GroupedGemmCall& c, int half_n) {
   const int64_t w_rows = c.swiglu ? 2 * static_cast<int64_t>(c.n_out) : c.n_out;
-  return make_operand_map(c.w, c.num_experts, w_rows, c.k, c.w_stride_row, c.w_stride_e);
+  return make_operand_map(c.w, c.num_experts, w_rows, c.k, c.w_stride_row, c.w_stride_e, half_n);
+}
+
+// Width of one B half (multiple of 8, at most 128).  The grid runs in waves of
+// `sms` tiles; a narrower tile can fill the last wave better: minimise
+// waves * width.  `m_tiles` is the expected number of 128-row blocks over all
+// experts (the real one is only known on the device).
+int pick_half_n(int n_out, bool swiglu, int64_t m_tiles, int sms, int forced) {
+  if (forced > 0) return forced;
+  const int per_half = swiglu ? 1 : 2;  // output columns per tile = per_half * half_n
+  int best = 128;
+  double best_cost = 1e300;
+  for (int half = 128; half >= 64; half -= 8) {
+    const int64_t n_blocks = ceil_div<int64_t>(n_out, per_half * half);
+    const int64_t waves = ceil_div<int64_t>(std::max<int64_t>(1, m_tiles) * n_blocks, sms);
+    // small fixed cost per tile (pipeline fill, epilogue hand-over)
+    const double cost = static_cast<double>(waves) * (half + 4);
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = half;
+    }
+  }
+  return best;
 }
 
 }  // namespace
@@ -586,9 +626,10 @@ void launch_grouped_gemm(const GroupedGemmCall& c, cudaStream_t stream) {
              "the output must be 16-byte aligned");
   const CUtensorMap tmap_a = make_operand_map(c.x, c.num_experts, c.rows_per_expert, c.k,
                                               c.x_stride_row, c.x_stride_e);
-  const CUtensorMap tmap_b = weight_map(c);
-  const GroupedGemmArgs g = base_args(c);
   const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
+  GroupedGemmArgs g = base_args(c);
+  g.half_n = pick_half_n(c.n_out, c.swiglu, expected_m_tiles(c), grid, c.half_n);
+  const CUtensorMap tmap_b = weight_map(c, g.half_n);
   if (c.swiglu) launch_variant<true, false, false>(tmap_a, tmap_b, g, c.num_experts, grid, stream);
   else launch_variant<false, false, false>(tmap_a, tmap_b, g, c.num_experts, grid, stream);
 }
@@ -609,11 +650,12 @@ void launch_gemm_from_staging(const GroupedGemmCall& c, const A2AParams& p,
   const CUtensorMap tmap_a = make_operand_map(p.peer[p.rank] + p.off_disp_stage, 1, slots,
                                               p.hidden_dim, p.slot_bytes / 2,
                                               slots * p.slot_bytes / 2);
-  const CUtensorMap tmap_b = weight_map(c);
+  const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
   GroupedGemmArgs g = base_args(c);
+  g.half_n = pick_half_n(c.n_out, c.swiglu, expected_m_tiles(c), grid, c.half_n);
+  const CUtensorMap tmap_b = weight_map(c, g.half_n);
   g.out_num_tokens = out_num_tokens;
   g.a2a = p;
-  const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
   launch_variant<true, true, false>(tmap_a, tmap_b, g, p.nle, grid, stream);
 }
 
@@ -624,19 +666,27 @@ void launch_gemm_to_peers(const GroupedGemmCall& c, const A2AParams& p, cudaStre
              "shape mismatch between the GEMM and the all-to-all");
   PPLX_CHECK(c.counts == reinterpret_cast<const int32_t*>(p.recv_count),
              "counts must be the all-to-all's received-row counts");
-  const int n_blocks = ceil_div(c.n_out, kBlockN);
+  const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
+  // The column-block count must divide the arrival units: take the widest tile that does.
+  int half_n = 0;
+  for (int half = 128; half >= 64 && half_n == 0; half -= 8) {
+    if (p.comb_units % ceil_div(c.n_out, 2 * half) == 0) half_n = half;
+  }
+  PPLX_CHECK(half_n != 0, "combine units (" << p.comb_units
+                                            << ") match no column blocking of the output");
+  const int n_blocks = ceil_div(c.n_out, 2 * half_n);
   PPLX_CHECK(p.comb_units % n_blocks == 0,
              "combine units (" << p.comb_units << ") must be a multiple of the "
                                << n_blocks << " column blocks of the output");
   PPLX_CHECK(p.dp_size <= 8, "at most 8 replicas per DP group");
   const CUtensorMap tmap_a = make_operand_map(c.x, c.num_experts, c.rows_per_expert, c.k,
                                               c.x_stride_row, c.x_stride_e);
-  const CUtensorMap tmap_b = weight_map(c);
   GroupedGemmArgs g = base_args(c);
+  g.half_n = half_n;
+  const CUtensorMap tmap_b = weight_map(c, g.half_n);
   g.out = nullptr;
   g.arrival_units_per_tile = static_cast<uint32_t>(p.comb_units / n_blocks);
   g.a2a = p;
-  const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
   launch_variant<false, false, true>(tmap_a, tmap_b, g, c.num_experts, grid, stream);
 }
 

@@ -88,7 +88,9 @@ A2AParams make_layout(const A2AConfig& c) {
   p.hidden_bytes = c.hidden_dim_bytes;
   p.scale_bytes = c.hidden_dim_scale_bytes;
   p.trailer_off = round_up(c.hidden_dim_bytes + c.hidden_dim_scale_bytes, 16);
-  p.slot_bytes = p.trailer_off + 16;
+  // Slots start on 128-byte lines: full-line P2P writes, and TMA reads of a row
+  // (fused up projection) never straddle an extra line.
+  p.slot_bytes = round_up(p.trailer_off + 16, 128);
   const int tokens_per_sender = ceil_div(c.max_num_tokens, c.dp_size);
   p.region_slots = tokens_per_sender * std::min(c.experts_per_token, p.nle);
   p.cap = c.max_num_tokens * p.num_dp_groups;
@@ -357,6 +359,7 @@ void AllToAll::fused_up(const FusedFfnCall& f, cudaStream_t stream) {
   c.n_out = f.inter_dim;
   c.k = params_.hidden_dim;
   c.swiglu = true;
+  c.expected_total_rows = f.expected_total_rows;
   c.num_sms = max_blocks_ > 0 ? std::min(max_blocks_, num_sms_) : num_sms_;
   launch_gemm_from_staging(c, params_, f.out_num_tokens, stream);
 }

@@ -78,18 +78,21 @@ class MoELayer:
         if out is None:
             out = torch.empty(self.max_num_tokens, self.cfg.hidden_dim, dtype=torch.bfloat16,
                               device=self.device)
+        # Rows this rank expects under uniform routing: steers the GEMM tile width only.
+        expect = x.size(0) * self.cfg.experts_per_token * (self.world_size // self.dp_size) \
+            // self.world_size
         if fused:
             self.ata.fused_dispatch(x, indices, bound_m)
-            self.ata.fused_up(self.w13, self.h, self.counts, self.gemm_status)
+            self.ata.fused_up(self.w13, self.h, self.counts, self.gemm_status, expect)
             self.ata.fused_down(self.h, self.w2, self.gemm_status)
             self.ata.combine(out, indices, weights, self.expert_y, bound_m,
                              do_send=False, do_recv=True)
             return out
         self.ata.dispatch(self.counts, self.expert_x, None, x, None, indices, bound_m)
         grouped_gemm(self.expert_x, self.w13, self.counts, out=self.h, swiglu=True,
-                     status=self.gemm_status)
+                     status=self.gemm_status, expected_rows=expect)
         grouped_gemm(self.h, self.w2, self.counts, out=self.expert_y, swiglu=False,
-                     status=self.gemm_status)
+                     status=self.gemm_status, expected_rows=expect)
         self.ata.combine(out, indices, weights, self.expert_y, bound_m)
         return out
 

@@ -42,6 +42,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--half-n", type=int, default=0, help="force the B half width (0 = choose)")
     args = ap.parse_args()
     if args.shape:
         E, rows, K, N, swiglu = SHAPES[args.shape]
@@ -64,7 +65,8 @@ def main() -> None:
 
     results = {}
     for name, fn in (("ours", lambda: grouped_gemm(x, w, counts, out=out, swiglu=swiglu,
-                                                   status=status)), ("torch_matmul", lib)):
+                                                   status=status, expected_rows=E * rows,
+                                                   half_n=args.half_n)), ("torch_matmul", lib)):
         times = []
         for it in range(args.warmup + args.iters):
             if not args.no_flush:

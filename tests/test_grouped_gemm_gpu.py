@@ -8,7 +8,7 @@ from pplx_kernels_b200.ops.grouped_gemm import grouped_gemm, grouped_gemm_refere
 pytestmark = pytest.mark.gpu
 
 
-def _case(E, rows, K, N, counts, swiglu, seed=0):
+def _case(E, rows, K, N, counts, swiglu, seed=0, half_n=0):
     dev = torch.device("cuda", 0)
     g = torch.Generator(device="cpu").manual_seed(seed)
     x = (torch.randn(E, rows, K, generator=g) * 0.5).to(torch.bfloat16).to(dev)
@@ -17,7 +17,7 @@ def _case(E, rows, K, N, counts, swiglu, seed=0):
     cnt = torch.tensor(counts, dtype=torch.int32, device=dev)
     out = torch.full((E, rows, N), float("nan"), dtype=torch.bfloat16, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    grouped_gemm(x, w, cnt, out=out, swiglu=swiglu, status=status)
+    grouped_gemm(x, w, cnt, out=out, swiglu=swiglu, status=status, half_n=half_n)
     torch.cuda.synchronize()
     assert int(status.item()) == 0, "a pipeline wait ran out"
     want = grouped_gemm_reference(x, w, cnt, swiglu)
@@ -49,3 +49,10 @@ def test_long_k_wraps_the_stage_ring_many_times():
 def test_more_tiles_than_sms():
     _case(E=8, rows=512, K=256, N=1536, counts=[512, 500, 3, 512, 256, 129, 0, 512], swiglu=False,
           seed=4)
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("half_n", [64, 72, 112, 120])
+def test_narrow_tiles(swiglu, half_n):
+    # Tile widths other than 256 columns, with column tails on the last block.
+    _case(E=3, rows=256, K=320, N=448, counts=[200, 256, 17], swiglu=swiglu, seed=5, half_n=half_n)
