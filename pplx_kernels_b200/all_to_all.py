@@ -95,6 +95,30 @@ class AllToAll:
             do_recv,
         )
 
+    def dispatch_quant(
+        self,
+        out_expert_num_tokens: torch.Tensor,
+        out_expert_x: torch.Tensor,
+        out_expert_x_scale: torch.Tensor,
+        dp_x: torch.Tensor,
+        indices: torch.Tensor,
+        bound_m: torch.Tensor | None,
+        do_send: bool = True,
+        do_recv: bool = True,
+    ) -> None:
+        """Dispatch of bf16 tokens with the fp8 block quantisation fused into the send.
+
+        ``dp_x`` is ``[m, hidden]`` bfloat16; experts receive ``float8_e4m3fn`` rows in
+        ``out_expert_x`` and one fp32 scale per 128 columns in ``out_expert_x_scale``
+        (``x ~= q * scale``, ``scale = max(amax, 1e-4) / 448``).  The object must have been
+        created with ``hidden_dim_bytes = hidden`` and
+        ``hidden_dim_scale_bytes = ceil(hidden / 128) * 4``.
+        """
+        assert self._ptr is not None and self._has_scales
+        _ops.all_to_all_dispatch_quant(
+            self._ptr, out_expert_num_tokens, out_expert_x, out_expert_x_scale, dp_x, indices,
+            bound_m, do_send, do_recv)
+
     def combine(
         self,
         out_tokens: torch.Tensor,

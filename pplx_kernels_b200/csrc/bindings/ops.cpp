@@ -175,7 +175,8 @@ DispatchCall make_dispatch_call(const AllToAll& ata, at::Tensor& out_expert_num_
                                 const std::optional<at::Tensor>& out_expert_x_scale,
                                 const at::Tensor& dp_x, const std::optional<at::Tensor>& dp_x_scale,
                                 const at::Tensor& indices,
-                                const std::optional<at::Tensor>& bound_m) {
+                                const std::optional<at::Tensor>& bound_m,
+                                bool quantize = false) {
   const A2AParams& p = ata.params();
   TORCH_CHECK(out_expert_num_tokens.is_cuda() && out_expert_num_tokens.dim() == 1 &&
                   out_expert_num_tokens.scalar_type() == at::kInt &&
@@ -190,8 +191,13 @@ DispatchCall make_dispatch_call(const AllToAll& ata, at::Tensor& out_expert_num_
               "out_expert_x rows must be hidden_dim_bytes long");
   TORCH_CHECK(dp_x.is_cuda() && dp_x.dim() == 2 && dp_x.is_contiguous(),
               "dp_x must be a contiguous 2-D CUDA tensor");
-  TORCH_CHECK(dp_x.size(1) * static_cast<int64_t>(dp_x.element_size()) == p.hidden_bytes,
-              "dp_x rows must be hidden_dim_bytes long");
+  if (quantize) {
+    TORCH_CHECK(dp_x.scalar_type() == at::kBFloat16 && dp_x.size(1) == p.hidden_dim,
+                "quantising dispatch takes bfloat16 tokens of [num_tokens, hidden_dim]");
+  } else {
+    TORCH_CHECK(dp_x.size(1) * static_cast<int64_t>(dp_x.element_size()) == p.hidden_bytes,
+                "dp_x rows must be hidden_dim_bytes long");
+  }
   TORCH_CHECK(indices.is_cuda() && indices.dim() == 2 && indices.is_contiguous() &&
                   indices.element_size() == 4 && indices.size(1) == p.topk,
               "indices must be a contiguous 32-bit CUDA tensor of [num_tokens, experts_per_token]");
@@ -234,6 +240,7 @@ DispatchCall make_dispatch_call(const AllToAll& ata, at::Tensor& out_expert_num_
     c.bound_m = static_cast<const uint32_t*>(bound_m->data_ptr());
   }
   c.num_tokens = static_cast<int>(indices.size(0));
+  c.quantize = quantize;
   return c;
 }
 
@@ -301,6 +308,25 @@ void dispatch_op(int64_t ptr, at::Tensor& out_expert_num_tokens, at::Tensor& out
   });
 }
 
+// dispatch with the bf16 -> fp8 (e4m3, fp32 scale per 128 columns) conversion fused
+// into the send.  No counterpart in the reference, which never interprets the payload.
+void dispatch_quant_op(int64_t ptr, at::Tensor& out_expert_num_tokens, at::Tensor& out_expert_x,
+                       at::Tensor& out_expert_x_scale, const at::Tensor& dp_x,
+                       const at::Tensor& indices, const std::optional<at::Tensor>& bound_m,
+                       bool do_send, bool do_recv) {
+  AllToAll* ata = lookup(ptr);
+  const c10::cuda::OptionalCUDAGuard guard(dp_x.device());
+  guarded([&] {
+    const DispatchCall call =
+        make_dispatch_call(*ata, out_expert_num_tokens, out_expert_x, out_expert_x_scale, dp_x,
+                           std::nullopt, indices, bound_m, /*quantize=*/true);
+    ata->dispatch(call, split_mode(do_send, do_recv), at::cuda::getCurrentCUDAStream());
+  });
+}
+
+void fake_dispatch_quant(int64_t, at::Tensor&, at::Tensor&, at::Tensor&, const at::Tensor&,
+                         const at::Tensor&, const std::optional<at::Tensor>&, bool, bool) {}
+
 void combine_op(int64_t ptr, at::Tensor& out_tokens, const at::Tensor& indices,
                 const at::Tensor& weights, const at::Tensor& expert_y,
                 const std::optional<at::Tensor>& bound_m, bool do_send, bool do_recv) {
@@ -346,6 +372,31 @@ void dispatch_group_op(std::vector<int64_t> ptrs, std::vector<at::Tensor> out_ex
     const c10::cuda::OptionalCUDAGuard guard(dp_x[0].device());
     AllToAll::dispatch_group(ranks, calls, split_mode(do_send, do_recv),
                              at::cuda::getCurrentCUDAStream());
+  });
+}
+
+void dispatch_quant_group_op(std::vector<int64_t> ptrs,
+                             std::vector<at::Tensor> out_expert_num_tokens,
+                             std::vector<at::Tensor> out_expert_x,
+                             std::vector<at::Tensor> out_expert_x_scale,
+                             std::vector<at::Tensor> dp_x, std::vector<at::Tensor> indices,
+                             std::vector<at::Tensor> bound_m) {
+  const size_t n = ptrs.size();
+  TORCH_CHECK(n > 0 && out_expert_num_tokens.size() == n && out_expert_x.size() == n &&
+                  out_expert_x_scale.size() == n && dp_x.size() == n && indices.size() == n &&
+                  bound_m.size() == n,
+              "dispatch_quant_group: list lengths differ");
+  guarded([&] {
+    std::vector<AllToAll*> ranks;
+    std::vector<DispatchCall> calls;
+    for (size_t r = 0; r < n; ++r) {
+      ranks.push_back(lookup(ptrs[r]));
+      calls.push_back(make_dispatch_call(*ranks[r], out_expert_num_tokens[r], out_expert_x[r],
+                                         out_expert_x_scale[r], dp_x[r], std::nullopt, indices[r],
+                                         opt(bound_m[r]), /*quantize=*/true));
+    }
+    const c10::cuda::OptionalCUDAGuard guard(dp_x[0].device());
+    AllToAll::dispatch_group(ranks, calls, SplitMode::kNone, at::cuda::getCurrentCUDAStream());
   });
 }
 
@@ -691,10 +742,19 @@ void register_all_to_all_ops(torch::Library& m) {
     m.impl(c.c_str(), c10::kMeta, &fake_combine);
   }
 
+  m.def("all_to_all_dispatch_quant(int ptr, Tensor! out_expert_num_tokens, Tensor! out_expert_x, "
+        "Tensor! out_expert_x_scale, Tensor dp_x, Tensor indices, Tensor? bound_m, bool do_send, "
+        "bool do_recv) -> ()");
+  m.impl("all_to_all_dispatch_quant", c10::kCUDA, &dispatch_quant_op);
+  m.impl("all_to_all_dispatch_quant", c10::kMeta, &fake_dispatch_quant);
   m.def("all_to_all_dispatch_group(int[] ptrs, Tensor[] out_expert_num_tokens, "
         "Tensor[] out_expert_x, Tensor[] out_expert_x_scale, Tensor[] dp_x, Tensor[] dp_x_scale, "
         "Tensor[] indices, Tensor[] bound_m, bool do_send, bool do_recv) -> ()",
         &dispatch_group_op);
+  m.def("all_to_all_dispatch_quant_group(int[] ptrs, Tensor[] out_expert_num_tokens, "
+        "Tensor[] out_expert_x, Tensor[] out_expert_x_scale, Tensor[] dp_x, Tensor[] indices, "
+        "Tensor[] bound_m) -> ()",
+        &dispatch_quant_group_op);
   m.def("all_to_all_combine_group(int[] ptrs, Tensor[] out_tokens, Tensor[] indices, "
         "Tensor[] weights, Tensor[] expert_y, Tensor[] bound_m, bool do_send, bool do_recv) -> ()",
         &combine_group_op);

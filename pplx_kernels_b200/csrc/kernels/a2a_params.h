@@ -130,6 +130,8 @@ struct DispatchArgs {
   const uint32_t* indices;   // [m][topk]
   const uint32_t* bound_m;   // optional device scalar
   int num_tokens;            // indices.size(0)
+  int quantize;              // x is bf16 [m][hidden_bytes values]; the send converts it to
+                             // e4m3 + one fp32 scale per 128 columns on the fly
   int packed;                // send only: two-hop protocol, rows land at their final,
                              // expert-major position in the destination's staging
 };

@@ -33,6 +33,13 @@
 // by local expert, then by source rank -- and step 4 signals per (destination,
 // expert) instead of per destination.
 //
+// Quantising send (a.quantize): the caller's tokens are bf16 and the wire format
+// is fp8 e4m3 with one fp32 scale per 128 columns.  The warp that copies a row
+// part converts it on the fly -- amax over each 128-column block (8 lanes x 16
+// values, reduced with shuffles), scale = max(amax, 1e-4) / 448, value / scale
+// rounded to e4m3 -- so no separate quantisation kernel and no fp8 copy of the
+// activations in HBM is needed.
+//
 // Rows are split over several warps whenever there are fewer rows than warps, so
 // that a single token still moves with the whole block's memory parallelism.
 //
@@ -40,6 +47,8 @@
 // waits at all, so the kernel needs no cooperative launch.  In fused mode a
 // block may sit in a receive wait while a peer still has blocks to schedule, so
 // the host keeps the grid within what is resident at once.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
 #include "../core/device_utils.cuh"
@@ -110,6 +119,60 @@ __device__ __forceinline__ uint32_t* counts_ptr(const A2AParams& p, int dst, int
 
 __device__ __forceinline__ uint32_t* arrived_ptr(const A2AParams& p, int dst, int parity, int src) {
   return reinterpret_cast<uint32_t*>(p.peer[dst] + p.off_arrived) + parity * p.world + src;
+}
+
+// Quantises columns [16 * v0, 16 * v1) of one bf16 row to e4m3 (v = 16-value output
+// vectors; v0 is a multiple of 8 so that 128-column blocks are not split between
+// warps) and stores payload and scales into the slot.
+__device__ __forceinline__ void warp_quantize_row(uint8_t* slot, float* slot_scales,
+                                                  const __nv_bfloat16* src, int v0, int v1,
+                                                  int nvec, int lane) {
+  for (int base = v0; base < v1; base += 32) {
+    const int v = base + lane;
+    const bool live = v < v1 && v < nvec;
+    float f[16];
+    float amax = 0.f;
+    if (live) {
+      const int4 lo = ptx::ld_nc_v4(src + static_cast<size_t>(v) * 16);
+      const int4 hi = ptx::ld_nc_v4(src + static_cast<size_t>(v) * 16 + 8);
+      const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&lo);
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&hi);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 x = __bfloat1622float2(a[j]);
+        const float2 y = __bfloat1622float2(b[j]);
+        f[2 * j] = x.x;
+        f[2 * j + 1] = x.y;
+        f[8 + 2 * j] = y.x;
+        f[8 + 2 * j + 1] = y.y;
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(f[j]));
+    }
+    // 8 consecutive lanes hold one 128-column block.
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+    if (!live) continue;
+    amax = fmaxf(amax, 1e-4f);
+    const float inv = 448.0f / amax;
+    uint32_t q[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t p0 = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * j] * inv, f[4 * j + 1] * inv),
+                                                   __NV_SATFINITE, __NV_E4M3);
+      const uint32_t p1 = __nv_cvt_float2_to_fp8x2(
+          make_float2(f[4 * j + 2] * inv, f[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+      q[j] = p0 | (p1 << 16);
+    }
+    int4 out;
+    out.x = q[0];
+    out.y = q[1];
+    out.z = q[2];
+    out.w = q[3];
+    ptx::st_v4(slot + static_cast<size_t>(v) * 16, out);
+    if ((lane & 7) == 0) slot_scales[v >> 3] = amax / 448.0f;
+  }
 }
 
 __device__ __forceinline__ void send_phase(const DispatchArgs& a, const DispatchSmem& sm,
@@ -279,13 +342,22 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
 
     uint8_t* slot = p.peer[dst] + p.off_disp_stage + (region_first + pos) * p.slot_bytes;
     const uint8_t* src = a.x + static_cast<int64_t>(i) * a.x_stride_row;
-    const int v0 = (c * nvec) / split;
-    const int v1 = ((c + 1) * nvec) / split;
-    ptx::warp_copy_v4<ptx::LoadKind::kNonCoherent>(slot + (static_cast<size_t>(v0) << 4),
-                                                   src + (static_cast<size_t>(v0) << 4), v1 - v0,
-                                                   lane);
+    if (a.quantize) {
+      // Parts are cut at multiples of 32 output vectors (512 columns).
+      const int groups = ceil_div<int>(nvec, 32);
+      const int v0 = ((c * groups) / split) * 32;
+      const int v1 = min((((c + 1) * groups) / split) * 32, nvec);
+      warp_quantize_row(slot, reinterpret_cast<float*>(slot + p.hidden_bytes),
+                        reinterpret_cast<const __nv_bfloat16*>(src), v0, v1, nvec, lane);
+    } else {
+      const int v0 = (c * nvec) / split;
+      const int v1 = ((c + 1) * nvec) / split;
+      ptx::warp_copy_v4<ptx::LoadKind::kNonCoherent>(slot + (static_cast<size_t>(v0) << 4),
+                                                     src + (static_cast<size_t>(v0) << 4),
+                                                     v1 - v0, lane);
+    }
     if (c == split - 1) {
-      if (nscale > 0) {
+      if (nscale > 0 && !a.quantize) {
         float* sdst = reinterpret_cast<float*>(slot + p.hidden_bytes);
         const float* ssrc = a.x_scale + static_cast<int64_t>(i) * a.x_scale_stride_row;
         for (int j = lane; j < nscale; j += 32) sdst[j] = __ldg(ssrc + j * a.x_scale_stride_col);

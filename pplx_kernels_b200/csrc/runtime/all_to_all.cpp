@@ -217,8 +217,17 @@ DispatchArgs AllToAll::make_dispatch_args(const DispatchCall& c) const {
   PPLX_CHECK(c.out_rows >= p.cap, "dispatch: out_expert_x holds "
                                       << c.out_rows << " rows per expert, need " << p.cap);
   const bool has_scale = p.scale_bytes > 0;
-  PPLX_CHECK(has_scale == (c.out_scale.data != nullptr) && has_scale == (c.x_scale.data != nullptr),
-             "dispatch: scale tensors must be given exactly when hidden_dim_scale_bytes > 0");
+  if (c.quantize) {
+    PPLX_CHECK(p.hidden_bytes == p.hidden_dim && p.scale_bytes == ceil_div(p.hidden_dim, 128) * 4,
+               "quantising dispatch needs an object created for a 1-byte payload with one fp32 "
+               "scale per 128 columns");
+    PPLX_CHECK(c.out_scale.data != nullptr && c.x_scale.data == nullptr,
+               "quantising dispatch takes out_expert_x_scale but no dp_x_scale");
+  } else {
+    PPLX_CHECK(
+        has_scale == (c.out_scale.data != nullptr) && has_scale == (c.x_scale.data != nullptr),
+        "dispatch: scale tensors must be given exactly when hidden_dim_scale_bytes > 0");
+  }
   PPLX_CHECK(reinterpret_cast<uintptr_t>(c.out_x.data) % 16 == 0 &&
                  reinterpret_cast<uintptr_t>(c.x.data) % 16 == 0 && c.out_x.stride_row % 16 == 0 &&
                  c.out_x.stride_outer % 16 == 0 && c.x.stride_row % 16 == 0,
@@ -241,6 +250,7 @@ DispatchArgs AllToAll::make_dispatch_args(const DispatchCall& c) const {
   a.indices = c.indices;
   a.bound_m = c.bound_m;
   a.num_tokens = c.num_tokens;
+  a.quantize = c.quantize ? 1 : 0;
   return a;
 }
 

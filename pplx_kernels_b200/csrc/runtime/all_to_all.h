@@ -59,6 +59,9 @@ struct DispatchCall {
   int num_tokens = 0;
   // Capacity checks (rows per expert the caller's buffers can hold).
   int64_t out_rows = 0;
+  // x holds bf16 values (hidden_dim_bytes of them per row) that the send quantises to
+  // e4m3 + fp32 scale per 128 columns; x_scale is then unused.
+  bool quantize = false;
 };
 
 struct CombineCall {

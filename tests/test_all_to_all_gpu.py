@@ -290,3 +290,71 @@ def test_sleep_on_stream_takes_about_that_long():
     end.record()
     torch.cuda.synchronize()
     assert 1.5 <= start.elapsed_time(end) <= 50.0
+
+
+# ------------------------------------------------------------ quantising send ----
+
+
+@pytest.mark.parametrize("world,hidden", [(1, 7168), (4, 1024), (2, 640)])
+def test_dispatch_with_fused_fp8_quantisation(world, hidden):
+    from pplx_kernels_b200.ops.quant import block_dequant, per_token_block_quant
+
+    from pplx_kernels_b200.ops.reference import simulate_dispatch
+
+    device = torch.device("cuda", 0)
+    cfg = MoEConfig(num_experts=16, experts_per_token=4, hidden_dim=hidden, max_num_tokens=24,
+                    in_dtype=torch.float8_e4m3fn)
+    ranks = pk.AllToAll.local_world(cfg.max_num_tokens, cfg.num_experts, cfg.experts_per_token,
+                                    world, 1, hidden, cfg.hidden_dim_bytes,
+                                    cfg.hidden_dim_scale_bytes)
+    for r in ranks:
+        r.set_debug_checks(True)
+        r.set_timeout_ms(3000)
+    inputs = world_inputs(cfg, world, 1, seed=81)
+    gen = torch.Generator().manual_seed(82)
+    xs = [(torch.randn(i.num_tokens, hidden, generator=gen) * 3).to(torch.bfloat16) for i in inputs]
+    nle = cfg.num_experts // world
+    rows = cfg.max_num_tokens * world
+    counts = [torch.full((nle,), -1, dtype=torch.int32, device=device) for _ in range(world)]
+    ex = [torch.zeros(nle, rows, hidden, dtype=torch.uint8, device=device).view(torch.float8_e4m3fn)
+          for _ in range(world)]
+    es = [torch.zeros(nle, rows, cfg.hidden_dim_scale, device=device) for _ in range(world)]
+    idx = [as_index_tensor(i.indices, device) for i in inputs]
+    if world == 1:
+        ranks[0].dispatch_quant(counts[0], ex[0], es[0], xs[0].to(device), idx[0], None)
+    else:
+        # group launch through the generic op: quantising variant of every rank
+        from pplx_kernels_b200.ops import _ops
+        _ops.all_to_all_dispatch_quant_group(
+            [r._ptr for r in ranks], counts, ex, es, [x.to(device) for x in xs], idx,
+            [torch.empty(0, device=device)] * world)
+    torch.cuda.synchronize()
+    for r in ranks:
+        r.check_status()
+    expected = simulate_dispatch(inputs, cfg.num_experts, 1)
+    for r in range(world):
+        assert counts[r].cpu().tolist() == expected[r].counts()
+        for le, src_rows in enumerate(expected[r].rows):
+            n = len(src_rows)
+            if n == 0:
+                continue
+            want_q, want_s = per_token_block_quant(torch.stack([xs[s][i] for s, i, _ in src_rows]))
+            got_q, got_s = ex[r][le, :n].cpu(), es[r][le, :n].cpu()
+            # Pair the rows through their scale vectors, which must agree exactly.  A small
+            # share of payload bytes may differ by one e4m3 step: bf16 / bf16 ratios land on
+            # rounding midpoints surprisingly often, and the host-side float -> e4m3
+            # conversion of the oracle does not break those ties the way cvt.rn does.
+            order_w = torch.argsort(want_s[:, 0] * 1e3 + want_s[:, -1], stable=True)
+            order_g = torch.argsort(got_s[:, 0] * 1e3 + got_s[:, -1], stable=True)
+            torch.testing.assert_close(got_s[order_g], want_s[order_w], rtol=1e-6, atol=0)
+            gq, wq = got_q[order_g], want_q[order_w]
+            mismatch = (gq.view(torch.uint8) != wq.view(torch.uint8)).float().mean().item()
+            assert mismatch < 1e-2, f"rank {r} expert {le}: {mismatch:.4f} of the bytes differ"
+            torch.testing.assert_close(block_dequant(gq, got_s[order_g]),
+                                       block_dequant(wq, want_s[order_w]), rtol=0.13, atol=1e-6)
+    # the oracle itself is a faithful quantiser: dequantised values are close to the originals
+    q, sc = per_token_block_quant(xs[0])
+    rel = (block_dequant(q, sc) - xs[0].float()).abs().max() / xs[0].float().abs().max()
+    assert rel < 0.07
+    for r in ranks:
+        r.destroy()
