@@ -10,7 +10,7 @@ source and every header it can include, and everything is linked into one shared
 object inside the package so that it travels with a copy of the source tree.
 nvcc cross-compiles, so the build needs no GPU.
 
-Usage: ``python -m pplx_kernels_b200.build [--force] [--verbose] [--ptxas-info]``.
+Usage: ``python -m pplx_kernels_b200.build [--force] [--verbose] [--ptxas-info] [--cpp-tests]``.
 """
 
 from __future__ import annotations
@@ -145,15 +145,47 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     return LIB_PATH
 
 
+def build_cpp_tests(verbose: bool = False) -> list[Path]:
+    """Builds the torch-free C++ executables (test_all_to_all, bench_all_to_all).
+
+    Role parity: the WITH_TESTS / WITH_BENCHMARKS targets of the reference's CMake build
+    (csrc/all_to_all/CMakeLists.txt:41-74), without MPI: the test runs its ranks on one GPU
+    and the benchmark finds its peers through the socket bootstrap.
+    """
+    build()
+    bin_dir = BUILD_DIR / "bin"
+    bin_dir.mkdir(exist_ok=True)
+    objs = [o for o in BUILD_DIR.glob("*.o") if not o.name.startswith("bindings_")]
+    out = []
+    for name in ("test_all_to_all", "bench_all_to_all"):
+        exe = bin_dir / name
+        cmd = ["g++", "-std=c++20", "-O2", f"-I{CUDA_HOME / 'include'}",
+               str(CSRC / "tests" / f"{name}.cpp"), *map(str, objs), "-o", str(exe),
+               f"-L{CUDA_HOME / 'lib64'}", f"-Wl,-rpath,{CUDA_HOME / 'lib64'}", "-lcudart",
+               "-lpthread", "-ldl"]
+        if verbose:
+            print(shlex.join(cmd), flush=True)
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"building {name} failed:\n{res.stdout}\n{res.stderr}")
+        out.append(exe)
+    return out
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true", help="recompile everything")
     ap.add_argument("--verbose", action="store_true", help="print the compiler commands")
     ap.add_argument("--ptxas-info", action="store_true",
                     help="pass -Xptxas -v and print register/shared-memory usage")
+    ap.add_argument("--cpp-tests", action="store_true",
+                    help="also build the C++ test and benchmark executables under _build/bin")
     args = ap.parse_args()
     path = build(force=args.force, verbose=args.verbose, ptxas_info=args.ptxas_info)
     print(path)
+    if args.cpp_tests:
+        for exe in build_cpp_tests(verbose=args.verbose):
+            print(exe)
 
 
 if __name__ == "__main__":
