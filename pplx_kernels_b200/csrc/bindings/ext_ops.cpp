@@ -14,7 +14,7 @@ namespace {
 // out[e, :counts[e]] = act(x[e, :counts[e]] @ w[e]^T), bf16 in / bf16 out.
 void grouped_gemm_op(const at::Tensor& x, const at::Tensor& w, const at::Tensor& counts,
                      at::Tensor& out, bool swiglu, const std::optional<at::Tensor>& status,
-                     int64_t expected_rows, int64_t half_n) {
+                     int64_t expected_rows, int64_t half_n, int64_t cta_pair) {
   TORCH_CHECK(x.is_cuda() && w.is_cuda() && counts.is_cuda() && out.is_cuda(),
               "grouped_gemm: all tensors must be CUDA tensors");
   TORCH_CHECK(x.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 &&
@@ -56,6 +56,7 @@ void grouped_gemm_op(const at::Tensor& x, const at::Tensor& w, const at::Tensor&
   c.swiglu = swiglu;
   c.expected_total_rows = expected_rows;
   c.half_n = static_cast<int>(half_n);
+  c.cta_pair = static_cast<int>(cta_pair);
   try {
     launch_grouped_gemm(c, at::cuda::getCurrentCUDAStream());
   } catch (const Error& e) {
@@ -64,13 +65,13 @@ void grouped_gemm_op(const at::Tensor& x, const at::Tensor& w, const at::Tensor&
 }
 
 void fake_grouped_gemm(const at::Tensor&, const at::Tensor&, const at::Tensor&, at::Tensor&, bool,
-                       const std::optional<at::Tensor>&, int64_t, int64_t) {}
+                       const std::optional<at::Tensor>&, int64_t, int64_t, int64_t) {}
 
 }  // namespace
 
 void register_extension_ops(torch::Library& m) {
   m.def("grouped_gemm(Tensor x, Tensor w, Tensor counts, Tensor! out, bool swiglu, "
-        "Tensor!? status, int expected_rows=0, int half_n=0) -> ()");
+        "Tensor!? status, int expected_rows=0, int half_n=0, int cta_pair=-1) -> ()");
   m.impl("grouped_gemm", c10::kCUDA, &grouped_gemm_op);
   m.impl("grouped_gemm", c10::kMeta, &fake_grouped_gemm);
 }

@@ -51,6 +51,8 @@ struct GroupedGemmCall {
   int num_sms = 0;           // 0 = all
   int half_n = 0;            // 0 = choose; else weight rows per B half (multiple of 8, 64..128)
   int64_t expected_total_rows = 0;  // hint for the tile-width choice; 0 = capacity
+  int cta_pair = -1;         // -1 = choose, 0 = one CTA per 128-row tile, 1 = CTA pair per
+                             // 256-row tile (tcgen05 cta_group::2)
 };
 
 // out[e, :counts[e]] = act(x[e, :counts[e]] @ w[e]^T); rows beyond counts[e] are untouched.

@@ -17,6 +17,15 @@
 //               bf16 conversion, masked 16-byte global stores; overlaps with the
 //               MMAs of the next tile through the second accumulator
 //
+// With kTwoCta the kernel runs as clusters of two CTAs that share one 256-row tile
+// (tcgen05 cta_group::2): each CTA loads its own 128 rows of A and HALF of the
+// weight tile, the leader CTA issues M = 256 MMAs that read both CTAs' shared
+// memory, and each CTA keeps and drains the accumulator of its own 128 rows.
+// Per SM that halves the weight traffic into shared memory and the shared-memory
+// reads per MMA, which is what limits the one-CTA form.  No TMA multicast is
+// involved: the two CTAs load different data; only barrier arrivals
+// (tcgen05.commit) are delivered to both CTAs.
+//
 // Tiles are (expert, 256-column block, 128-row block) with the row block varying
 // fastest, so CTAs that run at the same time share a weight tile in L2.  The
 // row counts are read on the device, so the launch is graph-capturable and does
@@ -63,20 +72,23 @@ constexpr int kBlockM = 128;
 constexpr int kBlockN = 256;
 constexpr int kBlockK = 64;   // 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kStages = 4;
+constexpr int kStages = 4;      // one CTA per tile: 16 KiB of A + 32 KiB of B per stage
+constexpr int kStages2 = 6;     // CTA pair: 16 KiB of A + 16 KiB of B per stage and CTA
+constexpr int kMaxStages = 6;
 constexpr int kThreads = 256;
 constexpr int kTmemCols = 512;
 constexpr uint32_t kABytes = kBlockM * kBlockK * 2;  // 16 KiB
 constexpr uint32_t kBBytes = kBlockN * kBlockK * 2;  // 32 KiB
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kStageBytes2 = kABytes + kBBytes / 2;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;     // 2 s per wait
 constexpr int kMaxExperts = 1024;
 
 constexpr uint32_t kNoSignal = 0xffffffffu;
 
 struct SharedControl {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
@@ -111,11 +123,11 @@ struct TileCoord {
 // Tiles of one group are ordered (n_blk, m_blk) with m_blk fastest.
 template <bool kFromStaging>
 __device__ __forceinline__ TileCoord locate_tile(const GroupTable& gt, int num_groups,
-                                                 const A2AParams& p, uint32_t t) {
+                                                 const A2AParams& p, uint32_t t, int tile_m) {
   TileCoord c;
   c.group = find_group(gt.tile_start, num_groups, t);
   c.rows = static_cast<int>(gt.rows[c.group]);
-  const int m_tiles = ceil_div<int>(c.rows, kBlockM);
+  const int m_tiles = ceil_div<int>(c.rows, tile_m);
   const uint32_t rem = t - gt.tile_start[c.group];
   c.n_blk = static_cast<int>(rem / m_tiles);
   c.m_blk = static_cast<int>(rem - static_cast<uint32_t>(c.n_blk) * m_tiles);
@@ -135,7 +147,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-template <bool SWIGLU, bool kFromStaging, bool kToPeers>
+template <bool SWIGLU, bool kFromStaging, bool kToPeers, bool kTwoCta>
 __global__ void __launch_bounds__(kThreads, 1)
     grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         const __grid_constant__ CUtensorMap tmap_b,
@@ -144,7 +156,15 @@ __global__ void __launch_bounds__(kThreads, 1)
   // Stage ring first (1024-byte aligned tiles), control block and tile table after.
   uint8_t* stages = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  SharedControl* ctl = reinterpret_cast<SharedControl*>(stages + kStages * kStageBytes);
+  constexpr int kNumStages = kTwoCta ? kStages2 : kStages;
+  constexpr uint32_t kStageStride = kTwoCta ? kStageBytes2 : kStageBytes;
+  SharedControl* ctl = reinterpret_cast<SharedControl*>(stages + kNumStages * kStageStride);
+  // A CTA pair works on one tile of 256 rows; this CTA owns rows [128 * cta_rank, +128).
+  const uint32_t cta_rank = kTwoCta ? tc::cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0u;
+  const int tile_m = kTwoCta ? 2 * kBlockM : kBlockM;
+  const uint32_t worker = kTwoCta ? blockIdx.x >> 1 : blockIdx.x;   // tile-loop index
+  const uint32_t workers = kTwoCta ? gridDim.x >> 1 : gridDim.x;
   const A2AParams& p = g.a2a;
   const int num_groups = g.num_experts;
   GroupTable gt;
@@ -163,7 +183,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int half_n = g.half_n;
   const int tile_n = 2 * half_n;
   const uint32_t b_half_bytes = static_cast<uint32_t>(half_n) * kBlockK * 2;
-  const uint32_t stage_tx_bytes = kABytes + 2 * b_half_bytes;
+  // Bytes that complete one stage: both B halves from this CTA, or (pair) A and one
+  // B half from each of the two CTAs, all counted on the leader's barrier.
+  const uint32_t stage_tx_bytes = kTwoCta ? 2 * (kABytes + b_half_bytes) : kABytes + 2 * b_half_bytes;
   const int out_cols_per_tile = SWIGLU ? half_n : tile_n;
   const int n_blocks = ceil_div<int>(g.n_out, out_cols_per_tile);
   const int num_kb = ceil_div<int>(g.k, kBlockK);
@@ -196,7 +218,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       gt.a_row0[le] = first;
       gt.out_row0[le] = 0;
       const uint32_t rows = min(gt.rows[le], static_cast<uint32_t>(p.cap));
-      gt.tile_start[le] = static_cast<uint32_t>(ceil_div<int>(static_cast<int>(rows), kBlockM) * n_blocks);
+      gt.tile_start[le] = static_cast<uint32_t>(ceil_div<int>(static_cast<int>(rows), tile_m) * n_blocks);
       if (blockIdx.x == 0) {
         if (g.out_num_tokens != nullptr) g.out_num_tokens[le] = static_cast<int32_t>(gt.rows[le]);
         p.recv_count[le] = rows;
@@ -210,7 +232,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       gt.rows[e] = static_cast<uint32_t>(rows);
       gt.a_row0[e] = 0;
       gt.out_row0[e] = 0;
-      gt.tile_start[e] = static_cast<uint32_t>(ceil_div<int>(rows, kBlockM) * n_blocks);
+      gt.tile_start[e] = static_cast<uint32_t>(ceil_div<int>(rows, tile_m) * n_blocks);
     }
   }
   if constexpr (kToPeers) {
@@ -229,13 +251,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   }
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kNumStages; ++s) {
       tc::mbar_init(&ctl->full[s], 1);
       tc::mbar_init(&ctl->empty[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       tc::mbar_init(&ctl->tmem_full[b], 1);
-      tc::mbar_init(&ctl->tmem_empty[b], 4);
+      tc::mbar_init(&ctl->tmem_empty[b], kTwoCta ? 8 : 4);  // epilogue warps of the tile
     }
     tc::fence_mbar_init();
     tc::tma_prefetch_desc(&tmap_a);
@@ -244,11 +266,18 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   if (warp == 0) warp_exclusive_scan_smem(gt.tile_start, num_groups, lane, true);
   if (warp == 2) {
-    tc::tmem_alloc(&ctl->tmem_base, kTmemCols);
-    tc::tmem_relinquish();
+    if constexpr (kTwoCta) {
+      tc::tmem_alloc_2cta(&ctl->tmem_base, kTmemCols);
+      tc::tmem_relinquish_2cta();
+    } else {
+      tc::tmem_alloc(&ctl->tmem_base, kTmemCols);
+      tc::tmem_relinquish();
+    }
   }
   tc::tc_fence_before_sync();
   __syncthreads();
+  // The peer must see initialised barriers before anything arrives on them remotely.
+  if constexpr (kTwoCta) tc::cluster_sync();
   tc::tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
   const uint32_t total_tiles = gt.tile_start[num_groups];
@@ -261,8 +290,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t pending_phase = 0;  // parity of the phase each stage was last filled in
       bool ok = *abort_flag == 0u;
       int last_group = -1;  // expert whose rows are known to have landed
-      for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        const TileCoord c = locate_tile<kFromStaging>(gt, num_groups, p, t);
+      for (uint32_t t = worker; t < total_tiles && ok; t += workers) {
+        const TileCoord c = locate_tile<kFromStaging>(gt, num_groups, p, t, tile_m);
         if constexpr (kFromStaging) {
           if (c.group != last_group) {
             // The expert's rows were stored by peers: wait for its arrival counter,
@@ -286,25 +315,36 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = tc::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, kWaitLimitNs);
           if (!ok) break;
-          uint8_t* a_dst = stages + stage * kStageBytes;
+          uint8_t* a_dst = stages + stage * kStageStride;
           uint8_t* b_dst = a_dst + kABytes;
-          tc::mbar_arrive_expect_tx(&ctl->full[stage], stage_tx_bytes);
           pending |= 1u << stage;
           pending_phase = (pending_phase & ~(1u << stage)) | (phase << stage);
-          tc::tma_load_3d(a_dst, &tmap_a, &ctl->full[stage], kb * kBlockK,
-                          c.a_row0 + c.m_blk * kBlockM, c.a_plane);
-          if constexpr (SWIGLU) {
-            const int row = c.n_blk * half_n;
-            tc::tma_load_3d(b_dst, &tmap_b, &ctl->full[stage], kb * kBlockK, row, c.w_plane);
-            tc::tma_load_3d(b_dst + b_half_bytes, &tmap_b, &ctl->full[stage], kb * kBlockK,
-                            g.n_out + row, c.w_plane);
+          const int a_row = c.a_row0 + c.m_blk * tile_m + static_cast<int>(cta_rank) * kBlockM;
+          if constexpr (kTwoCta) {
+            // This CTA's rows of A and its half of the weight tile; the bytes of both CTAs
+            // are counted on the leader's barrier, which only the leader arms.
+            if (leader) tc::mbar_arrive_expect_tx(&ctl->full[stage], stage_tx_bytes);
+            int b_row;
+            if constexpr (SWIGLU) b_row = (cta_rank == 0 ? 0 : g.n_out) + c.n_blk * half_n;
+            else b_row = c.n_blk * tile_n + static_cast<int>(cta_rank) * half_n;
+            tc::tma_load_3d_2cta(a_dst, &tmap_a, &ctl->full[stage], kb * kBlockK, a_row, c.a_plane);
+            tc::tma_load_3d_2cta(b_dst, &tmap_b, &ctl->full[stage], kb * kBlockK, b_row, c.w_plane);
           } else {
-            const int row = c.n_blk * tile_n;
-            tc::tma_load_3d(b_dst, &tmap_b, &ctl->full[stage], kb * kBlockK, row, c.w_plane);
-            tc::tma_load_3d(b_dst + b_half_bytes, &tmap_b, &ctl->full[stage], kb * kBlockK,
-                            row + half_n, c.w_plane);
+            tc::mbar_arrive_expect_tx(&ctl->full[stage], stage_tx_bytes);
+            tc::tma_load_3d(a_dst, &tmap_a, &ctl->full[stage], kb * kBlockK, a_row, c.a_plane);
+            if constexpr (SWIGLU) {
+              const int row = c.n_blk * half_n;
+              tc::tma_load_3d(b_dst, &tmap_b, &ctl->full[stage], kb * kBlockK, row, c.w_plane);
+              tc::tma_load_3d(b_dst + b_half_bytes, &tmap_b, &ctl->full[stage], kb * kBlockK,
+                              g.n_out + row, c.w_plane);
+            } else {
+              const int row = c.n_blk * tile_n;
+              tc::tma_load_3d(b_dst, &tmap_b, &ctl->full[stage], kb * kBlockK, row, c.w_plane);
+              tc::tma_load_3d(b_dst + b_half_bytes, &tmap_b, &ctl->full[stage], kb * kBlockK,
+                              row + half_n, c.w_plane);
+            }
           }
-          if (++stage == kStages) {
+          if (++stage == kNumStages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -315,9 +355,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         // leaves: their destination is this CTA's shared memory.
         uint64_t t0;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < kNumStages; ++s) {
           if (!((pending >> s) & 1u)) continue;
-          while (!tc::mbar_try_wait(&ctl->full[s], (pending_phase >> s) & 1u)) {
+          // (The non-leader of a pair has no barrier of its own to watch; it just sits
+          // out the time limit, which is far longer than any load takes.)
+          while (!leader || !tc::mbar_try_wait(&ctl->full[s], (pending_phase >> s) & 1u)) {
             uint64_t t1;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
             if (t1 - t0 > 100000000ull) break;  // 100 ms in total
@@ -327,12 +369,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (tc::elect_one()) {
-      const uint32_t idesc = tc::make_instr_desc(1u, kBlockM, tile_n);
+    if (leader && tc::elect_one()) {
+      const uint32_t idesc = tc::make_instr_desc(1u, tile_m, tile_n);
       uint32_t stage = 0, phase = 0;
       uint32_t local = 0;
       bool ok = *abort_flag == 0u;
-      for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+      for (uint32_t t = worker; t < total_tiles && ok; t += workers, ++local) {
         const uint32_t buf = local & 1u;
         const uint32_t use = local >> 1;  // how often this accumulator was used before
         ok = tc::mbar_wait(&ctl->tmem_empty[buf], (use & 1u) ^ 1u, abort_flag, kWaitLimitNs);
@@ -343,22 +385,33 @@ __global__ void __launch_bounds__(kThreads, 1)
           ok = tc::mbar_wait(&ctl->full[stage], phase, abort_flag, kWaitLimitNs);
           if (!ok) break;
           tc::tc_fence_after_sync();
-          const uint8_t* a_src = stages + stage * kStageBytes;
+          const uint8_t* a_src = stages + stage * kStageStride;
           const uint64_t a_desc = tc::make_smem_desc_sw128(a_src);
           const uint64_t b_desc = tc::make_smem_desc_sw128(a_src + kABytes);
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            tc::mma_f16_ss(tmem_d, tc::advance_smem_desc(a_desc, k * kUmmaK * 2),
-                           tc::advance_smem_desc(b_desc, k * kUmmaK * 2), idesc,
-                           (kb | k) != 0);
+            if constexpr (kTwoCta) {
+              tc::mma_f16_ss_2cta(tmem_d, tc::advance_smem_desc(a_desc, k * kUmmaK * 2),
+                                  tc::advance_smem_desc(b_desc, k * kUmmaK * 2), idesc,
+                                  (kb | k) != 0);
+            } else {
+              tc::mma_f16_ss(tmem_d, tc::advance_smem_desc(a_desc, k * kUmmaK * 2),
+                             tc::advance_smem_desc(b_desc, k * kUmmaK * 2), idesc,
+                             (kb | k) != 0);
+            }
           }
-          tc::mma_commit(&ctl->empty[stage]);  // stage reusable once these MMAs have read it
-          if (++stage == kStages) {
+          // Stage reusable (in both CTAs of a pair) once these MMAs have read it.
+          if constexpr (kTwoCta) tc::mma_commit_2cta(&ctl->empty[stage], 0x3);
+          else tc::mma_commit(&ctl->empty[stage]);
+          if (++stage == kNumStages) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) tc::mma_commit(&ctl->tmem_full[buf]);
+        if (ok) {
+          if constexpr (kTwoCta) tc::mma_commit_2cta(&ctl->tmem_full[buf], 0x3);
+          else tc::mma_commit(&ctl->tmem_full[buf]);
+        }
       }
     }
     __syncwarp();
@@ -367,15 +420,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     uint32_t local = 0;
     bool ok = *abort_flag == 0u;
     const int row_bytes_out = g.n_out * 2;
-    for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
-      const TileCoord c = locate_tile<kFromStaging>(gt, num_groups, p, t);
+    for (uint32_t t = worker; t < total_tiles && ok; t += workers, ++local) {
+      const TileCoord c = locate_tile<kFromStaging>(gt, num_groups, p, t, tile_m);
       const uint32_t buf = local & 1u;
       const uint32_t use = local >> 1;
       ok = tc::mbar_wait(&ctl->tmem_full[buf], use & 1u, abort_flag, kWaitLimitNs);
       if (!ok) break;
       tc::tc_fence_after_sync();
       const int tile_row = ew * 32 + lane;
-      const int row = c.m_blk * kBlockM + tile_row;  // row inside the group
+      const int row = c.m_blk * tile_m + static_cast<int>(cta_rank) * kBlockM + tile_row;
       const bool row_ok = row < c.rows;
       const int out_row = c.out_row0 + row;
 
@@ -466,7 +519,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       // Accumulator drained: hand it back to the MMA warp.
       tc::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&ctl->tmem_empty[buf]);
+      if (lane == 0) {
+        if constexpr (kTwoCta) tc::mbar_arrive_on_leader(&ctl->tmem_empty[buf]);
+        else tc::mbar_arrive(&ctl->tmem_empty[buf]);
+      }
 
       if constexpr (kToPeers) {
         // One fence for the whole tile, then the adds.  The sig arrays are double
@@ -495,9 +551,13 @@ __global__ void __launch_bounds__(kThreads, 1)
   // ---- teardown -------------------------------------------------------------
   tc::tc_fence_before_sync();
   __syncthreads();
+  // Neither CTA of a pair may leave while the other can still touch its shared or
+  // tensor memory.
+  if constexpr (kTwoCta) tc::cluster_sync();
   if (warp == 2) {
     tc::tc_fence_after_sync();
-    tc::tmem_dealloc(tmem_base, kTmemCols);
+    if constexpr (kTwoCta) tc::tmem_dealloc_2cta(tmem_base, kTmemCols);
+    else tc::tmem_dealloc(tmem_base, kTmemCols);
   }
   if (tid == 0 && ctl->abort_flag != 0u && g.status != nullptr) *g.status = 1u;
   (void)parity;
@@ -544,18 +604,50 @@ CUtensorMap make_operand_map(const void* base, int64_t experts, int64_t rows, in
 }
 
 size_t smem_bytes(int num_groups) {
+  static_assert(kStages * kStageBytes == kStages2 * kStageBytes2, "both rings use 192 KiB");
   return 1024 + kStages * kStageBytes + sizeof(SharedControl) +
          sizeof(uint32_t) * (4 * static_cast<size_t>(num_groups) + 1);
 }
 
-template <bool SWIGLU, bool kFromStaging, bool kToPeers>
-void launch_variant(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
-                    const GroupedGemmArgs& g, int num_groups, int grid, cudaStream_t stream) {
-  auto* kernel = grouped_gemm_kernel<SWIGLU, kFromStaging, kToPeers>;
+template <bool SWIGLU, bool kFromStaging, bool kToPeers, bool kTwoCta>
+void launch_one(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GroupedGemmArgs& g,
+                int num_groups, int grid, cudaStream_t stream) {
+  auto* kernel = grouped_gemm_kernel<SWIGLU, kFromStaging, kToPeers, kTwoCta>;
   CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   static_cast<int>(smem_bytes(kMaxExperts))));
-  kernel<<<grid, kThreads, smem_bytes(num_groups), stream>>>(tmap_a, tmap_b, g);
-  CUDA_CHECK(cudaGetLastError());
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(kTwoCta ? (grid & ~1) : grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem_bytes(num_groups);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr{};
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = kTwoCta ? 2 : 1;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, tmap_a, tmap_b, g));
+}
+
+template <bool SWIGLU, bool kFromStaging, bool kToPeers>
+void launch_variant(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
+                    const GroupedGemmArgs& g, int num_groups, int grid, bool two_cta,
+                    cudaStream_t stream) {
+  if (two_cta && grid >= 2) {
+    launch_one<SWIGLU, kFromStaging, kToPeers, true>(tmap_a, tmap_b, g, num_groups, grid, stream);
+  } else {
+    launch_one<SWIGLU, kFromStaging, kToPeers, false>(tmap_a, tmap_b, g, num_groups, grid, stream);
+  }
+}
+
+// A CTA pair pays off when experts have enough rows to fill 256-row tiles.
+bool want_two_cta(const GroupedGemmCall& c) {
+  if (c.cta_pair >= 0) return c.cta_pair != 0;
+  const int64_t rows = c.expected_total_rows > 0
+                           ? c.expected_total_rows
+                           : static_cast<int64_t>(c.num_experts) * c.rows_per_expert;
+  return rows / std::max(1, c.num_experts) > 160;
 }
 
 void check_common(const GroupedGemmCall& c) {
@@ -568,12 +660,11 @@ void check_common(const GroupedGemmCall& c) {
 
 // Without a device round trip the host only knows the capacity; callers that know
 // better pass an estimate of the total rows.
-int64_t expected_m_tiles(const GroupedGemmCall& c) {
+int64_t expected_m_tiles(const GroupedGemmCall& c, int tile_m) {
   const int64_t rows = c.expected_total_rows > 0
                            ? c.expected_total_rows
                            : static_cast<int64_t>(c.num_experts) * c.rows_per_expert;
-  return std::max<int64_t>(c.num_experts > 0 ? 1 : 0,
-                           ceil_div<int64_t>(rows, kBlockM));
+  return std::max<int64_t>(c.num_experts > 0 ? 1 : 0, ceil_div<int64_t>(rows, tile_m));
 }
 
 GroupedGemmArgs base_args(const GroupedGemmCall& c) {
@@ -627,11 +718,13 @@ void launch_grouped_gemm(const GroupedGemmCall& c, cudaStream_t stream) {
   const CUtensorMap tmap_a = make_operand_map(c.x, c.num_experts, c.rows_per_expert, c.k,
                                               c.x_stride_row, c.x_stride_e);
   const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
+  const bool two_cta = want_two_cta(c);
   GroupedGemmArgs g = base_args(c);
-  g.half_n = pick_half_n(c.n_out, c.swiglu, expected_m_tiles(c), grid, c.half_n);
+  g.half_n = pick_half_n(c.n_out, c.swiglu, expected_m_tiles(c, two_cta ? 256 : 128),
+                         two_cta ? grid / 2 : grid, c.half_n);
   const CUtensorMap tmap_b = weight_map(c, g.half_n);
-  if (c.swiglu) launch_variant<true, false, false>(tmap_a, tmap_b, g, c.num_experts, grid, stream);
-  else launch_variant<false, false, false>(tmap_a, tmap_b, g, c.num_experts, grid, stream);
+  if (c.swiglu) launch_variant<true, false, false>(tmap_a, tmap_b, g, c.num_experts, grid, two_cta, stream);
+  else launch_variant<false, false, false>(tmap_a, tmap_b, g, c.num_experts, grid, two_cta, stream);
 }
 
 void launch_gemm_from_staging(const GroupedGemmCall& c, const A2AParams& p,
@@ -651,12 +744,14 @@ void launch_gemm_from_staging(const GroupedGemmCall& c, const A2AParams& p,
                                               p.hidden_dim, p.slot_bytes / 2,
                                               slots * p.slot_bytes / 2);
   const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
+  const bool two_cta = want_two_cta(c);
   GroupedGemmArgs g = base_args(c);
-  g.half_n = pick_half_n(c.n_out, c.swiglu, expected_m_tiles(c), grid, c.half_n);
+  g.half_n = pick_half_n(c.n_out, c.swiglu, expected_m_tiles(c, two_cta ? 256 : 128),
+                         two_cta ? grid / 2 : grid, c.half_n);
   const CUtensorMap tmap_b = weight_map(c, g.half_n);
   g.out_num_tokens = out_num_tokens;
   g.a2a = p;
-  launch_variant<true, true, false>(tmap_a, tmap_b, g, p.nle, grid, stream);
+  launch_variant<true, true, false>(tmap_a, tmap_b, g, p.nle, grid, two_cta, stream);
 }
 
 void launch_gemm_to_peers(const GroupedGemmCall& c, const A2AParams& p, cudaStream_t stream) {
@@ -667,6 +762,7 @@ void launch_gemm_to_peers(const GroupedGemmCall& c, const A2AParams& p, cudaStre
   PPLX_CHECK(c.counts == reinterpret_cast<const int32_t*>(p.recv_count),
              "counts must be the all-to-all's received-row counts");
   const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
+  const bool two_cta = want_two_cta(c);
   // The column-block count must divide the arrival units: take the widest tile that does.
   int half_n = 0;
   for (int half = 128; half >= 64 && half_n == 0; half -= 8) {
@@ -687,7 +783,7 @@ void launch_gemm_to_peers(const GroupedGemmCall& c, const A2AParams& p, cudaStre
   g.out = nullptr;
   g.arrival_units_per_tile = static_cast<uint32_t>(p.comb_units / n_blocks);
   g.a2a = p;
-  launch_variant<false, false, true>(tmap_a, tmap_b, g, c.num_experts, grid, stream);
+  launch_variant<false, false, true>(tmap_a, tmap_b, g, c.num_experts, grid, two_cta, stream);
 }
 
 }  // namespace pplx

@@ -43,6 +43,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--half-n", type=int, default=0, help="force the B half width (0 = choose)")
+    ap.add_argument("--cta-pair", type=int, default=-1, help="1 = CTA pair, 0 = single, -1 = choose")
     args = ap.parse_args()
     if args.shape:
         E, rows, K, N, swiglu = SHAPES[args.shape]
@@ -66,7 +67,7 @@ def main() -> None:
     results = {}
     for name, fn in (("ours", lambda: grouped_gemm(x, w, counts, out=out, swiglu=swiglu,
                                                    status=status, expected_rows=E * rows,
-                                                   half_n=args.half_n)), ("torch_matmul", lib)):
+                                                   half_n=args.half_n, cta_pair=args.cta_pair)), ("torch_matmul", lib)):
         times = []
         for it in range(args.warmup + args.iters):
             if not args.no_flush:

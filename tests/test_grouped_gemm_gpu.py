@@ -8,7 +8,7 @@ from pplx_kernels_b200.ops.grouped_gemm import grouped_gemm, grouped_gemm_refere
 pytestmark = pytest.mark.gpu
 
 
-def _case(E, rows, K, N, counts, swiglu, seed=0, half_n=0):
+def _case(E, rows, K, N, counts, swiglu, seed=0, half_n=0, cta_pair=-1):
     dev = torch.device("cuda", 0)
     g = torch.Generator(device="cpu").manual_seed(seed)
     x = (torch.randn(E, rows, K, generator=g) * 0.5).to(torch.bfloat16).to(dev)
@@ -17,7 +17,8 @@ def _case(E, rows, K, N, counts, swiglu, seed=0, half_n=0):
     cnt = torch.tensor(counts, dtype=torch.int32, device=dev)
     out = torch.full((E, rows, N), float("nan"), dtype=torch.bfloat16, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
-    grouped_gemm(x, w, cnt, out=out, swiglu=swiglu, status=status, half_n=half_n)
+    grouped_gemm(x, w, cnt, out=out, swiglu=swiglu, status=status, half_n=half_n,
+                 cta_pair=cta_pair)
     torch.cuda.synchronize()
     assert int(status.item()) == 0, "a pipeline wait ran out"
     want = grouped_gemm_reference(x, w, cnt, swiglu)
@@ -56,3 +57,16 @@ def test_more_tiles_than_sms():
 def test_narrow_tiles(swiglu, half_n):
     # Tile widths other than 256 columns, with column tails on the last block.
     _case(E=3, rows=256, K=320, N=448, counts=[200, 256, 17], swiglu=swiglu, seed=5, half_n=half_n)
+
+
+@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("cta_pair", [0, 1])
+def test_cta_pair_and_single_forms_agree_with_the_reference(swiglu, cta_pair):
+    # Row counts around the 128 / 256 tile edges, an empty expert, several K blocks.
+    _case(E=5, rows=640, K=448, N=512, counts=[640, 129, 0, 256, 300], swiglu=swiglu, seed=6,
+          cta_pair=cta_pair)
+
+
+def test_cta_pair_long_k_and_narrow_tiles():
+    _case(E=2, rows=512, K=2048, N=448, counts=[512, 257], swiglu=True, seed=7, half_n=112,
+          cta_pair=1)
