@@ -195,12 +195,12 @@ class AllToAll:
         _ops.moe_fused_up(self._ptr, w13, h, out_expert_num_tokens, status, expected_rows)
 
     def fused_down(self, h: torch.Tensor, w2: torch.Tensor,
-                   status: torch.Tensor | None = None) -> None:
+                   status: torch.Tensor | None = None, expected_rows: int = 0) -> None:
         """Down projection whose epilogue stores each row to its token's home rank(s).
 
         Call before ``combine(..., do_send=False, do_recv=True)``; it replaces the send half.
         """
-        _ops.moe_fused_down(self._ptr, h, w2, status)
+        _ops.moe_fused_down(self._ptr, h, w2, status, expected_rows)
 
     def set_trace(self, on: bool) -> None:
         """Turns the per-phase device time stamps of block 0 on or off."""

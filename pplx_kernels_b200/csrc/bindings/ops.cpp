@@ -546,7 +546,7 @@ void moe_fused_up_op(int64_t ptr, const at::Tensor& w13, at::Tensor& h,
 
 // Down projection whose epilogue stores to the tokens' home ranks (before combine with do_send=False).
 void moe_fused_down_op(int64_t ptr, const at::Tensor& h, const at::Tensor& w2,
-                       const std::optional<at::Tensor>& status) {
+                       const std::optional<at::Tensor>& status, int64_t expected_rows) {
   AllToAll* ata = lookup(ptr);
   check_bf16_3d(w2, "w2");
   check_bf16_3d(h, "h");
@@ -564,6 +564,7 @@ void moe_fused_down_op(int64_t ptr, const at::Tensor& h, const at::Tensor& w2,
   f.rows_per_expert = static_cast<int>(h.size(1));
   f.inter_dim = static_cast<int>(h.size(2));
   f.status = status_word(status);
+  f.expected_total_rows = expected_rows;
   const c10::cuda::OptionalCUDAGuard guard(h.device());
   guarded([&] { ata->fused_down(f, at::cuda::getCurrentCUDAStream()); });
 }
@@ -571,7 +572,7 @@ void moe_fused_down_op(int64_t ptr, const at::Tensor& h, const at::Tensor& w2,
 void fake_moe_fused_up(int64_t, const at::Tensor&, at::Tensor&, const std::optional<at::Tensor>&,
                        const std::optional<at::Tensor>&, int64_t) {}
 void fake_moe_fused_down(int64_t, const at::Tensor&, const at::Tensor&,
-                         const std::optional<at::Tensor>&) {}
+                         const std::optional<at::Tensor>&, int64_t) {}
 
 void set_trace_op(int64_t ptr, bool on) { lookup(ptr)->set_trace(on); }
 
@@ -777,7 +778,8 @@ void register_all_to_all_ops(torch::Library& m) {
         "Tensor!? status, int expected_rows=0) -> ()");
   m.impl("moe_fused_up", c10::kCUDA, &moe_fused_up_op);
   m.impl("moe_fused_up", c10::kMeta, &fake_moe_fused_up);
-  m.def("moe_fused_down(int ptr, Tensor h, Tensor w2, Tensor!? status) -> ()");
+  m.def("moe_fused_down(int ptr, Tensor h, Tensor w2, Tensor!? status, "
+        "int expected_rows=0) -> ()");
   m.impl("moe_fused_down", c10::kCUDA, &moe_fused_down_op);
   m.impl("moe_fused_down", c10::kMeta, &fake_moe_fused_down);
   m.def("all_to_all_read_trace(int ptr) -> int[]", &read_trace_op);

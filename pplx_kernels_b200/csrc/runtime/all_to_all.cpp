@@ -390,6 +390,7 @@ void AllToAll::fused_down(const FusedFfnCall& f, cudaStream_t stream) {
   c.n_out = params_.hidden_dim;
   c.k = f.inter_dim;
   c.swiglu = false;
+  c.expected_total_rows = f.expected_total_rows;
   c.num_sms = max_blocks_ > 0 ? std::min(max_blocks_, num_sms_) : num_sms_;
   launch_gemm_to_peers(c, params_, stream);
 }

@@ -90,7 +90,7 @@ struct FusedFfnCall {
   int inter_dim = 0;
   int32_t* out_num_tokens = nullptr;  // up only, optional
   uint32_t* status = nullptr;         // optional device word, 1 if a pipeline wait ran out
-  int64_t expected_total_rows = 0;    // up only: hint for the tile-width choice, 0 = capacity
+  int64_t expected_total_rows = 0;    // hint for the tile shape choice, 0 = capacity
 };
 
 class AllToAll {

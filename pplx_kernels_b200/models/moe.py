@@ -84,7 +84,7 @@ class MoELayer:
         if fused:
             self.ata.fused_dispatch(x, indices, bound_m)
             self.ata.fused_up(self.w13, self.h, self.counts, self.gemm_status, expect)
-            self.ata.fused_down(self.h, self.w2, self.gemm_status)
+            self.ata.fused_down(self.h, self.w2, self.gemm_status, expect)
             self.ata.combine(out, indices, weights, self.expert_y, bound_m,
                              do_send=False, do_recv=True)
             return out

@@ -19,7 +19,8 @@ def _inputs(cfg: MoEModelConfig, m: int, seed: int, dev):
 
 
 @pytest.mark.parametrize("fused", [False, True])
-@pytest.mark.parametrize("cfg,m", [(TINY, 40), (MoEModelConfig("t2", 4, 2, 512, 256), 200)])
+@pytest.mark.parametrize("cfg,m", [(TINY, 40), (MoEModelConfig("t2", 4, 2, 512, 256), 200),
+                                   (MoEModelConfig("t3", 2, 2, 256, 256), 300)])
 def test_single_rank_layer_matches_reference(cfg, m, fused):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -63,15 +64,17 @@ def test_layer_in_a_cuda_graph():
     layer.destroy()
 
 
-@pytest.mark.parametrize("world,dp_size", [(2, 1), (4, 2)])
-def test_fused_layer_in_an_emulated_world(world, dp_size):
+@pytest.mark.parametrize("world,dp_size,m", [(2, 1, 24), (4, 2, 24), (2, 1, 400)])
+def test_fused_layer_in_an_emulated_world(world, dp_size, m):
     """All ranks on one GPU.  Every step is launched for all ranks before the next step
     begins, so no kernel ever waits for a later launch."""
     import pplx_kernels_b200 as pk
 
-    cfg, m = TINY, 24
+    # m = 400 gives every expert enough rows for the CTA-pair form of both GEMMs.
+    cfg = TINY
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
+    expect = m * cfg.experts_per_token // dp_size
     atas = pk.AllToAll.local_world(m, cfg.num_experts, cfg.experts_per_token, world, dp_size,
                                    cfg.hidden_dim, cfg.hidden_dim * 2, 0)
     layers = [MoELayer(cfg, m, rank=r, world_size=world, dp_size=dp_size, device=dev,
@@ -92,9 +95,9 @@ def test_fused_layer_in_an_emulated_world(world, dp_size):
             o.fill_(float("nan"))
         pk.fused_dispatch_group(atas, [d[0] for d in per_rank], idx_dev, [None] * world)
         for l in layers:
-            l.ata.fused_up(l.w13, l.h, l.counts, l.gemm_status)
+            l.ata.fused_up(l.w13, l.h, l.counts, l.gemm_status, expect)
         for l in layers:
-            l.ata.fused_down(l.h, l.w2, l.gemm_status)
+            l.ata.fused_down(l.h, l.w2, l.gemm_status, expect)
         pk.combine_group(atas, outs, idx_dev, [d[2] for d in per_rank],
                          [l.expert_y for l in layers], [None] * world,
                          do_send=False, do_recv=True)
