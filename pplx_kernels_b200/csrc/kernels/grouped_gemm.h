@@ -11,6 +11,8 @@
 
 namespace pplx {
 
+constexpr int kNumTileWidths = 5;
+
 // Device-side arguments (the tensor maps travel as separate kernel parameters).
 struct GroupedGemmArgs {
   const int32_t* counts;   // [num_experts] valid rows per expert
@@ -22,10 +24,10 @@ struct GroupedGemmArgs {
   int rows_per_expert;     // capacity of x / out per expert
   int n_out;               // output columns (the intermediate size for SwiGLU)
   int k;
-  int half_n;              // weight rows per B half; the tile is 2 * half_n columns wide
+  int widths[kNumTileWidths];  // candidate weight rows per B half (the tile is twice as wide
+                               // in columns); 0 = not available.  Chosen on the device.
   // Only read by the kernels fused with the all-to-all:
   int32_t* out_num_tokens;          // optional [nle]: per-expert totals for the caller
-  uint32_t arrival_units_per_tile;  // units added to a token's counter per column block
   A2AParams a2a;
 };
 

@@ -86,6 +86,12 @@ constexpr int kMaxExperts = 1024;
 
 constexpr uint32_t kNoSignal = 0xffffffffu;
 
+// One tensor map of the weights per candidate tile width (the TMA box height is
+// fixed in the map); the kernel picks the width once it knows the real row counts.
+struct WeightMaps {
+  CUtensorMap m[kNumTileWidths];
+};
+
 struct SharedControl {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
@@ -150,7 +156,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 template <bool SWIGLU, bool kFromStaging, bool kToPeers, bool kTwoCta>
 __global__ void __launch_bounds__(kThreads, 1)
     grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                        const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ WeightMaps wmaps,
                         const __grid_constant__ GroupedGemmArgs g) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // Stage ring first (1024-byte aligned tiles), control block and tile table after.
@@ -178,16 +184,6 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int lane = tid & 31;
   volatile uint32_t* abort_flag = &ctl->abort_flag;
 
-  // The B tile is two halves of g.half_n weight rows each (gate and up rows for
-  // SwiGLU, consecutive rows otherwise); the accumulator is 2 * half_n columns wide.
-  const int half_n = g.half_n;
-  const int tile_n = 2 * half_n;
-  const uint32_t b_half_bytes = static_cast<uint32_t>(half_n) * kBlockK * 2;
-  // Bytes that complete one stage: both B halves from this CTA, or (pair) A and one
-  // B half from each of the two CTAs, all counted on the leader's barrier.
-  const uint32_t stage_tx_bytes = kTwoCta ? 2 * (kABytes + b_half_bytes) : kABytes + 2 * b_half_bytes;
-  const int out_cols_per_tile = SWIGLU ? half_n : tile_n;
-  const int n_blocks = ceil_div<int>(g.n_out, out_cols_per_tile);
   const int num_kb = ceil_div<int>(g.k, kBlockK);
 
   // ---- set-up ---------------------------------------------------------------
@@ -218,7 +214,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       gt.a_row0[le] = first;
       gt.out_row0[le] = 0;
       const uint32_t rows = min(gt.rows[le], static_cast<uint32_t>(p.cap));
-      gt.tile_start[le] = static_cast<uint32_t>(ceil_div<int>(static_cast<int>(rows), tile_m) * n_blocks);
+      gt.tile_start[le] = static_cast<uint32_t>(ceil_div<int>(static_cast<int>(rows), tile_m));
       if (blockIdx.x == 0) {
         if (g.out_num_tokens != nullptr) g.out_num_tokens[le] = static_cast<int32_t>(gt.rows[le]);
         p.recv_count[le] = rows;
@@ -232,7 +228,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       gt.rows[e] = static_cast<uint32_t>(rows);
       gt.a_row0[e] = 0;
       gt.out_row0[e] = 0;
-      gt.tile_start[e] = static_cast<uint32_t>(ceil_div<int>(rows, tile_m) * n_blocks);
+      gt.tile_start[e] = static_cast<uint32_t>(ceil_div<int>(rows, tile_m));
     }
   }
   if constexpr (kToPeers) {
@@ -261,7 +257,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     tc::fence_mbar_init();
     tc::tma_prefetch_desc(&tmap_a);
-    tc::tma_prefetch_desc(&tmap_b);
   }
   __syncthreads();
   if (warp == 0) warp_exclusive_scan_smem(gt.tile_start, num_groups, lane, true);
@@ -280,7 +275,42 @@ __global__ void __launch_bounds__(kThreads, 1)
   if constexpr (kTwoCta) tc::cluster_sync();
   tc::tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
+
+  // Tile width.  gt.tile_start holds the prefix of ROW blocks per expert; with the
+  // real total the width that minimises (waves of tiles) x (time of one tile) is
+  // chosen among the candidates the host prepared -- every CTA computes the same.
+  // The B tile is two halves of half_n weight rows each (gate and up rows for
+  // SwiGLU, consecutive rows otherwise); the accumulator is 2 * half_n columns wide.
+  const uint32_t total_m_tiles = gt.tile_start[num_groups];
+  int width_idx = 0;
+  {
+    uint64_t best = ~0ull;
+    for (int i = 0; i < kNumTileWidths; ++i) {
+      const int half = g.widths[i];
+      if (half <= 0) continue;
+      const uint32_t nb = ceil_div<uint32_t>(g.n_out, (SWIGLU ? 1 : 2) * half);
+      const uint64_t waves = ceil_div<uint64_t>(static_cast<uint64_t>(total_m_tiles) * nb, workers);
+      const uint64_t cost = waves * static_cast<uint64_t>(half + (kTwoCta ? 40 : 88));
+      if (cost < best) {
+        best = cost;
+        width_idx = i;
+      }
+    }
+  }
+  const CUtensorMap& tmap_b = wmaps.m[width_idx];
+  const int half_n = g.widths[width_idx];
+  const int tile_n = 2 * half_n;
+  const uint32_t b_half_bytes = static_cast<uint32_t>(half_n) * kBlockK * 2;
+  // Bytes that complete one stage: both B halves from this CTA, or (pair) A and one
+  // B half from each of the two CTAs, all counted on the leader's barrier.
+  const uint32_t stage_tx_bytes = kTwoCta ? 2 * (kABytes + b_half_bytes) : kABytes + 2 * b_half_bytes;
+  const int out_cols_per_tile = SWIGLU ? half_n : tile_n;
+  const int n_blocks = ceil_div<int>(g.n_out, out_cols_per_tile);
+  __syncthreads();
+  for (int i = tid; i <= num_groups; i += blockDim.x) gt.tile_start[i] *= static_cast<uint32_t>(n_blocks);
+  __syncthreads();
   const uint32_t total_tiles = gt.tile_start[num_groups];
+  if (warp == 0 && lane == 0) tc::tma_prefetch_desc(&tmap_b);
 
   // ---- roles ----------------------------------------------------------------
   if (warp == 0) {
@@ -533,7 +563,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (ew == 0) {
           ptx::fence_acq_rel_sys();
-          const uint32_t units = g.arrival_units_per_tile;
+          const uint32_t units = static_cast<uint32_t>(p.comb_units / n_blocks);
           for (int j = lane; j < kBlockM; j += 32) {
             const uint32_t tok = ctl->sig_token[buf][j];
             if (tok == kNoSignal) continue;
@@ -610,7 +640,7 @@ size_t smem_bytes(int num_groups) {
 }
 
 template <bool SWIGLU, bool kFromStaging, bool kToPeers, bool kTwoCta>
-void launch_one(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const GroupedGemmArgs& g,
+void launch_one(const CUtensorMap& tmap_a, const WeightMaps& tmap_b, const GroupedGemmArgs& g,
                 int num_groups, int grid, cudaStream_t stream) {
   auto* kernel = grouped_gemm_kernel<SWIGLU, kFromStaging, kToPeers, kTwoCta>;
   CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -631,7 +661,7 @@ void launch_one(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const Grou
 }
 
 template <bool SWIGLU, bool kFromStaging, bool kToPeers>
-void launch_variant(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
+void launch_variant(const CUtensorMap& tmap_a, const WeightMaps& tmap_b,
                     const GroupedGemmArgs& g, int num_groups, int grid, bool two_cta,
                     cudaStream_t stream) {
   if (two_cta && grid >= 2) {
@@ -641,13 +671,15 @@ void launch_variant(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b,
   }
 }
 
-// A CTA pair pays off when experts have enough rows to fill 256-row tiles.
+// A CTA pair is ~15 % faster per flop, but an expert's last 256-row tile wastes up
+// to 256 rows of MMA work (128 for single CTAs).  With rows per expert only known
+// on the device, the pair form is chosen when that worst case stays small.
 bool want_two_cta(const GroupedGemmCall& c) {
   if (c.cta_pair >= 0) return c.cta_pair != 0;
   const int64_t rows = c.expected_total_rows > 0
                            ? c.expected_total_rows
                            : static_cast<int64_t>(c.num_experts) * c.rows_per_expert;
-  return rows / std::max(1, c.num_experts) > 160;
+  return rows / std::max(1, c.num_experts) >= 2048;
 }
 
 void check_common(const GroupedGemmCall& c) {
@@ -656,15 +688,6 @@ void check_common(const GroupedGemmCall& c) {
   PPLX_CHECK(c.n_out > 0 && c.n_out % 8 == 0, "the output width must be a positive multiple of 8");
   PPLX_CHECK(c.half_n == 0 || (c.half_n % 8 == 0 && c.half_n >= 16 && c.half_n <= 128),
              "half_n must be a multiple of 8 in [16, 128]");
-}
-
-// Without a device round trip the host only knows the capacity; callers that know
-// better pass an estimate of the total rows.
-int64_t expected_m_tiles(const GroupedGemmCall& c, int tile_m) {
-  const int64_t rows = c.expected_total_rows > 0
-                           ? c.expected_total_rows
-                           : static_cast<int64_t>(c.num_experts) * c.rows_per_expert;
-  return std::max<int64_t>(c.num_experts > 0 ? 1 : 0, ceil_div<int64_t>(rows, tile_m));
 }
 
 GroupedGemmArgs base_args(const GroupedGemmCall& c) {
@@ -681,31 +704,27 @@ GroupedGemmArgs base_args(const GroupedGemmCall& c) {
   return g;
 }
 
-CUtensorMap weight_map(const GroupedGemmCall& c, int half_n) {
+// Candidate tile widths (weight rows per B half) and one weight map for each.  A
+// forced width leaves a single candidate; `units` > 0 (peer-storing epilogue) keeps
+// only the widths whose column-block count divides the arrival units of a row.
+WeightMaps weight_maps(const GroupedGemmCall& c, GroupedGemmArgs& g, int units) {
+  static const int kCandidates[kNumTileWidths] = {128, 112, 96, 80, 64};
   const int64_t w_rows = c.swiglu ? 2 * static_cast<int64_t>(c.n_out) : c.n_out;
-  return make_operand_map(c.w, c.num_experts, w_rows, c.k, c.w_stride_row, c.w_stride_e, half_n);
-}
-
-// Width of one B half (multiple of 8, at most 128).  The grid runs in waves of
-// `sms` tiles; a narrower tile can fill the last wave better: minimise
-// waves * width.  `m_tiles` is the expected number of 128-row blocks over all
-// experts (the real one is only known on the device).
-int pick_half_n(int n_out, bool swiglu, int64_t m_tiles, int sms, int forced) {
-  if (forced > 0) return forced;
-  const int per_half = swiglu ? 1 : 2;  // output columns per tile = per_half * half_n
-  int best = 128;
-  double best_cost = 1e300;
-  for (int half = 128; half >= 64; half -= 8) {
-    const int64_t n_blocks = ceil_div<int64_t>(n_out, per_half * half);
-    const int64_t waves = ceil_div<int64_t>(std::max<int64_t>(1, m_tiles) * n_blocks, sms);
-    // small fixed cost per tile (pipeline fill, epilogue hand-over)
-    const double cost = static_cast<double>(waves) * (half + 4);
-    if (cost < best_cost - 1e-9) {
-      best_cost = cost;
-      best = half;
-    }
+  WeightMaps maps{};
+  int valid = 0;
+  for (int i = 0; i < kNumTileWidths; ++i) {
+    int half = kCandidates[i];
+    if (c.half_n > 0) half = (i == 0) ? c.half_n : 0;
+    if (half > 0 && units > 0 && units % ceil_div(c.n_out, 2 * half) != 0) half = 0;
+    g.widths[i] = half;
+    // Unused slots still need a well-formed map.
+    maps.m[i] = make_operand_map(c.w, c.num_experts, w_rows, c.k, c.w_stride_row, c.w_stride_e,
+                                 half > 0 ? half : 128);
+    valid += half > 0;
   }
-  return best;
+  PPLX_CHECK(valid > 0, "no tile width fits: the arrival units of a row ("
+                            << units << ") must be a multiple of the output's column blocks");
+  return maps;
 }
 
 }  // namespace
@@ -720,9 +739,7 @@ void launch_grouped_gemm(const GroupedGemmCall& c, cudaStream_t stream) {
   const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
   const bool two_cta = want_two_cta(c);
   GroupedGemmArgs g = base_args(c);
-  g.half_n = pick_half_n(c.n_out, c.swiglu, expected_m_tiles(c, two_cta ? 256 : 128),
-                         two_cta ? grid / 2 : grid, c.half_n);
-  const CUtensorMap tmap_b = weight_map(c, g.half_n);
+  const WeightMaps tmap_b = weight_maps(c, g, 0);
   if (c.swiglu) launch_variant<true, false, false>(tmap_a, tmap_b, g, c.num_experts, grid, two_cta, stream);
   else launch_variant<false, false, false>(tmap_a, tmap_b, g, c.num_experts, grid, two_cta, stream);
 }
@@ -746,9 +763,7 @@ void launch_gemm_from_staging(const GroupedGemmCall& c, const A2AParams& p,
   const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
   const bool two_cta = want_two_cta(c);
   GroupedGemmArgs g = base_args(c);
-  g.half_n = pick_half_n(c.n_out, c.swiglu, expected_m_tiles(c, two_cta ? 256 : 128),
-                         two_cta ? grid / 2 : grid, c.half_n);
-  const CUtensorMap tmap_b = weight_map(c, g.half_n);
+  const WeightMaps tmap_b = weight_maps(c, g, 0);
   g.out_num_tokens = out_num_tokens;
   g.a2a = p;
   launch_variant<true, true, false>(tmap_a, tmap_b, g, p.nle, grid, two_cta, stream);
@@ -763,25 +778,12 @@ void launch_gemm_to_peers(const GroupedGemmCall& c, const A2AParams& p, cudaStre
              "counts must be the all-to-all's received-row counts");
   const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
   const bool two_cta = want_two_cta(c);
-  // The column-block count must divide the arrival units: take the widest tile that does.
-  int half_n = 0;
-  for (int half = 128; half >= 64 && half_n == 0; half -= 8) {
-    if (p.comb_units % ceil_div(c.n_out, 2 * half) == 0) half_n = half;
-  }
-  PPLX_CHECK(half_n != 0, "combine units (" << p.comb_units
-                                            << ") match no column blocking of the output");
-  const int n_blocks = ceil_div(c.n_out, 2 * half_n);
-  PPLX_CHECK(p.comb_units % n_blocks == 0,
-             "combine units (" << p.comb_units << ") must be a multiple of the "
-                               << n_blocks << " column blocks of the output");
   PPLX_CHECK(p.dp_size <= 8, "at most 8 replicas per DP group");
   const CUtensorMap tmap_a = make_operand_map(c.x, c.num_experts, c.rows_per_expert, c.k,
                                               c.x_stride_row, c.x_stride_e);
   GroupedGemmArgs g = base_args(c);
-  g.half_n = half_n;
-  const CUtensorMap tmap_b = weight_map(c, g.half_n);
+  const WeightMaps tmap_b = weight_maps(c, g, p.comb_units);
   g.out = nullptr;
-  g.arrival_units_per_tile = static_cast<uint32_t>(p.comb_units / n_blocks);
   g.a2a = p;
   launch_variant<false, false, true>(tmap_a, tmap_b, g, c.num_experts, grid, two_cta, stream);
 }

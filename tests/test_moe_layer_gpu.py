@@ -70,11 +70,11 @@ def test_fused_layer_in_an_emulated_world(world, dp_size, m):
     begins, so no kernel ever waits for a later launch."""
     import pplx_kernels_b200 as pk
 
-    # m = 400 gives every expert enough rows for the CTA-pair form of both GEMMs.
+    # For m = 400 a large row hint selects the CTA-pair form of both GEMMs.
     cfg = TINY
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    expect = m * cfg.experts_per_token // dp_size
+    expect = (1 << 20) if m >= 400 else m * cfg.experts_per_token // dp_size
     atas = pk.AllToAll.local_world(m, cfg.num_experts, cfg.experts_per_token, world, dp_size,
                                    cfg.hidden_dim, cfg.hidden_dim * 2, 0)
     layers = [MoELayer(cfg, m, rank=r, world_size=world, dp_size=dp_size, device=dev,
