@@ -99,7 +99,10 @@ void Runtime::alltoall(void* dest, const void* src, size_t chunk_bytes, cudaStre
   a.chunk_bytes = chunk_bytes;
   a.rank = my_pe();
   a.world = world;
-  const int blocks = static_cast<int>(std::clamp<size_t>(chunk_bytes / (16 * 512 * 4), 1, 16));
+  // Enough blocks to keep every SM storing: about two waves over all peers.
+  const int per_peer = std::max(1, 2 * get_sm_count() / world);
+  const int blocks = static_cast<int>(
+      std::clamp<size_t>(chunk_bytes / (16 * 512 * 4), 1, static_cast<size_t>(per_peer)));
   CUDA_CHECK(launch_alltoall_copy(a, blocks, stream));
   barrier_on_stream(stream);
 }

@@ -108,7 +108,10 @@ def bench_config(cfg: MoEConfig, rank: int, world: int, dev: torch.device, zipf:
     }
     disp_bytes = cfg.max_num_tokens * cfg.experts_per_token * per_token
     comb_bytes = cfg.max_num_tokens * cfg.experts_per_token * cfg.hidden_dim * cfg.out_dtype.itemsize
-    remote = (world - 1) / world if world > 1 else 1.0
+    # One GPU: nothing crosses NVLink; the floor is then local traffic (staging write +
+    # staging read + output write) over the measured copy bandwidth, expressed through the
+    # same formula with an equivalent "remote share".
+    remote = (world - 1) / world if world > 1 else 3.0 * NVLINK_GBS / 6542.0
     for k, name in enumerate(names):
         if (name == "torch_all_to_all" and (world == 1 or not dense_ok)) or (
                 name == "symm_all_to_all" and not dense_ok):
