@@ -23,7 +23,6 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import statistics
 import sys
 import time
 
@@ -45,21 +44,134 @@ def _peaks() -> dict:
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "fallback": True}
 
 
+def _unavailable(why: str) -> None:
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+
+
 def reference_arm(args: argparse.Namespace) -> None:
-    """Runs the unmodified reference if it could be installed under baseline/_ref."""
+    """The UNMODIFIED reference (installed under baseline/_ref) through its own
+    public API: ``pplx_kernels.AllToAll.intranode`` -- its CUDA-IPC / NVLink kernels -- with
+    ``dispatch`` and ``combine`` called as its own tests and benchmark call them.  Same shape,
+    same synthetic data, same timing as the other arm."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    lib = os.path.join(ref_dir, "pplx_kernels", "libpplx_kernels.so")
-    if not os.path.exists(lib):
-        print(json.dumps({
-            "impl": "reference",
-            "unavailable": "offline install failed: the reference's setup.py passes "
-                           "'-WITH_TESTS=OFF' to cmake, which cmake 3.x+ rejects, and its "
-                           "CMakeLists needs find_package(NVSHMEM) + MPI, neither of which "
-                           "has a CMake package in this image",
-        }))
-        return
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "reference library present but no runner is wired up"}))
+    if not os.path.exists(os.path.join(ref_dir, "pplx_kernels", "libpplx_kernels.so")):
+        return _unavailable("baseline/_ref is empty: the offline install of the reference has "
+                            "not been run on this machine (recipe in DESIGN.md)")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2:
+        return _unavailable("the reference refuses a single rank: AllToAll.intranode asserts "
+                            "world_size // dp_size > 1 (src/pplx_kernels/all_to_all.py:101)")
+    sys.path.insert(0, ref_dir)
+    import torch.distributed as dist
+    from pplx_kernels.all_to_all import AllToAll as RefAllToAll  # the reference's own class
+
+    from pplx_kernels_b200.utils.clocks import ClockSampler
+    from pplx_kernels_b200.utils.testing import MoEConfig, make_rank_inputs
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group(backend="cpu:gloo,cuda:nccl", device_id=dev)
+    try:
+        torch._C._distributed_c10d._register_process_group("default", dist.group.WORLD)
+    except Exception:
+        pass
+    tokens = args.tokens
+    cfg = MoEConfig(256, 8, 7168, tokens, torch.float8_e4m3fn, torch.bfloat16)
+    nle = cfg.num_experts // world
+    inp = make_rank_inputs(cfg, torch.Generator().manual_seed(1000 + rank), num_tokens=tokens,
+                           softmax_weights=True)
+    ata = RefAllToAll.intranode(
+        max_num_tokens=tokens, num_experts=cfg.num_experts,
+        experts_per_token=cfg.experts_per_token, rank=rank, world_size=world, dp_size=1,
+        hidden_dim=cfg.hidden_dim, hidden_dim_bytes=cfg.hidden_dim_bytes,
+        hidden_dim_scale_bytes=cfg.hidden_dim_scale_bytes)
+    h_x, h_scale = inp.x.view(torch.uint8).pin_memory(), inp.x_scale.pin_memory()
+    h_idx, h_w = inp.indices.pin_memory(), inp.weights.pin_memory()
+    x, x_scale = inp.x.to(dev), inp.x_scale.to(dev)
+    indices = inp.indices.to(dev).view(torch.uint32)
+    weights = inp.weights.to(dev)
+    bound_m = torch.tensor([tokens], dtype=torch.int32, device=dev).view(torch.uint32)
+    rows = tokens * world
+    counts = torch.zeros(nle, dtype=torch.int32, device=dev)
+    expert_x = torch.zeros(nle, rows, cfg.hidden_dim, dtype=torch.uint8, device=dev).view(cfg.in_dtype)
+    expert_scale = torch.zeros(nle, rows, cfg.hidden_dim_scale, device=dev)
+    expert_y = torch.randn(nle, rows, cfg.hidden_dim, device=dev).to(cfg.out_dtype)
+    out = torch.zeros(tokens, cfg.hidden_dim, dtype=cfg.out_dtype, device=dev)
+    h_out = torch.empty(tokens, cfg.hidden_dim, dtype=cfg.out_dtype).pin_memory()
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    sync_word = torch.zeros(1, device=dev)
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    def run(e2e: bool) -> torch.Tensor:
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+        for i in range(warmup + steps):
+            flush.add_(1)
+            dist.all_reduce(sync_word)  # device-side barrier on the launching stream
+            e = evs[i - warmup] if i >= warmup else None
+            if e:
+                e[0].record()
+            if e2e:
+                x.view(torch.uint8).copy_(h_x, non_blocking=True)
+                x_scale.copy_(h_scale, non_blocking=True)
+                indices.view(torch.int32).copy_(h_idx, non_blocking=True)
+                weights.copy_(h_w, non_blocking=True)
+            ata.dispatch(out_expert_num_tokens=counts, out_expert_x=expert_x,
+                         out_expert_x_scale=expert_scale, dp_x=x, dp_x_scale=x_scale,
+                         indices=indices, bound_m=bound_m)
+            if e:
+                e[1].record()
+            ata.combine(out_tokens=out, indices=indices, weights=weights, expert_y=expert_y,
+                        bound_m=bound_m)
+            if e2e:
+                h_out.copy_(out, non_blocking=True)
+            if e:
+                e[2].record()
+        torch.cuda.synchronize()
+        t = torch.tensor([[a.elapsed_time(b) for a, b in ((e[0], e[1]), (e[1], e[2]), (e[0], e[2]))]
+                          for e in evs], dtype=torch.float64, device=dev) * 1e3
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.cpu()
+
+    with ClockSampler(local_rank) as sampler:
+        t_main = run(False)
+        t_e2e = run(True)
+    ata.destroy()
+    step_mean = float(t_main[:, 2].mean())
+    value = world * tokens / (step_mean * 1e-6)
+    pub = PUBLISHED_US.get(tokens)
+    line = {
+        "metric": "MoE dispatch+combine tokens/s (DeepSeek-V3 shape: 256 experts, top-8, hidden "
+                  "7168, fp8 dispatch + bf16 combine)",
+        "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": step_mean / 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": (value / (world * tokens / ((pub["dispatch"] + pub["combine"]) * 1e-6))
+                        if pub else None),
+        "dtype": "fp8_e4m3 dispatch (fp32 scale per 128) / bf16 combine",
+        "data": "synthetic (uniform random distinct top-8 routing, random tokens, softmax weights)",
+        "config": {"model": "DeepSeek-V3 MoE layer all-to-all", "global_batch": world * tokens,
+                   "seq_len": 1, "tokens_per_gpu": tokens, "parallelism": f"ep{world}",
+                   "l2": "flushed between steps (256 MiB write)",
+                   "timing": "CUDA events per step, max over ranks, mean over steps",
+                   "reference_path": "pplx_kernels.AllToAll.intranode (unmodified, sm_100a build)"},
+        "latency_us": {str(tokens): {"dispatch_us_p50": float(t_main[:, 0].median()),
+                                     "combine_us_p50": float(t_main[:, 1].median()),
+                                     "step_us_p50": float(t_main[:, 2].median())}},
+        "clocks": sampler.summary(),
+        "e2e": {"value": world * tokens / (float(t_e2e[:, 2].mean()) * 1e-6), "unit": "tokens/s",
+                "us_per_step": float(t_e2e[:, 2].mean()),
+                "h2d_bytes_per_step": sum(t.numel() * t.element_size()
+                                          for t in (h_x, h_scale, h_idx, h_w)),
+                "d2h_bytes_per_step": h_out.numel() * h_out.element_size()},
+        "gpu_launches": 2 * steps,
+        "impl": "reference",
+    }
+    if rank == 0:
+        print(json.dumps(line))
+    dist.barrier()
+    dist.destroy_process_group()
 
 
 class Bench:
@@ -205,8 +317,10 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=128, help="tokens per GPU of the headline run")
     args = ap.parse_args()
     if args.impl == "reference":
-        if int(os.environ.get("RANK", "0")) == 0:
+        try:
             reference_arm(args)
+        except Exception as exn:  # the reference arm must never take the run down
+            _unavailable(f"reference run failed: {type(exn).__name__}: {str(exn)[:200]}")
         return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
