@@ -315,6 +315,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--tokens", type=int, default=128, help="tokens per GPU of the headline run")
+    ap.add_argument("--no-moe", action="store_true", help="skip the MoE-layer measurement")
     args = ap.parse_args()
     if args.impl == "reference":
         try:
@@ -380,6 +381,15 @@ def main() -> None:
             "combine_us_p50": float(t[:, 1].median()),
             "step_us_p50": float(t[:, 2].median()),
         }
+
+    # The second half of the headline metric: tokens/s of the whole MoE layer (dispatch ->
+    # SwiGLU expert FFN on the tcgen05 grouped GEMM -> combine), Mixtral-8x7B shape, bf16.
+    moe = None
+    if not args.no_moe:
+        from pplx_kernels_b200.utils.bench_moe import measure as measure_moe
+
+        moe = measure_moe("mixtral-8x7b", 512, iters=10, warmup=3, rank=rank, world=world,
+                          dev=torch.device("cuda", local_rank), flush=flush)
 
     # Roofline of the headline step: bytes that must move over the slower path.
     cfg = bench_main.cfg
@@ -450,6 +460,7 @@ def main() -> None:
             "d2h_bytes_per_step": d2h,
         },
         "gpu_launches": 2 * steps,
+        "moe_layer": moe,
         "impl": "ours",
     }
     if rank == 0:

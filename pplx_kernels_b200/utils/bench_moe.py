@@ -24,34 +24,21 @@ from pplx_kernels_b200.models.moe import MoELayer
 from pplx_kernels_b200.utils.testing import as_index_tensor, routing
 
 
-def main() -> None:
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--model", choices=sorted(CONFIGS), default="mixtral-8x7b")
-    ap.add_argument("--tokens", type=int, default=512, help="tokens per GPU")
-    ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--zipf", type=float, default=0.0)
-    ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays")
-    args = ap.parse_args()
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.init_process_group(backend="cpu:gloo,cuda:nccl", device_id=dev)
-    cfg = CONFIGS[args.model]
-    m = args.tokens
+def measure(model: str, tokens: int, iters: int, warmup: int, rank: int, world: int,
+            dev: torch.device, zipf: float = 0.0, graph: bool = False,
+            flush: torch.Tensor | None = None) -> dict:
+    """Times the MoE layer of `model` at `tokens` per GPU, composed and fused.  With more than one
+    rank torch.distributed must be initialised (NCCL for CUDA tensors)."""
+    cfg = CONFIGS[model]
+    m = tokens
     layer = MoELayer(cfg, max_num_tokens=m, rank=rank, world_size=world, device=dev)
     gen = torch.Generator().manual_seed(100 + rank)
     x = torch.randn(m, cfg.hidden_dim, generator=gen).to(torch.bfloat16).to(dev)
-    idx = as_index_tensor(routing(m, cfg.num_experts, cfg.experts_per_token, gen, args.zipf), dev)
+    idx = as_index_tensor(routing(m, cfg.num_experts, cfg.experts_per_token, gen, zipf), dev)
     w = torch.softmax(torch.randn(m, cfg.experts_per_token, generator=gen), dim=-1).to(dev)
     out = torch.zeros(m, cfg.hidden_dim, dtype=torch.bfloat16, device=dev)
-    flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    if flush is None:
+        flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
 
     def barrier() -> None:
         if world > 1:
@@ -59,35 +46,36 @@ def main() -> None:
 
     res = {}
     for name, fused in (("composed", False), ("fused", True)):
-        graph = None
-        if args.graph:
+        cuda_graph = None
+        if graph:
             layer(x, idx, w, out=out, fused=fused)
             torch.cuda.synchronize()
             barrier()
             stream = torch.cuda.Stream()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.stream(stream), torch.cuda.graph(graph, stream=stream):
+            cuda_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(stream), torch.cuda.graph(cuda_graph, stream=stream):
                 layer(x, idx, w, out=out, fused=fused)
         times = []
-        for it in range(args.warmup + args.iters):
+        for it in range(warmup + iters):
             flush.add_(1)
             torch.cuda.synchronize()
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            if graph is not None:
-                graph.replay()
+            if cuda_graph is not None:
+                cuda_graph.replay()
             else:
                 layer(x, idx, w, out=out, fused=fused)
             e1.record()
             torch.cuda.synchronize()
-            if it >= args.warmup:
+            if it >= warmup:
                 times.append(e0.elapsed_time(e1) * 1e3)
         t = torch.tensor(times, dtype=torch.float64, device=dev)
         if world > 1:
             torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         res[name] = float(t.median())
     layer.check_status()
+    layer.destroy()
 
     peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
     try:
@@ -108,17 +96,39 @@ def main() -> None:
         "nvlink_us_each_way": wire_bytes / 770e3,
     }
     floor = max(floors["compute_us"], floors["weights_hbm_us"], 2 * floors["nvlink_us_each_way"])
+    best = min(res["fused"], res["composed"])
+    return {
+        "model": cfg.name, "n_gpus": world, "tokens_per_gpu": m, "graph": graph, "zipf": zipf,
+        "composed_us_p50": res["composed"], "fused_us_p50": res["fused"],
+        "fused_tokens_per_s": world * m / (res["fused"] * 1e-6),
+        "composed_tokens_per_s": world * m / (res["composed"] * 1e-6),
+        "floors_us": floors,
+        "fused_frac_of_roofline": floor / res["fused"],
+        "best_frac_of_roofline": floor / best,
+    }
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", choices=sorted(CONFIGS), default="mixtral-8x7b")
+    ap.add_argument("--tokens", type=int, default=512, help="tokens per GPU")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--zipf", type=float, default=0.0)
+    ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays")
+    args = ap.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        torch.distributed.init_process_group(backend="cpu:gloo,cuda:nccl", device_id=dev)
+    row = measure(args.model, args.tokens, args.iters, args.warmup, rank, world, dev, args.zipf,
+                  args.graph)
     if rank == 0:
-        print(json.dumps({
-            "model": cfg.name, "n_gpus": world, "tokens_per_gpu": m, "graph": args.graph,
-            "zipf": args.zipf,
-            "composed_us_p50": res["composed"], "fused_us_p50": res["fused"],
-            "fused_tokens_per_s": world * m / (res["fused"] * 1e-6),
-            "composed_tokens_per_s": world * m / (res["composed"] * 1e-6),
-            "floors_us": floors,
-            "fused_frac_of_roofline": floor / res["fused"],
-        }))
-    layer.destroy()
+        print(json.dumps(row))
     if world > 1:
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
