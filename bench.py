@@ -44,6 +44,40 @@ def _peaks() -> dict:
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "fallback": True}
 
 
+class PackedInputs:
+    """One pinned host buffer and one device buffer holding [x | x_scale | indices | weights]
+    of a step, so that the end-to-end path uploads a step's inputs with a single copy.  Both
+    arms use it."""
+
+    def __init__(self, inp, dev: torch.device) -> None:
+        parts = [inp.x.view(torch.uint8).reshape(-1), inp.x_scale.view(torch.uint8).reshape(-1),
+                 inp.indices.to(torch.int32).view(torch.uint8).reshape(-1),
+                 inp.weights.view(torch.uint8).reshape(-1)]
+        offs, total = [], 0
+        for t in parts:
+            offs.append(total)
+            total += (t.numel() + 255) // 256 * 256
+        self.host = torch.zeros(total, dtype=torch.uint8).pin_memory()
+        for o, t in zip(offs, parts):
+            self.host[o:o + t.numel()].copy_(t)
+        self.dev = self.host.to(dev)
+        m, hidden = inp.x.shape
+
+        def view(i: int, t: torch.Tensor, dtype: torch.dtype, shape) -> torch.Tensor:
+            return self.dev[offs[i]:offs[i] + t.numel()].view(dtype).view(shape)
+
+        self.x = view(0, parts[0], inp.x.dtype, (m, hidden))
+        self.x_scale = view(1, parts[1], torch.float32, tuple(inp.x_scale.shape))
+        self.indices = view(2, parts[2], torch.uint32, tuple(inp.indices.shape))
+        self.weights = view(3, parts[3], torch.float32, tuple(inp.weights.shape))
+
+    def upload(self) -> None:
+        self.dev.copy_(self.host, non_blocking=True)
+
+    def nbytes(self) -> int:
+        return self.host.numel()
+
+
 def _unavailable(why: str) -> None:
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why}))
@@ -88,11 +122,8 @@ def reference_arm(args: argparse.Namespace) -> None:
         experts_per_token=cfg.experts_per_token, rank=rank, world_size=world, dp_size=1,
         hidden_dim=cfg.hidden_dim, hidden_dim_bytes=cfg.hidden_dim_bytes,
         hidden_dim_scale_bytes=cfg.hidden_dim_scale_bytes)
-    h_x, h_scale = inp.x.view(torch.uint8).pin_memory(), inp.x_scale.pin_memory()
-    h_idx, h_w = inp.indices.pin_memory(), inp.weights.pin_memory()
-    x, x_scale = inp.x.to(dev), inp.x_scale.to(dev)
-    indices = inp.indices.to(dev).view(torch.uint32)
-    weights = inp.weights.to(dev)
+    packed = PackedInputs(inp, dev)
+    x, x_scale, indices, weights = packed.x, packed.x_scale, packed.indices, packed.weights
     bound_m = torch.tensor([tokens], dtype=torch.int32, device=dev).view(torch.uint32)
     rows = tokens * world
     counts = torch.zeros(nle, dtype=torch.int32, device=dev)
@@ -114,10 +145,7 @@ def reference_arm(args: argparse.Namespace) -> None:
             if e:
                 e[0].record()
             if e2e:
-                x.view(torch.uint8).copy_(h_x, non_blocking=True)
-                x_scale.copy_(h_scale, non_blocking=True)
-                indices.view(torch.int32).copy_(h_idx, non_blocking=True)
-                weights.copy_(h_w, non_blocking=True)
+                packed.upload()
             ata.dispatch(out_expert_num_tokens=counts, out_expert_x=expert_x,
                          out_expert_x_scale=expert_scale, dp_x=x, dp_x_scale=x_scale,
                          indices=indices, bound_m=bound_m)
@@ -162,8 +190,7 @@ def reference_arm(args: argparse.Namespace) -> None:
         "clocks": sampler.summary(),
         "e2e": {"value": world * tokens / (float(t_e2e[:, 2].mean()) * 1e-6), "unit": "tokens/s",
                 "us_per_step": float(t_e2e[:, 2].mean()),
-                "h2d_bytes_per_step": sum(t.numel() * t.element_size()
-                                          for t in (h_x, h_scale, h_idx, h_w)),
+                "h2d_bytes_per_step": packed.nbytes(),
                 "d2h_bytes_per_step": h_out.numel() * h_out.element_size()},
         "gpu_launches": 2 * steps,
         "impl": "reference",
@@ -191,16 +218,11 @@ class Bench:
         nle = cfg.num_experts // self.world
         gen = torch.Generator().manual_seed(1000 + self.rank)
         inp = make_rank_inputs(cfg, gen, num_tokens=tokens, softmax_weights=True)
-        # Host copies in pinned memory (the end-to-end path uploads them every step).
-        self.h_x = inp.x.view(torch.uint8).pin_memory()
-        self.h_scale = inp.x_scale.pin_memory()
-        self.h_idx = inp.indices.pin_memory()
-        self.h_w = inp.weights.pin_memory()
+        # Host copy in pinned memory (the end-to-end path uploads it every step).
         dev = self.device
-        self.x = inp.x.to(dev)
-        self.x_scale = inp.x_scale.to(dev)
-        self.indices = as_index_tensor(inp.indices, dev)
-        self.weights = inp.weights.to(dev)
+        self.packed = PackedInputs(inp, dev)
+        self.x, self.x_scale = self.packed.x, self.packed.x_scale
+        self.indices, self.weights = self.packed.indices, self.packed.weights
         self.bound_m = torch.tensor([tokens], dtype=torch.int32, device=dev).view(torch.uint32)
         rows = tokens * self.world
         self.counts = torch.zeros(nle, dtype=torch.int32, device=dev)
@@ -222,16 +244,13 @@ class Bench:
         self.ata.combine(self.out, self.indices, self.weights, self.expert_y, self.bound_m)
 
     def upload(self) -> None:
-        self.x.view(torch.uint8).copy_(self.h_x, non_blocking=True)
-        self.x_scale.copy_(self.h_scale, non_blocking=True)
-        self.indices.view(torch.int32).copy_(self.h_idx, non_blocking=True)
-        self.weights.copy_(self.h_w, non_blocking=True)
+        self.packed.upload()
 
     def download(self) -> None:
         self.h_out.copy_(self.out, non_blocking=True)
 
     def h2d_bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in (self.h_x, self.h_scale, self.h_idx, self.h_w))
+        return self.packed.nbytes()
 
     def d2h_bytes(self) -> int:
         return self.h_out.numel() * self.h_out.element_size()
@@ -349,7 +368,7 @@ def main() -> None:
     results: dict[int, dict] = {}
     e2e_us = None
     bench_main = Bench(args.tokens)
-    with ClockSampler(local_rank) as sampler:
+    with ClockSampler(local_rank, period_ms=50) as sampler:
         if world > 1:
             torch.distributed.barrier()
         torch.cuda.synchronize()
@@ -359,8 +378,8 @@ def main() -> None:
         if world > 1:
             torch.distributed.barrier()
         wall1 = time.perf_counter()
+        t_e2e = time_steps(bench_main, steps, warmup, flush, e2e=True)
     clocks = sampler.summary()
-    t_e2e = time_steps(bench_main, steps, warmup, flush, e2e=True)
     e2e_us = float(t_e2e[:, 2].mean())
     nccl_us = nccl_baseline(bench_main, min(steps, 50), 5, flush)
     h2d, d2h = bench_main.h2d_bytes(), bench_main.d2h_bytes()
