@@ -46,7 +46,7 @@ def _sources() -> list[Path]:
 
 def _headers() -> list[Path]:
     hs: list[Path] = []
-    for ext in ("*.h", "*.cuh", "*.hpp"):
+    for ext in ("*.h", "*.cuh", "*.hpp", "*.inl"):
         hs += sorted(CSRC.rglob(ext))
     return hs
 

@@ -76,3 +76,32 @@ void launch_gemm_from_staging(const GroupedGemmCall& call, const A2AParams& p,
 void launch_gemm_to_peers(const GroupedGemmCall& call, const A2AParams& p, cudaStream_t stream);
 
 }  // namespace pplx
+
+namespace pplx {
+
+// Block-scaled fp8 (e4m3) grouped GEMM.  Payload strides in bytes (= elements), scale
+// strides in floats; the innermost strides are 1.  sa: one scale per row and 128 columns
+// of K; sw: one per 128 x 128 block of w.
+struct Fp8GemmCall {
+  const void* x = nullptr;      // e4m3 [E][rows][k]
+  int64_t x_stride_e = 0, x_stride_row = 0;
+  const float* sa = nullptr;    // [E][rows][ceil(k / 128)]
+  int64_t sa_stride_e = 0, sa_stride_row = 0;
+  const void* w = nullptr;      // e4m3 [E][n_out or 2 * n_out][k]
+  int64_t w_stride_e = 0, w_stride_row = 0;
+  const float* sw = nullptr;    // [E][ceil(w rows / 128)][ceil(k / 128)]
+  int64_t sw_stride_e = 0, sw_stride_row = 0;
+  const int32_t* counts = nullptr;
+  void* out = nullptr;          // bf16 [E][rows][n_out], or e4m3 with swiglu_quant
+  int64_t out_stride_e = 0, out_stride_row = 0;  // elements
+  float* out_scale = nullptr;   // swiglu_quant: [E][rows][n_out / 128]
+  int64_t os_stride_e = 0, os_stride_row = 0;
+  uint32_t* status = nullptr;
+  int num_experts = 0, rows_per_expert = 0, n_out = 0, k = 0;
+  bool swiglu_quant = false;    // w = [gate; up]; result silu(gate) * up quantised to e4m3
+  int num_sms = 0;
+};
+
+void launch_grouped_gemm_fp8(const Fp8GemmCall& call, cudaStream_t stream);
+
+}  // namespace pplx

@@ -1,0 +1,280 @@
+// Kernel body of grouped_gemm_fp8_sm100.cu (included there; kept in a second file
+// only for length).
+namespace pplx {
+namespace {
+
+struct Fp8GemmArgs {
+  const int32_t* counts;   // [E]
+  const float* sa;         // [E][rows][kblocks]
+  int64_t sa_stride_e, sa_stride_row;
+  const float* sw;         // [E][ceil(w_rows / 128)][kblocks]
+  int64_t sw_stride_e, sw_stride_row;
+  void* out;               // bf16 [E][rows][n_out]  or  e4m3 [E][rows][n_out]
+  int64_t out_stride_e, out_stride_row;  // elements
+  float* out_scale;        // kSwiGLUQuant: [E][rows][n_out / 128]
+  int64_t os_stride_e, os_stride_row;
+  uint32_t* status;
+  int num_experts, rows_per_expert, n_out, k;
+};
+
+template <bool kSwiGLUQuant>
+__global__ void __launch_bounds__(kThreads, 1)
+    grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                            const __grid_constant__ CUtensorMap tmap_b,
+                            const __grid_constant__ Fp8GemmArgs g) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* stages = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  SharedControl* ctl = reinterpret_cast<SharedControl*>(stages + kStages * kStageBytes);
+  uint32_t* tile_start = reinterpret_cast<uint32_t*>(ctl + 1);  // [E + 1]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+  const int out_cols_per_tile = kSwiGLUQuant ? kTileN / 2 : kTileN;
+  const int n_blocks = ceil_div<int>(g.n_out, out_cols_per_tile);
+  const int num_kb = ceil_div<int>(g.k, kBlockKBytes);
+
+  for (int e = tid; e < g.num_experts; e += blockDim.x) {
+    const int rows = min(max(g.counts[e], 0), g.rows_per_expert);
+    tile_start[e] = static_cast<uint32_t>(ceil_div<int>(rows, kBlockM) * n_blocks);
+  }
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      tc::mbar_init(&ctl->full[s], 1);
+      tc::mbar_init(&ctl->empty[s], 1);
+    }
+    tc::mbar_init(&ctl->part_full, 1);
+    tc::mbar_init(&ctl->part_empty, 4);
+    ctl->abort_flag = 0;
+    tc::fence_mbar_init();
+    tc::tma_prefetch_desc(&tmap_a);
+    tc::tma_prefetch_desc(&tmap_b);
+  }
+  __syncthreads();
+  if (warp == 0) warp_exclusive_scan_smem(tile_start, g.num_experts, lane, true);
+  if (warp == 2) {
+    tc::tmem_alloc(&ctl->tmem_base, kTmemCols);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tmem_base = ctl->tmem_base;
+  const uint32_t total_tiles = tile_start[g.num_experts];
+
+  if (warp == 0) {
+    if (tc::elect_one()) {
+      uint32_t stage = 0, phase = 0, pending = 0, pending_phase = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const Fp8Tile c = locate(tile_start, g.counts, g.num_experts, g.rows_per_expert, t);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = tc::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, kWaitLimitNs);
+          if (!ok) break;
+          uint8_t* a_dst = stages + stage * kStageBytes;
+          uint8_t* b_dst = a_dst + kABytes;
+          tc::mbar_arrive_expect_tx(&ctl->full[stage], kStageBytes);
+          pending |= 1u << stage;
+          pending_phase = (pending_phase & ~(1u << stage)) | (phase << stage);
+          tc::tma_load_3d(a_dst, &tmap_a, &ctl->full[stage], kb * kBlockKBytes, c.m_blk * kBlockM,
+                          c.expert);
+          // Two halves of 128 weight rows: gate and up rows, or consecutive rows.
+          const int row0 = kSwiGLUQuant ? c.n_blk * (kTileN / 2) : c.n_blk * kTileN;
+          const int row1 = kSwiGLUQuant ? g.n_out + row0 : row0 + kTileN / 2;
+          tc::tma_load_3d(b_dst, &tmap_b, &ctl->full[stage], kb * kBlockKBytes, row0, c.expert);
+          tc::tma_load_3d(b_dst + kBBytes / 2, &tmap_b, &ctl->full[stage], kb * kBlockKBytes, row1,
+                          c.expert);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok || *abort_flag != 0u) {
+        const uint64_t t0 = ptx::globaltimer_ns();
+        for (int s = 0; s < kStages; ++s) {
+          if (!((pending >> s) & 1u)) continue;
+          while (!tc::mbar_try_wait(&ctl->full[s], (pending_phase >> s) & 1u)) {
+            if (ptx::globaltimer_ns() - t0 > 100000000ull) break;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (tc::elect_one()) {
+      // kind::f8f6f4, e4m3 x e4m3 -> f32, M = 128, N = 256.
+      const uint32_t idesc = tc::make_instr_desc(0u, kBlockM, kTileN);
+      uint32_t stage = 0, phase = 0, round = 0;
+      bool ok = true;
+      for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        for (int kb = 0; kb < num_kb && ok; ++kb, ++round) {
+          // The scratch accumulator is reused for every K block.
+          ok = tc::mbar_wait(&ctl->part_empty, (round & 1u) ^ 1u, abort_flag, kWaitLimitNs);
+          if (!ok) break;
+          ok = tc::mbar_wait(&ctl->full[stage], phase, abort_flag, kWaitLimitNs);
+          if (!ok) break;
+          tc::tc_fence_after_sync();
+          const uint8_t* a_src = stages + stage * kStageBytes;
+          const uint64_t a_desc = tc::make_smem_desc_sw128(a_src);
+          const uint64_t b_desc = tc::make_smem_desc_sw128(a_src + kABytes);
+#pragma unroll
+          for (int k = 0; k < kBlockKBytes / kUmmaKBytes; ++k) {
+            tc::mma_f8_ss(tmem_base, tc::advance_smem_desc(a_desc, k * kUmmaKBytes),
+                          tc::advance_smem_desc(b_desc, k * kUmmaKBytes), idesc, k != 0);
+          }
+          tc::mma_commit(&ctl->empty[stage]);
+          tc::mma_commit(&ctl->part_full);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp >= 4) {
+    const int ew = warp - 4;
+    const uint32_t lane_base = static_cast<uint32_t>(ew * 32) << 16;
+    const uint32_t t_part = tmem_base + lane_base;        // scratch, columns [0, 256)
+    const uint32_t t_acc = tmem_base + lane_base + 256;   // result, columns [256, 512)
+    const int kblocks = num_kb;
+    uint32_t round = 0;
+    bool ok = true;
+    for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const Fp8Tile c = locate(tile_start, g.counts, g.num_experts, g.rows_per_expert, t);
+      const int row = c.m_blk * kBlockM + ew * 32 + lane;
+      const bool row_ok = row < c.rows;
+      const int safe_row = row_ok ? row : 0;
+      const float* sa_row = g.sa + c.expert * g.sa_stride_e + safe_row * g.sa_stride_row;
+      // Weight scale rows of the two halves of the tile.
+      const int wrow0 = kSwiGLUQuant ? c.n_blk * (kTileN / 2) : c.n_blk * kTileN;
+      const int wrow1 = kSwiGLUQuant ? g.n_out + wrow0 : wrow0 + kTileN / 2;
+      const int last_block = (((kSwiGLUQuant ? 2 : 1) * g.n_out) - 1) / 128;
+      const float* sw0 =
+          g.sw + c.expert * g.sw_stride_e + min(wrow0 / 128, last_block) * g.sw_stride_row;
+      const float* sw1 =
+          g.sw + c.expert * g.sw_stride_e + min(wrow1 / 128, last_block) * g.sw_stride_row;
+      for (int kb = 0; kb < kblocks && ok; ++kb, ++round) {
+        const float a_scale = __ldg(sa_row + kb);
+        const float s0 = a_scale * __ldg(sw0 + kb);
+        const float s1 = a_scale * __ldg(sw1 + kb);
+        ok = tc::mbar_wait(&ctl->part_full, round & 1u, abort_flag, kWaitLimitNs);
+        if (!ok) break;
+        tc::tc_fence_after_sync();
+#pragma unroll 1
+        for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
+          const float s = chunk < kTileN / 64 ? s0 : s1;
+          uint32_t part[32], acc[32];
+          tc::tmem_ld_32x32(t_part + chunk * 32, part);
+          if (kb != 0) tc::tmem_ld_32x32(t_acc + chunk * 32, acc);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float prev = kb != 0 ? __uint_as_float(acc[j]) : 0.f;
+            acc[j] = __float_as_uint(fmaf(__uint_as_float(part[j]), s, prev));
+          }
+          tmem_st_32x32(t_acc + chunk * 32, acc);
+        }
+        tmem_st_wait();
+        tc::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&ctl->part_empty);
+      }
+      if (!ok) break;
+
+      // ---- tile epilogue: the result of this warp's 32 rows is in t_acc ----------
+      if constexpr (kSwiGLUQuant) {
+        // 128 output columns = one scale block: silu(gate) * up, amax, e4m3.
+        float h[4][32];
+        float amax = 0.f;
+#pragma unroll
+        for (int chunk = 0; chunk < 4; ++chunk) {
+          uint32_t gate[32], up[32];
+          tc::tmem_ld_32x32(t_acc + chunk * 32, gate);
+          tc::tmem_ld_32x32(t_acc + 128 + chunk * 32, up);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float v = silu(__uint_as_float(gate[j])) * __uint_as_float(up[j]);
+            h[chunk][j] = v;
+            amax = fmaxf(amax, fabsf(v));
+          }
+        }
+        amax = fmaxf(amax, 1e-4f);
+        const float inv = 448.0f / amax;
+        if (row_ok) {
+          const int col0 = c.n_blk * 128;
+          uint8_t* orow = static_cast<uint8_t*>(g.out) + c.expert * g.out_stride_e +
+                          static_cast<int64_t>(row) * g.out_stride_row + col0;
+#pragma unroll
+          for (int chunk = 0; chunk < 4; ++chunk) {
+#pragma unroll
+            for (int v = 0; v < 2; ++v) {
+              if (col0 + chunk * 32 + v * 16 + 16 > g.n_out) continue;
+              uint32_t q[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int b = v * 16 + 4 * j;
+                const uint32_t p0 = __nv_cvt_float2_to_fp8x2(
+                    make_float2(h[chunk][b] * inv, h[chunk][b + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+                const uint32_t p1 = __nv_cvt_float2_to_fp8x2(
+                    make_float2(h[chunk][b + 2] * inv, h[chunk][b + 3] * inv), __NV_SATFINITE,
+                    __NV_E4M3);
+                q[j] = p0 | (p1 << 16);
+              }
+              int4 o;
+              o.x = q[0];
+              o.y = q[1];
+              o.z = q[2];
+              o.w = q[3];
+              *reinterpret_cast<int4*>(orow + chunk * 32 + v * 16) = o;
+            }
+          }
+          g.out_scale[c.expert * g.os_stride_e + static_cast<int64_t>(row) * g.os_stride_row +
+                      c.n_blk] = amax / 448.0f;
+        }
+      } else {
+        __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(g.out) + c.expert * g.out_stride_e +
+                              static_cast<int64_t>(row) * g.out_stride_row;
+        const int col0 = c.n_blk * kTileN;
+#pragma unroll 1
+        for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
+          uint32_t acc[32];
+          tc::tmem_ld_32x32(t_acc + chunk * 32, acc);
+          tc::tmem_ld_wait();
+          if (!row_ok) continue;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const int col = col0 + chunk * 32 + v * 8;
+            if (col + 8 > g.n_out) continue;
+            int4 o;
+            uint32_t* w = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(acc[v * 8 + 2 * j]),
+                                                             __uint_as_float(acc[v * 8 + 2 * j + 1]));
+              w[j] = *reinterpret_cast<const uint32_t*>(&b);
+            }
+            *reinterpret_cast<int4*>(orow + col) = o;
+          }
+        }
+      }
+      // The next tile's first K block overwrites t_acc only after its own scratch is
+      // full, which the MMA warp can only produce after this warp's part_empty
+      // arrivals above; the loads of t_acc here are complete (wait::ld).
+      tc::tc_fence_before_sync();
+    }
+  }
+
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 2) {
+    tc::tc_fence_after_sync();
+    tc::tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (tid == 0 && ctl->abort_flag != 0u && g.status != nullptr) *g.status = 1u;
+}
+
+}  // namespace
+}  // namespace pplx

@@ -50,3 +50,61 @@ def grouped_gemm_reference(x: torch.Tensor, w: torch.Tensor, counts: torch.Tenso
             y = torch.nn.functional.silu(gate) * up
         out[e, :m] = y
     return out
+
+
+def grouped_gemm_fp8(xq: torch.Tensor, sa: torch.Tensor, wq: torch.Tensor, sw: torch.Tensor,
+                     counts: torch.Tensor, swiglu_quant: bool = False,
+                     out: torch.Tensor | None = None, out_scale: torch.Tensor | None = None,
+                     status: torch.Tensor | None = None):
+    """Block-scaled fp8 grouped GEMM (tcgen05 ``kind::f8f6f4``).
+
+    ``xq`` [E, rows, K] and ``wq`` [E, N (or 2N), K] are ``float8_e4m3fn``; ``sa`` [E, rows,
+    K/128] holds one fp32 scale per row and 128 columns, ``sw`` [E, ceil(w rows/128), K/128]
+    one per 128 x 128 block of the weight.  Plain: returns bf16 [E, rows, N].  With
+    ``swiglu_quant`` (``wq`` stacks gate and up rows): returns ``(hq, hs)`` -- silu(gate) * up
+    quantised to e4m3 with one fp32 scale per row and 128 columns, the input format of the
+    next GEMM.
+    """
+    E, rows, _ = xq.shape
+    n_out = wq.size(1) // 2 if swiglu_quant else wq.size(1)
+    if swiglu_quant:
+        if out is None:
+            out = torch.empty(E, rows, n_out, dtype=torch.float8_e4m3fn, device=xq.device)
+        if out_scale is None:
+            out_scale = torch.empty(E, rows, n_out // 128, dtype=torch.float32, device=xq.device)
+    elif out is None:
+        out = torch.empty(E, rows, n_out, dtype=torch.bfloat16, device=xq.device)
+    _ops.grouped_gemm_fp8(xq, sa, wq, sw, counts, out, out_scale, swiglu_quant, status)
+    return (out, out_scale) if swiglu_quant else out
+
+
+def quantize_weight_blocks(w: torch.Tensor, block: int = 128) -> tuple[torch.Tensor, torch.Tensor]:
+    """w: [E, N, K] -> (e4m3 [E, N, K], fp32 scales [E, ceil(N/block), ceil(K/block)])."""
+    E, N, K = w.shape
+    nb, kb = (N + block - 1) // block, (K + block - 1) // block
+    wf = torch.nn.functional.pad(w.to(torch.float32), (0, kb * block - K, 0, nb * block - N))
+    v = wf.view(E, nb, block, kb, block)
+    amax = v.abs().amax(dim=(2, 4)).clamp(min=1e-4)
+    q = (v * (448.0 / amax)[:, :, None, :, None]).clamp(-448.0, 448.0)
+    q = q.view(E, nb * block, kb * block)[:, :N, :K].to(torch.float8_e4m3fn).contiguous()
+    return q, (amax / 448.0).contiguous()
+
+
+def grouped_gemm_fp8_reference(xq: torch.Tensor, sa: torch.Tensor, wq: torch.Tensor,
+                               sw: torch.Tensor, counts: torch.Tensor,
+                               swiglu: bool = False) -> torch.Tensor:
+    """Plain PyTorch fp32 statement: dequantise both operands, multiply, optional SwiGLU."""
+    E, rows, K = xq.shape
+    x = xq.to(torch.float32) * sa.repeat_interleave(128, dim=2)[:, :, :K]
+    w = wq.to(torch.float32) * sw.repeat_interleave(128, dim=1)[:, : wq.size(1)].repeat_interleave(
+        128, dim=2)[:, :, :K]
+    n_out = wq.size(1) // 2 if swiglu else wq.size(1)
+    out = torch.zeros(E, rows, n_out, dtype=torch.float32, device=xq.device)
+    for e, m in enumerate(counts.tolist()):
+        if m == 0:
+            continue
+        y = x[e, :m] @ w[e].t()
+        if swiglu:
+            y = torch.nn.functional.silu(y[:, :n_out]) * y[:, n_out:]
+        out[e, :m] = y
+    return out
