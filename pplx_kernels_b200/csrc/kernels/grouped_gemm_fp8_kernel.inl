@@ -43,8 +43,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc::mbar_init(&ctl->full[s], 1);
       tc::mbar_init(&ctl->empty[s], 1);
     }
-    tc::mbar_init(&ctl->part_full, 1);
-    tc::mbar_init(&ctl->part_empty, 4);
+    for (int b = 0; b < 2; ++b) {
+      tc::mbar_init(&ctl->part_full[b], 1);
+      tc::mbar_init(&ctl->part_empty[b], 8);
+    }
     ctl->abort_flag = 0;
     tc::fence_mbar_init();
     tc::tma_prefetch_desc(&tmap_a);
@@ -109,8 +111,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         for (int kb = 0; kb < num_kb && ok; ++kb, ++round) {
-          // The scratch accumulator is reused for every K block.
-          ok = tc::mbar_wait(&ctl->part_empty, (round & 1u) ^ 1u, abort_flag, kWaitLimitNs);
+          // K blocks alternate between the two scratch accumulators.
+          const uint32_t buf = round & 1u;
+          ok = tc::mbar_wait(&ctl->part_empty[buf], ((round >> 1) & 1u) ^ 1u, abort_flag,
+                             kWaitLimitNs);
           if (!ok) break;
           ok = tc::mbar_wait(&ctl->full[stage], phase, abort_flag, kWaitLimitNs);
           if (!ok) break;
@@ -120,11 +124,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           const uint64_t b_desc = tc::make_smem_desc_sw128(a_src + kABytes);
 #pragma unroll
           for (int k = 0; k < kBlockKBytes / kUmmaKBytes; ++k) {
-            tc::mma_f8_ss(tmem_base, tc::advance_smem_desc(a_desc, k * kUmmaKBytes),
+            tc::mma_f8_ss(tmem_base + buf * kTileN, tc::advance_smem_desc(a_desc, k * kUmmaKBytes),
                           tc::advance_smem_desc(b_desc, k * kUmmaKBytes), idesc, k != 0);
           }
           tc::mma_commit(&ctl->empty[stage]);
-          tc::mma_commit(&ctl->part_full);
+          tc::mma_commit(&ctl->part_full[buf]);
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -134,16 +138,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     __syncwarp();
   } else if (warp >= 4) {
-    const int ew = warp - 4;
-    const uint32_t lane_base = static_cast<uint32_t>(ew * 32) << 16;
-    const uint32_t t_part = tmem_base + lane_base;        // scratch, columns [0, 256)
-    const uint32_t t_acc = tmem_base + lane_base + 256;   // result, columns [256, 512)
-    const int kblocks = num_kb;
+    const int ew = (warp - 4) & 3;      // tensor-memory lanes [32 * ew, +32)
+    const int half = (warp - 4) >> 2;   // columns [64 * half, +64) of each 128-column half
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(ew * 32) << 16);
     uint32_t round = 0;
     bool ok = true;
     for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const Fp8Tile c = locate(tile_start, g.counts, g.num_experts, g.rows_per_expert, t);
-      const int row = c.m_blk * kBlockM + ew * 32 + lane;
+      const int tile_row = ew * 32 + lane;
+      const int row = c.m_blk * kBlockM + tile_row;
       const bool row_ok = row < c.rows;
       const int safe_row = row_ok ? row : 0;
       const float* sa_row = g.sa + c.expert * g.sa_stride_e + safe_row * g.sa_stride_row;
@@ -155,115 +158,119 @@ __global__ void __launch_bounds__(kThreads, 1)
           g.sw + c.expert * g.sw_stride_e + min(wrow0 / 128, last_block) * g.sw_stride_row;
       const float* sw1 =
           g.sw + c.expert * g.sw_stride_e + min(wrow1 / 128, last_block) * g.sw_stride_row;
-      for (int kb = 0; kb < kblocks && ok; ++kb, ++round) {
+
+      // acc[0..63]: columns 64*half.. of the first 128-column half of the tile,
+      // acc[64..127]: the same columns of the second half.
+      float acc[128];
+#pragma unroll
+      for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+      for (int kb = 0; kb < num_kb && ok; ++kb, ++round) {
         const float a_scale = __ldg(sa_row + kb);
         const float s0 = a_scale * __ldg(sw0 + kb);
         const float s1 = a_scale * __ldg(sw1 + kb);
-        ok = tc::mbar_wait(&ctl->part_full, round & 1u, abort_flag, kWaitLimitNs);
+        const uint32_t buf = round & 1u;
+        ok = tc::mbar_wait(&ctl->part_full[buf], (round >> 1) & 1u, abort_flag, kWaitLimitNs);
         if (!ok) break;
         tc::tc_fence_after_sync();
-#pragma unroll 1
-        for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
-          const float s = chunk < kTileN / 64 ? s0 : s1;
-          uint32_t part[32], acc[32];
-          tc::tmem_ld_32x32(t_part + chunk * 32, part);
-          if (kb != 0) tc::tmem_ld_32x32(t_acc + chunk * 32, acc);
-          tc::tmem_ld_wait();
+        const uint32_t t_part = t_lane + buf * kTileN + half * 64;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float prev = kb != 0 ? __uint_as_float(acc[j]) : 0.f;
-            acc[j] = __float_as_uint(fmaf(__uint_as_float(part[j]), s, prev));
+        for (int q = 0; q < 8; ++q) {  // 8 pieces of 16 columns: 4 per tile half
+          uint32_t part[16];
+          tmem_ld_32x16(t_part + (q >> 2) * 128 + (q & 3) * 16, part);
+          tc::tmem_ld_wait();
+          const float s = (q >> 2) == 0 ? s0 : s1;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            acc[q * 16 + j] = fmaf(__uint_as_float(part[j]), s, acc[q * 16 + j]);
           }
-          tmem_st_32x32(t_acc + chunk * 32, acc);
         }
-        tmem_st_wait();
         tc::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) tc::mbar_arrive(&ctl->part_empty);
+        if (lane == 0) tc::mbar_arrive(&ctl->part_empty[buf]);
+      }
+      // All eight epilogue warps leave together or not at all: the barriers below must
+      // never be entered by only some of them.
+      {
+        uint32_t all_ok;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p, q;\n\t"
+            "setp.ne.u32 q, %1, 0;\n\t"
+            "bar.red.and.pred p, 1, 256, q;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(all_ok)
+            : "r"(ok ? 1u : 0u)
+            : "memory");
+        ok = all_ok != 0u;
       }
       if (!ok) break;
 
-      // ---- tile epilogue: the result of this warp's 32 rows is in t_acc ----------
+      // ---- tile epilogue ------------------------------------------------------
       if constexpr (kSwiGLUQuant) {
-        // 128 output columns = one scale block: silu(gate) * up, amax, e4m3.
-        float h[4][32];
+        // acc[0..63] = gate, acc[64..127] = up for output columns 64*half.. of this tile's
+        // 128 output columns (one scale block); the row maximum needs the other half too.
         float amax = 0.f;
 #pragma unroll
-        for (int chunk = 0; chunk < 4; ++chunk) {
-          uint32_t gate[32], up[32];
-          tc::tmem_ld_32x32(t_acc + chunk * 32, gate);
-          tc::tmem_ld_32x32(t_acc + 128 + chunk * 32, up);
-          tc::tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float v = silu(__uint_as_float(gate[j])) * __uint_as_float(up[j]);
-            h[chunk][j] = v;
-            amax = fmaxf(amax, fabsf(v));
-          }
+        for (int j = 0; j < 64; ++j) {
+          acc[j] = silu(acc[j]) * acc[64 + j];
+          amax = fmaxf(amax, fabsf(acc[j]));
         }
-        amax = fmaxf(amax, 1e-4f);
+        ctl->row_amax[half][tile_row] = amax;
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        amax = fmaxf(fmaxf(ctl->row_amax[0][tile_row], ctl->row_amax[1][tile_row]), 1e-4f);
         const float inv = 448.0f / amax;
         if (row_ok) {
-          const int col0 = c.n_blk * 128;
+          const int col0 = c.n_blk * 128 + half * 64;
           uint8_t* orow = static_cast<uint8_t*>(g.out) + c.expert * g.out_stride_e +
                           static_cast<int64_t>(row) * g.out_stride_row + col0;
 #pragma unroll
-          for (int chunk = 0; chunk < 4; ++chunk) {
-#pragma unroll
-            for (int v = 0; v < 2; ++v) {
-              if (col0 + chunk * 32 + v * 16 + 16 > g.n_out) continue;
-              uint32_t q[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int b = v * 16 + 4 * j;
-                const uint32_t p0 = __nv_cvt_float2_to_fp8x2(
-                    make_float2(h[chunk][b] * inv, h[chunk][b + 1] * inv), __NV_SATFINITE, __NV_E4M3);
-                const uint32_t p1 = __nv_cvt_float2_to_fp8x2(
-                    make_float2(h[chunk][b + 2] * inv, h[chunk][b + 3] * inv), __NV_SATFINITE,
-                    __NV_E4M3);
-                q[j] = p0 | (p1 << 16);
-              }
-              int4 o;
-              o.x = q[0];
-              o.y = q[1];
-              o.z = q[2];
-              o.w = q[3];
-              *reinterpret_cast<int4*>(orow + chunk * 32 + v * 16) = o;
-            }
-          }
-          g.out_scale[c.expert * g.os_stride_e + static_cast<int64_t>(row) * g.os_stride_row +
-                      c.n_blk] = amax / 448.0f;
-        }
-      } else {
-        __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(g.out) + c.expert * g.out_stride_e +
-                              static_cast<int64_t>(row) * g.out_stride_row;
-        const int col0 = c.n_blk * kTileN;
-#pragma unroll 1
-        for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
-          uint32_t acc[32];
-          tc::tmem_ld_32x32(t_acc + chunk * 32, acc);
-          tc::tmem_ld_wait();
-          if (!row_ok) continue;
-#pragma unroll
           for (int v = 0; v < 4; ++v) {
-            const int col = col0 + chunk * 32 + v * 8;
+            if (col0 + v * 16 + 16 > g.n_out) continue;
+            uint32_t q[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int b = v * 16 + 4 * j;
+              const uint32_t p0 = __nv_cvt_float2_to_fp8x2(
+                  make_float2(acc[b] * inv, acc[b + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+              const uint32_t p1 = __nv_cvt_float2_to_fp8x2(
+                  make_float2(acc[b + 2] * inv, acc[b + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+              q[j] = p0 | (p1 << 16);
+            }
+            int4 o;
+            o.x = q[0];
+            o.y = q[1];
+            o.z = q[2];
+            o.w = q[3];
+            *reinterpret_cast<int4*>(orow + v * 16) = o;
+          }
+          if (half == 0) {
+            g.out_scale[c.expert * g.os_stride_e + static_cast<int64_t>(row) * g.os_stride_row +
+                        c.n_blk] = amax / 448.0f;
+          }
+        }
+        // row_amax is rewritten by the next tile only after every warp passed this point.
+        asm volatile("bar.sync 3, 256;" ::: "memory");
+      } else {
+        if (row_ok) {
+          __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(g.out) + c.expert * g.out_stride_e +
+                                static_cast<int64_t>(row) * g.out_stride_row;
+#pragma unroll
+          for (int v = 0; v < 16; ++v) {  // 16 vectors of 8 columns
+            const int col = c.n_blk * kTileN + (v >> 3) * 128 + half * 64 + (v & 7) * 8;
             if (col + 8 > g.n_out) continue;
             int4 o;
             uint32_t* w = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(acc[v * 8 + 2 * j]),
-                                                             __uint_as_float(acc[v * 8 + 2 * j + 1]));
+              const __nv_bfloat162 b =
+                  __floats2bfloat162_rn(acc[v * 8 + 2 * j], acc[v * 8 + 2 * j + 1]);
               w[j] = *reinterpret_cast<const uint32_t*>(&b);
             }
             *reinterpret_cast<int4*>(orow + col) = o;
           }
         }
       }
-      // The next tile's first K block overwrites t_acc only after its own scratch is
-      // full, which the MMA warp can only produce after this warp's part_empty
-      // arrivals above; the loads of t_acc here are complete (wait::ld).
-      tc::tc_fence_before_sync();
     }
   }
 

@@ -9,13 +9,13 @@
 // this kernel is the fp8 arm of the MoE layer that goes beyond it.
 //
 // fp32 scales per 128 columns are not the hardware's block-scale format, so each
-// 128-wide K block is multiplied on the tensor cores into a scratch accumulator
-// in tensor memory (four K = 32 MMAs, M = 128, N = 256) and the epilogue warps
-// fold it, times the two scales, into the running result that lives in a second
-// region of tensor memory (tcgen05.ld / fma / tcgen05.st).  The MMAs of the next
-// K block overlap with that through TMA-fed stages; the scratch accumulator itself
-// is single-buffered, which is enough for the weight-streaming-bound shapes this
-// serves (decode batches: a few hundred rows per expert at most).
+// 128-wide K block is multiplied on the tensor cores into one of two scratch
+// accumulators in tensor memory (four K = 32 MMAs, M = 128, N = 256) and eight
+// epilogue warps fold it, times the two scales, into the running result that
+// they keep in REGISTERS: warps 4-7 own output columns [0, 64) of each half of the
+// tile, warps 8-11 columns [64, 128), so a thread holds 128 fp32 accumulators and
+// only reads tensor memory (tcgen05.ld), while the MMAs of the next K block fill
+// the other scratch accumulator.
 //
 // Epilogues:  kBf16   plain down projection, bf16 result, 256 columns per tile
 //             kSwiGLUQuant   w stacks gate and up rows; the tile is 128 gate + 128 up
@@ -24,7 +24,7 @@
 //                     scale per row and tile -- the input format of the next GEMM.
 //
 // Roles: warp 0 TMA producer, warp 1 MMA issuer, warp 2 tensor-memory allocation,
-// warps 4-7 scale-and-accumulate + epilogue.  All waits are bounded; on expiry the
+// warps 4-11 scale-and-accumulate + epilogue.  All waits are bounded; on expiry the
 // CTA drains, frees its tensor memory and reports through *status.
 #include <algorithm>
 
@@ -47,8 +47,8 @@ constexpr int kTileN = 256;        // weight rows per tile (UMMA N)
 constexpr int kBlockKBytes = 128;  // 128 e4m3 values = one swizzle row = one scale block
 constexpr int kUmmaKBytes = 32;
 constexpr int kStages = 4;
-constexpr int kThreads = 256;
-constexpr int kTmemCols = 512;     // [0, 256): scratch of one K block; [256, 512): result
+constexpr int kThreads = 384;
+constexpr int kTmemCols = 512;     // two scratch accumulators of 256 columns
 constexpr uint32_t kABytes = kBlockM * kBlockKBytes;
 constexpr uint32_t kBBytes = kTileN * kBlockKBytes;
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
@@ -58,30 +58,24 @@ constexpr int kMaxExperts = 1024;
 struct SharedControl {
   uint64_t full[kStages];
   uint64_t empty[kStages];
-  uint64_t part_full;   // scratch accumulator holds a finished K block
-  uint64_t part_empty;  // scratch accumulator may be overwritten
+  uint64_t part_full[2];   // scratch accumulator holds a finished K block
+  uint64_t part_empty[2];  // scratch accumulator may be overwritten
   uint32_t tmem_base;
   uint32_t abort_flag;
+  float row_amax[2][kBlockM];  // SwiGLU epilogue: per-row maxima of the two column halves
 };
 
 __device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
 
-__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+// 32 lanes x 16 consecutive columns.
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
-      :
-      : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
-        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
-        "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
-        "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
-        "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_st_wait() {
-  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
 }
 
 struct Fp8Tile {

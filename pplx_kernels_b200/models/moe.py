@@ -127,3 +127,107 @@ def moe_reference(x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
             o = (h @ w2[e].to(torch.float32).t()).to(torch.bfloat16).to(torch.float32)
             out[sel] += o * weights[sel, k : k + 1].to(torch.float32)
     return out
+
+
+class MoELayerFP8:
+    """The same expert FFN with block-scaled fp8 weights and activations.
+
+    Tokens enter as bf16; ``dispatch_quant`` converts them to e4m3 with one fp32 scale per 128
+    columns while sending; the up projection runs on ``kind::f8f6f4`` tensor cores with the
+    weights' 128 x 128 block scales, applies SwiGLU and re-quantises its result in its
+    epilogue; the down projection produces bf16 rows for ``combine``.  (DeepSeek-V3 / Qwen3
+    style fp8 inference.)
+    """
+
+    def __init__(self, cfg: MoEModelConfig, max_num_tokens: int, rank: int = 0,
+                 world_size: int = 1, dp_size: int = 1, device: torch.device | None = None,
+                 seed: int = 0, group_name: str = "default", init_std: float = 0.02) -> None:
+        from ..ops.grouped_gemm import quantize_weight_blocks
+
+        assert cfg.num_experts % world_size == 0 and cfg.intermediate_dim % 128 == 0
+        self.cfg = cfg
+        self.rank, self.world_size, self.dp_size = rank, world_size, dp_size
+        self.max_num_tokens = max_num_tokens
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.nle = cfg.num_experts // world_size
+        self.rows = max_num_tokens * (world_size // dp_size)
+        H, I = cfg.hidden_dim, cfg.intermediate_dim
+        nscale = (H + 127) // 128
+        self.ata = AllToAll.intranode(max_num_tokens, cfg.num_experts, cfg.experts_per_token,
+                                      rank, world_size, dp_size, H, H, nscale * 4,
+                                      group_name=group_name)
+        gen = torch.Generator(device="cpu")
+        w13, w2 = [], []
+        for le in range(self.nle):
+            gen.manual_seed(seed * 100003 + rank * self.nle + le)
+            w13.append(torch.randn(2 * I, H, generator=gen) * init_std)
+            w2.append(torch.randn(H, I, generator=gen) * init_std)
+        dev = self.device
+        self.w13_q, self.w13_s = (t.to(dev) for t in quantize_weight_blocks(torch.stack(w13)))
+        self.w2_q, self.w2_s = (t.to(dev) for t in quantize_weight_blocks(torch.stack(w2)))
+        self.counts = torch.zeros(self.nle, dtype=torch.int32, device=dev)
+        self.expert_x = torch.zeros(self.nle, self.rows, H, dtype=torch.uint8,
+                                    device=dev).view(torch.float8_e4m3fn)
+        self.expert_scale = torch.zeros(self.nle, self.rows, nscale, device=dev)
+        self.h = torch.zeros(self.nle, self.rows, I, dtype=torch.uint8,
+                             device=dev).view(torch.float8_e4m3fn)
+        self.h_scale = torch.zeros(self.nle, self.rows, I // 128, device=dev)
+        self.expert_y = torch.zeros(self.nle, self.rows, H, dtype=torch.bfloat16, device=dev)
+        self.gemm_status = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def forward(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
+                out: torch.Tensor | None = None,
+                bound_m: torch.Tensor | None = None) -> torch.Tensor:
+        from ..ops.grouped_gemm import grouped_gemm_fp8
+
+        if out is None:
+            out = torch.empty(self.max_num_tokens, self.cfg.hidden_dim, dtype=torch.bfloat16,
+                              device=self.device)
+        self.ata.dispatch_quant(self.counts, self.expert_x, self.expert_scale, x, indices, bound_m)
+        grouped_gemm_fp8(self.expert_x, self.expert_scale, self.w13_q, self.w13_s, self.counts,
+                         swiglu_quant=True, out=self.h, out_scale=self.h_scale,
+                         status=self.gemm_status)
+        grouped_gemm_fp8(self.h, self.h_scale, self.w2_q, self.w2_s, self.counts,
+                         out=self.expert_y, status=self.gemm_status)
+        self.ata.combine(out, indices, weights, self.expert_y, bound_m)
+        return out
+
+    __call__ = forward
+
+    def dequantized_weights(self) -> tuple[torch.Tensor, torch.Tensor]:
+        """fp32 views of this rank's weights as the kernels see them (for references)."""
+        def deq(q: torch.Tensor, s: torch.Tensor) -> torch.Tensor:
+            full = s.repeat_interleave(128, dim=1)[:, : q.size(1)].repeat_interleave(128, dim=2)
+            return q.to(torch.float32) * full[:, :, : q.size(2)]
+
+        return deq(self.w13_q, self.w13_s), deq(self.w2_q, self.w2_s)
+
+    def check_status(self) -> None:
+        self.ata.check_status()
+        if int(self.gemm_status.item()) != 0:
+            raise RuntimeError("pplx_kernels_b200: a grouped GEMM pipeline wait ran out")
+
+    def destroy(self) -> None:
+        self.ata.destroy()
+
+
+def moe_reference_fp8(x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
+                      w13: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+    """Plain PyTorch statement of the fp8 layer: activations pass through the same block
+    quantisation as in the kernels (before each GEMM), weights are given de-quantised."""
+    from ..ops.quant import block_dequant, per_token_block_quant
+
+    m = x.size(0)
+    I = w2.size(2)
+    xq = block_dequant(*per_token_block_quant(x.cpu())).to(x.device)
+    out = torch.zeros(m, x.size(1), dtype=torch.float32, device=x.device)
+    idx = indices.to(torch.int64)
+    for k in range(idx.size(1)):
+        for e in idx[:, k].unique().tolist():
+            sel = (idx[:, k] == e).nonzero().flatten()
+            y = xq[sel] @ w13[e].t()
+            h = torch.nn.functional.silu(y[:, :I]) * y[:, I:]
+            h = block_dequant(*per_token_block_quant(h.cpu())).to(x.device)
+            o = (h @ w2[e].t()).to(torch.bfloat16).to(torch.float32)
+            out[sel] += o * weights[sel, k : k + 1].to(torch.float32)
+    return out

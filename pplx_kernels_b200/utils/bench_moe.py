@@ -20,7 +20,7 @@ import os
 import torch
 
 from pplx_kernels_b200.models.configs import CONFIGS
-from pplx_kernels_b200.models.moe import MoELayer
+from pplx_kernels_b200.models.moe import MoELayer, MoELayerFP8
 from pplx_kernels_b200.utils.testing import as_index_tensor, routing
 
 
@@ -108,6 +108,60 @@ def measure(model: str, tokens: int, iters: int, warmup: int, rank: int, world: 
     }
 
 
+def measure_fp8(model: str, tokens: int, iters: int, warmup: int, rank: int, world: int,
+                dev: torch.device, graph: bool = True, replays: int = 1) -> dict:
+    """The fp8 layer (quantising dispatch -> fp8 GEMMs -> combine); with `graph` the forward
+    pass is captured once and each timed sample is `replays` back-to-back replays."""
+    cfg = CONFIGS[model]
+    m = tokens
+    layer = MoELayerFP8(cfg, max_num_tokens=m, rank=rank, world_size=world, device=dev)
+    gen = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(m, cfg.hidden_dim, generator=gen).to(torch.bfloat16).to(dev)
+    idx = as_index_tensor(routing(m, cfg.num_experts, cfg.experts_per_token, gen), dev)
+    w = torch.softmax(torch.randn(m, cfg.experts_per_token, generator=gen), dim=-1).to(dev)
+    out = torch.zeros(m, cfg.hidden_dim, dtype=torch.bfloat16, device=dev)
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    layer(x, idx, w, out=out)
+    torch.cuda.synchronize()
+    if world > 1:
+        torch.distributed.barrier()
+    cuda_graph = None
+    if graph:
+        stream = torch.cuda.Stream()
+        cuda_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(stream), torch.cuda.graph(cuda_graph, stream=stream):
+            layer(x, idx, w, out=out)
+    times = []
+    for it in range(warmup + iters):
+        flush.add_(1)
+        torch.cuda.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(replays):
+            if cuda_graph is not None:
+                cuda_graph.replay()
+            else:
+                layer(x, idx, w, out=out)
+        e1.record()
+        torch.cuda.synchronize()
+        if it >= warmup:
+            times.append(e0.elapsed_time(e1) * 1e3 / replays)
+    t = torch.tensor(times, dtype=torch.float64, device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    layer.check_status()
+    layer.destroy()
+    nle = cfg.num_experts // world
+    weight_bytes = nle * 3 * cfg.hidden_dim * cfg.intermediate_dim  # one byte per weight
+    us = float(t.median())
+    return {"model": cfg.name, "dtype": "fp8 block-scaled", "n_gpus": world, "tokens_per_gpu": m,
+            "graph": graph, "replays_per_sample": replays, "us_per_layer_p50": us,
+            "tokens_per_s": world * m / (us * 1e-6),
+            "weights_hbm_floor_us": weight_bytes / 6542e3}
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", choices=sorted(CONFIGS), default="mixtral-8x7b")
@@ -116,6 +170,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--zipf", type=float, default=0.0)
     ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays")
+    ap.add_argument("--fp8", action="store_true", help="block-scaled fp8 layer (MoELayerFP8)")
+    ap.add_argument("--replays", type=int, default=1, help="graph replays per timed sample")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -125,8 +181,12 @@ def main() -> None:
     dev = torch.device("cuda", local_rank)
     if world > 1:
         torch.distributed.init_process_group(backend="cpu:gloo,cuda:nccl", device_id=dev)
-    row = measure(args.model, args.tokens, args.iters, args.warmup, rank, world, dev, args.zipf,
-                  args.graph)
+    if args.fp8:
+        row = measure_fp8(args.model, args.tokens, args.iters, args.warmup, rank, world, dev,
+                          args.graph, args.replays)
+    else:
+        row = measure(args.model, args.tokens, args.iters, args.warmup, rank, world, dev,
+                      args.zipf, args.graph)
     if rank == 0:
         print(json.dumps(row))
     if world > 1:

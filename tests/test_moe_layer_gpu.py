@@ -112,3 +112,48 @@ def test_fused_layer_in_an_emulated_world(world, dp_size, m):
     assert total == groups * m * cfg.experts_per_token
     for l in layers:
         l.destroy()
+
+
+def test_fp8_layer_matches_reference():
+    from pplx_kernels_b200.models.moe import MoELayerFP8, moe_reference_fp8
+
+    cfg, m = MoEModelConfig("q", 8, 2, 512, 256), 96
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    layer = MoELayerFP8(cfg, max_num_tokens=m, init_std=0.05)
+    x, idx, w = _inputs(cfg, m, seed=21, dev=dev)
+    want = moe_reference_fp8(x, idx.to(dev), w, *layer.dequantized_weights())
+    for _ in range(2):
+        out = layer(x, as_index_tensor(idx, dev), w)
+        torch.cuda.synchronize()
+        layer.check_status()
+        # two e4m3 roundings of the activations on top of bf16: a few percent of the row scale
+        err = (out[:m].float() - want).abs()
+        assert (err <= 0.06 * want.abs() + 0.03 * want.abs().amax()).all(), err.max()
+    layer.destroy()
+
+
+def test_fp8_layer_graph_replayed_1000_times():
+    from pplx_kernels_b200.models.moe import MoELayerFP8, moe_reference_fp8
+
+    cfg, m = MoEModelConfig("q2", 16, 4, 256, 128), 16
+    dev = torch.device("cuda", 0)
+    layer = MoELayerFP8(cfg, max_num_tokens=m, init_std=0.05)
+    x, idx, w = _inputs(cfg, m, seed=22, dev=dev)
+    idx_dev = as_index_tensor(idx, dev)
+    out = torch.zeros(m, cfg.hidden_dim, dtype=torch.bfloat16, device=dev)
+    layer(x, idx_dev, w, out=out)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream), torch.cuda.graph(graph, stream=stream):
+        layer(x, idx_dev, w, out=out)
+    out.zero_()
+    for _ in range(1000):
+        graph.replay()
+    torch.cuda.synchronize()
+    layer.check_status()
+    want = moe_reference_fp8(x, idx.to(dev), w, *layer.dequantized_weights())
+    err = (out.float() - want).abs()
+    assert (err <= 0.06 * want.abs() + 0.03 * want.abs().amax()).all(), err.max()
+    layer.destroy()
