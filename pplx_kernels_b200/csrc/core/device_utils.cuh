@@ -1,5 +1,5 @@
-// Small device-side building blocks: warp reductions, a block-wide exclusive
-// scan over a shared-memory array, and an upper-bound search in a prefix array.
+// Small device-side building blocks: warp reductions, a one-warp exclusive scan
+// over a shared-memory array, and an upper-bound search in a prefix array.
 //
 // Role parity: csrc/core/device_utils.cuh:19-57 of the reference (warp_sum,
 // warp_and, half_warp_reduce_max).
@@ -33,41 +33,6 @@ __device__ __forceinline__ uint32_t warp_inclusive_scan(uint32_t v, int lane) {
   }
   return v;
 }
-
-// In-place exclusive scan of data[0..n) in shared memory; data[n] receives the
-// total.  All threads of the block must call it; `warp_tmp` is 33 words of shared
-// memory.  Ends with a __syncthreads().  blockDim.x must be a multiple of 32 and
-// at most 1024.
-__device__ inline void block_exclusive_scan(uint32_t* data, int n, uint32_t* warp_tmp) {
-  const int tid = threadIdx.x;
-  const int lane = tid & 31;
-  const int warp = tid >> 5;
-  const int nwarps = blockDim.x >> 5;
-  if (tid == 0) warp_tmp[32] = 0;  // running carry
-  __syncthreads();
-  for (int base = 0; base < n; base += blockDim.x) {
-    const int i = base + tid;
-    const uint32_t v = (i < n) ? data[i] : 0u;
-    const uint32_t inc = warp_inclusive_scan(v, lane);
-    if (lane == 31) warp_tmp[warp] = inc;
-    __syncthreads();
-    if (warp == 0) {
-      const uint32_t w = (lane < nwarps) ? warp_tmp[lane] : 0u;
-      const uint32_t winc = warp_inclusive_scan(w, lane);
-      warp_tmp[lane] = winc - w;  // exclusive offset of each warp
-      if (lane == 31) warp_tmp[33] = winc;  // chunk total
-    }
-    __syncthreads();
-    const uint32_t carry = warp_tmp[32];
-    if (i < n) data[i] = carry + warp_tmp[warp] + inc - v;
-    __syncthreads();
-    if (tid == 0) warp_tmp[32] = carry + warp_tmp[33];
-    __syncthreads();
-  }
-  if (tid == 0) data[n] = warp_tmp[32];
-  __syncthreads();
-}
-constexpr int kScanTmpWords = 34;
 
 // Exclusive scan of data[0..n) in shared memory by ONE warp (all 32 lanes call
 // it); data[n] receives the total when `write_total`.  Each lane owns a

@@ -55,7 +55,6 @@ __device__ __forceinline__ int split_factor(uint32_t rows, uint32_t warps, int n
 
 struct CombineSmem {
   uint32_t* estart;   // [nle + 1]
-  uint32_t* tmp;      // [kScanTmpWords]
   uint32_t* sig_tok;  // [nwarps] token whose part a warp stored this round, or kNoSignal
   uint32_t* sig_grp;  // [nwarps] first rank of the token's DP group
 };
@@ -64,8 +63,7 @@ constexpr uint32_t kNoSignal = 0xffffffffu;
 __device__ __forceinline__ CombineSmem carve(uint32_t* s, int nle) {
   CombineSmem m;
   m.estart = s;
-  m.tmp = m.estart + nle + 1;
-  m.sig_tok = m.tmp + kScanTmpWords;
+  m.sig_tok = m.estart + nle + 1;
   m.sig_grp = m.sig_tok + kCombineThreads / 32;
   return m;
 }
@@ -391,7 +389,7 @@ cudaError_t dispatch_types(DType in, DType out, F&& fn) {
 }  // namespace
 
 size_t combine_smem_bytes(const A2AParams& p) {
-  return sizeof(uint32_t) * (static_cast<size_t>(p.nle) + 1 + kScanTmpWords + 2 * (kCombineThreads / 32));
+  return sizeof(uint32_t) * (static_cast<size_t>(p.nle) + 1 + 2 * (kCombineThreads / 32));
 }
 
 int combine_threads() { return kCombineThreads; }

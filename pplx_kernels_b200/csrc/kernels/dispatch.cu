@@ -84,7 +84,6 @@ struct DispatchSmem {
   uint32_t* fstart;  // [P + 1]  counts, then their exclusive scan
   uint32_t* rbase;   // [P]
   uint32_t* sent;    // [kMaxWorld]
-  uint32_t* tmp;     // [kScanTmpWords]
   uint32_t* rowpos;  // [kRowCap] staging slot of each row this block sends
 };
 
@@ -97,8 +96,7 @@ __device__ __forceinline__ DispatchSmem carve(uint32_t* s, int E, int P) {
   m.fstart = m.bef + E;
   m.rbase = m.fstart + P + 1;
   m.sent = m.rbase + P;
-  m.tmp = m.sent + kMaxWorld;
-  m.rowpos = m.tmp + kScanTmpWords;
+  m.rowpos = m.sent + kMaxWorld;
   return m;
 }
 
@@ -553,7 +551,7 @@ __global__ void __launch_bounds__(kDispatchThreads, 1)
 
 size_t dispatch_smem_bytes(const A2AParams& p) {
   const size_t E = p.num_experts, P = static_cast<size_t>(p.world) * p.nle;
-  return sizeof(uint32_t) * (4 * E + (P + 1) + P + kMaxWorld + kScanTmpWords + kRowCap);
+  return sizeof(uint32_t) * (4 * E + (P + 1) + P + kMaxWorld + kRowCap);
 }
 
 int dispatch_threads() { return kDispatchThreads; }

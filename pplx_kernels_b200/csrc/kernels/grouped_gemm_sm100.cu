@@ -123,7 +123,6 @@ struct TileCoord {
   int a_row0;
   int w_plane;   // expert whose weights apply
   int out_row0;
-  int src;       // source rank (kFromStaging), else -1
 };
 
 // Tiles of one group are ordered (n_blk, m_blk) with m_blk fastest.
@@ -141,7 +140,6 @@ __device__ __forceinline__ TileCoord locate_tile(const GroupTable& gt, int num_g
   c.out_row0 = static_cast<int>(gt.out_row0[c.group]);
   c.w_plane = c.group;
   c.a_plane = kFromStaging ? 0 : c.group;
-  c.src = -1;
   (void)p;
   return c;
 }

@@ -142,7 +142,7 @@ AllToAll::AllToAll(const A2AConfig& cfg, std::shared_ptr<SymmetricAllocation> ar
   params_.recv_count = recv_count_.get();
   params_.row_src = row_src_.get();
   params_.status = status_.get();
-  params_.timeout_ns = static_cast<uint64_t>(env_long("PPLX_B200_TIMEOUT_MS", 10000)) * 1000000ull;
+  params_.timeout_ns = static_cast<uint64_t>(env_long("PPLX_B200_TIMEOUT_MS", 20000)) * 1000000ull;
   params_.debug_checks = env_long("PPLX_B200_DEBUG_CHECKS", 0) != 0 ? 1 : 0;
   num_sms_ = get_sm_count();
   max_blocks_ = static_cast<int>(env_long("PPLX_B200_NUM_SMS", 0));

@@ -111,7 +111,7 @@ StreamBarrier::StreamBarrier(Bootstrap& bs) {
   CUDA_CHECK(cudaMemset(epoch_, 0, sizeof(uint32_t)));
   CUDA_CHECK(cudaMalloc(&status_, sizeof(Status)));
   CUDA_CHECK(cudaMemset(status_, 0, sizeof(Status)));
-  timeout_ns_ = static_cast<uint64_t>(env_long("PPLX_B200_TIMEOUT_MS", 10000)) * 1000000ull;
+  timeout_ns_ = static_cast<uint64_t>(env_long("PPLX_B200_TIMEOUT_MS", 20000)) * 1000000ull;
 }
 
 StreamBarrier::~StreamBarrier() {

@@ -29,6 +29,21 @@ from ..ops.grouped_gemm import grouped_gemm
 from .configs import MoEModelConfig
 
 
+def _random_expert_weights(cfg: MoEModelConfig, first_expert: int, count: int, seed: int,
+                           std: float, device: torch.device) -> tuple[torch.Tensor, torch.Tensor]:
+    """N(0, std) weights of experts [first_expert, first_expert + count), generated on the
+    device and seeded by GLOBAL expert id, so that every world size holds the same model."""
+    H, I = cfg.hidden_dim, cfg.intermediate_dim
+    gen = torch.Generator(device=device)
+    w13 = torch.empty(count, 2 * I, H, dtype=torch.float32, device=device)
+    w2 = torch.empty(count, H, I, dtype=torch.float32, device=device)
+    for le in range(count):
+        gen.manual_seed(seed * 100003 + first_expert + le)
+        w13[le].normal_(0.0, std, generator=gen)
+        w2[le].normal_(0.0, std, generator=gen)
+    return w13, w2
+
+
 class MoELayer:
     def __init__(self, cfg: MoEModelConfig, max_num_tokens: int, rank: int = 0,
                  world_size: int = 1, dp_size: int = 1, device: torch.device | None = None,
@@ -47,15 +62,10 @@ class MoELayer:
             H, H * 2, 0, group_name=group_name)
         # Random-init weights of this rank's experts; every rank seeds by global expert id so
         # that any world size holds the same model.
-        gen = torch.Generator(device="cpu")
-        w13, w2 = [], []
-        for le in range(self.nle):
-            gen.manual_seed(seed * 100003 + rank * self.nle + le)
-            w13.append(torch.randn(2 * I, H, generator=gen) * init_std)
-            w2.append(torch.randn(H, I, generator=gen) * init_std)
-        self.w13 = torch.stack(w13).to(torch.bfloat16).to(self.device)  # [nle, 2I, H]
-        self.w2 = torch.stack(w2).to(torch.bfloat16).to(self.device)    # [nle, H, I]
         dev = self.device
+        w13, w2 = _random_expert_weights(cfg, rank * self.nle, self.nle, seed, init_std, dev)
+        self.w13 = w13.to(torch.bfloat16)  # [nle, 2I, H]
+        self.w2 = w2.to(torch.bfloat16)    # [nle, H, I]
         self.counts = torch.zeros(self.nle, dtype=torch.int32, device=dev)
         self.expert_x = torch.zeros(self.nle, self.rows, H, dtype=torch.bfloat16, device=dev)
         self.h = torch.zeros(self.nle, self.rows, I, dtype=torch.bfloat16, device=dev)
@@ -156,15 +166,11 @@ class MoELayerFP8:
         self.ata = AllToAll.intranode(max_num_tokens, cfg.num_experts, cfg.experts_per_token,
                                       rank, world_size, dp_size, H, H, nscale * 4,
                                       group_name=group_name)
-        gen = torch.Generator(device="cpu")
-        w13, w2 = [], []
-        for le in range(self.nle):
-            gen.manual_seed(seed * 100003 + rank * self.nle + le)
-            w13.append(torch.randn(2 * I, H, generator=gen) * init_std)
-            w2.append(torch.randn(H, I, generator=gen) * init_std)
         dev = self.device
-        self.w13_q, self.w13_s = (t.to(dev) for t in quantize_weight_blocks(torch.stack(w13)))
-        self.w2_q, self.w2_s = (t.to(dev) for t in quantize_weight_blocks(torch.stack(w2)))
+        w13, w2 = _random_expert_weights(cfg, rank * self.nle, self.nle, seed, init_std, dev)
+        self.w13_q, self.w13_s = quantize_weight_blocks(w13)
+        self.w2_q, self.w2_s = quantize_weight_blocks(w2)
+        del w13, w2
         self.counts = torch.zeros(self.nle, dtype=torch.int32, device=dev)
         self.expert_x = torch.zeros(self.nle, self.rows, H, dtype=torch.uint8,
                                     device=dev).view(torch.float8_e4m3fn)

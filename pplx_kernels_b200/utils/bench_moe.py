@@ -32,6 +32,8 @@ def measure(model: str, tokens: int, iters: int, warmup: int, rank: int, world: 
     cfg = CONFIGS[model]
     m = tokens
     layer = MoELayer(cfg, max_num_tokens=m, rank=rank, world_size=world, device=dev)
+    if world > 1:
+        torch.distributed.barrier()  # weight initialisation takes a different time per rank
     gen = torch.Generator().manual_seed(100 + rank)
     x = torch.randn(m, cfg.hidden_dim, generator=gen).to(torch.bfloat16).to(dev)
     idx = as_index_tensor(routing(m, cfg.num_experts, cfg.experts_per_token, gen, zipf), dev)
