@@ -78,6 +78,24 @@ class PackedInputs:
         return self.host.numel()
 
 
+def _capture(step) -> tuple["torch.cuda.CUDAGraph | None", str]:
+    """Captures `step` into a CUDA graph after one eager run on the capture stream."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    try:
+        with torch.cuda.graph(graph, stream=side):
+            step()
+    except Exception as exc:  # noqa: BLE001 - reported in the JSON line
+        return None, f"capture failed: {type(exc).__name__}: {str(exc)[:120]}"
+    torch.cuda.synchronize()
+    return graph, ""
+
+
 def _unavailable(why: str) -> None:
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why}))
@@ -163,9 +181,41 @@ def reference_arm(args: argparse.Namespace) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.cpu()
 
+    def step_e2e() -> None:
+        packed.upload()
+        ata.dispatch(out_expert_num_tokens=counts, out_expert_x=expert_x,
+                     out_expert_x_scale=expert_scale, dp_x=x, dp_x_scale=x_scale,
+                     indices=indices, bound_m=bound_m)
+        ata.combine(out_tokens=out, indices=indices, weights=weights, expert_y=expert_y,
+                    bound_m=bound_m)
+        h_out.copy_(out, non_blocking=True)
+
+    def run_graph() -> tuple[float | None, str]:
+        """The end-to-end step as one CUDA-graph replay (the reference advertises capture)."""
+        graph, why = _capture(step_e2e)
+        ok = torch.tensor([1.0 if graph is not None else 0.0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() < 1.0:
+            return None, why or "capture failed on another rank"
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(steps)]
+        for i in range(warmup + steps):
+            flush.add_(1)
+            dist.all_reduce(sync_word)
+            e = evs[i - warmup] if i >= warmup else None
+            if e:
+                e[0].record()
+            graph.replay()
+            if e:
+                e[1].record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) for a, b in evs], dtype=torch.float64, device=dev) * 1e3
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.mean()), ""
+
     with ClockSampler(local_rank) as sampler:
         t_main = run(False)
         t_e2e = run(True)
+        graph_us, graph_why = (None, "disabled") if args.no_graph else run_graph()
     ata.destroy()
     step_mean = float(t_main[:, 2].mean())
     value = world * tokens / (step_mean * 1e-6)
@@ -191,7 +241,9 @@ def reference_arm(args: argparse.Namespace) -> None:
         "e2e": {"value": world * tokens / (float(t_e2e[:, 2].mean()) * 1e-6), "unit": "tokens/s",
                 "us_per_step": float(t_e2e[:, 2].mean()),
                 "h2d_bytes_per_step": packed.nbytes(),
-                "d2h_bytes_per_step": h_out.numel() * h_out.element_size()},
+                "d2h_bytes_per_step": h_out.numel() * h_out.element_size(),
+                "mode": "eager calls of the public API",
+                "graph_replay_us_per_step": graph_us, "graph_replay_note": graph_why},
         "gpu_launches": 2 * steps,
         "impl": "reference",
     }
@@ -301,6 +353,40 @@ def time_steps(b: Bench, steps: int, warmup: int, flush: torch.Tensor, e2e: bool
     return _max_over_ranks(t, b.world).cpu()
 
 
+def time_graph_steps(b: Bench, steps: int, warmup: int, flush: torch.Tensor) -> tuple[float | None, str]:
+    """Mean microseconds of the end-to-end step (upload, dispatch, combine, read-back)
+    replayed as one CUDA graph; max over ranks."""
+
+    def step() -> None:
+        b.upload()
+        b.dispatch()
+        b.combine()
+        b.download()
+
+    graph, why = _capture(step)
+    ok = torch.tensor([1.0 if graph is not None else 0.0], device=b.device)
+    if b.world > 1:
+        import torch.distributed as dist
+
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if ok.item() < 1.0:
+        return None, why or "capture failed on another rank"
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(steps)]
+    for i in range(warmup + steps):
+        flush.add_(1)
+        _rank_barrier(b.world)
+        e = evs[i - warmup] if i >= warmup else None
+        if e:
+            e[0].record()
+        graph.replay()
+        if e:
+            e[1].record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(c) for a, c in evs], dtype=torch.float64,
+                     device=b.device) * 1e3
+    return float(_max_over_ranks(t, b.world).mean()), ""
+
+
 def nccl_baseline(b: Bench, steps: int, warmup: int, flush: torch.Tensor) -> float | None:
     """p50 microseconds of torch all_to_all_single on the reference's dense shape."""
     if b.world == 1:
@@ -335,6 +421,8 @@ def main() -> None:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--tokens", type=int, default=128, help="tokens per GPU of the headline run")
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE-layer measurement")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="skip the CUDA-graph replay of the end-to-end step")
     args = ap.parse_args()
     if args.impl == "reference":
         try:
@@ -379,6 +467,8 @@ def main() -> None:
             torch.distributed.barrier()
         wall1 = time.perf_counter()
         t_e2e = time_steps(bench_main, steps, warmup, flush, e2e=True)
+        graph_us, graph_why = ((None, "disabled") if args.no_graph
+                               else time_graph_steps(bench_main, steps, warmup, flush))
     clocks = sampler.summary()
     e2e_us = float(t_e2e[:, 2].mean())
     nccl_us = nccl_baseline(bench_main, min(steps, 50), 5, flush)
@@ -477,6 +567,9 @@ def main() -> None:
             "us_per_step": e2e_us,
             "h2d_bytes_per_step": h2d,
             "d2h_bytes_per_step": d2h,
+            "mode": "eager calls of the public API",
+            "graph_replay_us_per_step": graph_us,
+            "graph_replay_note": graph_why,
         },
         "gpu_launches": 2 * steps,
         "moe_layer": moe,

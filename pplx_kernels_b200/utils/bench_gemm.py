@@ -2,6 +2,7 @@
 
     python -m pplx_kernels_b200.utils.bench_gemm --shape mixtral_up
     python -m pplx_kernels_b200.utils.bench_gemm --experts 8 --rows 512 --k 2048 --n 768 --swiglu
+    python -m pplx_kernels_b200.utils.bench_gemm --shape mixtral_up --fp8
 
 Times with CUDA events after warm-up, flushing L2 between iterations; prints one
 JSON line with achieved TFLOP/s and the fraction of the measured bf16 peak
@@ -17,7 +18,12 @@ import statistics
 
 import torch
 
-from pplx_kernels_b200.ops.grouped_gemm import grouped_gemm
+from pplx_kernels_b200.ops.grouped_gemm import (
+    grouped_gemm,
+    grouped_gemm_fp8,
+    quantize_weight_blocks,
+)
+from pplx_kernels_b200.ops.quant import per_token_block_quant
 
 SHAPES = {
     # name: (experts, rows per expert, K, N, swiglu)
@@ -44,6 +50,8 @@ def main() -> None:
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--half-n", type=int, default=0, help="force the B half width (0 = choose)")
     ap.add_argument("--cta-pair", type=int, default=-1, help="1 = CTA pair, 0 = single, -1 = choose")
+    ap.add_argument("--fp8", action="store_true",
+                    help="block-scaled e4m3 kernel (with --swiglu its output is quantised too)")
     args = ap.parse_args()
     if args.shape:
         E, rows, K, N, swiglu = SHAPES[args.shape]
@@ -64,10 +72,24 @@ def main() -> None:
         for e in range(E):
             torch.matmul(x[e], w[e].t())
 
+    if args.fp8:
+        xq, sa = per_token_block_quant(x.view(E * rows, K))
+        xq, sa = xq.view(E, rows, K), sa.view(E, rows, -1)
+        wq, sw = quantize_weight_blocks(w)
+        out8 = torch.empty(E, rows, N, dtype=torch.float8_e4m3fn, device=dev) if swiglu else out
+        out8_scale = (torch.empty(E, rows, N // 128, dtype=torch.float32, device=dev)
+                      if swiglu else None)
+
+        def ours():
+            grouped_gemm_fp8(xq, sa, wq, sw, counts, swiglu_quant=swiglu, out=out8,
+                             out_scale=out8_scale, status=status)
+    else:
+        def ours():
+            grouped_gemm(x, w, counts, out=out, swiglu=swiglu, status=status,
+                         expected_rows=E * rows, half_n=args.half_n, cta_pair=args.cta_pair)
+
     results = {}
-    for name, fn in (("ours", lambda: grouped_gemm(x, w, counts, out=out, swiglu=swiglu,
-                                                   status=status, expected_rows=E * rows,
-                                                   half_n=args.half_n, cta_pair=args.cta_pair)), ("torch_matmul", lib)):
+    for name, fn in (("ours", ours), ("torch_matmul", lib)):
         times = []
         for it in range(args.warmup + args.iters):
             if not args.no_flush:
@@ -92,6 +114,7 @@ def main() -> None:
     tf = flops / results["ours"] / 1e6
     print(json.dumps({
         "shape": {"experts": E, "rows": rows, "k": K, "n": N, "swiglu": swiglu},
+        "dtype": "fp8_e4m3 block-scaled" if args.fp8 else "bf16",
         "us_p50": results["ours"],
         "tflops": tf,
         "frac_of_measured_bf16_peak": tf / peak if peak else None,
