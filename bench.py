@@ -120,11 +120,13 @@ def reference_arm(args: argparse.Namespace) -> None:
     import torch.distributed as dist
     from pplx_kernels.all_to_all import AllToAll as RefAllToAll  # the reference's own class
 
+    from pplx_kernels_b200.parallel.affinity import bind_to_device_numa_node
     from pplx_kernels_b200.utils.clocks import ClockSampler
     from pplx_kernels_b200.utils.testing import MoEConfig, make_rank_inputs
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    numa = bind_to_device_numa_node(local_rank)  # same host placement in both arms
     dist.init_process_group(backend="cpu:gloo,cuda:nccl", device_id=dev)
     try:
         torch._C._distributed_c10d._register_process_group("default", dist.group.WORLD)
@@ -233,7 +235,8 @@ def reference_arm(args: argparse.Namespace) -> None:
                    "seq_len": 1, "tokens_per_gpu": tokens, "parallelism": f"ep{world}",
                    "l2": "flushed between steps (256 MiB write)",
                    "timing": "CUDA events per step, max over ranks, mean over steps",
-                   "reference_path": "pplx_kernels.AllToAll.intranode (unmodified, sm_100a build)"},
+                   "reference_path": "pplx_kernels.AllToAll.intranode (unmodified, sm_100a build)",
+                   "host_placement": numa},
         "latency_us": {str(tokens): {"dispatch_us_p50": float(t_main[:, 0].median()),
                                      "combine_us_p50": float(t_main[:, 1].median()),
                                      "step_us_p50": float(t_main[:, 2].median())}},
@@ -436,6 +439,9 @@ def main() -> None:
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     torch.cuda.set_device(local_rank)
+    from pplx_kernels_b200.parallel.affinity import bind_to_device_numa_node
+
+    numa = bind_to_device_numa_node(local_rank)  # before any pinned allocation
     if world > 1:
         import torch.distributed as dist
 
@@ -555,6 +561,7 @@ def main() -> None:
             "parallelism": f"ep{world}",
             "l2": "flushed between steps (256 MiB write)",
             "timing": "CUDA events per step, max over ranks, mean over steps",
+            "host_placement": numa,
         },
         "latency_us": {str(k): v for k, v in results.items()},
         "published_reference_us": {str(k): v for k, v in PUBLISHED_US.items()},

@@ -121,13 +121,12 @@ __device__ __forceinline__ void st_cs_v4(void* p, const int4& v) {
 }
 
 // Warp-wide copy of `nvec` 16-byte vectors.  Loads are issued in batches of
-// eight before the first store of the batch, so a lane keeps eight requests in
-// flight instead of paying one memory latency per vector.
+// kBatch before the first store of the batch, so a lane keeps that many requests
+// in flight instead of paying one memory latency per vector.
 enum class LoadKind { kNonCoherent, kL2Only };
 
-template <LoadKind K>
+template <LoadKind K, int kBatch = 8>
 __device__ __forceinline__ void warp_copy_v4(void* dst, const void* src, int nvec, int lane) {
-  constexpr int kBatch = 8;
   uint8_t* d = static_cast<uint8_t*>(dst);
   const uint8_t* s = static_cast<const uint8_t*>(src);
   for (int v0 = lane; v0 < nvec; v0 += 32 * kBatch) {
@@ -146,6 +145,11 @@ __device__ __forceinline__ void warp_copy_v4(void* dst, const void* src, int nve
       if (v < nvec) st_v4(d + (static_cast<size_t>(v) << 4), r[u]);
     }
   }
+}
+
+// Hint: bring the 128-byte line at `p` into L2.
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {

@@ -210,8 +210,9 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
         for (int r = 0; r < p.dp_size; ++r) {
           uint8_t* slot = p.peer[group_first + r] + p.off_comb_stage +
                           (static_cast<size_t>(token) * p.topk + k) * row_bytes;
-          ptx::warp_copy_v4<ptx::LoadKind::kNonCoherent>(slot + (v0 << 4), src + (v0 << 4), nv,
-                                                         lane);
+          // 16 loads in flight per lane: half of a 14 KiB bf16 row in one round trip.
+          ptx::warp_copy_v4<ptx::LoadKind::kNonCoherent, 16>(slot + (v0 << 4), src + (v0 << 4),
+                                                             nv, lane);
         }
         sig_token = token;
         sig_group = static_cast<uint32_t>(group_first);

@@ -192,6 +192,25 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
   const int u_begin = min(static_cast<int>(blockIdx.x) * per_block, n_entries);
   const int u_end = min(u_begin + per_block, n_entries);
 
+  // The rows this block will copy are known before their destinations are: ask
+  // for them now, so that they arrive in L2 while the histogram is built.
+  {
+    const int rows_here = u_end - u_begin;
+    const int src_bytes = a.quantize ? 2 * p.hidden_bytes : p.hidden_bytes;
+    if (rows_here > 0 && rows_here <= kRowCap) {
+      const int parts = split_factor(rows_here, nwarps, p.hidden_bytes >> 4);
+      for (int unit = warp; unit < rows_here * parts; unit += nwarps) {
+        const int r = unit / parts;
+        const int c = unit - r * parts;
+        const int i = ((u_begin + r) / topk) * p.dp_size + dp_rank;
+        const uint8_t* src = a.x + static_cast<int64_t>(i) * a.x_stride_row;
+        const int b0 = ((c * src_bytes) / parts) & ~127;
+        const int b1 = ((c + 1) * src_bytes) / parts;
+        for (int b = b0 + lane * 128; b < b1; b += 32 * 128) ptx::prefetch_l2(src + b);
+      }
+    }
+  }
+
   for (int e = tid; e < E; e += blockDim.x) {
     sm.hist[e] = 0;
     sm.base[e] = 0;

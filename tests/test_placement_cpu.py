@@ -26,3 +26,41 @@ def test_invalid_layouts_are_rejected():
 def test_model_configs():
     assert set(CONFIGS) >= {"mixtral-8x7b", "qwen3-30b-a3b", "deepseek-v3"}
     assert MIXTRAL_8X7B.flops_per_token() == 2 * 3 * 4096 * 14336 * 2
+
+
+def test_cpulist_parsing_and_device_lookup(tmp_path):
+    from pplx_kernels_b200.parallel import affinity
+
+    assert affinity.parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert affinity.parse_cpulist("") == set()
+    assert affinity.pci_address(0, 0x1B, 0) == "0000:1b:00.0"
+
+    dev = tmp_path / "bus" / "pci" / "devices" / "0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "local_cpulist").write_text("4-7\n")
+    assert affinity.device_local_cpus("0000:1b:00.0", tmp_path) == {4, 5, 6, 7}
+
+    # no local_cpulist: fall back to the node's cpulist
+    dev2 = tmp_path / "bus" / "pci" / "devices" / "0000:9b:00.0"
+    dev2.mkdir(parents=True)
+    (dev2 / "numa_node").write_text("1\n")
+    node = tmp_path / "devices" / "system" / "node" / "node1"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text("56-59\n")
+    assert affinity.device_local_cpus("0000:9b:00.0", tmp_path) == {56, 57, 58, 59}
+
+    # unknown device, or a node of -1: nothing to bind to
+    assert affinity.device_local_cpus("0000:ff:00.0", tmp_path) == set()
+    (dev2 / "numa_node").write_text("-1\n")
+    assert affinity.device_local_cpus("0000:9b:00.0", tmp_path) == set()
+
+
+def test_bind_without_a_gpu_is_a_no_op():
+    import os
+
+    from pplx_kernels_b200.parallel import affinity
+
+    before = os.sched_getaffinity(0)
+    info = affinity.bind_to_device_numa_node(0)
+    assert info["bound"] is False and info["reason"]
+    assert os.sched_getaffinity(0) == before
