@@ -102,14 +102,14 @@ def _unavailable(why: str) -> None:
 
 
 def reference_arm(args: argparse.Namespace) -> None:
-    """The UNMODIFIED reference (installed under baseline/_ref) through its own
+    """The UNMODIFIED reference (installed under baseline/_ref by the offline pip command) through its own
     public API: ``pplx_kernels.AllToAll.intranode`` -- its CUDA-IPC / NVLink kernels -- with
     ``dispatch`` and ``combine`` called as its own tests and benchmark call them.  Same shape,
     same synthetic data, same timing as the other arm."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.exists(os.path.join(ref_dir, "pplx_kernels", "libpplx_kernels.so")):
         return _unavailable("baseline/_ref is empty: the offline install of the reference has "
-                            "not been run on this machine (recipe in DESIGN.md)")
+                            "not been run on this machine")
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -55,7 +55,7 @@ __device__ __forceinline__ int split_factor(uint32_t rows, uint32_t warps, int n
 
 struct CombineSmem {
   uint32_t* estart;   // [nle + 1]
-  uint32_t* sig_tok;  // [nwarps] token whose part a warp stored this round, or kNoSignal
+  uint32_t* sig_tok;  // [nwarps] token whose part a warp stored in the current pass, or kNoSignal
   uint32_t* sig_grp;  // [nwarps] first rank of the token's DP group
 };
 constexpr uint32_t kNoSignal = 0xffffffffu;
@@ -260,7 +260,7 @@ __device__ __forceinline__ void recv_phase(const CombineArgs& a, const CombineSm
   const uint32_t per_round = static_cast<uint32_t>(topk) * static_cast<uint32_t>(p.comb_units);
   const uint32_t complete = ptx::ld_volatile(p.comb_iter) * per_round;
   if (blockIdx.x == 0) {
-    // Tokens beyond bound_m receive nothing in this round; advance their counters
+    // Tokens beyond bound_m receive nothing in this combine; advance their counters
     // here so that every counter grows by the same amount per combine.
     for (int i = m + tid; i < p.max_tokens; i += blockDim.x) atomicAdd(arrived + i, per_round);
   }

@@ -4,7 +4,7 @@
 //
 // Who needs it: code that runs where cudaMalloc is off limits -- inside a CUDA
 // graph capture of a host framework that forbids allocation while capturing, in
-// a real-time serving loop whose memory budget is fixed at start-up, or behind a
+// a real-time serving loop whose device memory is all handed out at start-up, or behind a
 // plugin interface that hands the callee tensors and a stream and nothing else.
 // The regular path (`AllToAll` + `dispatch`) allocates its staging arena and
 // counters with cudaMalloc when the object is created; this function instead

@@ -107,3 +107,20 @@ def test_socket_bootstrap_reports_an_unreachable_hub():
     uid[20:40] = 65  # a socket name nobody listens on
     with pytest.raises(RuntimeError, match="could not reach rank 0"):
         _ops.bootstrap_selftest(uid, 1, 2, 300)
+
+
+def test_bench_reference_arm_declines_a_single_rank():
+    """`bench.py --impl reference` with one rank prints the `unavailable` line and exits 0
+    (the reference asserts more than one rank; nothing touches a GPU before that check)."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
+    out = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference"],
+                         capture_output=True, text=True, timeout=300, env=env, cwd=root)
+    assert out.returncode == 0, out.stderr[-2000:]
+    line = json.loads(out.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["unavailable"]

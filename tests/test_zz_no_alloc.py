@@ -2,7 +2,7 @@
 
 Some callers of this library cannot allocate device memory: code running under
 a stream capture of a framework that forbids allocation while capturing, serving
-loops with a memory budget fixed at start-up, and plugins that only receive
+loops whose device memory is all handed out at start-up, and plugins that only receive
 tensors and a stream.  For them the library exports one C function,
 ``pplx_b200_dispatch_single_rank_noalloc``, whose staging memory is a fixed
 16 MiB array inside the library image.  This test calls it through its exported
