@@ -124,3 +124,23 @@ def test_bench_reference_arm_declines_a_single_rank():
     assert out.returncode == 0, out.stderr[-2000:]
     line = json.loads(out.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and line["unavailable"]
+
+
+def test_cmake_project_configures(tmp_path):
+    """The CMake description of the native build configures for sm_100a without a GPU."""
+    import os
+    import shutil
+    import subprocess
+
+    cmake = shutil.which("cmake")
+    if cmake is None or shutil.which("ninja") is None:
+        pytest.skip("cmake or ninja is not installed")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run(
+        [cmake, "-S", os.path.join(root, "pplx_kernels_b200", "csrc"), "-B", str(tmp_path), "-G",
+         "Ninja", "-DWITH_TORCH_BINDINGS=OFF", "-DWITH_TESTS=ON", "-DWITH_BENCHMARKS=ON"],
+        capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    ninja = (tmp_path / "build.ninja").read_text()
+    assert "arch=compute_100a,code=[sm_100a]" in ninja or "sm_100a" in ninja
+    assert "test_all_to_all" in ninja and "bench_all_to_all" in ninja
