@@ -304,6 +304,10 @@ class Bench:
     def combine(self) -> None:
         self.ata.combine(self.out, self.indices, self.weights, self.expert_y, self.bound_m)
 
+    def combine_to_host(self) -> None:
+        """combine whose reduction writes the tokens straight into the pinned host buffer."""
+        self.ata.combine(self.h_out, self.indices, self.weights, self.expert_y, self.bound_m)
+
     def upload(self) -> None:
         self.packed.upload()
 
@@ -365,6 +369,27 @@ def time_steps(b: Bench, steps: int, warmup: int, flush: torch.Tensor, e2e: bool
         [[e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2]), e[0].elapsed_time(e[2])] for e in evs],
         dtype=torch.float64, device=b.device) * 1e3
     return _max_over_ranks(t, b.world).cpu()
+
+
+def time_host_out_steps(b: Bench, steps: int, warmup: int, flush: torch.Tensor) -> float:
+    """Mean microseconds of the end-to-end step in which combine writes its result to pinned
+    host memory itself (upload, dispatch, combine-to-host); max over ranks."""
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(steps)]
+    for i in range(warmup + steps):
+        flush.add_(1)
+        _rank_barrier(b.world)
+        e = evs[i - warmup] if i >= warmup else None
+        if e:
+            e[0].record()
+        b.upload()
+        b.dispatch()
+        b.combine_to_host()
+        if e:
+            e[1].record()
+    torch.cuda.synchronize()
+    t = torch.tensor([a.elapsed_time(c) for a, c in evs], dtype=torch.float64,
+                     device=b.device) * 1e3
+    return float(_max_over_ranks(t, b.world).mean())
 
 
 def time_graph_steps(b: Bench, steps: int, warmup: int, flush: torch.Tensor) -> tuple[float | None, str]:
@@ -487,6 +512,7 @@ def main() -> None:
         t_e2e = time_steps(bench_main, steps, warmup, flush, e2e=True, mid_event=False)
         graph_us, graph_why = ((None, "disabled") if args.no_graph
                                else time_graph_steps(bench_main, steps, warmup, flush))
+        host_out_us = time_host_out_steps(bench_main, steps, warmup, flush)
     clocks = sampler.summary()
     e2e_us = float(t_e2e[:, 2].mean())
     nccl_us = nccl_baseline(bench_main, min(steps, 50), 5, flush)
@@ -592,6 +618,7 @@ def main() -> None:
             "mode": "eager calls of the public API",
             "graph_replay_us_per_step": graph_us,
             "graph_replay_note": graph_why,
+            "combine_writes_host_us_per_step": host_out_us,
         },
         "gpu_launches": 2 * steps,
         "wall_note": "wall clock covers both timing passes of the kernel-only arm",

@@ -129,6 +129,9 @@ class AllToAll:
         do_send: bool = True,
         do_recv: bool = True,
     ) -> None:
+        """``out_tokens`` may also be a pinned host tensor: the reduction then writes the
+        tokens to host memory itself (valid once the stream has been synchronised) and the
+        separate device-to-host copy of small decode batches goes away."""
         assert self._ptr is not None
         self._combine_fn(
             self._ptr,

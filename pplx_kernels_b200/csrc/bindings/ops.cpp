@@ -258,9 +258,13 @@ CombineCall make_combine_call(const AllToAll& ata, at::Tensor& out_tokens,
                               const at::Tensor& expert_y,
                               const std::optional<at::Tensor>& bound_m) {
   const A2AParams& p = ata.params();
-  TORCH_CHECK(out_tokens.is_cuda() && out_tokens.dim() == 2 && out_tokens.stride(1) == 1 &&
-                  out_tokens.size(1) == p.hidden_dim,
-              "out_tokens must be a CUDA tensor of [*, hidden_dim] with unit column stride");
+  // Extension over the reference: out_tokens may live in pinned host memory; the
+  // reduction then writes its result across PCIe itself and no copy follows.
+  const bool host_out = out_tokens.is_cpu() && out_tokens.is_pinned();
+  TORCH_CHECK((out_tokens.is_cuda() || host_out) && out_tokens.dim() == 2 &&
+                  out_tokens.stride(1) == 1 && out_tokens.size(1) == p.hidden_dim,
+              "out_tokens must be a CUDA (or pinned host) tensor of [*, hidden_dim] with unit "
+              "column stride");
   TORCH_CHECK(out_tokens.scalar_type() == at::kHalf || out_tokens.scalar_type() == at::kBFloat16,
               "out_tokens must be float16 or bfloat16");
   TORCH_CHECK(indices.is_cuda() && indices.dim() == 2 && indices.size(1) == p.topk,
@@ -277,6 +281,13 @@ CombineCall make_combine_call(const AllToAll& ata, at::Tensor& out_tokens,
               "num_dp_groups, hidden_dim]");
   CombineCall c;
   c.out_tokens = out_tokens.data_ptr();
+  if (host_out) {
+    void* mapped = nullptr;
+    const cudaError_t err = cudaHostGetDevicePointer(&mapped, out_tokens.data_ptr(), 0);
+    TORCH_CHECK(err == cudaSuccess, "out_tokens: pinned memory is not mapped into the device (",
+                cudaGetErrorString(err), ")");
+    c.out_tokens = mapped;
+  }
   c.out_stride_row = out_tokens.stride(0);
   c.weights = weights.data_ptr<float>();
   c.w_stride_row = weights.stride(0);

@@ -358,3 +358,33 @@ def test_dispatch_with_fused_fp8_quantisation(world, hidden):
     assert rel < 0.07
     for r in ranks:
         r.destroy()
+
+
+def test_combine_writes_into_pinned_host_memory():
+    """out_tokens in pinned host memory: the reduction stores across PCIe itself and the result
+    equals the one written to device memory."""
+    cfg = small(torch.bfloat16, num_experts=16, experts_per_token=4, hidden_dim=1024,
+                max_num_tokens=32)
+    ata, inputs, buf = _single_rank(cfg, seed=71)
+    _dispatch(ata, buf)
+    buf.make_expert_y()
+    _combine(ata, buf)
+    torch.cuda.synchronize()
+    verify_combine(cfg, inputs, 0, buf)
+    want = buf.out.cpu()
+
+    _dispatch(ata, buf)
+    host = torch.full(tuple(buf.out.shape), float("nan"), dtype=buf.out.dtype).pin_memory()
+    ata.combine(host, buf.indices, buf.weights, buf.expert_y, buf.bound_m)
+    torch.cuda.synchronize()
+    ata.check_status()
+    m = inputs[0].num_tokens
+    assert torch.equal(host[:m], want[:m])
+    # pageable host memory is refused
+    _dispatch(ata, buf)
+    with pytest.raises(RuntimeError, match="pinned host"):
+        ata.combine(torch.empty(tuple(buf.out.shape), dtype=buf.out.dtype), buf.indices,
+                    buf.weights, buf.expert_y, buf.bound_m)
+    _combine(ata, buf)
+    torch.cuda.synchronize()
+    ata.destroy()
