@@ -47,7 +47,8 @@ struct A2AParams {
   int world;
   int dp_size;
   int num_dp_groups;
-  int num_experts;
+  int num_experts;       // padded to nle * world
+  int num_real_experts;  // what the caller configured (<= num_experts)
   int nle;           // experts owned by each rank
   int topk;
   int max_tokens;    // per DP group and step

@@ -228,6 +228,10 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
     if (e < static_cast<uint32_t>(E)) {
       atomicAdd(&sm.hist[e], 1u);
       if (idx < u_begin) atomicAdd(&sm.base[e], 1u);
+      // An index in the padding above the configured expert count is delivered to a
+      // surplus slot of the last rank; with checks on it is reported as well.
+      if (p.debug_checks && e >= static_cast<uint32_t>(p.num_real_experts) && blockIdx.x == 0)
+        report_failure(p.status, kBadExpert, kPhaseDispatchCounts, i, p.num_real_experts, e, p.rank);
     } else if (p.debug_checks) {
       report_failure(p.status, kBadExpert, kPhaseDispatchCounts, i, E, e, p.rank);
     }

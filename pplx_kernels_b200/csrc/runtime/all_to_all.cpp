@@ -57,9 +57,7 @@ void AllToAll::validate(const A2AConfig& c) {
   PPLX_CHECK(c.rank >= 0 && c.rank < c.world_size, "rank out of range");
   PPLX_CHECK(c.dp_size >= 1 && c.world_size % c.dp_size == 0, "dp_size must divide world_size");
   PPLX_CHECK(c.max_num_tokens > 0, "max_num_tokens must be positive");
-  PPLX_CHECK(c.num_experts > 0 && c.num_experts % c.world_size == 0,
-             "num_experts (" << c.num_experts << ") must be a positive multiple of world_size ("
-                             << c.world_size << ")");
+  PPLX_CHECK(c.num_experts > 0, "num_experts must be positive");
   PPLX_CHECK(c.experts_per_token > 0 && c.experts_per_token <= c.num_experts,
              "experts_per_token out of range");
   PPLX_CHECK(c.experts_per_token < (1 << 16), "experts_per_token too large");
@@ -80,8 +78,13 @@ A2AParams make_layout(const A2AConfig& c) {
   p.world = c.world_size;
   p.dp_size = c.dp_size;
   p.num_dp_groups = c.world_size / c.dp_size;
-  p.num_experts = c.num_experts;
-  p.nle = c.num_experts / c.world_size;
+  // Experts are dealt out in blocks of ceil(num_experts / world_size): expert e lives on
+  // rank e / nle as local expert e % nle (the reference's rule, all_to_all.cpp:8-42).  When
+  // the division leaves a remainder the last rank(s) own fewer experts; the kernels work on
+  // the padded count nle * world_size, whose surplus experts simply never receive a row.
+  p.nle = ceil_div(c.num_experts, c.world_size);
+  p.num_experts = p.nle * c.world_size;
+  p.num_real_experts = c.num_experts;
   p.topk = c.experts_per_token;
   p.max_tokens = c.max_num_tokens;
   p.hidden_dim = c.hidden_dim;

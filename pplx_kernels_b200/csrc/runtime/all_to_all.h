@@ -5,8 +5,9 @@
 // (internode.h:16-133).  One class serves both API flavours: inside one NVSwitch
 // box every peer is reachable by load/store, so "internode" differs only in how
 // the ranks find one another.  Relaxations against the reference: a single DP
-// group (including world_size 1) is accepted, and num_experts must divide evenly
-// over the ranks (the reference mixes ceil and floor there).
+// group (including world_size 1) is accepted.  num_experts need not divide evenly over
+// the ranks: each rank owns ceil(num_experts / world_size) expert slots and the last
+// rank(s) fewer real experts (the reference mixes ceil and floor there).
 #pragma once
 
 #include <memory>

@@ -70,7 +70,7 @@ def simulate_dispatch(
 ) -> list[ExpectedDispatch]:
     """``inputs[r]`` is rank r's data; ranks of one DP group must hold equal data."""
     world = len(inputs)
-    nle = num_experts // world
+    nle = -(-num_experts // world)  # blocks of ceil(E / W); the last rank(s) own fewer
     out = [ExpectedDispatch([[] for _ in range(nle)]) for _ in range(world)]
     for src in range(world):
         dp_rank = src % dp_size
@@ -127,7 +127,6 @@ class ReferenceAllToAll:
         group: dist.ProcessGroup | None = None,
     ) -> None:
         assert world_size % dp_size == 0
-        assert num_experts % world_size == 0
         self.max_num_tokens = max_num_tokens
         self.num_experts = num_experts
         self.topk = experts_per_token
@@ -135,7 +134,7 @@ class ReferenceAllToAll:
         self.world = world_size
         self.dp_size = dp_size
         self.num_dp_groups = world_size // dp_size
-        self.nle = num_experts // world_size
+        self.nle = -(-num_experts // world_size)
         self.hidden_dim = hidden_dim
         self.hidden_bytes = hidden_dim_bytes
         self.scale_bytes = hidden_dim_scale_bytes

@@ -12,14 +12,15 @@ class EPLayout:
     dp_size: int = 1
 
     def __post_init__(self) -> None:
-        if self.num_experts % self.world_size:
-            raise ValueError("num_experts must be a multiple of world_size")
+        if self.num_experts <= 0:
+            raise ValueError("num_experts must be positive")
         if self.world_size % self.dp_size:
             raise ValueError("dp_size must divide world_size")
 
     @property
     def num_local_experts(self) -> int:
-        return self.num_experts // self.world_size
+        """Expert slots per rank: blocks of ceil(E / W); the last rank(s) own fewer real ones."""
+        return -(-self.num_experts // self.world_size)
 
     @property
     def num_dp_groups(self) -> int:
@@ -34,7 +35,7 @@ class EPLayout:
 
     def local_experts(self, rank: int) -> range:
         n = self.num_local_experts
-        return range(rank * n, (rank + 1) * n)
+        return range(min(rank * n, self.num_experts), min((rank + 1) * n, self.num_experts))
 
     def dp_group(self, rank: int) -> int:
         return rank // self.dp_size

@@ -31,7 +31,7 @@ class RankBuffers:
     def __init__(self, cfg: MoEConfig, world: int, dp_size: int, inp: RankInputs,
                  device: torch.device, strided_scale: bool = False,
                  use_bound_m: bool = True) -> None:
-        nle = cfg.num_experts // world
+        nle = -(-cfg.num_experts // world)
         rows = cfg.max_num_tokens * (world // dp_size)
         self.cfg = cfg
         self.num_tokens = inp.num_tokens

@@ -47,6 +47,14 @@ def test_expert_parallel_sizes(world, dp_size):
     run_local_world(cfg, world=world, dp_size=dp_size, seed=5)
 
 
+@pytest.mark.parametrize("world,dp_size,num_experts", [(4, 1, 10), (4, 2, 7), (8, 1, 9), (2, 1, 5)])
+def test_expert_count_that_does_not_divide_evenly(world, dp_size, num_experts):
+    """Blocks of ceil(E / W) experts per rank; the last rank(s) own fewer (or none)."""
+    cfg = small(torch.float8_e4m3fn, num_experts=num_experts, experts_per_token=3,
+                hidden_dim=256, max_num_tokens=12)
+    run_local_world(cfg, world=world, dp_size=dp_size, seed=17, iterations=2)
+
+
 def test_float32_expert_outputs():
     run_local_world(small(), world=2, dp_size=1, seed=3, y_dtype=torch.float32)
 

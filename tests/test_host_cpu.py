@@ -45,7 +45,7 @@ def test_unique_id_is_128_bytes():
     [
         (dict(hidden_dim_bytes=1000), "multiple of 16"),
         (dict(hidden_dim_scale_bytes=6), "multiple of 4"),
-        (dict(num_experts=0), "multiple of world_size"),
+        (dict(num_experts=0), "num_experts must be positive"),
         (dict(experts_per_token=0), "experts_per_token"),
         (dict(max_num_tokens=0), "max_num_tokens"),
     ],

@@ -18,9 +18,18 @@ def test_block_partition_and_dp_groups():
 
 def test_invalid_layouts_are_rejected():
     with pytest.raises(ValueError):
-        EPLayout(num_experts=7, world_size=2)
+        EPLayout(num_experts=0, world_size=2)
     with pytest.raises(ValueError):
         EPLayout(num_experts=8, world_size=4, dp_size=3)
+
+
+def test_uneven_expert_count_uses_blocks_of_the_ceiling():
+    lay = EPLayout(num_experts=10, world_size=4)
+    assert lay.num_local_experts == 3
+    assert [lay.owner(e) for e in range(10)] == [0, 0, 0, 1, 1, 1, 2, 2, 2, 3]
+    assert list(lay.local_experts(3)) == [9]
+    lay = EPLayout(num_experts=5, world_size=4)
+    assert lay.num_local_experts == 2 and list(lay.local_experts(3)) == []
 
 
 def test_model_configs():

@@ -27,7 +27,7 @@ def _oracle_worker(pgi: ProcessGroupInfo, cfg: MoEConfig, dp_size: int, identity
     inputs = _world_inputs(cfg, num_dp, dp_size, seed=7, softmax_weights=identity,
                            num_tokens=cfg.max_num_tokens if identity else None)
     mine = inputs[rank]
-    nle = cfg.num_experts // world
+    nle = -(-cfg.num_experts // world)
     ata = ReferenceAllToAll(cfg.max_num_tokens, cfg.num_experts, cfg.experts_per_token, rank,
                             world, dp_size, cfg.hidden_dim, cfg.hidden_dim_bytes,
                             cfg.hidden_dim_scale_bytes)
@@ -69,6 +69,12 @@ def test_oracle_identity_world2():
     cfg = MoEConfig(num_experts=8, experts_per_token=2, hidden_dim=128, max_num_tokens=16,
                     in_dtype=torch.float32, out_dtype=torch.float32)
     parallel_launch(2, _oracle_worker, cfg, 1, True, use_cuda=False)
+
+
+def test_oracle_uneven_expert_count_world4():
+    # 10 experts over 4 ranks: blocks of 3, the last rank owns one real expert.
+    cfg = MoEConfig(num_experts=10, experts_per_token=3, hidden_dim=64, max_num_tokens=9)
+    parallel_launch(4, _oracle_worker, cfg, 1, False, use_cuda=False)
 
 
 def test_oracle_dp_groups_world4_bf16():
