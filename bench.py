@@ -96,6 +96,19 @@ def _capture(step) -> tuple["torch.cuda.CUDAGraph | None", str]:
     return graph, ""
 
 
+def _e2e_entry(world: int, tokens: int, modes: dict[str, float | None], h2d: int, d2h: int,
+               note: str) -> dict:
+    """The end-to-end entry of the JSON line.  Every mode is the whole step through the
+    library's public API with the upload of the step's inputs from pinned memory and the
+    arrival of its result in host memory inside the timed region; `value` is the best mode
+    the library supports, the same rule for both arms, and all modes are listed."""
+    have = {k: v for k, v in modes.items() if v is not None}
+    best = min(have, key=have.get)
+    return {"value": world * tokens / (have[best] * 1e-6), "unit": "tokens/s",
+            "us_per_step": have[best], "mode": best, "modes_us_per_step": modes,
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "note": note}
+
+
 def _unavailable(why: str) -> None:
     if int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why}))
@@ -247,12 +260,10 @@ def reference_arm(args: argparse.Namespace) -> None:
                                      "step_us_p50": float(t_step[:, 2].median()),
                                      "step_us_mean_with_mid_event": float(t_main[:, 2].mean())}},
         "clocks": sampler.summary(),
-        "e2e": {"value": world * tokens / (float(t_e2e[:, 2].mean()) * 1e-6), "unit": "tokens/s",
-                "us_per_step": float(t_e2e[:, 2].mean()),
-                "h2d_bytes_per_step": packed.nbytes(),
-                "d2h_bytes_per_step": h_out.numel() * h_out.element_size(),
-                "mode": "eager calls of the public API",
-                "graph_replay_us_per_step": graph_us, "graph_replay_note": graph_why},
+        "e2e": _e2e_entry(world, tokens,
+                          {"eager calls, copy engine both ways": float(t_e2e[:, 2].mean()),
+                           "one CUDA graph replay per step": graph_us},
+                          packed.nbytes(), h_out.numel() * h_out.element_size(), graph_why),
         "gpu_launches": 2 * steps,
         "impl": "reference",
     }
@@ -609,17 +620,12 @@ def main() -> None:
         "roofline": roofline,
         "clocks": clocks,
         "wall_ms_per_step_incl_flush_and_barrier": (wall1 - wall0) * 1e3 / (steps + warmup),
-        "e2e": {
-            "value": world * args.tokens / (e2e_us * 1e-6),
-            "unit": "tokens/s",
-            "us_per_step": e2e_us,
-            "h2d_bytes_per_step": h2d,
-            "d2h_bytes_per_step": d2h,
-            "mode": "eager calls of the public API",
-            "graph_replay_us_per_step": graph_us,
-            "graph_replay_note": graph_why,
-            "combine_writes_host_us_per_step": host_out_us,
-        },
+        "e2e": _e2e_entry(world, args.tokens,
+                          {"eager calls, copy engine both ways": e2e_us,
+                           "one CUDA graph replay per step": graph_us,
+                           "eager calls, combine writes the tokens to pinned host memory":
+                               host_out_us},
+                          h2d, d2h, graph_why),
         "gpu_launches": 2 * steps,
         "wall_note": "wall clock covers both timing passes of the kernel-only arm",
         "moe_layer": moe,
