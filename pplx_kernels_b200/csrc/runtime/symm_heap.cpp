@@ -33,7 +33,30 @@ struct HandleBlob {
   int32_t device;
   int32_t pid;
   uint64_t bytes;
+  char pci_bus_id[32];  // "0000:1b:00.0": identifies the GPU whatever each rank's device order
 };
+
+// Fails with a readable message when the peer's GPU is visible to this process but not
+// reachable by loads and stores (no NVLink / PCIe P2P path).  A GPU this process cannot
+// see at all (a narrowed CUDA_VISIBLE_DEVICES) is left to cudaIpcOpenMemHandle to judge.
+void check_peer_reachable(int my_device, const HandleBlob& peer, int peer_rank) {
+  if (peer.pci_bus_id[0] == '\0') return;
+  int peer_device = -1;
+  if (cudaDeviceGetByPCIBusId(&peer_device, peer.pci_bus_id) != cudaSuccess) {
+    cudaGetLastError();  // not visible here: clear the sticky-free error and move on
+    return;
+  }
+  if (peer_device == my_device) return;  // ranks that share a GPU
+  int can = 0;
+  if (cudaDeviceCanAccessPeer(&can, my_device, peer_device) != cudaSuccess) {
+    cudaGetLastError();
+    return;
+  }
+  PPLX_CHECK(can != 0, "peer access between device " << my_device << " and device " << peer_device
+                           << " (rank " << peer_rank << ", " << peer.pci_bus_id
+                           << ") is not available: all ranks of one object must sit in one "
+                              "NVLink / PCIe peer-to-peer domain");
+}
 
 }  // namespace
 
@@ -60,6 +83,11 @@ std::shared_ptr<SymmetricAllocation> SymmetricAllocation::create(Bootstrap& bs, 
   HandleBlob mine{};
   CUDA_CHECK(cudaIpcGetMemHandle(&mine.handle, alloc->local_owner_.get()));
   mine.device = alloc->device_;
+  if (cudaDeviceGetPCIBusId(mine.pci_bus_id, sizeof(mine.pci_bus_id), alloc->device_) !=
+      cudaSuccess) {
+    cudaGetLastError();
+    mine.pci_bus_id[0] = '\0';
+  }
   mine.pid = static_cast<int32_t>(::getpid());
   mine.bytes = bytes;
   std::vector<HandleBlob> all(world);
@@ -71,6 +99,7 @@ std::shared_ptr<SymmetricAllocation> SymmetricAllocation::create(Bootstrap& bs, 
                                           << bytes);
     PPLX_CHECK(all[r].pid != mine.pid,
                "two ranks share a process; use create_local_world for that");
+    check_peer_reachable(alloc->device_, all[r], r);
     void* p = nullptr;
     CUDA_CHECK(cudaIpcOpenMemHandle(&p, all[r].handle, cudaIpcMemLazyEnablePeerAccess));
     alloc->peers_[r] = p;
