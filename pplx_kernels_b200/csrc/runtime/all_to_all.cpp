@@ -212,8 +212,10 @@ int AllToAll::combine_grid(int num_tokens) const {
 
 DispatchArgs AllToAll::make_dispatch_args(const DispatchCall& c) const {
   const A2AParams& p = params_;
-  PPLX_CHECK(c.out_num_tokens != nullptr && c.out_x.data != nullptr && c.x.data != nullptr &&
-                 c.indices != nullptr,
+  // A rank may come with no tokens at all (empty tensors have no storage).
+  const bool empty = c.num_tokens == 0;
+  PPLX_CHECK(c.out_num_tokens != nullptr && c.out_x.data != nullptr &&
+                 (empty || (c.x.data != nullptr && c.indices != nullptr)),
              "dispatch: missing tensor");
   PPLX_CHECK(c.num_tokens >= 0 && c.num_tokens <= p.max_tokens,
              "dispatch: " << c.num_tokens << " tokens exceed max_num_tokens " << p.max_tokens);
@@ -227,9 +229,9 @@ DispatchArgs AllToAll::make_dispatch_args(const DispatchCall& c) const {
     PPLX_CHECK(c.out_scale.data != nullptr && c.x_scale.data == nullptr,
                "quantising dispatch takes out_expert_x_scale but no dp_x_scale");
   } else {
-    PPLX_CHECK(
-        has_scale == (c.out_scale.data != nullptr) && has_scale == (c.x_scale.data != nullptr),
-        "dispatch: scale tensors must be given exactly when hidden_dim_scale_bytes > 0");
+    PPLX_CHECK(has_scale == (c.out_scale.data != nullptr) &&
+                   (empty || has_scale == (c.x_scale.data != nullptr)),
+               "dispatch: scale tensors must be given exactly when hidden_dim_scale_bytes > 0");
   }
   PPLX_CHECK(reinterpret_cast<uintptr_t>(c.out_x.data) % 16 == 0 &&
                  reinterpret_cast<uintptr_t>(c.x.data) % 16 == 0 && c.out_x.stride_row % 16 == 0 &&
@@ -259,7 +261,8 @@ DispatchArgs AllToAll::make_dispatch_args(const DispatchCall& c) const {
 
 CombineArgs AllToAll::make_combine_args(const CombineCall& c) const {
   const A2AParams& p = params_;
-  PPLX_CHECK(c.out_tokens != nullptr && c.weights != nullptr && c.expert_y != nullptr,
+  PPLX_CHECK(c.expert_y != nullptr &&
+                 (c.num_tokens == 0 || (c.out_tokens != nullptr && c.weights != nullptr)),
              "combine: missing tensor");
   PPLX_CHECK(c.num_tokens >= 0 && c.num_tokens <= p.max_tokens,
              "combine: " << c.num_tokens << " tokens exceed max_num_tokens " << p.max_tokens);
@@ -306,7 +309,8 @@ void AllToAll::dispatch_send_packed(const DispatchCall& call, cudaStream_t strea
 
 DispatchArgs AllToAll::make_packed_send_args(const DispatchCall& c) const {
   const A2AParams& p = params_;
-  PPLX_CHECK(c.x.data != nullptr && c.indices != nullptr, "packed dispatch: missing tensor");
+  PPLX_CHECK(c.num_tokens == 0 || (c.x.data != nullptr && c.indices != nullptr),
+             "packed dispatch: missing tensor");
   PPLX_CHECK(p.scale_bytes == 0, "packed dispatch carries no scales");
   PPLX_CHECK(c.num_tokens >= 0 && c.num_tokens <= p.max_tokens,
              "dispatch: " << c.num_tokens << " tokens exceed max_num_tokens " << p.max_tokens);

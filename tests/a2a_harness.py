@@ -20,8 +20,14 @@ EXPERT_GAIN = 1.5
 
 
 def world_inputs(cfg: MoEConfig, world: int, dp_size: int, seed: int, **kw) -> list[RankInputs]:
+    """`num_tokens` may be a list with one entry per DP group."""
     gen = torch.Generator().manual_seed(seed)
-    per_group = [make_rank_inputs(cfg, gen, **kw) for _ in range(world // dp_size)]
+    counts = kw.pop("num_tokens", None)
+    groups = world // dp_size
+    if not isinstance(counts, (list, tuple)):
+        counts = [counts] * groups
+    assert len(counts) == groups
+    per_group = [make_rank_inputs(cfg, gen, num_tokens=counts[g], **kw) for g in range(groups)]
     return [per_group[r // dp_size] for r in range(world)]
 
 

@@ -55,6 +55,17 @@ def test_expert_count_that_does_not_divide_evenly(world, dp_size, num_experts):
     run_local_world(cfg, world=world, dp_size=dp_size, seed=17, iterations=2)
 
 
+@pytest.mark.parametrize("use_bound_m", [True, False])
+@pytest.mark.parametrize("counts", [[0, 5, 0, 12], [0, 0, 0, 0], [1, 0, 0, 0]])
+def test_ranks_without_tokens(counts, use_bound_m):
+    """bound_m = 0 on some or all ranks: they still post counts, forward what they receive
+    and keep their arrival counters in step."""
+    cfg = small(torch.float8_e4m3fn, num_experts=16, experts_per_token=4, hidden_dim=256,
+                max_num_tokens=12)
+    run_local_world(cfg, world=4, dp_size=1, seed=23, iterations=3, num_tokens=counts,
+                    use_bound_m=use_bound_m)
+
+
 def test_float32_expert_outputs():
     run_local_world(small(), world=2, dp_size=1, seed=3, y_dtype=torch.float32)
 
