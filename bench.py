@@ -78,6 +78,17 @@ class PackedInputs:
         return self.host.numel()
 
 
+# File descriptor of the real standard output.  main() points descriptor 1 at standard error
+# for the duration of the run, so that whatever native libraries print (NCCL's version banner,
+# for one) does not land between the caller and the one JSON line it parses.
+_RESULT_FD = 1
+
+
+def _emit(line: dict) -> None:
+    sys.stdout.flush()
+    os.write(_RESULT_FD, (json.dumps(line) + "\n").encode())
+
+
 def _capture(step) -> tuple["torch.cuda.CUDAGraph | None", str]:
     """Captures `step` into a CUDA graph after one eager run on the capture stream."""
     side = torch.cuda.Stream()
@@ -111,7 +122,7 @@ def _e2e_entry(world: int, tokens: int, modes: dict[str, float | None], h2d: int
 
 def _unavailable(why: str) -> None:
     if int(os.environ.get("RANK", "0")) == 0:
-        print(json.dumps({"impl": "reference", "unavailable": why}))
+        _emit({"impl": "reference", "unavailable": why})
 
 
 def reference_arm(args: argparse.Namespace) -> None:
@@ -268,7 +279,7 @@ def reference_arm(args: argparse.Namespace) -> None:
         "impl": "reference",
     }
     if rank == 0:
-        print(json.dumps(line))
+        _emit(line)
     dist.barrier()
     dist.destroy_process_group()
 
@@ -474,6 +485,10 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true",
                     help="skip the CUDA-graph replay of the end-to-end step")
     args = ap.parse_args()
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         try:
             reference_arm(args)
@@ -632,7 +647,7 @@ def main() -> None:
         "impl": "ours",
     }
     if rank == 0:
-        print(json.dumps(line))
+        _emit(line)
     if world > 1:
         import pplx_kernels_b200 as pk
 
