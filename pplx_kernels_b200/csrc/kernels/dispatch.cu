@@ -18,8 +18,8 @@
 //           rows the block stored to the destination's arrival counter with a
 //           release at system scope.
 //  RECV  1. Every block reads all (source, expert) counts (bounded wait) and
-//           derives row offsets with a block scan; block 0 writes the per-expert
-//           totals.
+//           derives row offsets (sources in rank order, then a warp scan of the
+//           group sizes); block 0 writes the per-expert totals.
 //        2. One warp per received row waits (bounded) until its source's arrival
 //           counter is complete, then copies slot -> out_expert_x / scale and
 //           records (source rank, token, k) for combine.

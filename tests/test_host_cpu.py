@@ -144,3 +144,18 @@ def test_cmake_project_configures(tmp_path):
     ninja = (tmp_path / "build.ninja").read_text()
     assert "arch=compute_100a,code=[sm_100a]" in ninja or "sm_100a" in ninja
     assert "test_all_to_all" in ninja and "bench_all_to_all" in ninja
+
+
+def test_bench_end_to_end_entry_picks_the_best_supported_mode():
+    import importlib.util
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    e = bench._e2e_entry(8, 128, {"eager": 250.0, "graph": None, "host": 200.0}, 10, 20, "")
+    assert e["mode"] == "host" and e["us_per_step"] == 200.0
+    assert abs(e["value"] - 8 * 128 / 200e-6) < 1e-3
+    assert e["modes_us_per_step"]["graph"] is None
+    assert e["h2d_bytes_per_step"] == 10 and e["d2h_bytes_per_step"] == 20
