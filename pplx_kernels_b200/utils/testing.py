@@ -152,3 +152,60 @@ def parallel_launch(world_size: int, worker: Callable[..., None], *args: Any,
         nprocs=world_size,
         join=True,
     )
+
+
+def _worker_from_env(local_rank: int, world_size: int, local_size: int, node_rank: int,
+                     addr: str, port: int, use_cuda: bool, worker: Callable[..., None],
+                     args: tuple[Any, ...]) -> None:
+    import torch.distributed as dist
+
+    rank = node_rank * local_size + local_rank
+    if use_cuda:
+        torch.cuda.set_device(local_rank)
+        device = torch.device("cuda", local_rank)
+        backend = "cpu:gloo,cuda:nccl"
+    else:
+        device = torch.device("cpu")
+        backend = "gloo"
+    dist.init_process_group(backend=backend, init_method=f"tcp://{addr}:{port}",
+                            world_size=world_size, rank=rank)
+    try:
+        pgi = ProcessGroupInfo(world_size, local_size, rank, node_rank, local_rank, device)
+        worker(pgi, *args)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def launch_env_present() -> bool:
+    """True when the variables `parallel_launch_from_env` reads are all set."""
+    return all(k in os.environ for k in ("WORLD_SIZE", "WORLD_LOCAL_SIZE", "NODE_RANK",
+                                         "MASTER_ADDR", "MASTER_PORT"))
+
+
+def parallel_launch_from_env(worker: Callable[..., None], *args: Any,
+                             use_cuda: bool | None = None) -> None:
+    """Runs ``worker(pgi, *args)`` in ``WORLD_LOCAL_SIZE`` processes of this host as ranks
+    ``NODE_RANK * WORLD_LOCAL_SIZE + local rank`` of a ``WORLD_SIZE`` job that meets at
+    ``MASTER_ADDR:MASTER_PORT``.
+
+    Role parity: ``parallel_launch_from_env`` of the reference (tests/distributed_utils.py:
+    119-136), which starts its multi-node tests this way.  An `AllToAll` object of this
+    library spans one NVLink domain, so `WORLD_SIZE` normally equals `WORLD_LOCAL_SIZE`; the
+    launcher itself does not care.
+    """
+    world_size = int(os.environ["WORLD_SIZE"])
+    local_size = int(os.environ["WORLD_LOCAL_SIZE"])
+    node_rank = int(os.environ["NODE_RANK"])
+    addr = os.environ["MASTER_ADDR"]
+    port = int(os.environ["MASTER_PORT"])
+    assert world_size % local_size == 0 and 0 <= node_rank < world_size // local_size
+    if use_cuda is None:
+        use_cuda = torch.cuda.is_available()
+    os.environ.setdefault("NCCL_NVLS_ENABLE", os.environ.get("NCCL_NVLS_ENABLE", "0"))
+    torch.multiprocessing.spawn(
+        _worker_from_env,
+        args=(world_size, local_size, node_rank, addr, port, use_cuda, worker, args),
+        nprocs=local_size,
+        join=True,
+    )

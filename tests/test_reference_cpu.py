@@ -102,3 +102,32 @@ def test_simulate_dispatch_counts_rows_once():
                 assert (src // 2, i, k) not in seen
                 assert i % 2 == src % 2
                 seen.add((src // 2, i, k))
+
+
+def _env_worker(pgi: ProcessGroupInfo, expect_world: int) -> None:
+    import torch.distributed as dist
+
+    assert pgi.world_size == expect_world and pgi.world_local_size == expect_world
+    assert pgi.rank == pgi.node_rank * pgi.world_local_size + pgi.local_rank
+    t = torch.tensor([float(pgi.rank)])
+    dist.all_reduce(t)
+    assert t.item() == sum(range(expect_world))
+
+
+def test_launch_from_environment_variables(monkeypatch):
+    from pplx_kernels_b200.utils.testing import (
+        free_port,
+        launch_env_present,
+        parallel_launch_from_env,
+    )
+
+    for k in ("WORLD_SIZE", "WORLD_LOCAL_SIZE", "NODE_RANK", "MASTER_ADDR", "MASTER_PORT"):
+        monkeypatch.delenv(k, raising=False)
+    assert not launch_env_present()
+    monkeypatch.setenv("WORLD_SIZE", "2")
+    monkeypatch.setenv("WORLD_LOCAL_SIZE", "2")
+    monkeypatch.setenv("NODE_RANK", "0")
+    monkeypatch.setenv("MASTER_ADDR", "127.0.0.1")
+    monkeypatch.setenv("MASTER_PORT", str(free_port()))
+    assert launch_env_present()
+    parallel_launch_from_env(_env_worker, 2, use_cuda=False)
