@@ -73,3 +73,21 @@ def test_bind_without_a_gpu_is_a_no_op():
     info = affinity.bind_to_device_numa_node(0)
     assert info["bound"] is False and info["reason"]
     assert os.sched_getaffinity(0) == before
+
+
+def test_logging_prefix_and_routing_description(capsys):
+    import logging
+
+    import torch
+
+    from pplx_kernels_b200.utils.logging_utils import describe_routing, init_logging
+
+    log = init_logging(rank=3, level="DEBUG")
+    log.debug("hello")
+    logging.shutdown()
+    err = capsys.readouterr().err
+    assert "[rank 3]" in err and "hello" in err
+    text = describe_routing(torch.tensor([[0, 5], [9, 5]]), num_experts=10, world_size=4)
+    assert text.splitlines()[0] == "rank 0: 1 rows, per expert [1, 0, 0]"
+    assert text.splitlines()[1] == "rank 1: 2 rows, per expert [0, 0, 2]"
+    assert text.splitlines()[3] == "rank 3: 1 rows, per expert [1]"
