@@ -1,5 +1,6 @@
 """CPU tests of the pure-torch oracle over gloo (world_size 2 and 4)."""
 
+import pytest
 import torch
 
 from pplx_kernels_b200.ops.reference import (
@@ -131,3 +132,43 @@ def test_launch_from_environment_variables(monkeypatch):
     monkeypatch.setenv("MASTER_PORT", str(free_port()))
     assert launch_env_present()
     parallel_launch_from_env(_env_worker, 2, use_cuda=False)
+
+
+def test_simulated_world_invariants_over_random_shapes():
+    """Property check of the single-process oracle over random worlds, DP sizes, expert counts
+    (even and uneven) and token counts (including none): every (group, token, k) is delivered
+    exactly once, to the rank and slot that own the expert, by the rank of the group whose turn
+    it is; and with weights that sum to one an identity expert gives the tokens back."""
+    hypothesis = pytest.importorskip("hypothesis")
+    st = hypothesis.strategies
+
+    @hypothesis.settings(max_examples=40, deadline=None)
+    @hypothesis.given(world=st.sampled_from([1, 2, 4, 8]), dp_pow=st.integers(0, 3),
+                      experts=st.integers(1, 24), topk=st.integers(1, 4),
+                      tokens=st.integers(0, 9), seed=st.integers(0, 10_000))
+    def check(world, dp_pow, experts, topk, tokens, seed):
+        dp_size = min(world, 1 << dp_pow)
+        topk = min(topk, experts)
+        cfg = MoEConfig(num_experts=experts, experts_per_token=topk, hidden_dim=8,
+                        max_num_tokens=max(tokens, 1), in_dtype=torch.float32,
+                        out_dtype=torch.float32)
+        inputs = _world_inputs(cfg, world // dp_size, dp_size, seed=seed, num_tokens=tokens,
+                               softmax_weights=True)
+        expected = simulate_dispatch(inputs, experts, dp_size)
+        nle = -(-experts // world)
+        seen = set()
+        for dst, e in enumerate(expected):
+            assert len(e.rows) == nle
+            for le, rows in enumerate(e.rows):
+                for src, i, k in rows:
+                    g = int(inputs[src].indices[i, k])
+                    assert g // nle == dst and g % nle == le
+                    assert i % dp_size == src % dp_size
+                    assert (src // dp_size, i, k) not in seen
+                    seen.add((src // dp_size, i, k))
+        assert len(seen) == (world // dp_size) * tokens * topk
+        for rank in range(world):
+            out = simulate_combine(inputs, lambda e, row: row.float(), torch.float32, rank)
+            torch.testing.assert_close(out, inputs[rank].x[:tokens].float(), rtol=1e-5, atol=1e-5)
+
+    check()
