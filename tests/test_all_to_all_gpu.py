@@ -407,3 +407,90 @@ def test_combine_writes_into_pinned_host_memory():
     _combine(ata, buf)
     torch.cuda.synchronize()
     ata.destroy()
+
+
+def test_a_rank_may_run_one_dispatch_ahead_of_a_peer():
+    """Rank S, whose tokens of step n use none of rank A's experts, finishes its combine
+    without waiting for A and sends the rows of dispatch n + 1 to A before A has read the
+    rows of dispatch n.  Flags and staging are kept per parity, so A still receives step n
+    intact."""
+    from pplx_kernels_b200.ops.reference import RankInputs
+
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    cfg = small(torch.bfloat16, num_experts=8, experts_per_token=2, hidden_dim=256,
+                max_num_tokens=6)
+    gen = torch.Generator().manual_seed(91)
+
+    def make(m: int, lo: int, hi: int) -> RankInputs:
+        idx = torch.stack([lo + torch.randperm(hi - lo, generator=gen)[:2] for _ in range(m)])
+        return RankInputs(x=torch.randn(m, cfg.hidden_dim, generator=gen).to(cfg.in_dtype),
+                          x_scale=None, indices=idx.to(torch.int64),
+                          weights=torch.rand(m, 2, generator=gen), num_tokens=m)
+
+    A, S = 0, 1  # A owns experts 0-3, S owns experts 4-7
+    step_n = [make(5, 0, 8), make(6, 4, 8)]      # S's tokens stay on S's own experts
+    step_n1 = [make(4, 0, 8), make(6, 0, 4)]     # now every row of S goes to A
+    ranks = pk.AllToAll.local_world(cfg.max_num_tokens, cfg.num_experts, cfg.experts_per_token,
+                                    2, 1, cfg.hidden_dim, cfg.hidden_dim_bytes,
+                                    cfg.hidden_dim_scale_bytes)
+    try:
+        for r in ranks:
+            r.set_debug_checks(True)
+            r.set_timeout_ms(3000)
+        bn = [RankBuffers(cfg, 2, 1, step_n[r], device) for r in range(2)]
+        bn1 = [RankBuffers(cfg, 2, 1, step_n1[r], device) for r in range(2)]
+
+        def dispatch(who, bufs, **kw):
+            pk.dispatch_group([ranks[r] for r in who], [bufs[r].counts for r in who],
+                              [bufs[r].expert_x for r in who], [None for _ in who],
+                              [bufs[r].x for r in who], [None for _ in who],
+                              [bufs[r].indices for r in who], [bufs[r].bound_m for r in who],
+                              **kw)
+
+        def combine(who, bufs, **kw):
+            pk.combine_group([ranks[r] for r in who], [bufs[r].out for r in who],
+                             [bufs[r].indices for r in who], [bufs[r].weights for r in who],
+                             [bufs[r].expert_y for r in who], [bufs[r].bound_m for r in who],
+                             **kw)
+
+        def check(who):
+            torch.cuda.synchronize()
+            for r in who:
+                ranks[r].check_status()
+
+        dispatch([A, S], bn, do_send=True, do_recv=False)
+        dispatch([S], bn, do_send=False, do_recv=True)
+        check([S])
+        verify_dispatch(cfg, step_n, 1, S, bn[S])
+        bn[S].make_expert_y()
+        combine([S], bn, do_send=True, do_recv=False)
+        combine([S], bn, do_send=False, do_recv=True)
+        check([S])
+        verify_combine(cfg, step_n, S, bn[S])
+
+        dispatch([S], bn1, do_send=True, do_recv=False)   # S is one dispatch ahead of A
+        check([S])
+
+        dispatch([A], bn, do_send=False, do_recv=True)    # A reads step n only now
+        check([A])
+        verify_dispatch(cfg, step_n, 1, A, bn[A])
+        bn[A].make_expert_y()
+        combine([A], bn, do_send=True, do_recv=False)
+        combine([A], bn, do_send=False, do_recv=True)
+        check([A])
+        verify_combine(cfg, step_n, A, bn[A])
+
+        dispatch([A], bn1, do_send=True, do_recv=False)
+        dispatch([A, S], bn1, do_send=False, do_recv=True)
+        check([A, S])
+        for r in (A, S):
+            verify_dispatch(cfg, step_n1, 1, r, bn1[r])
+            bn1[r].make_expert_y()
+        combine([A, S], bn1)
+        check([A, S])
+        for r in (A, S):
+            verify_combine(cfg, step_n1, r, bn1[r])
+    finally:
+        for r in ranks:
+            r.destroy()
