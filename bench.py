@@ -9,13 +9,19 @@ tokens and weights are synthetic.
     python bench.py --gpus 1 --steps 200 --warmup 20
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 \
         --master-addr 127.0.0.1 --master-port 29501 bench.py --gpus 8
+    ... bench.py --impl reference --gpus 8      # the unmodified reference, same harness
+
+Both arms run the same code in this file: the same tensors, the same timing
+loops, the same rank barrier (an NCCL all-reduce of one word on the launching
+stream) and the same JSON keys; only the ``AllToAll`` object differs.  The
+reference arm imports nothing that maps this repository's native library.
 
 Timing: every step is bracketed by CUDA events on the launching stream, after a
-write of a 256 MiB buffer that flushes the 126 MB L2 and (for N > 1) a device
-barrier across ranks so that all ranks start together; per step the maximum over
-ranks is taken, then the mean over the K timed steps gives ``ms_per_step`` and
-the aggregate tokens/s; p50 values are reported next to it.  Rank 0 prints one
-JSON line.
+write of a 256 MiB buffer that flushes the 126 MB L2 and (for N > 1) the rank
+barrier so that all ranks start together; per step the maximum over ranks is
+taken, then the mean over the K timed steps gives ``ms_per_step`` and the
+aggregate tokens/s; p50 values are reported next to it.  Rank 0 prints one JSON
+line.
 """
 
 from __future__ import annotations
@@ -23,7 +29,9 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import subprocess
 import sys
+import tempfile
 import time
 
 import torch
@@ -33,7 +41,16 @@ sys.path.insert(0, ROOT)
 
 # Published EP8 NVLink numbers of the reference (its README.md:60-81), in microseconds.
 PUBLISHED_US = {1: {"dispatch": 41.6, "combine": 41.7}, 128: {"dispatch": 83.6, "combine": 102.3}}
-NVLINK_GBS = 770.0  # measured peer-copy bandwidth per direction on this pool
+PUBLISHED_WORLD = 8
+# Peer-copy bandwidth per direction used for the NVLink floor when the run cannot measure it
+# itself (a single GPU, or the measurement failed): GB/s of a large device-to-peer copy on an
+# NVSwitch-connected B200.
+NVLINK_GBS_DEFAULT = 770.0
+
+METRIC = ("MoE dispatch+combine tokens/s (DeepSeek-V3 shape: 256 experts, top-8, hidden 7168, "
+          "fp8 dispatch + bf16 combine)")
+DTYPE = "fp8_e4m3 dispatch (fp32 scale per 128) / bf16 combine"
+DATA = "synthetic (uniform random distinct top-8 routing, random tokens, softmax weights)"
 
 
 def _peaks() -> dict:
@@ -42,6 +59,31 @@ def _peaks() -> dict:
             return json.load(f)
     except OSError:
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "fallback": True}
+
+
+# File descriptor of the real standard output.  main() points descriptor 1 at standard error
+# for the duration of the run, so that whatever native libraries print (NCCL's version banner,
+# for one) does not land between the caller and the one JSON line it parses.
+_RESULT_FD = 1
+
+
+def _emit(line: dict) -> None:
+    sys.stdout.flush()
+    os.write(_RESULT_FD, (json.dumps(line) + "\n").encode())
+
+
+def _env_rank() -> tuple[int, int, int]:
+    return (int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
+            int(os.environ.get("LOCAL_RANK", "0")))
+
+
+def _repo_native_mapped() -> bool:
+    """True if this process has mapped this repository's native library."""
+    try:
+        with open("/proc/self/maps") as f:
+            return "libpplx_kernels_b200" in f.read()
+    except OSError:
+        return False
 
 
 class PackedInputs:
@@ -63,13 +105,17 @@ class PackedInputs:
         self.dev = self.host.to(dev)
         m, hidden = inp.x.shape
 
-        def view(i: int, t: torch.Tensor, dtype: torch.dtype, shape) -> torch.Tensor:
-            return self.dev[offs[i]:offs[i] + t.numel()].view(dtype).view(shape)
+        def view(buf: torch.Tensor, i: int, t: torch.Tensor, dtype: torch.dtype, shape) -> torch.Tensor:
+            return buf[offs[i]:offs[i] + t.numel()].view(dtype).view(shape)
 
-        self.x = view(0, parts[0], inp.x.dtype, (m, hidden))
-        self.x_scale = view(1, parts[1], torch.float32, tuple(inp.x_scale.shape))
-        self.indices = view(2, parts[2], torch.uint32, tuple(inp.indices.shape))
-        self.weights = view(3, parts[3], torch.float32, tuple(inp.weights.shape))
+        shapes = [(inp.x.dtype, (m, hidden)), (torch.float32, tuple(inp.x_scale.shape)),
+                  (torch.uint32, tuple(inp.indices.shape)), (torch.float32, tuple(inp.weights.shape))]
+        self.x, self.x_scale, self.indices, self.weights = (
+            view(self.dev, i, parts[i], dt, sh) for i, (dt, sh) in enumerate(shapes))
+        # The same four tensors as views of the pinned host buffer (for a dispatch that reads
+        # its inputs from host memory itself).
+        self.h_x, self.h_x_scale, self.h_indices, self.h_weights = (
+            view(self.host, i, parts[i], dt, sh) for i, (dt, sh) in enumerate(shapes))
 
     def upload(self) -> None:
         self.dev.copy_(self.host, non_blocking=True)
@@ -78,236 +124,29 @@ class PackedInputs:
         return self.host.numel()
 
 
-# File descriptor of the real standard output.  main() points descriptor 1 at standard error
-# for the duration of the run, so that whatever native libraries print (NCCL's version banner,
-# for one) does not land between the caller and the one JSON line it parses.
-_RESULT_FD = 1
+class Arm:
+    """The tensors of one benchmark arm and its all-to-all object.
 
+    `kind` is "ours", "ref-intranode" or "ref-internode"; everything except the construction
+    of ``self.ata`` is the same for all three.
+    """
 
-def _emit(line: dict) -> None:
-    sys.stdout.flush()
-    os.write(_RESULT_FD, (json.dumps(line) + "\n").encode())
+    def __init__(self, kind: str, tokens: int, rank: int, world: int, dev: torch.device) -> None:
+        from pplx_kernels_b200.utils.testing import MoEConfig, make_rank_inputs
 
-
-def _capture(step) -> tuple["torch.cuda.CUDAGraph | None", str]:
-    """Captures `step` into a CUDA graph after one eager run on the capture stream."""
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-        step()
-    torch.cuda.current_stream().wait_stream(side)
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    try:
-        with torch.cuda.graph(graph, stream=side):
-            step()
-    except Exception as exc:  # noqa: BLE001 - reported in the JSON line
-        return None, f"capture failed: {type(exc).__name__}: {str(exc)[:120]}"
-    torch.cuda.synchronize()
-    return graph, ""
-
-
-def _e2e_entry(world: int, tokens: int, modes: dict[str, float | None], h2d: int, d2h: int,
-               note: str) -> dict:
-    """The end-to-end entry of the JSON line.  Every mode is the whole step through the
-    library's public API with the upload of the step's inputs from pinned memory and the
-    arrival of its result in host memory inside the timed region; `value` is the best mode
-    the library supports, the same rule for both arms, and all modes are listed."""
-    have = {k: v for k, v in modes.items() if v is not None}
-    best = min(have, key=have.get)
-    return {"value": world * tokens / (have[best] * 1e-6), "unit": "tokens/s",
-            "us_per_step": have[best], "mode": best, "modes_us_per_step": modes,
-            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "note": note}
-
-
-def _unavailable(why: str) -> None:
-    if int(os.environ.get("RANK", "0")) == 0:
-        _emit({"impl": "reference", "unavailable": why})
-
-
-def reference_arm(args: argparse.Namespace) -> None:
-    """The UNMODIFIED reference (installed under baseline/_ref by the offline pip command) through its own
-    public API: ``pplx_kernels.AllToAll.intranode`` -- its CUDA-IPC / NVLink kernels -- with
-    ``dispatch`` and ``combine`` called as its own tests and benchmark call them.  Same shape,
-    same synthetic data, same timing as the other arm."""
-    ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    if not os.path.exists(os.path.join(ref_dir, "pplx_kernels", "libpplx_kernels.so")):
-        return _unavailable("baseline/_ref is empty: the offline install of the reference has "
-                            "not been run on this machine")
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if world < 2:
-        return _unavailable("the reference refuses a single rank: AllToAll.intranode asserts "
-                            "world_size // dp_size > 1 (src/pplx_kernels/all_to_all.py:101)")
-    sys.path.insert(0, ref_dir)
-    import torch.distributed as dist
-    from pplx_kernels.all_to_all import AllToAll as RefAllToAll  # the reference's own class
-
-    from pplx_kernels_b200.parallel.affinity import bind_to_device_numa_node
-    from pplx_kernels_b200.utils.clocks import ClockSampler
-    from pplx_kernels_b200.utils.testing import MoEConfig, make_rank_inputs
-
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    numa = bind_to_device_numa_node(local_rank)  # same host placement in both arms
-    dist.init_process_group(backend="cpu:gloo,cuda:nccl", device_id=dev)
-    try:
-        torch._C._distributed_c10d._register_process_group("default", dist.group.WORLD)
-    except Exception:
-        pass
-    tokens = args.tokens
-    cfg = MoEConfig(256, 8, 7168, tokens, torch.float8_e4m3fn, torch.bfloat16)
-    nle = cfg.num_experts // world
-    inp = make_rank_inputs(cfg, torch.Generator().manual_seed(1000 + rank), num_tokens=tokens,
-                           softmax_weights=True)
-    ata = RefAllToAll.intranode(
-        max_num_tokens=tokens, num_experts=cfg.num_experts,
-        experts_per_token=cfg.experts_per_token, rank=rank, world_size=world, dp_size=1,
-        hidden_dim=cfg.hidden_dim, hidden_dim_bytes=cfg.hidden_dim_bytes,
-        hidden_dim_scale_bytes=cfg.hidden_dim_scale_bytes)
-    packed = PackedInputs(inp, dev)
-    x, x_scale, indices, weights = packed.x, packed.x_scale, packed.indices, packed.weights
-    bound_m = torch.tensor([tokens], dtype=torch.int32, device=dev).view(torch.uint32)
-    rows = tokens * world
-    counts = torch.zeros(nle, dtype=torch.int32, device=dev)
-    expert_x = torch.zeros(nle, rows, cfg.hidden_dim, dtype=torch.uint8, device=dev).view(cfg.in_dtype)
-    expert_scale = torch.zeros(nle, rows, cfg.hidden_dim_scale, device=dev)
-    expert_y = torch.randn(nle, rows, cfg.hidden_dim, device=dev).to(cfg.out_dtype)
-    out = torch.zeros(tokens, cfg.hidden_dim, dtype=cfg.out_dtype, device=dev)
-    h_out = torch.empty(tokens, cfg.hidden_dim, dtype=cfg.out_dtype).pin_memory()
-    flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
-    sync_word = torch.zeros(1, device=dev)
-    steps, warmup = args.steps, max(args.warmup, 3)
-
-    def run(e2e: bool, mid_event: bool = True) -> torch.Tensor:
-        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
-        for i in range(warmup + steps):
-            flush.add_(1)
-            dist.all_reduce(sync_word)  # device-side barrier on the launching stream
-            e = evs[i - warmup] if i >= warmup else None
-            if e:
-                e[0].record()
-                if not mid_event:
-                    e[1].record()
-            if e2e:
-                packed.upload()
-            ata.dispatch(out_expert_num_tokens=counts, out_expert_x=expert_x,
-                         out_expert_x_scale=expert_scale, dp_x=x, dp_x_scale=x_scale,
-                         indices=indices, bound_m=bound_m)
-            if e and mid_event:
-                e[1].record()
-            ata.combine(out_tokens=out, indices=indices, weights=weights, expert_y=expert_y,
-                        bound_m=bound_m)
-            if e2e:
-                h_out.copy_(out, non_blocking=True)
-            if e:
-                e[2].record()
-        torch.cuda.synchronize()
-        t = torch.tensor([[a.elapsed_time(b) for a, b in ((e[0], e[1]), (e[1], e[2]), (e[0], e[2]))]
-                          for e in evs], dtype=torch.float64, device=dev) * 1e3
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return t.cpu()
-
-    def step_e2e() -> None:
-        packed.upload()
-        ata.dispatch(out_expert_num_tokens=counts, out_expert_x=expert_x,
-                     out_expert_x_scale=expert_scale, dp_x=x, dp_x_scale=x_scale,
-                     indices=indices, bound_m=bound_m)
-        ata.combine(out_tokens=out, indices=indices, weights=weights, expert_y=expert_y,
-                    bound_m=bound_m)
-        h_out.copy_(out, non_blocking=True)
-
-    def run_graph() -> tuple[float | None, str]:
-        """The end-to-end step as one CUDA-graph replay (the reference advertises capture)."""
-        graph, why = _capture(step_e2e)
-        ok = torch.tensor([1.0 if graph is not None else 0.0], device=dev)
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-        if ok.item() < 1.0:
-            return None, why or "capture failed on another rank"
-        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(steps)]
-        for i in range(warmup + steps):
-            flush.add_(1)
-            dist.all_reduce(sync_word)
-            e = evs[i - warmup] if i >= warmup else None
-            if e:
-                e[0].record()
-            graph.replay()
-            if e:
-                e[1].record()
-        torch.cuda.synchronize()
-        t = torch.tensor([a.elapsed_time(b) for a, b in evs], dtype=torch.float64, device=dev) * 1e3
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.mean()), ""
-
-    with ClockSampler(local_rank) as sampler:
-        t_main = run(False)
-        t_step = run(False, mid_event=False)
-        t_e2e = run(True, mid_event=False)
-        graph_us, graph_why = (None, "disabled") if args.no_graph else run_graph()
-    ata.destroy()
-    step_mean = float(t_step[:, 2].mean())
-    value = world * tokens / (step_mean * 1e-6)
-    pub = PUBLISHED_US.get(tokens)
-    line = {
-        "metric": "MoE dispatch+combine tokens/s (DeepSeek-V3 shape: 256 experts, top-8, hidden "
-                  "7168, fp8 dispatch + bf16 combine)",
-        "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
-        "ms_per_step": step_mean / 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": (value / (world * tokens / ((pub["dispatch"] + pub["combine"]) * 1e-6))
-                        if pub else None),
-        "dtype": "fp8_e4m3 dispatch (fp32 scale per 128) / bf16 combine",
-        "data": "synthetic (uniform random distinct top-8 routing, random tokens, softmax weights)",
-        "config": {"model": "DeepSeek-V3 MoE layer all-to-all", "global_batch": world * tokens,
-                   "seq_len": 1, "tokens_per_gpu": tokens, "parallelism": f"ep{world}",
-                   "l2": "flushed between steps (256 MiB write)",
-                   "timing": "CUDA events around each step (dispatch + combine, nothing recorded "
-                             "in between), max over ranks, mean over steps; dispatch/combine p50 "
-                             "from a second pass with an event between the two",
-                   "reference_path": "pplx_kernels.AllToAll.intranode (unmodified, sm_100a build)",
-                   "host_placement": numa},
-        "latency_us": {str(tokens): {"dispatch_us_p50": float(t_main[:, 0].median()),
-                                     "combine_us_p50": float(t_main[:, 1].median()),
-                                     "step_us_p50": float(t_step[:, 2].median()),
-                                     "step_us_mean_with_mid_event": float(t_main[:, 2].mean())}},
-        "clocks": sampler.summary(),
-        "e2e": _e2e_entry(world, tokens,
-                          {"eager calls, copy engine both ways": float(t_e2e[:, 2].mean()),
-                           "one CUDA graph replay per step": graph_us},
-                          packed.nbytes(), h_out.numel() * h_out.element_size(), graph_why),
-        "gpu_launches": 2 * steps,
-        "impl": "reference",
-    }
-    if rank == 0:
-        _emit(line)
-    dist.barrier()
-    dist.destroy_process_group()
-
-
-class Bench:
-    def __init__(self, tokens: int) -> None:
-        import pplx_kernels_b200 as pk
-        from pplx_kernels_b200.utils.testing import MoEConfig, as_index_tensor, make_rank_inputs
-
-        self.pk = pk
-        self.rank = int(os.environ.get("RANK", "0"))
-        self.world = int(os.environ.get("WORLD_SIZE", "1"))
-        self.device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-        self.cfg = MoEConfig(num_experts=256, experts_per_token=8, hidden_dim=7168,
-                             max_num_tokens=tokens, in_dtype=torch.float8_e4m3fn,
-                             out_dtype=torch.bfloat16)
-        cfg = self.cfg
-        self.tokens = tokens
-        nle = cfg.num_experts // self.world
-        gen = torch.Generator().manual_seed(1000 + self.rank)
-        inp = make_rank_inputs(cfg, gen, num_tokens=tokens, softmax_weights=True)
-        # Host copy in pinned memory (the end-to-end path uploads it every step).
-        dev = self.device
+        self.kind, self.rank, self.world, self.device, self.tokens = kind, rank, world, dev, tokens
+        cfg = MoEConfig(num_experts=256, experts_per_token=8, hidden_dim=7168,
+                        max_num_tokens=tokens, in_dtype=torch.float8_e4m3fn,
+                        out_dtype=torch.bfloat16)
+        self.cfg = cfg
+        nle = cfg.num_experts // world
+        inp = make_rank_inputs(cfg, torch.Generator().manual_seed(1000 + rank), num_tokens=tokens,
+                               softmax_weights=True)
         self.packed = PackedInputs(inp, dev)
         self.x, self.x_scale = self.packed.x, self.packed.x_scale
         self.indices, self.weights = self.packed.indices, self.packed.weights
         self.bound_m = torch.tensor([tokens], dtype=torch.int32, device=dev).view(torch.uint32)
-        rows = tokens * self.world
+        rows = tokens * world
         self.counts = torch.zeros(nle, dtype=torch.int32, device=dev)
         self.expert_x = torch.zeros(nle, rows, cfg.hidden_dim, dtype=torch.uint8,
                                     device=dev).view(cfg.in_dtype)
@@ -315,13 +154,29 @@ class Bench:
         self.expert_y = torch.randn(nle, rows, cfg.hidden_dim, device=dev).to(cfg.out_dtype)
         self.out = torch.zeros(tokens, cfg.hidden_dim, dtype=cfg.out_dtype, device=dev)
         self.h_out = torch.empty(tokens, cfg.hidden_dim, dtype=cfg.out_dtype).pin_memory()
-        self.ata = pk.AllToAll.intranode(
-            cfg.max_num_tokens, cfg.num_experts, cfg.experts_per_token, self.rank, self.world, 1,
-            cfg.hidden_dim, cfg.hidden_dim_bytes, cfg.hidden_dim_scale_bytes)
+        kwargs = dict(max_num_tokens=tokens, num_experts=cfg.num_experts,
+                      experts_per_token=cfg.experts_per_token, rank=rank, world_size=world,
+                      dp_size=1, hidden_dim=cfg.hidden_dim, hidden_dim_bytes=cfg.hidden_dim_bytes,
+                      hidden_dim_scale_bytes=cfg.hidden_dim_scale_bytes)
+        if kind == "ours":
+            import pplx_kernels_b200 as pk
+
+            self.ata = pk.AllToAll.intranode(**kwargs)
+        else:
+            from pplx_kernels.all_to_all import AllToAll as RefAllToAll  # the reference's class
+
+            make = RefAllToAll.intranode if kind == "ref-intranode" else RefAllToAll.internode
+            self.ata = make(**kwargs)
 
     def dispatch(self) -> None:
         self.ata.dispatch(self.counts, self.expert_x, self.expert_scale, self.x, self.x_scale,
                           self.indices, self.bound_m)
+
+    def dispatch_from_host(self) -> None:
+        """dispatch whose send reads tokens, scales and routing from pinned host memory."""
+        p = self.packed
+        self.ata.dispatch(self.counts, self.expert_x, self.expert_scale, p.h_x, p.h_x_scale,
+                          p.h_indices, self.bound_m)
 
     def combine(self) -> None:
         self.ata.combine(self.out, self.indices, self.weights, self.expert_y, self.bound_m)
@@ -329,6 +184,11 @@ class Bench:
     def combine_to_host(self) -> None:
         """combine whose reduction writes the tokens straight into the pinned host buffer."""
         self.ata.combine(self.h_out, self.indices, self.weights, self.expert_y, self.bound_m)
+
+    def combine_host_both(self) -> None:
+        """combine that reads the weights from, and writes the tokens to, pinned host memory."""
+        self.ata.combine(self.h_out, self.packed.h_indices, self.packed.h_weights, self.expert_y,
+                         self.bound_m)
 
     def upload(self) -> None:
         self.packed.upload()
@@ -343,135 +203,464 @@ class Bench:
         return self.h_out.numel() * self.h_out.element_size()
 
     def close(self) -> None:
-        self.ata.check_status()
+        if self.kind == "ours":
+            self.ata.check_status()
         self.ata.destroy()
 
 
-def _rank_barrier(world: int) -> None:
-    if world > 1:
-        from pplx_kernels_b200 import nvshmem_barrier_all_on_current_stream
+class Harness:
+    """Timing loops shared by both arms."""
 
-        nvshmem_barrier_all_on_current_stream()
+    def __init__(self, world: int, dev: torch.device, steps: int, warmup: int) -> None:
+        self.world, self.dev, self.steps, self.warmup = world, dev, steps, warmup
+        self.flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+        self.sync_word = torch.zeros(1, device=dev)
 
+    def rank_barrier(self) -> None:
+        """Device-side barrier on the launching stream: an NCCL all-reduce of one word."""
+        if self.world > 1:
+            torch.distributed.all_reduce(self.sync_word)
 
-def _max_over_ranks(t: torch.Tensor, world: int) -> torch.Tensor:
-    if world > 1:
-        import torch.distributed as dist
+    def max_over_ranks(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return t
 
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return t
+    def all_agree(self, ok: bool) -> bool:
+        flag = torch.tensor([1.0 if ok else 0.0], device=self.dev)
+        if self.world > 1:
+            torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
+        return flag.item() >= 1.0
 
-
-def time_steps(b: Bench, steps: int, warmup: int, flush: torch.Tensor, e2e: bool,
-               mid_event: bool = True) -> torch.Tensor:
-    """Returns [steps, 3] microseconds (dispatch, combine, whole step), max over ranks.
-    Without `mid_event` nothing is recorded between dispatch and combine (the whole-step
-    figure then carries no event in the middle; the first two columns are meaningless)."""
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
-    for i in range(warmup + steps):
-        flush.add_(1)
-        _rank_barrier(b.world)
-        e = evs[i - warmup] if i >= warmup else None
-        if e:
-            e[0].record()
-            if not mid_event:
+    def time_pair(self, first, second, steps: int | None = None) -> torch.Tensor:
+        """[steps, 3] microseconds (first, second, both) with an event between the two calls,
+        max over ranks."""
+        steps = steps or self.steps
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+        for i in range(self.warmup + steps):
+            self.flush.add_(1)
+            self.rank_barrier()
+            e = evs[i - self.warmup] if i >= self.warmup else None
+            if e:
+                e[0].record()
+            first()
+            if e:
                 e[1].record()
-        if e2e:
-            b.upload()
-        b.dispatch()
-        if e and mid_event:
-            e[1].record()
-        b.combine()
-        if e2e:
-            b.download()
-        if e:
-            e[2].record()
-    torch.cuda.synchronize()
-    t = torch.tensor(
-        [[e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2]), e[0].elapsed_time(e[2])] for e in evs],
-        dtype=torch.float64, device=b.device) * 1e3
-    return _max_over_ranks(t, b.world).cpu()
+            second()
+            if e:
+                e[2].record()
+        torch.cuda.synchronize()
+        t = torch.tensor([[e[0].elapsed_time(e[1]), e[1].elapsed_time(e[2]),
+                           e[0].elapsed_time(e[2])] for e in evs],
+                         dtype=torch.float64, device=self.dev) * 1e3
+        return self.max_over_ranks(t).cpu()
+
+    def time_step(self, step, steps: int | None = None) -> torch.Tensor:
+        """[steps] microseconds of `step()` with nothing recorded inside it, max over ranks."""
+        steps = steps or self.steps
+        evs = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(steps)]
+        for i in range(self.warmup + steps):
+            self.flush.add_(1)
+            self.rank_barrier()
+            e = evs[i - self.warmup] if i >= self.warmup else None
+            if e:
+                e[0].record()
+            step()
+            if e:
+                e[1].record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) for a, b in evs], dtype=torch.float64,
+                         device=self.dev) * 1e3
+        return self.max_over_ranks(t).cpu()
+
+    def time_graph(self, step) -> tuple[float | None, str]:
+        """Mean microseconds of `step()` captured once and replayed as one CUDA graph."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph: torch.cuda.CUDAGraph | None = torch.cuda.CUDAGraph()
+        why = ""
+        try:
+            with torch.cuda.graph(graph, stream=side):
+                step()
+        except Exception as exc:  # noqa: BLE001 - reported in the JSON line
+            graph, why = None, f"capture failed: {type(exc).__name__}: {str(exc)[:120]}"
+        torch.cuda.synchronize()
+        if not self.all_agree(graph is not None):
+            return None, why or "capture failed on another rank"
+        return float(self.time_step(graph.replay).mean()), ""
 
 
-def time_host_out_steps(b: Bench, steps: int, warmup: int, flush: torch.Tensor) -> float:
-    """Mean microseconds of the end-to-end step in which combine writes its result to pinned
-    host memory itself (upload, dispatch, combine-to-host); max over ranks."""
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(steps)]
-    for i in range(warmup + steps):
-        flush.add_(1)
-        _rank_barrier(b.world)
-        e = evs[i - warmup] if i >= warmup else None
-        if e:
-            e[0].record()
-        b.upload()
-        b.dispatch()
-        b.combine_to_host()
-        if e:
-            e[1].record()
-    torch.cuda.synchronize()
-    t = torch.tensor([a.elapsed_time(c) for a, c in evs], dtype=torch.float64,
-                     device=b.device) * 1e3
-    return float(_max_over_ranks(t, b.world).mean())
-
-
-def time_graph_steps(b: Bench, steps: int, warmup: int, flush: torch.Tensor) -> tuple[float | None, str]:
-    """Mean microseconds of the end-to-end step (upload, dispatch, combine, read-back)
-    replayed as one CUDA graph; max over ranks."""
+def measure_arm(kind: str, h: Harness, tokens: int, rank: int, world: int, no_graph: bool) -> dict:
+    """Every figure of one arm: kernel-only latencies at `tokens` and at 1 token per GPU, and
+    the end-to-end step in every mode the arm supports."""
+    arm = Arm(kind, tokens, rank, world, h.dev)
 
     def step() -> None:
-        b.upload()
-        b.dispatch()
-        b.combine()
-        b.download()
+        arm.dispatch()
+        arm.combine()
 
-    graph, why = _capture(step)
-    ok = torch.tensor([1.0 if graph is not None else 0.0], device=b.device)
-    if b.world > 1:
-        import torch.distributed as dist
+    def step_e2e() -> None:
+        arm.upload()
+        arm.dispatch()
+        arm.combine()
+        arm.download()
 
-        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-    if ok.item() < 1.0:
-        return None, why or "capture failed on another rank"
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(steps)]
-    for i in range(warmup + steps):
-        flush.add_(1)
-        _rank_barrier(b.world)
-        e = evs[i - warmup] if i >= warmup else None
-        if e:
-            e[0].record()
-        graph.replay()
-        if e:
-            e[1].record()
+    if world > 1:
+        torch.distributed.barrier()
     torch.cuda.synchronize()
-    t = torch.tensor([a.elapsed_time(c) for a, c in evs], dtype=torch.float64,
-                     device=b.device) * 1e3
-    return float(_max_over_ranks(t, b.world).mean()), ""
+    wall0 = time.perf_counter()
+    t_pair = h.time_pair(arm.dispatch, arm.combine)
+    t_step = h.time_step(step)
+    torch.cuda.synchronize()
+    if world > 1:
+        torch.distributed.barrier()
+    wall1 = time.perf_counter()
+    modes: dict[str, float | None] = {
+        "eager calls, copy engine both ways": float(h.time_step(step_e2e).mean())}
+    graph_why = "disabled"
+    if not no_graph:
+        modes["one CUDA graph replay per step"], graph_why = h.time_graph(step_e2e)
+    if kind == "ours":
+        def step_host_out() -> None:
+            arm.upload()
+            arm.dispatch()
+            arm.combine_to_host()
+
+        def step_host_both() -> None:
+            arm.dispatch_from_host()
+            arm.combine_host_both()
+
+        modes["eager calls, combine writes the tokens to pinned host memory"] = float(
+            h.time_step(step_host_out).mean())
+        try:
+            modes["eager calls, dispatch reads its inputs from and combine writes the tokens to "
+                  "pinned host memory"] = float(h.time_step(step_host_both).mean())
+            if not no_graph:
+                modes["one CUDA graph replay per step, inputs read from and tokens written to "
+                      "pinned host memory"], _ = h.time_graph(step_host_both)
+        except RuntimeError as exn:  # an older native library without host-input support
+            graph_why = (graph_why + "; " if graph_why else "") + f"host-input mode: {str(exn)[:100]}"
+    res = {
+        "latency_us": {str(tokens): {
+            "dispatch_us_p50": float(t_pair[:, 0].median()),
+            "combine_us_p50": float(t_pair[:, 1].median()),
+            "step_us_p50": float(t_step.median()),
+            "step_us_mean": float(t_step.mean()),
+            "step_us_mean_with_mid_event": float(t_pair[:, 2].mean())}},
+        "e2e_modes_us_per_step": modes,
+        "e2e_note": graph_why,
+        "h2d_bytes": arm.h2d_bytes(), "d2h_bytes": arm.d2h_bytes(),
+        "wall_ms_per_step_incl_flush_and_barrier":
+            (wall1 - wall0) * 1e3 / (2 * (h.steps + h.warmup)),
+    }
+    arm.close()
+    if tokens != 1:
+        one = Arm(kind, 1, rank, world, h.dev)
+        t = h.time_pair(one.dispatch, one.combine, steps=min(h.steps, 100))
+        one.close()
+        res["latency_us"]["1"] = {"dispatch_us_p50": float(t[:, 0].median()),
+                                  "combine_us_p50": float(t[:, 1].median()),
+                                  "step_us_p50": float(t[:, 2].median())}
+    return res
 
 
-def nccl_baseline(b: Bench, steps: int, warmup: int, flush: torch.Tensor) -> float | None:
-    """p50 microseconds of torch all_to_all_single on the reference's dense shape."""
-    if b.world == 1:
+def e2e_entry(world: int, tokens: int, res: dict) -> dict:
+    """The end-to-end entry of the JSON line.  Every mode is the whole step through the
+    library's public API with the step's inputs starting in pinned host memory and its result
+    ending there, inside the timed region; `value` is the best mode the library supports, the
+    same rule for both arms, and all modes are listed."""
+    modes = res["e2e_modes_us_per_step"]
+    have = {k: v for k, v in modes.items() if v is not None}
+    best = min(have, key=have.get)
+    return {"value": world * tokens / (have[best] * 1e-6), "unit": "tokens/s",
+            "us_per_step": have[best], "mode": best, "modes_us_per_step": modes,
+            "h2d_bytes_per_step": res["h2d_bytes"], "d2h_bytes_per_step": res["d2h_bytes"],
+            "note": res["e2e_note"]}
+
+
+def config_entry(world: int, tokens: int, numa: str) -> dict:
+    return {"model": "DeepSeek-V3 MoE layer all-to-all", "global_batch": world * tokens,
+            "seq_len": 1, "tokens_per_gpu": tokens, "parallelism": f"ep{world}",
+            "l2": "flushed between steps (256 MiB write)",
+            "timing": "CUDA events around each step (dispatch + combine, nothing recorded in "
+                      "between), ranks aligned by an NCCL all-reduce of one word before the first "
+                      "event, max over ranks, mean over steps; dispatch/combine p50 from a second "
+                      "pass with an event between the two",
+            "host_placement": numa}
+
+
+def vs_published(world: int, tokens: int, value: float) -> float | None:
+    """value / the reference's published tokens/s; the published rows are EP8 only."""
+    pub = PUBLISHED_US.get(tokens)
+    if pub is None or world != PUBLISHED_WORLD:
         return None
-    import torch.distributed as dist
+    return value / (world * tokens / ((pub["dispatch"] + pub["combine"]) * 1e-6))
 
-    cfg = b.cfg
+
+def base_line(world: int, tokens: int, steps: int, warmup: int, numa: str, res: dict) -> dict:
+    main = res["latency_us"][str(tokens)]
+    value = world * tokens / (main["step_us_mean"] * 1e-6)
+    return {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": main["step_us_mean"] / 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": vs_published(world, tokens, value), "dtype": DTYPE,
+            "data": DATA, "config": config_entry(world, tokens, numa),
+            "latency_us": res["latency_us"],
+            "published_reference_us": {str(k): v for k, v in PUBLISHED_US.items()},
+            "published_reference_world": PUBLISHED_WORLD,
+            "e2e": e2e_entry(world, tokens, res),
+            "wall_ms_per_step_incl_flush_and_barrier":
+                res["wall_ms_per_step_incl_flush_and_barrier"]}
+
+
+def init_distributed(world: int, local_rank: int) -> None:
+    if world > 1:
+        torch.distributed.init_process_group(backend="cpu:gloo,cuda:nccl",
+                                             device_id=torch.device("cuda", local_rank))
+        try:
+            torch._C._distributed_c10d._register_process_group("default",
+                                                               torch.distributed.group.WORLD)
+        except Exception:  # noqa: BLE001 - already registered
+            pass
+
+
+# ------------------------------------------------------------------ reference arm ----
+
+def _unavailable(why: str) -> None:
+    if int(os.environ.get("RANK", "0")) == 0:
+        _emit({"impl": "reference", "unavailable": why})
+
+
+def _reference_sub_arm(args: argparse.Namespace, kind: str) -> dict:
+    """Measures one transport of the reference in this process."""
+    rank, world, local_rank = _env_rank()
+    dev = torch.device("cuda", local_rank)
+    if kind == "ref-internode":
+        # The path of the reference's own benchmark (tests/bench_all_to_all.py:60, 239-241):
+        # NVSHMEM initialised from a unique id, then AllToAll.internode.
+        import torch.distributed as dist
+        from pplx_kernels import nvshmem as ref_nvshmem
+
+        uid = (ref_nvshmem.nvshmem_get_unique_id() if rank == 0
+               else ref_nvshmem.nvshmem_alloc_empty_unique_id())
+        dist.broadcast(uid, src=0)
+        ref_nvshmem.nvshmem_init(uid, rank, world)
+    h = Harness(world, dev, args.steps, max(args.warmup, 3))
+    res = measure_arm(kind, h, args.tokens, rank, world, args.no_graph)
+    if kind == "ref-internode":
+        ref_nvshmem.nvshmem_finalize()
+    return res
+
+
+def _internode_child(args: argparse.Namespace) -> dict:
+    """Runs the NVSHMEM sub-arm in child processes (one per rank, started by every rank of the
+    parent job) so that a failure or a hang of NVSHMEM's bring-up cannot take the parent's
+    result with it.  Returns the child's result, or {"unavailable": reason}."""
+    rank, world, local_rank = _env_rank()
+    out_dir = os.environ.get("TMPDIR", tempfile.gettempdir())
+    out_file = os.path.join(out_dir, f"pplx_ref_internode_{os.environ.get('MASTER_PORT', '0')}.json")
+    if rank == 0 and os.path.exists(out_file):
+        os.remove(out_file)
+    torch.distributed.barrier()
+    env = dict(os.environ)
+    env["MASTER_PORT"] = str(int(os.environ.get("MASTER_PORT", "29500")) + 23)
+    # The children rendezvous among themselves: rank 0 of them hosts the store on the new port
+    # (under torchrun the workers would otherwise look for the launcher's store there).
+    env["TORCHELASTIC_USE_AGENT_STORE"] = "False"
+    # The symmetric heap must hold the reference's buffers (about 1.9 GB at 128 tokens).
+    env.setdefault("NVSHMEM_SYMMETRIC_SIZE", "6G")
+    env.setdefault("NVSHMEM_REMOTE_TRANSPORT", "none")
+    env.setdefault("NVSHMEM_DISABLE_CUDA_VMM", "0")
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference", "--ref-sub",
+           "internode", "--out-file", out_file, "--gpus", str(world), "--steps", str(args.steps),
+           "--warmup", str(args.warmup), "--tokens", str(args.tokens)]
+    if args.no_graph:
+        cmd.append("--no-graph")
+    why = ""
+    try:
+        proc = subprocess.run(cmd, env=env, capture_output=True, text=True,
+                              timeout=args.ref_child_timeout)
+        if proc.returncode != 0:
+            tail = (proc.stderr or proc.stdout or "").strip().splitlines()[-3:]
+            why = f"exit code {proc.returncode}: " + " | ".join(tail)[-300:]
+    except subprocess.TimeoutExpired:
+        why = f"did not finish within {args.ref_child_timeout} s"
+    ok = torch.tensor([0.0 if why else 1.0], device=torch.device("cuda", local_rank))
+    torch.distributed.all_reduce(ok, op=torch.distributed.ReduceOp.MIN)
+    reasons: list = [None] * world
+    torch.distributed.all_gather_object(reasons, why)
+    if ok.item() < 1.0:
+        first = next((f"rank {r}: {w}" for r, w in enumerate(reasons) if w), "unknown")
+        return {"unavailable": "AllToAll.internode over NVSHMEM (child processes): " + first}
+    if rank != 0:
+        return {}
+    try:
+        with open(out_file) as f:
+            return json.load(f)
+    except (OSError, ValueError) as exn:
+        return {"unavailable": f"child result unreadable: {exn}"}
+
+
+def reference_arm(args: argparse.Namespace) -> None:
+    """The UNMODIFIED reference (installed under baseline/_ref by the offline pip command)
+    through its own public API.  Two transports are measured with the harness of the other arm:
+    ``AllToAll.intranode`` (its CUDA-IPC / NVLink kernels) in this process and
+    ``AllToAll.internode`` (its NVSHMEM kernels over NVSHMEM's NVLink transport, the path its own
+    benchmark uses) in child processes.  The faster one is the arm's `value`."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.exists(os.path.join(ref_dir, "pplx_kernels", "libpplx_kernels.so")):
+        return _unavailable("baseline/_ref is empty: the offline install of the reference has "
+                            "not been run on this machine")
+    rank, world, local_rank = _env_rank()
+    if world < 2:
+        return _unavailable("the reference refuses a single rank: AllToAll.intranode asserts "
+                            "world_size // dp_size > 1 (src/pplx_kernels/all_to_all.py:101)")
+    sys.path.insert(0, ref_dir)
+    from pplx_kernels_b200.parallel.affinity import bind_to_device_numa_node
+    from pplx_kernels_b200.utils.clocks import ClockSampler
+
+    torch.cuda.set_device(local_rank)
+    numa = bind_to_device_numa_node(local_rank)  # same host placement in both arms
+    init_distributed(world, local_rank)
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    if args.ref_sub == "internode":  # child process of _internode_child
+        res = _reference_sub_arm(args, "ref-internode")
+        if rank == 0:
+            with open(args.out_file + ".tmp", "w") as f:
+                json.dump(res, f)
+            os.replace(args.out_file + ".tmp", args.out_file)
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+        return
+
+    with ClockSampler(local_rank, period_ms=50) as sampler:
+        intra = _reference_sub_arm(args, "ref-intranode")
+    clocks = sampler.summary()
+    inter = {"unavailable": "skipped (--ref-sub intranode)"}
+    if args.ref_sub == "both":
+        inter = _internode_child(args)
+
+    def step_mean(res: dict) -> float:
+        return res["latency_us"][str(args.tokens)]["step_us_mean"]
+
+    best, best_name = intra, "AllToAll.intranode"
+    if rank == 0 and "unavailable" not in inter and step_mean(inter) < step_mean(intra):
+        best, best_name = inter, "AllToAll.internode"
+    if rank == 0:
+        line = base_line(world, args.tokens, steps, warmup, numa, best)
+        line.update({
+            "clocks": clocks, "gpu_launches": 2 * steps, "impl": "reference",
+            "reference_path": f"pplx_kernels.{best_name} (unmodified, sm_100a build); the faster "
+                              "of the two transports, both listed under sub_arms",
+            "sub_arms": {"intranode": intra, "internode (NVSHMEM, NVLink transport)": inter},
+            "repo_native_library_mapped": _repo_native_mapped(),
+        })
+        _emit(line)
+    torch.distributed.barrier()
+    torch.distributed.destroy_process_group()
+
+
+# ------------------------------------------------------------------------ own arm ----
+
+def nccl_baseline(h: Harness, cfg, tokens: int) -> float | None:
+    """p50 microseconds of torch all_to_all_single on the reference's dense shape."""
+    if h.world == 1:
+        return None
     per_token = cfg.hidden_dim_bytes + cfg.hidden_dim_scale_bytes
-    shape = (b.world, cfg.num_experts // b.world, b.tokens * per_token)
-    src = torch.zeros(shape, dtype=torch.uint8, device=b.device)
+    shape = (h.world, cfg.num_experts // h.world, tokens * per_token)
+    src = torch.zeros(shape, dtype=torch.uint8, device=h.dev)
     dst = torch.empty_like(src)
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(steps)]
-    for i in range(warmup + steps):
-        flush.add_(1)
-        _rank_barrier(b.world)
-        if i >= warmup:
-            evs[i - warmup][0].record()
-        dist.all_to_all_single(dst, src)
-        if i >= warmup:
-            evs[i - warmup][1].record()
-    torch.cuda.synchronize()
-    t = torch.tensor([e[0].elapsed_time(e[1]) for e in evs], dtype=torch.float64,
-                     device=b.device) * 1e3
-    return float(_max_over_ranks(t, b.world).median())
+    t = h.time_step(lambda: torch.distributed.all_to_all_single(dst, src), steps=min(h.steps, 50))
+    return float(t.median())
+
+
+def measured_nvlink_gbs(world: int) -> tuple[float, str]:
+    """Peer-store bandwidth per direction seen by a plain copy kernel of the library (every
+    rank stores 64 MiB into each peer at once), or the default when there is no peer."""
+    if world < 2:
+        return NVLINK_GBS_DEFAULT, "default (single GPU)"
+    try:
+        from pplx_kernels_b200.utils.peer_bandwidth import measure_peer_store_gbs
+
+        return measure_peer_store_gbs(), "measured: all ranks store to all peers at once, copy kernel"
+    except Exception as exn:  # noqa: BLE001 - the floor falls back to the default
+        return NVLINK_GBS_DEFAULT, f"default ({type(exn).__name__}: {str(exn)[:80]})"
+
+
+def own_arm(args: argparse.Namespace) -> None:
+    rank, world, local_rank = _env_rank()
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    from pplx_kernels_b200.parallel.affinity import bind_to_device_numa_node
+    from pplx_kernels_b200.utils.clocks import ClockSampler
+
+    numa = bind_to_device_numa_node(local_rank)  # before any pinned allocation
+    init_distributed(world, local_rank)
+    if world > 1:
+        from pplx_kernels_b200.parallel.runtime import init_runtime_from_torch
+
+        init_runtime_from_torch()
+    steps, warmup = args.steps, max(args.warmup, 3)
+    h = Harness(world, dev, steps, warmup)
+    with ClockSampler(local_rank, period_ms=50) as sampler:
+        res = measure_arm("ours", h, args.tokens, rank, world, args.no_graph)
+    clocks = sampler.summary()
+    from pplx_kernels_b200.utils.testing import DEEPSEEK_V3 as cfg
+
+    nccl_us = nccl_baseline(h, cfg, args.tokens)
+    res["latency_us"][str(args.tokens)]["nccl_all_to_all_single_us_p50"] = nccl_us
+    link_gbs, link_how = measured_nvlink_gbs(world)
+
+    # The second half of the headline metric: tokens/s of the whole MoE layer (dispatch ->
+    # SwiGLU expert FFN on the tcgen05 grouped GEMM -> combine), Mixtral-8x7B shape, bf16.
+    moe = None
+    if not args.no_moe:
+        from pplx_kernels_b200.utils.bench_moe import measure as measure_moe
+
+        moe = measure_moe("mixtral-8x7b", 512, iters=10, warmup=3, rank=rank, world=world,
+                          dev=dev, flush=h.flush)
+
+    # Roofline of the headline step: bytes that must move over the slower path.
+    peaks = _peaks()
+    slot = cfg.hidden_dim_bytes + cfg.hidden_dim_scale_bytes + 16
+    rows = args.tokens * cfg.experts_per_token
+    disp_bytes = rows * slot
+    comb_bytes = rows * cfg.hidden_dim * 2
+    if world > 1:
+        remote = (world - 1) / world
+        floor_us = {"dispatch": disp_bytes * remote / link_gbs / 1e3,
+                    "combine": comb_bytes * remote / link_gbs / 1e3}
+        bound = f"NVLink {link_gbs:.0f} GB/s per direction ({link_how})"
+    else:
+        # single GPU: staging write + staging read + output write per row (dispatch);
+        # staging write + staging read per row plus the token write (combine)
+        hbm = float(peaks["hbm_gbs"])
+        floor_us = {"dispatch": 3 * disp_bytes / hbm / 1e3, "combine": 2.125 * comb_bytes / hbm / 1e3}
+        bound = f"HBM {hbm:.0f} GB/s of measured copy bandwidth"
+    main_res = res["latency_us"][str(args.tokens)]
+    roofline = {
+        "bound": bound,
+        "dispatch_floor_us": floor_us["dispatch"],
+        "combine_floor_us": floor_us["combine"],
+        "dispatch_frac": floor_us["dispatch"] / main_res["dispatch_us_p50"],
+        "combine_frac": floor_us["combine"] / main_res["combine_us_p50"],
+    }
+    line = base_line(world, args.tokens, steps, warmup, numa, res)
+    line.update({"roofline": roofline, "clocks": clocks, "gpu_launches": 2 * steps,
+                 "moe_layer": moe, "impl": "ours"})
+    if rank == 0:
+        _emit(line)
+    if world > 1:
+        from pplx_kernels_b200.parallel.runtime import finalize_runtime
+
+        torch.distributed.barrier()
+        finalize_runtime()
+        torch.distributed.destroy_process_group()
 
 
 def main() -> None:
@@ -484,6 +673,11 @@ def main() -> None:
     ap.add_argument("--no-moe", action="store_true", help="skip the MoE-layer measurement")
     ap.add_argument("--no-graph", action="store_true",
                     help="skip the CUDA-graph replay of the end-to-end step")
+    ap.add_argument("--ref-sub", choices=["both", "intranode", "internode"], default="both",
+                    help="reference arm: which transport(s) to measure")
+    ap.add_argument("--ref-child-timeout", type=int, default=300,
+                    help="seconds the NVSHMEM sub-arm's child processes may take")
+    ap.add_argument("--out-file", default="", help=argparse.SUPPRESS)
     args = ap.parse_args()
     global _RESULT_FD
     sys.stdout.flush()
@@ -493,167 +687,11 @@ def main() -> None:
         try:
             reference_arm(args)
         except Exception as exn:  # the reference arm must never take the run down
+            if args.ref_sub == "internode":
+                raise
             _unavailable(f"reference run failed: {type(exn).__name__}: {str(exn)[:200]}")
         return
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
-    torch.cuda.set_device(local_rank)
-    from pplx_kernels_b200.parallel.affinity import bind_to_device_numa_node
-
-    numa = bind_to_device_numa_node(local_rank)  # before any pinned allocation
-    if world > 1:
-        import torch.distributed as dist
-
-        import pplx_kernels_b200 as pk
-
-        dist.init_process_group(backend="cpu:gloo,cuda:nccl",
-                                device_id=torch.device("cuda", local_rank))
-        uid = pk.nvshmem_get_unique_id() if rank == 0 else pk.nvshmem_alloc_empty_unique_id()
-        dist.broadcast(uid, src=0)
-        pk.nvshmem_init(uid, rank, world)
-
-    from pplx_kernels_b200.utils.clocks import ClockSampler
-
-    steps, warmup = args.steps, max(args.warmup, 3)
-    flush = torch.zeros(256 << 20, dtype=torch.uint8, device="cuda")
-    peaks = _peaks()
-
-    results: dict[int, dict] = {}
-    e2e_us = None
-    bench_main = Bench(args.tokens)
-    with ClockSampler(local_rank, period_ms=50) as sampler:
-        if world > 1:
-            torch.distributed.barrier()
-        torch.cuda.synchronize()
-        wall0 = time.perf_counter()
-        t_main = time_steps(bench_main, steps, warmup, flush, e2e=False)
-        t_step = time_steps(bench_main, steps, warmup, flush, e2e=False, mid_event=False)
-        torch.cuda.synchronize()
-        if world > 1:
-            torch.distributed.barrier()
-        wall1 = time.perf_counter()
-        t_e2e = time_steps(bench_main, steps, warmup, flush, e2e=True, mid_event=False)
-        graph_us, graph_why = ((None, "disabled") if args.no_graph
-                               else time_graph_steps(bench_main, steps, warmup, flush))
-        host_out_us = time_host_out_steps(bench_main, steps, warmup, flush)
-    clocks = sampler.summary()
-    e2e_us = float(t_e2e[:, 2].mean())
-    nccl_us = nccl_baseline(bench_main, min(steps, 50), 5, flush)
-    h2d, d2h = bench_main.h2d_bytes(), bench_main.d2h_bytes()
-    bench_main.close()
-    results[args.tokens] = {
-        "dispatch_us_p50": float(t_main[:, 0].median()),
-        "combine_us_p50": float(t_main[:, 1].median()),
-        "step_us_p50": float(t_step[:, 2].median()),
-        "step_us_mean": float(t_step[:, 2].mean()),
-        "step_us_mean_with_mid_event": float(t_main[:, 2].mean()),
-        "nccl_all_to_all_single_us_p50": nccl_us,
-    }
-    for extra_tokens in ([1] if args.tokens != 1 else []):
-        b = Bench(extra_tokens)
-        t = time_steps(b, min(steps, 100), warmup, flush, e2e=False)
-        b.close()
-        results[extra_tokens] = {
-            "dispatch_us_p50": float(t[:, 0].median()),
-            "combine_us_p50": float(t[:, 1].median()),
-            "step_us_p50": float(t[:, 2].median()),
-        }
-
-    # The second half of the headline metric: tokens/s of the whole MoE layer (dispatch ->
-    # SwiGLU expert FFN on the tcgen05 grouped GEMM -> combine), Mixtral-8x7B shape, bf16.
-    moe = None
-    if not args.no_moe:
-        from pplx_kernels_b200.utils.bench_moe import measure as measure_moe
-
-        moe = measure_moe("mixtral-8x7b", 512, iters=10, warmup=3, rank=rank, world=world,
-                          dev=torch.device("cuda", local_rank), flush=flush)
-
-    # Roofline of the headline step: bytes that must move over the slower path.
-    cfg = bench_main.cfg
-    slot = cfg.hidden_dim_bytes + cfg.hidden_dim_scale_bytes + 16
-    rows = args.tokens * cfg.experts_per_token
-    disp_bytes = rows * slot
-    comb_bytes = rows * cfg.hidden_dim * 2
-    if world > 1:
-        remote = (world - 1) / world
-        floor_us = {"dispatch": disp_bytes * remote / NVLINK_GBS / 1e3,
-                    "combine": comb_bytes * remote / NVLINK_GBS / 1e3}
-        bound = f"NVLink {NVLINK_GBS:.0f} GB/s per direction (measured peer copy)"
-    else:
-        # single GPU: staging write + staging read + output write per row (dispatch);
-        # staging write + staging read per row plus the token write (combine)
-        hbm = float(peaks["hbm_gbs"])
-        floor_us = {"dispatch": 3 * disp_bytes / hbm / 1e3, "combine": 2.125 * comb_bytes / hbm / 1e3}
-        bound = f"HBM {hbm:.0f} GB/s of measured copy bandwidth"
-    main_res = results[args.tokens]
-    roofline = {
-        "bound": bound,
-        "dispatch_floor_us": floor_us["dispatch"],
-        "combine_floor_us": floor_us["combine"],
-        "dispatch_frac": floor_us["dispatch"] / main_res["dispatch_us_p50"],
-        "combine_frac": floor_us["combine"] / main_res["combine_us_p50"],
-    }
-
-    step_s = main_res["step_us_mean"] * 1e-6
-    value = world * args.tokens / step_s
-    pub = PUBLISHED_US.get(args.tokens)
-    vs = None
-    if pub:
-        # the published numbers are per-rank latencies at EP8; same tokens per GPU
-        vs = value / (world * args.tokens / ((pub["dispatch"] + pub["combine"]) * 1e-6))
-    line = {
-        "metric": "MoE dispatch+combine tokens/s (DeepSeek-V3 shape: 256 experts, top-8, hidden "
-                  "7168, fp8 dispatch + bf16 combine)",
-        "value": value,
-        "unit": "tokens/s",
-        "n_gpus": world,
-        "steps": steps,
-        "warmup": warmup,
-        "ms_per_step": main_res["step_us_mean"] / 1e3,
-        "higher_is_better": True,
-        "scaling": "weak",
-        "vs_baseline": vs,
-        "dtype": "fp8_e4m3 dispatch (fp32 scale per 128) / bf16 combine",
-        "data": "synthetic (uniform random distinct top-8 routing, random tokens, softmax weights)",
-        "config": {
-            "model": "DeepSeek-V3 MoE layer all-to-all",
-            "global_batch": world * args.tokens,
-            "seq_len": 1,
-            "tokens_per_gpu": args.tokens,
-            "parallelism": f"ep{world}",
-            "l2": "flushed between steps (256 MiB write)",
-            "timing": "CUDA events around each step (dispatch + combine, nothing recorded in "
-                      "between), max over ranks, mean over steps; dispatch/combine p50 from a "
-                      "second pass with an event between the two",
-            "host_placement": numa,
-        },
-        "latency_us": {str(k): v for k, v in results.items()},
-        "published_reference_us": {str(k): v for k, v in PUBLISHED_US.items()},
-        "roofline": roofline,
-        "clocks": clocks,
-        "wall_ms_per_step_incl_flush_and_barrier": (wall1 - wall0) * 1e3 / (steps + warmup),
-        "e2e": _e2e_entry(world, args.tokens,
-                          {"eager calls, copy engine both ways": e2e_us,
-                           "one CUDA graph replay per step": graph_us,
-                           "eager calls, combine writes the tokens to pinned host memory":
-                               host_out_us},
-                          h2d, d2h, graph_why),
-        "gpu_launches": 2 * steps,
-        "wall_note": "wall clock covers both timing passes of the kernel-only arm",
-        "moe_layer": moe,
-        "impl": "ours",
-    }
-    if rank == 0:
-        _emit(line)
-    if world > 1:
-        import pplx_kernels_b200 as pk
-
-        torch.distributed.barrier()
-        pk.nvshmem_finalize()
-        torch.distributed.destroy_process_group()
+    own_arm(args)
 
 
 if __name__ == "__main__":

@@ -131,7 +131,8 @@ class AllToAll:
     ) -> None:
         """``out_tokens`` may also be a pinned host tensor: the reduction then writes the
         tokens to host memory itself (valid once the stream has been synchronised) and the
-        separate device-to-host copy of small decode batches goes away."""
+        separate device-to-host copy of small decode batches goes away.  ``weights`` and
+        ``indices`` may be pinned host tensors as well."""
         assert self._ptr is not None
         self._combine_fn(
             self._ptr,
@@ -156,9 +157,33 @@ class AllToAll:
         keys = ("code", "phase", "peer", "expected", "observed", "block", "rank", "count")
         return dict(zip(keys, _ops.all_to_all_status(self._ptr), strict=True))
 
+    def peek_status(self) -> dict[str, int]:
+        """The host-visible mirror of the failure record.  Does not touch the device, so it
+        can be polled by a watchdog while kernels are still inside their waits."""
+        keys = ("code", "phase", "peer", "expected", "observed", "block", "rank", "count")
+        return dict(zip(keys, _ops.all_to_all_peek_status(self._ptr), strict=True))
+
     def check_status(self) -> None:
-        """Raises RuntimeError if a device-side wait ran out or a bounds check failed."""
+        """Raises RuntimeError if a device-side wait ran out or a bounds check failed.
+
+        Reads the host-visible mirror: synchronise the stream first to cover the kernels
+        launched so far.  Once a failure is recorded the object refuses further
+        ``dispatch`` / ``combine`` calls until it is destroyed or ``reset()``.
+        """
         _ops.all_to_all_check_status(self._ptr)
+
+    def reset(self) -> None:
+        """Clears this rank's flags, counters, staging and failure record.
+
+        Collective by contract: after a failure every rank calls ``reset()`` once none of the
+        object's kernels is in flight on any rank, and the ranks meet at a barrier of the
+        caller's (``torch.distributed.barrier()`` will do) before the next ``dispatch``.
+        """
+        _ops.all_to_all_reset(self._ptr)
+
+    def verify_canaries(self) -> None:
+        """Raises if a guard word behind one of the arena's regions was overwritten (synchronises)."""
+        _ops.all_to_all_verify_canaries(self._ptr)
 
     def set_timeout_ms(self, ms: float) -> None:
         _ops.all_to_all_set_timeout_ms(self._ptr, float(ms))
@@ -233,7 +258,8 @@ class AllToAll:
 
     def layout(self) -> dict[str, int]:
         keys = ("num_local_experts", "num_dp_groups", "rows_per_expert", "region_slots",
-                "slot_bytes", "arena_bytes")
+                "slot_bytes", "arena_bytes", "flag_in_data", "line_slot_bytes",
+                "line_combine_slot_bytes")
         return dict(zip(keys, _ops.all_to_all_layout(self._ptr), strict=True))
 
     # ------------------------------------------------------------ constructors --

@@ -170,6 +170,22 @@ void destroy(int64_t ptr) {
 
 // ------------------------------------------------------------ tensor glue ----
 
+// Inputs may live in pinned host memory instead of device memory (an extension over the
+// reference): the kernels then read them across PCIe themselves and no upload precedes
+// the call.  Returns the address the device uses for `t`.
+bool on_pinned_host(const at::Tensor& t) { return t.is_cpu() && t.is_pinned(); }
+
+const void* device_address(const at::Tensor& t, const char* name) {
+  if (t.is_cuda()) return t.data_ptr();
+  TORCH_CHECK(on_pinned_host(t), name, " must be a CUDA tensor or a pinned host tensor");
+  if (t.numel() == 0) return nullptr;
+  void* mapped = nullptr;
+  const cudaError_t err = cudaHostGetDevicePointer(&mapped, t.data_ptr(), 0);
+  TORCH_CHECK(err == cudaSuccess, name, ": pinned memory is not mapped into the device (",
+              cudaGetErrorString(err), ")");
+  return mapped;
+}
+
 DispatchCall make_dispatch_call(const AllToAll& ata, at::Tensor& out_expert_num_tokens,
                                 at::Tensor& out_expert_x,
                                 const std::optional<at::Tensor>& out_expert_x_scale,
@@ -189,8 +205,9 @@ DispatchCall make_dispatch_call(const AllToAll& ata, at::Tensor& out_expert_num_
   TORCH_CHECK(out_expert_x.size(2) * static_cast<int64_t>(out_expert_x.element_size()) ==
                   p.hidden_bytes,
               "out_expert_x rows must be hidden_dim_bytes long");
-  TORCH_CHECK(dp_x.is_cuda() && dp_x.dim() == 2 && dp_x.is_contiguous(),
-              "dp_x must be a contiguous 2-D CUDA tensor");
+  const bool host_in = on_pinned_host(dp_x);
+  TORCH_CHECK((dp_x.is_cuda() || host_in) && dp_x.dim() == 2 && dp_x.is_contiguous(),
+              "dp_x must be a contiguous 2-D CUDA (or pinned host) tensor");
   if (quantize) {
     TORCH_CHECK(dp_x.scalar_type() == at::kBFloat16 && dp_x.size(1) == p.hidden_dim,
                 "quantising dispatch takes bfloat16 tokens of [num_tokens, hidden_dim]");
@@ -198,18 +215,21 @@ DispatchCall make_dispatch_call(const AllToAll& ata, at::Tensor& out_expert_num_
     TORCH_CHECK(dp_x.size(1) * static_cast<int64_t>(dp_x.element_size()) == p.hidden_bytes,
                 "dp_x rows must be hidden_dim_bytes long");
   }
-  TORCH_CHECK(indices.is_cuda() && indices.dim() == 2 && indices.is_contiguous() &&
-                  indices.element_size() == 4 && indices.size(1) == p.topk,
-              "indices must be a contiguous 32-bit CUDA tensor of [num_tokens, experts_per_token]");
+  TORCH_CHECK((host_in ? on_pinned_host(indices) : indices.is_cuda()) && indices.dim() == 2 &&
+                  indices.is_contiguous() && indices.element_size() == 4 &&
+                  indices.size(1) == p.topk,
+              "indices must be a contiguous 32-bit tensor of [num_tokens, experts_per_token] in "
+              "the same kind of memory as dp_x");
   TORCH_CHECK(indices.size(0) == dp_x.size(0), "indices and dp_x disagree on the token count");
 
   DispatchCall c;
+  c.x_on_host = host_in;
   c.out_num_tokens = out_expert_num_tokens.data_ptr<int32_t>();
   c.out_x.data = static_cast<uint8_t*>(out_expert_x.data_ptr());
   c.out_x.stride_outer = out_expert_x.stride(0) * out_expert_x.element_size();
   c.out_x.stride_row = out_expert_x.stride(1) * out_expert_x.element_size();
   c.out_rows = out_expert_x.size(1);
-  c.x.data = static_cast<const uint8_t*>(dp_x.data_ptr());
+  c.x.data = static_cast<const uint8_t*>(device_address(dp_x, "dp_x"));
   c.x.stride_row = dp_x.stride(0) * dp_x.element_size();
   if (out_expert_x_scale.has_value()) {
     const at::Tensor& s = *out_expert_x_scale;
@@ -225,15 +245,16 @@ DispatchCall make_dispatch_call(const AllToAll& ata, at::Tensor& out_expert_num_
   }
   if (dp_x_scale.has_value()) {
     const at::Tensor& s = *dp_x_scale;
-    TORCH_CHECK(s.is_cuda() && s.dim() == 2 && s.scalar_type() == at::kFloat,
-                "dp_x_scale must be a 2-D float32 CUDA tensor");
+    TORCH_CHECK((host_in ? on_pinned_host(s) : s.is_cuda()) && s.dim() == 2 &&
+                    s.scalar_type() == at::kFloat,
+                "dp_x_scale must be a 2-D float32 tensor in the same kind of memory as dp_x");
     TORCH_CHECK(s.size(0) == dp_x.size(0) && s.size(1) * 4 == p.scale_bytes,
                 "dp_x_scale has the wrong shape");
-    c.x_scale.data = s.data_ptr<float>();
+    c.x_scale.data = static_cast<const float*>(device_address(s, "dp_x_scale"));
     c.x_scale.stride_row = s.stride(0);
     c.x_scale.stride_col = s.stride(1);
   }
-  c.indices = static_cast<const uint32_t*>(indices.data_ptr());
+  c.indices = static_cast<const uint32_t*>(device_address(indices, "indices"));
   if (bound_m.has_value()) {
     TORCH_CHECK(bound_m->is_cuda() && bound_m->numel() == 1 && bound_m->element_size() == 4,
                 "bound_m must be a 32-bit CUDA scalar tensor");
@@ -267,12 +288,14 @@ CombineCall make_combine_call(const AllToAll& ata, at::Tensor& out_tokens,
               "column stride");
   TORCH_CHECK(out_tokens.scalar_type() == at::kHalf || out_tokens.scalar_type() == at::kBFloat16,
               "out_tokens must be float16 or bfloat16");
-  TORCH_CHECK(indices.is_cuda() && indices.dim() == 2 && indices.size(1) == p.topk,
-              "indices must be a CUDA tensor of [num_tokens, experts_per_token]");
-  TORCH_CHECK(weights.is_cuda() && weights.dim() == 2 && weights.scalar_type() == at::kFloat &&
-                  weights.stride(1) == 1 && weights.size(0) == indices.size(0) &&
-                  weights.size(1) == p.topk,
-              "weights must be a float32 CUDA tensor of [num_tokens, experts_per_token]");
+  TORCH_CHECK((indices.is_cuda() || on_pinned_host(indices)) && indices.dim() == 2 &&
+                  indices.size(1) == p.topk,
+              "indices must be a CUDA (or pinned host) tensor of [num_tokens, experts_per_token]");
+  TORCH_CHECK((weights.is_cuda() || on_pinned_host(weights)) && weights.dim() == 2 &&
+                  weights.scalar_type() == at::kFloat && weights.stride(1) == 1 &&
+                  weights.size(0) == indices.size(0) && weights.size(1) == p.topk,
+              "weights must be a float32 CUDA (or pinned host) tensor of [num_tokens, "
+              "experts_per_token]");
   TORCH_CHECK(out_tokens.size(0) >= indices.size(0), "out_tokens has fewer rows than indices");
   TORCH_CHECK(expert_y.is_cuda() && expert_y.dim() == 3 && expert_y.stride(2) == 1 &&
                   expert_y.size(0) == p.nle && expert_y.size(1) >= p.cap &&
@@ -289,7 +312,7 @@ CombineCall make_combine_call(const AllToAll& ata, at::Tensor& out_tokens,
     c.out_tokens = mapped;
   }
   c.out_stride_row = out_tokens.stride(0);
-  c.weights = weights.data_ptr<float>();
+  c.weights = static_cast<const float*>(device_address(weights, "weights"));
   c.w_stride_row = weights.stride(0);
   c.expert_y = expert_y.data_ptr();
   c.y_stride_e = expert_y.stride(0);
@@ -310,7 +333,7 @@ void dispatch_op(int64_t ptr, at::Tensor& out_expert_num_tokens, at::Tensor& out
                  const std::optional<at::Tensor>& dp_x_scale, const at::Tensor& indices,
                  const std::optional<at::Tensor>& bound_m, bool do_send, bool do_recv) {
   AllToAll* ata = lookup(ptr);
-  const c10::cuda::OptionalCUDAGuard guard(dp_x.device());
+  const c10::cuda::OptionalCUDAGuard guard(out_expert_x.device());
   guarded([&] {
     const DispatchCall call = make_dispatch_call(*ata, out_expert_num_tokens, out_expert_x,
                                                  out_expert_x_scale, dp_x, dp_x_scale, indices,
@@ -326,7 +349,7 @@ void dispatch_quant_op(int64_t ptr, at::Tensor& out_expert_num_tokens, at::Tenso
                        const at::Tensor& indices, const std::optional<at::Tensor>& bound_m,
                        bool do_send, bool do_recv) {
   AllToAll* ata = lookup(ptr);
-  const c10::cuda::OptionalCUDAGuard guard(dp_x.device());
+  const c10::cuda::OptionalCUDAGuard guard(out_expert_x.device());
   guarded([&] {
     const DispatchCall call =
         make_dispatch_call(*ata, out_expert_num_tokens, out_expert_x, out_expert_x_scale, dp_x,
@@ -438,6 +461,20 @@ void combine_group_op(std::vector<int64_t> ptrs, std::vector<at::Tensor> out_tok
 std::vector<int64_t> status_op(int64_t ptr) {
   const Status s = guarded([&] { return lookup(ptr)->read_status(); });
   return {s.code, s.phase, s.peer, s.expected, s.observed, s.block, s.rank, s.count};
+}
+
+// The host-visible mirror of the failure record: no device synchronisation.
+std::vector<int64_t> peek_status_op(int64_t ptr) {
+  const Status s = lookup(ptr)->peek_status();
+  return {s.code, s.phase, s.peer, s.expected, s.observed, s.block, s.rank, s.count};
+}
+
+void reset_op(int64_t ptr) {
+  guarded([&] { lookup(ptr)->reset(); });
+}
+
+void verify_canaries_op(int64_t ptr) {
+  guarded([&] { lookup(ptr)->verify_canaries(); });
 }
 
 void check_status_op(int64_t ptr) {
@@ -595,7 +632,7 @@ std::vector<int64_t> read_trace_op(int64_t ptr) {
 std::vector<int64_t> layout_op(int64_t ptr) {
   const A2AParams& p = lookup(ptr)->params();
   return {p.nle, p.num_dp_groups, p.cap, p.region_slots, p.slot_bytes,
-          static_cast<int64_t>(p.arena_bytes)};
+          static_cast<int64_t>(p.arena_bytes), p.ll, p.ll_slot_bytes, p.ll_comb_slot_bytes};
 }
 
 // -------------------------------------------------------- symmetric memory ----
@@ -773,6 +810,9 @@ void register_all_to_all_ops(torch::Library& m) {
 
   m.def("all_to_all_status(int ptr) -> int[]", &status_op);
   m.def("all_to_all_check_status(int ptr) -> ()", &check_status_op);
+  m.def("all_to_all_peek_status(int ptr) -> int[]", &peek_status_op);
+  m.def("all_to_all_reset(int ptr) -> ()", &reset_op);
+  m.def("all_to_all_verify_canaries(int ptr) -> ()", &verify_canaries_op);
   m.def("all_to_all_set_timeout_ms(int ptr, float ms) -> ()", &set_timeout_ms_op);
   m.def("all_to_all_set_debug_checks(int ptr, bool on) -> ()", &set_debug_checks_op);
   m.def("all_to_all_set_max_blocks(int ptr, int n) -> ()", &set_max_blocks_op);

@@ -3,7 +3,8 @@
 // Role parity: csrc/core/buffer.h:13-161 of the reference (HostBuffer,
 // DeviceBuffer, Strided1D/2D/3D).  Differences: buffers are movable, zero-filled
 // on request, and a pinned buffer can be mapped so the device can write into it
-// (used for the status word that a kernel fills when a wait runs out).
+// (used for the host-visible mirror of the status block, which the kernel thread
+// that records a failure fills in).
 #pragma once
 
 #include <cstring>

@@ -32,6 +32,20 @@ __device__ __forceinline__ void report_failure(Status* st, uint32_t code, uint32
     st->observed = observed;
     st->block = blockIdx.x;
     st->rank = rank;
+    // Host-visible mirror: plain stores of the fields, then the code behind a fence, so
+    // that a host that reads a non-zero code also reads the fields that belong to it.
+    Status* host = reinterpret_cast<Status*>(st->mirror);
+    if (host != nullptr) {
+      host->phase = phase;
+      host->peer = peer;
+      host->expected = expected;
+      host->observed = observed;
+      host->block = blockIdx.x;
+      host->rank = rank;
+      host->count = 1u;
+      __threadfence_system();
+      *reinterpret_cast<volatile uint32_t*>(&host->code) = code;
+    }
   }
   atomicAdd(&st->count, 1u);
 }

@@ -22,10 +22,10 @@ int dispatch_threads();
 cudaError_t launch_dispatch(const DispatchArgs& a, bool send, bool recv, int grid,
                             cudaStream_t stream);
 
-// `nranks` ranks that share one device, as one cooperative grid of
-// (grid, nranks) blocks; `dev_args` is a device array of per-rank arguments.
-cudaError_t launch_dispatch_multi(const DispatchArgs* dev_args, int nranks, const A2AParams& p,
-                                  bool send, bool recv, int grid, cudaStream_t stream);
+// `nranks` (at most kMaxLocalRanks) ranks that share one device, as one cooperative grid
+// of (grid, nranks) blocks; the per-rank arguments travel as a kernel parameter.
+cudaError_t launch_dispatch_multi(const DispatchMulti& args, int nranks, bool send, bool recv,
+                                  int grid, cudaStream_t stream);
 
 size_t combine_smem_bytes(const A2AParams& p);
 int combine_threads();
@@ -34,8 +34,7 @@ int combine_threads();
 cudaError_t launch_combine(const CombineArgs& a, DType in, DType out, bool send, bool recv,
                            int grid, cudaStream_t stream);
 
-cudaError_t launch_combine_multi(const CombineArgs* dev_args, int nranks, const A2AParams& p,
-                                 DType in, DType out, bool send, bool recv, int grid,
-                                 cudaStream_t stream);
+cudaError_t launch_combine_multi(const CombineMulti& args, int nranks, DType in, DType out,
+                                 bool send, bool recv, int grid, cudaStream_t stream);
 
 }  // namespace pplx

@@ -61,6 +61,12 @@ struct A2AParams {
   int cap;           // rows per local expert in out_expert_x / expert_y
   int debug_checks;  // non-zero: bounds checks that record instead of corrupting
   int comb_units;    // arrival units one complete expert output row is worth (multiple of 16)
+  // Flag-in-data protocol (core/ll128.cuh) for the plain dispatch and combine.
+  int ll;                  // non-zero: in use
+  int ll_x_lines;          // 128-byte lines that carry a dispatch row's token payload
+  int ll_meta_lines;       // lines that carry its trailer and scales
+  int ll_slot_bytes;       // (ll_x_lines + ll_meta_lines) * 128
+  int ll_comb_slot_bytes;  // lines of one fp32 expert output row * 128
 
   // offsets into the symmetric arena (bytes, 256-aligned)
   size_t off_counts;        // u32 [2][world][nle]   value = count + 1, 0 = not posted
@@ -73,6 +79,8 @@ struct A2AParams {
                             //     memory is one array of world * region_slots slots with
                             //     rows grouped by local expert, then by source rank
   size_t off_comb_stage;    // u8  [max_tokens*topk][hidden_dim*4]
+  size_t off_ll_disp_stage; // u8  [world][region_slots][ll_slot_bytes], written only as lines
+  size_t off_ll_comb_stage; // u8  [max_tokens*topk][ll_comb_slot_bytes], written only as lines
   size_t arena_bytes;
 
   uint8_t* peer[kMaxWorld];  // arena base of every rank as mapped in this process
@@ -135,6 +143,7 @@ struct DispatchArgs {
                              // e4m3 + one fp32 scale per 128 columns on the fly
   int packed;                // send only: two-hop protocol, rows land at their final,
                              // expert-major position in the destination's staging
+  int x_on_host;             // x / x_scale / indices live in mapped pinned host memory
 };
 
 struct CombineArgs {
@@ -148,6 +157,18 @@ struct CombineArgs {
   int64_t y_stride_row;      // elements
   const uint32_t* bound_m;
   int num_tokens;
+  int ll;                    // this call uses the flag-in-data staging (send and receive halves
+                             // of one combine must agree; the GEMM-epilogue send does not use it)
+};
+
+// Arguments of several ranks that share one device, passed to a kernel by value (no
+// device-side staging, so the launch can be captured in a CUDA graph).
+constexpr int kMaxLocalRanks = 8;
+struct DispatchMulti {
+  DispatchArgs r[kMaxLocalRanks];
+};
+struct CombineMulti {
+  CombineArgs r[kMaxLocalRanks];
 };
 
 // Trailer written after payload + scales in every dispatch slot.

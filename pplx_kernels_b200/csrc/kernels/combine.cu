@@ -23,6 +23,14 @@
 //    the block synchronises, and one warp executes a single system-scope fence
 //    followed by relaxed adds.  (A fence per warp serialises inside an SM and
 //    was the largest item of the first version's latency.)
+//  * Flag-in-data mode (a.ll, the default): rows travel as 128-byte lines that carry
+//    their own flag (core/ll128.cuh).  The send is a plain loop of line stores with
+//    no barrier, fence or counter; the reduction is spread over (token, 4-line
+//    group) warp units that poll the top-k copies of their own lines and reduce them
+//    as soon as those have landed, so a token's first columns are reduced while its
+//    last ones are still on the wire.  The per-token counters are advanced locally
+//    so that a later combine in counter mode (after the GEMM-epilogue send) still
+//    finds them in step.
 //  * Block 0 of the send phase clears the counters of the dispatch that just
 //    ended and bumps the iteration counter.  The per-token counters used here
 //    are never cleared; see a2a_params.h.  Nothing waits on a last block.
@@ -31,6 +39,7 @@
 #include <cuda_runtime.h>
 
 #include "../core/device_utils.cuh"
+#include "../core/ll128.cuh"
 #include "../core/ptx.cuh"
 #include "../core/utils.h"
 #include "../core/wait.cuh"
@@ -162,7 +171,14 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
     if (tid < p.world) arrived[tid] = 0;
     reset_packed_flags(p, parity);
     __syncthreads();
-    if (tid == 0) *p.iter = *p.iter + 1u;
+    if (tid == 0) {
+      const uint32_t done = *p.iter;
+      // Exactly one dispatch must have started since the last combine.
+      const uint32_t started = ptx::ld_volatile(p.comb_iter);
+      if (started != done + 1u)
+        report_failure(p.status, kOutOfOrder, kPhaseCombinePayload, 0, done + 1u, started, p.rank);
+      *p.iter = done + 1u;
+    }
   }
   for (int le = tid; le < p.nle; le += blockDim.x) sm.estart[le] = p.recv_count[le];
   __syncthreads();
@@ -179,6 +195,39 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
   const int split = split_factor(total_rows, gwarps, nvec);
   const uint32_t n_units = total_rows * split;
   const uint32_t arrival_units = static_cast<uint32_t>(p.comb_units) / split;
+
+  if (a.ll) {
+    const int nlines = ll::lines_for(row_bytes);
+    const uint64_t flag = ll::kCombineTag | static_cast<uint64_t>(ptx::ld_volatile(p.comb_iter));
+    for (uint32_t unit = gwarp; unit < n_units; unit += gwarps) {
+      const uint32_t f = unit / split;
+      const int c = static_cast<int>(unit - f * split);
+      const int le = find_group(sm.estart, p.nle, f);
+      const uint32_t row = f - sm.estart[le];
+      const uint2 rs = p.row_src[static_cast<size_t>(le) * p.cap + row];
+      const int src_rank = static_cast<int>(rs.x & 0xffffu);
+      const uint32_t k = rs.x >> 16;
+      const uint32_t token = rs.y;
+      if (token >= static_cast<uint32_t>(p.max_tokens) || k >= static_cast<uint32_t>(p.topk) ||
+          src_rank >= p.world) {
+        if (lane == 0)
+          report_failure(p.status, kBadToken, kPhaseCombinePayload, src_rank, p.max_tokens, token,
+                         p.rank);
+        continue;
+      }
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(
+          y + le * a.y_stride_e + static_cast<int64_t>(row) * a.y_stride_row);
+      const int l0 = (c * nlines) / split;
+      const int l1 = ((c + 1) * nlines) / split;
+      const int group_first = (src_rank / p.dp_size) * p.dp_size;
+      for (int r = 0; r < p.dp_size; ++r) {
+        uint8_t* slot = p.peer[group_first + r] + p.off_ll_comb_stage +
+                        (static_cast<size_t>(token) * p.topk + k) * p.ll_comb_slot_bytes;
+        ll::warp_send_lines(slot, src, row_bytes, l0, l1, flag, lane);
+      }
+    }
+    return;
+  }
 
   // Rounds: in each, every warp stores at most one part; then one fence and the
   // adds for the whole block.  All warps take part in every round's barriers.
@@ -237,6 +286,145 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
     }
     __syncthreads();
   }
+}
+
+// 8 bytes of a row of T as floats, accumulated with weight w into acc[0 .. kPer).
+template <typename T>
+struct Half8;
+template <>
+struct Half8<float> {
+  static constexpr int kPer = 2;
+  static __device__ __forceinline__ void fma(float* acc, uint64_t v, float w) {
+    acc[0] = fmaf(w, __uint_as_float(static_cast<uint32_t>(v)), acc[0]);
+    acc[1] = fmaf(w, __uint_as_float(static_cast<uint32_t>(v >> 32)), acc[1]);
+  }
+};
+template <typename T2>
+struct Half8Of16 {
+  static constexpr int kPer = 4;
+  static __device__ __forceinline__ void fma(float* acc, uint64_t v, float w) {
+    const uint32_t lo = static_cast<uint32_t>(v), hi = static_cast<uint32_t>(v >> 32);
+    const float2 f0 = unpack2(*reinterpret_cast<const T2*>(&lo));
+    const float2 f1 = unpack2(*reinterpret_cast<const T2*>(&hi));
+    acc[0] = fmaf(w, f0.x, acc[0]);
+    acc[1] = fmaf(w, f0.y, acc[1]);
+    acc[2] = fmaf(w, f1.x, acc[2]);
+    acc[3] = fmaf(w, f1.y, acc[3]);
+  }
+};
+template <>
+struct Half8<__half> : Half8Of16<__half2> {};
+template <>
+struct Half8<__nv_bfloat16> : Half8Of16<__nv_bfloat162> {};
+
+__device__ __forceinline__ uint32_t pack2(float a, float b, __half*) {
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b, __nv_bfloat16*) {
+  const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Stores kPer consecutive results (2 or 4) starting at element `e0` of the output row.
+template <int kPer, typename U>
+__device__ __forceinline__ void store_results(U* out_row, int e0, const float* acc) {
+  if constexpr (kPer == 4) {
+    const uint64_t v = static_cast<uint64_t>(pack2(acc[0], acc[1], static_cast<U*>(nullptr))) |
+                       (static_cast<uint64_t>(pack2(acc[2], acc[3], static_cast<U*>(nullptr))) << 32);
+    ll::st8(out_row + e0, v);
+  } else {
+    ll::st4(out_row + e0, pack2(acc[0], acc[1], static_cast<U*>(nullptr)));
+  }
+}
+
+// Reduction of the flag-in-data mode.  A warp unit is (token, group of four lines): lane
+// (g, j) owns the 16 bytes at line 4c + g, offset 16 j of each of the token's top-k rows,
+// polls until all of them carry this combine's flag, and reduces them.
+template <typename T, typename U>
+__device__ __forceinline__ void recv_phase_ll(const CombineArgs& a, int m) {
+  const A2AParams& p = a.p;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int j = lane & 7, g = lane >> 3;
+  const WaitCtx w{p.status, p.timeout_ns, static_cast<uint32_t>(p.rank)};
+  constexpr int kPer = Half8<T>::kPer;
+
+  const int topk = p.topk;
+  const int row_bytes = p.hidden_dim * static_cast<int>(sizeof(T));
+  const int nlines = ll::lines_for(row_bytes);
+  const int groups = ceil_div<int>(nlines, 4);
+  const size_t slot_bytes = static_cast<size_t>(p.ll_comb_slot_bytes);
+  const uint8_t* stage = p.peer[p.rank] + p.off_ll_comb_stage;
+  const uint64_t flag = ll::kCombineTag | static_cast<uint64_t>(ptx::ld_volatile(p.comb_iter));
+  U* out = static_cast<U*>(a.out_tokens);
+
+  if (blockIdx.x == 0) {
+    // Nobody adds to the per-token counters in this mode; advance them all by one
+    // combine's worth so that the counter mode finds them in step afterwards.
+    uint32_t* arrived = reinterpret_cast<uint32_t*>(p.peer[p.rank] + p.off_comb_arrived);
+    const uint32_t per_round = static_cast<uint32_t>(topk) * static_cast<uint32_t>(p.comb_units);
+    for (int i = tid; i < p.max_tokens; i += blockDim.x) atomicAdd(arrived + i, per_round);
+  }
+
+  const uint32_t units = static_cast<uint32_t>(m) * groups;
+  const uint32_t gwarp = blockIdx.x * nwarps + warp;
+  const uint32_t gwarps = gridDim.x * nwarps;
+  for (uint32_t u = gwarp; u < units; u += gwarps) {
+    const int i = u / groups;
+    const int c = u - i * groups;
+    const int line = 4 * c + g;
+    const bool live = line < nlines;
+    const int o = line * ll::kLineData + j * 16;  // byte offset inside the row of T
+    const uint8_t* base = stage + static_cast<size_t>(i) * topk * slot_bytes +
+                          static_cast<size_t>(line) * ll::kLineBytes + j * 16;
+    const float* wrow = a.weights + static_cast<int64_t>(i) * a.w_stride_row;
+    float acc[2 * kPer];
+#pragma unroll
+    for (int t = 0; t < 2 * kPer; ++t) acc[t] = 0.f;
+    ll::Poll poll(w, kPhaseCombinePayload, static_cast<uint32_t>(i));
+    bool ok = true;
+    constexpr int kBatch = 8;
+    for (int k0 = 0; k0 < topk; k0 += kBatch) {
+      uint64_t xa[kBatch], xb[kBatch];
+      while (true) {
+        bool ready = true;
+        uint64_t seen = flag;
+#pragma unroll
+        for (int t = 0; t < kBatch; ++t) {
+          if (live && k0 + t < topk) {
+            ll::ld16(base + static_cast<size_t>(k0 + t) * slot_bytes, xa[t], xb[t]);
+            if (j == 7 && xb[t] != flag) {
+              ready = false;
+              seen = xb[t];
+            }
+          }
+        }
+        if (__all_sync(0xffffffffu, ready)) break;
+        if (!poll.again(lane, flag, seen)) {
+          ok = false;
+          break;
+        }
+      }
+      if (!ok) break;
+#pragma unroll
+      for (int t = 0; t < kBatch; ++t) {
+        if (live && k0 + t < topk) {
+          const float wk = __ldg(wrow + k0 + t);
+          Half8<T>::fma(acc, xa[t], wk);
+          if (j < 7) Half8<T>::fma(acc + kPer, xb[t], wk);
+        }
+      }
+    }
+    if (!ok || !live) continue;
+    U* out_row = out + static_cast<int64_t>(i) * a.out_stride_row;
+    const int e0 = o / static_cast<int>(sizeof(T));
+    if (o + 8 <= row_bytes) store_results<kPer>(out_row, e0, acc);
+    if (j < 7 && o + 16 <= row_bytes) store_results<kPer>(out_row, e0 + kPer, acc + kPer);
+  }
+  trace(p, kTrCombineReduced);
 }
 
 template <typename T, typename U>
@@ -323,7 +511,10 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a, uint32_t* sme
   if constexpr (SEND) send_phase<T>(a, sm);
   trace(p, kTrCombineSent);
   if constexpr (SEND && RECV) __syncthreads();
-  if constexpr (RECV) recv_phase<T, U>(a, sm, m);
+  if constexpr (RECV) {
+    if (a.ll) recv_phase_ll<T, U>(a, m);
+    else recv_phase<T, U>(a, sm, m);
+  }
   trace(p, kTrCombineEnd);
   __syncthreads();
   trace_block(p, kTrBlockCombineEnd);
@@ -338,9 +529,9 @@ __global__ void __launch_bounds__(kCombineThreads, 1)
 
 template <typename T, typename U, bool SEND, bool RECV>
 __global__ void __launch_bounds__(kCombineThreads, 1)
-    combine_kernel_multi(const CombineArgs* __restrict__ args) {
+    combine_kernel_multi(const __grid_constant__ CombineMulti m) {
   extern __shared__ __align__(16) uint32_t dyn_smem[];
-  combine_body<T, U, SEND, RECV>(args[blockIdx.y], dyn_smem);
+  combine_body<T, U, SEND, RECV>(m.r[blockIdx.y], dyn_smem);
 }
 
 template <typename T, typename U>
@@ -357,9 +548,9 @@ cudaError_t launch_typed(const CombineArgs& a, bool send, bool recv, int grid, s
 }
 
 template <typename T, typename U>
-cudaError_t launch_typed_multi(const CombineArgs* dev_args, int nranks, bool send, bool recv,
+cudaError_t launch_typed_multi(const CombineMulti& args, int nranks, bool send, bool recv,
                                int grid, size_t smem, cudaStream_t stream) {
-  void* params[] = {const_cast<CombineArgs**>(&dev_args)};
+  void* params[] = {const_cast<CombineMulti*>(&args)};
   const void* fn = nullptr;
   if (send && recv) fn = reinterpret_cast<const void*>(&combine_kernel_multi<T, U, true, true>);
   else if (send) fn = reinterpret_cast<const void*>(&combine_kernel_multi<T, U, true, false>);
@@ -403,12 +594,12 @@ cudaError_t launch_combine(const CombineArgs& a, DType in, DType out, bool send,
   });
 }
 
-cudaError_t launch_combine_multi(const CombineArgs* dev_args, int nranks, const A2AParams& p,
-                                 DType in, DType out, bool send, bool recv, int grid,
-                                 cudaStream_t stream) {
-  const size_t smem = combine_smem_bytes(p);
+cudaError_t launch_combine_multi(const CombineMulti& args, int nranks, DType in, DType out,
+                                 bool send, bool recv, int grid, cudaStream_t stream) {
+  if (nranks < 1 || nranks > kMaxLocalRanks) return cudaErrorInvalidValue;
+  const size_t smem = combine_smem_bytes(args.r[0].p);
   return dispatch_types(in, out, [&]<typename T, typename U>() {
-    return launch_typed_multi<T, U>(dev_args, nranks, send, recv, grid, smem, stream);
+    return launch_typed_multi<T, U>(args, nranks, send, recv, grid, smem, stream);
   });
 }
 

@@ -40,6 +40,13 @@
 // rounded to e4m3 -- so no separate quantisation kernel and no fp8 copy of the
 // activations in HBM is needed.
 //
+// Flag-in-data mode (p.ll, the default for the plain dispatch): step 3 writes each
+// row as 128-byte lines that carry their own flag (core/ll128.cuh) and step 4 does
+// not exist -- the sender never waits for its stores.  The receiver still lays out
+// its output from the counts, then polls each expected row line by line and copies
+// it out as soon as it is complete, whatever the rest of its source is doing.  The
+// packed and the quantising sends keep the counter protocol.
+//
 // Rows are split over several warps whenever there are fewer rows than warps, so
 // that a single token still moves with the whole block's memory parallelism.
 //
@@ -52,6 +59,7 @@
 #include <cuda_runtime.h>
 
 #include "../core/device_utils.cuh"
+#include "../core/ll128.cuh"
 #include "../core/ptx.cuh"
 #include "../core/utils.h"
 #include "../core/wait.cuh"
@@ -174,7 +182,7 @@ __device__ __forceinline__ void warp_quantize_row(uint8_t* slot, float* slot_sca
 }
 
 __device__ __forceinline__ void send_phase(const DispatchArgs& a, const DispatchSmem& sm,
-                                           int parity, int m) {
+                                           int parity, int m, uint32_t iter_now) {
   const A2AParams& p = a.p;
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -197,7 +205,7 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
   {
     const int rows_here = u_end - u_begin;
     const int src_bytes = a.quantize ? 2 * p.hidden_bytes : p.hidden_bytes;
-    if (rows_here > 0 && rows_here <= kRowCap) {
+    if (rows_here > 0 && rows_here <= kRowCap && !a.x_on_host) {
       const int parts = split_factor(rows_here, nwarps, p.hidden_bytes >> 4);
       for (int unit = warp; unit < rows_here * parts; unit += nwarps) {
         const int r = unit / parts;
@@ -217,7 +225,14 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
   }
   if (tid < kMaxWorld) sm.sent[tid] = 0;
   // A new round begins: the combine that follows this dispatch is one further.
-  if (blockIdx.x == 0 && tid == 0) *p.comb_iter = *p.comb_iter + 1u;
+  if (blockIdx.x == 0 && tid == 0) {
+    const uint32_t started = *p.comb_iter;
+    // Dispatches started must equal combines finished: anything else is two dispatches
+    // without a combine in between, which the flag protocol does not survive.
+    if (started != iter_now)
+      report_failure(p.status, kOutOfOrder, kPhaseDispatchCounts, 0, iter_now, started, p.rank);
+    *p.comb_iter = started + 1u;
+  }
   __syncthreads();
 
   for (int idx = tid; idx < n_entries; idx += blockDim.x) {
@@ -240,6 +255,8 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
   trace(p, kTrDispatchHist);
 
   const bool packed = a.packed != 0;
+  const bool ll = p.ll != 0 && !packed && !a.quantize;
+  const uint64_t flag = ll::kDispatchTag | static_cast<uint64_t>(iter_now + 1u);
   if (!packed) {
     if (blockIdx.x == 0) {
       for (int e = tid; e < E; e += blockDim.x) {
@@ -313,7 +330,9 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
       uint32_t pos = kNoSlot;
       if (e < static_cast<uint32_t>(E)) {
         pos = atomicAdd(&sm.base[e], 1u);
-        if (p.debug_checks && pos >= slot_limit) {
+        // Always checked: a token that names one expert twice would otherwise push its
+        // rows past the region that the distinct-expert rule sizes.
+        if (pos >= slot_limit) {
           report_failure(p.status, kSlotOverflow, kPhaseDispatchPayload, e / p.nle, slot_limit,
                          pos, p.rank);
           pos = kNoSlot;
@@ -349,7 +368,7 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
       pos = 0;
       if (lane == 0) pos = atomicAdd(&sm.base[e], 1u);
       pos = __shfl_sync(0xffffffffu, pos, 0);
-      if (p.debug_checks && pos >= slot_limit) {
+      if (pos >= slot_limit) {
         if (lane == 0)
           report_failure(p.status, kSlotOverflow, kPhaseDispatchPayload, dst, slot_limit, pos,
                          p.rank);
@@ -361,8 +380,24 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
       }
     }
 
-    uint8_t* slot = p.peer[dst] + p.off_disp_stage + (region_first + pos) * p.slot_bytes;
     const uint8_t* src = a.x + static_cast<int64_t>(i) * a.x_stride_row;
+    if (ll) {
+      uint8_t* slot =
+          p.peer[dst] + p.off_ll_disp_stage + (region_first + pos) * p.ll_slot_bytes;
+      const int l0 = (c * p.ll_x_lines) / split;
+      const int l1 = ((c + 1) * p.ll_x_lines) / split;
+      ll::warp_send_lines(slot, src, p.hidden_bytes, l0, l1, flag, lane);
+      if (c == split - 1) {
+        const uint32_t trailer[4] = {static_cast<uint32_t>(i), static_cast<uint32_t>(k),
+                                     static_cast<uint32_t>(le), static_cast<uint32_t>(p.rank)};
+        const float* ssrc =
+            nscale > 0 ? a.x_scale + static_cast<int64_t>(i) * a.x_scale_stride_row : nullptr;
+        ll::warp_send_meta(slot + p.ll_x_lines * ll::kLineBytes, p.ll_meta_lines, trailer, ssrc,
+                           a.x_scale_stride_col, nscale, flag, lane);
+      }
+      continue;
+    }
+    uint8_t* slot = p.peer[dst] + p.off_disp_stage + (region_first + pos) * p.slot_bytes;
     if (a.quantize) {
       // Parts are cut at multiples of 32 output vectors (512 columns).
       const int groups = ceil_div<int>(nvec, 32);
@@ -395,7 +430,9 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
   }
   trace(p, kTrDispatchStored);
   __syncthreads();
-  if (!packed) {
+  if (ll) {
+    // Nothing to signal: every line carries its own flag.
+  } else if (!packed) {
     if (tid < p.world && sm.sent[tid] > 0) {
       ptx::red_add_release_sys(arrived_ptr(p, tid, parity, p.rank), sm.sent[tid]);
     }
@@ -419,7 +456,7 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
 }
 
 __device__ __forceinline__ void recv_phase(const DispatchArgs& a, const DispatchSmem& sm,
-                                           int parity) {
+                                           int parity, uint32_t iter_now) {
   const A2AParams& p = a.p;
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -427,6 +464,8 @@ __device__ __forceinline__ void recv_phase(const DispatchArgs& a, const Dispatch
   const int nwarps = blockDim.x >> 5;
   const int P = p.world * p.nle;
   const WaitCtx w{p.status, p.timeout_ns, static_cast<uint32_t>(p.rank)};
+  const bool ll = p.ll != 0 && !a.quantize;
+  const uint64_t flag = ll::kDispatchTag | static_cast<uint64_t>(iter_now + 1u);
 
   uint32_t* counts = reinterpret_cast<uint32_t*>(p.peer[p.rank] + p.off_counts) +
                      a2a_counts_index(p, parity, 0, 0);
@@ -485,6 +524,48 @@ __device__ __forceinline__ void recv_phase(const DispatchArgs& a, const Dispatch
     const uint32_t slot_idx = f - src_first;
     const uint32_t row = sm.rbase[q] + (f - sm.fstart[q]);
 
+    // Always checked (one compare per row): counts that exceed what the buffers hold.
+    if (row >= static_cast<uint32_t>(p.cap) || slot_idx >= static_cast<uint32_t>(p.region_slots)) {
+      if (lane == 0)
+        report_failure(p.status, kRowOverflow, kPhaseDispatchPayload, s, p.cap, row, p.rank);
+      continue;
+    }
+
+    if (ll) {
+      // Poll the row's own lines; no counter, no acquire: a line is valid as a whole
+      // once its flag matches.
+      const uint8_t* slot = p.peer[p.rank] + p.off_ll_disp_stage +
+                            (static_cast<size_t>(s) * p.region_slots + slot_idx) * p.ll_slot_bytes;
+      uint8_t* dst =
+          a.out_x + le * a.out_x_stride_e + static_cast<int64_t>(row) * a.out_x_stride_row;
+      ll::Poll poll(w, kPhaseDispatchPayload, static_cast<uint32_t>(s));
+      const int l0 = (c * p.ll_x_lines) / split;
+      const int l1 = ((c + 1) * p.ll_x_lines) / split;
+      if (!ll::warp_recv_lines(dst, slot, p.hidden_bytes, l0, l1, flag, lane, poll)) continue;
+      if (c == split - 1) {
+        uint32_t trailer[4];
+        float* sdst = nscale > 0 ? a.out_scale + le * a.out_scale_stride_e +
+                                       static_cast<int64_t>(row) * a.out_scale_stride_row
+                                 : nullptr;
+        if (!ll::warp_recv_meta(slot + p.ll_x_lines * ll::kLineBytes, p.ll_meta_lines, sdst,
+                                a.out_scale_stride_col, nscale, flag, lane, poll, trailer))
+          continue;
+        if (lane == 0) {
+          if (trailer[0] >= static_cast<uint32_t>(p.max_tokens) ||
+              trailer[1] >= static_cast<uint32_t>(p.topk)) {
+            report_failure(p.status, kBadToken, kPhaseDispatchPayload, s, p.max_tokens, trailer[0],
+                           p.rank);
+          } else {
+            uint2 rs;
+            rs.x = static_cast<uint32_t>(s) | (trailer[1] << 16);
+            rs.y = trailer[0];
+            p.row_src[static_cast<size_t>(le) * p.cap + row] = rs;
+          }
+        }
+      }
+      continue;
+    }
+
     // Each warp acquires a source's counter itself once; a flag set by another
     // warp would not order this warp's loads after the peer's stores.
     bool ok = true;
@@ -499,13 +580,6 @@ __device__ __forceinline__ void recv_phase(const DispatchArgs& a, const Dispatch
       if (!ok) continue;
       acquired |= 1u << s;
     }
-    if (p.debug_checks &&
-        (row >= static_cast<uint32_t>(p.cap) || slot_idx >= static_cast<uint32_t>(p.region_slots))) {
-      if (lane == 0)
-        report_failure(p.status, kRowOverflow, kPhaseDispatchPayload, s, p.cap, row, p.rank);
-      continue;
-    }
-
     const uint8_t* slot =
         stage + (static_cast<size_t>(s) * p.region_slots + slot_idx) * p.slot_bytes;
     uint8_t* dst = a.out_x + le * a.out_x_stride_e + static_cast<int64_t>(row) * a.out_x_stride_row;
@@ -540,15 +614,16 @@ template <bool SEND, bool RECV>
 __device__ __forceinline__ void dispatch_body(const DispatchArgs& a, uint32_t* smem) {
   const A2AParams& p = a.p;
   const DispatchSmem sm = carve(smem, p.num_experts, p.world * p.nle);
-  const int parity = static_cast<int>(ptx::ld_volatile(p.iter) & 1u);
+  const uint32_t iter_now = ptx::ld_volatile(p.iter);
+  const int parity = static_cast<int>(iter_now & 1u);
   int m = a.num_tokens;
   if (a.bound_m != nullptr) m = min(m, static_cast<int>(__ldg(a.bound_m)));
   m = min(m, p.max_tokens);
   trace(p, kTrDispatchStart);
   trace_block(p, kTrBlockDispatchStart);
-  if constexpr (SEND) send_phase(a, sm, parity, m);
+  if constexpr (SEND) send_phase(a, sm, parity, m, iter_now);
   if constexpr (SEND && RECV) __syncthreads();
-  if constexpr (RECV) recv_phase(a, sm, parity);
+  if constexpr (RECV) recv_phase(a, sm, parity, iter_now);
   __syncthreads();
   trace_block(p, kTrBlockDispatchEnd);
 }
@@ -565,9 +640,9 @@ __global__ void __launch_bounds__(kDispatchThreads, 1)
 // cooperative to have them all resident.
 template <bool SEND, bool RECV>
 __global__ void __launch_bounds__(kDispatchThreads, 1)
-    dispatch_kernel_multi(const DispatchArgs* __restrict__ args) {
+    dispatch_kernel_multi(const __grid_constant__ DispatchMulti m) {
   extern __shared__ __align__(16) uint32_t dyn_smem[];
-  dispatch_body<SEND, RECV>(args[blockIdx.y], dyn_smem);
+  dispatch_body<SEND, RECV>(m.r[blockIdx.y], dyn_smem);
 }
 
 }  // namespace
@@ -579,28 +654,50 @@ size_t dispatch_smem_bytes(const A2AParams& p) {
 
 int dispatch_threads() { return kDispatchThreads; }
 
+namespace {
+
+// Histograms of many experts need more dynamic shared memory than a kernel gets by default.
+template <typename Kernel>
+cudaError_t allow_smem(Kernel kernel, size_t smem) {
+  if (smem <= 48 * 1024) return cudaSuccess;
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(smem));
+}
+
+}  // namespace
+
 cudaError_t launch_dispatch(const DispatchArgs& a, bool send, bool recv, int grid,
                             cudaStream_t stream) {
   const size_t smem = dispatch_smem_bytes(a.p);
+  cudaError_t err = cudaSuccess;
   if (send && recv) {
+    if ((err = allow_smem(dispatch_kernel<true, true>, smem)) != cudaSuccess) return err;
     dispatch_kernel<true, true><<<grid, kDispatchThreads, smem, stream>>>(a);
   } else if (send) {
+    if ((err = allow_smem(dispatch_kernel<true, false>, smem)) != cudaSuccess) return err;
     dispatch_kernel<true, false><<<grid, kDispatchThreads, smem, stream>>>(a);
   } else {
+    if ((err = allow_smem(dispatch_kernel<false, true>, smem)) != cudaSuccess) return err;
     dispatch_kernel<false, true><<<grid, kDispatchThreads, smem, stream>>>(a);
   }
   return cudaGetLastError();
 }
 
-cudaError_t launch_dispatch_multi(const DispatchArgs* dev_args, int nranks, const A2AParams& p,
-                                  bool send, bool recv, int grid, cudaStream_t stream) {
-  const size_t smem = dispatch_smem_bytes(p);
-  void* params[] = {const_cast<DispatchArgs**>(&dev_args)};
+cudaError_t launch_dispatch_multi(const DispatchMulti& args, int nranks, bool send, bool recv,
+                                  int grid, cudaStream_t stream) {
+  if (nranks < 1 || nranks > kMaxLocalRanks) return cudaErrorInvalidValue;
+  const size_t smem = dispatch_smem_bytes(args.r[0].p);
+  void* params[] = {const_cast<DispatchMulti*>(&args)};
   const dim3 g(grid, nranks);
   const void* fn = nullptr;
   if (send && recv) fn = reinterpret_cast<const void*>(&dispatch_kernel_multi<true, true>);
   else if (send) fn = reinterpret_cast<const void*>(&dispatch_kernel_multi<true, false>);
   else fn = reinterpret_cast<const void*>(&dispatch_kernel_multi<false, true>);
+  if (smem > 48 * 1024) {
+    const cudaError_t err = cudaFuncSetAttribute(
+        fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (err != cudaSuccess) return err;
+  }
   return cudaLaunchCooperativeKernel(fn, g, dim3(kDispatchThreads), params, smem, stream);
 }
 

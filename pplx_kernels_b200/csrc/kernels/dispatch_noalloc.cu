@@ -190,10 +190,14 @@ extern "C" __attribute__((visibility("default"))) int pplx_b200_dispatch_single_
     return fail(kPplxNoAllocBadArgument, msg, len, "token buffers must be 16-byte aligned");
   if (num_experts > kMaxExperts)
     return fail(kPplxNoAllocTooLarge, msg, len, "num_experts exceeds the maximum of 1024");
+  if (experts_per_token > num_experts)
+    return fail(kPplxNoAllocBadArgument, msg, len, "experts_per_token exceeds num_experts");
   const size_t slot_bytes =
       pplx::round_up<size_t>(static_cast<size_t>(hidden_dim_bytes) + hidden_dim_scale_bytes, 16);
+  // Checked by division so that no product can wrap: rows that fit into the staging.
+  const size_t rows_that_fit = kStageBytes / slot_bytes;
   const size_t need = static_cast<size_t>(num_tokens) * experts_per_token * slot_bytes;
-  if (need > kStageBytes) {
+  if (static_cast<size_t>(num_tokens) > rows_that_fit / static_cast<size_t>(experts_per_token)) {
     char text[200];
     std::snprintf(text, sizeof(text),
                   "num_tokens * experts_per_token * slot_bytes = %zu exceeds the built-in staging "

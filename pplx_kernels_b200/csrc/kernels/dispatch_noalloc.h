@@ -22,6 +22,19 @@
 //   slot_bytes = round_up(hidden_dim_bytes + hidden_dim_scale_bytes, 16);
 //   num_experts <= 1024.
 // The DeepSeek-V3 shape at 128 tokens (1024 rows of 7392 bytes) fits.
+// experts_per_token > num_experts is rejected with kPplxNoAllocBadArgument.
+//
+// Rows beyond `out_rows_per_expert`: an expert that receives more rows than its
+// output holds keeps the first `out_rows_per_expert` of them and drops the rest,
+// while `out_expert_num_tokens[e]` still reports the full count -- compare the two
+// if the output may be too small (out_rows_per_expert >= num_tokens never drops).
+//
+// Co-residency: the kernel's blocks wait for one another on a counter in the
+// array, so the grid is kept within the number of SMs and relies on all of its
+// blocks being resident together.  If another stream's work keeps some of them
+// off the GPU for longer than the internal limit of two seconds, the call does
+// not hang: the waiting blocks give up, `status` reads 1 and the outputs are
+// incomplete.
 // Every GPU that loads the library holds the 16 MiB (+ 256 B) array until the
 // process exits, whether or not this function is ever called.
 //

@@ -37,6 +37,7 @@ const char* code_name(uint32_t code) {
     case kSlotOverflow: return "staging slot out of range";
     case kRowOverflow: return "output row out of range";
     case kBadToken: return "token index out of range";
+    case kOutOfOrder: return "dispatch and combine did not alternate";
     default: return "unknown failure";
   }
 }
@@ -71,8 +72,12 @@ void AllToAll::validate(const A2AConfig& c) {
 
 namespace {
 
-// Fills geometry and arena offsets; pointers stay null.
-A2AParams make_layout(const A2AConfig& c) {
+constexpr size_t kCanaryBytes = 256;
+constexpr uint32_t kCanaryWord = 0xC0FFEE11u;
+
+// Fills geometry and arena offsets; pointers stay null.  `canaries` receives the offset of
+// the guard that follows each region.
+A2AParams make_layout(const A2AConfig& c, std::vector<size_t>* canaries = nullptr) {
   A2AParams p{};
   p.rank = c.rank;
   p.world = c.world_size;
@@ -98,22 +103,31 @@ A2AParams make_layout(const A2AConfig& c) {
   p.region_slots = tokens_per_sender * std::min(c.experts_per_token, p.nle);
   p.cap = c.max_num_tokens * p.num_dp_groups;
   p.comb_units = 16;
+  // Flag-in-data staging: a dispatch row is its payload lines followed by the lines of
+  // its meta stream (4 trailer words, then the scales); a combine row is sized for fp32.
+  p.ll_x_lines = ll::lines_for(c.hidden_dim_bytes);
+  p.ll_meta_lines = ll::lines_for(16 + c.hidden_dim_scale_bytes);
+  p.ll_slot_bytes = (p.ll_x_lines + p.ll_meta_lines) * ll::kLineBytes;
+  p.ll_comb_slot_bytes = ll::lines_for(c.hidden_dim * 4) * ll::kLineBytes;
 
+  // Every region is followed by a guard of kCanaryBytes that nothing may write.
   size_t off = 0;
-  p.off_counts = off;
-  off = align256(off + sizeof(uint32_t) * 2 * p.world * p.nle);
-  p.off_arrived = off;
-  off = align256(off + sizeof(uint32_t) * 2 * p.world);
-  p.off_comb_arrived = off;
-  off = align256(off + sizeof(uint32_t) * p.max_tokens);
-  p.off_counts_all = off;
-  off = align256(off + sizeof(uint32_t) * 2 * p.world * p.num_experts);
-  p.off_arrived_e = off;
-  off = align256(off + sizeof(uint32_t) * 2 * p.nle);
-  p.off_disp_stage = off;
-  off = align256(off + static_cast<size_t>(p.world) * p.region_slots * p.slot_bytes);
-  p.off_comb_stage = off;
-  off = align256(off + static_cast<size_t>(p.max_tokens) * p.topk * p.hidden_dim * 4);
+  auto region = [&](size_t bytes) {
+    const size_t at = off;
+    off = align256(off + bytes);
+    if (canaries != nullptr) canaries->push_back(off);
+    off += kCanaryBytes;
+    return at;
+  };
+  p.off_counts = region(sizeof(uint32_t) * 2 * p.world * p.nle);
+  p.off_arrived = region(sizeof(uint32_t) * 2 * p.world);
+  p.off_comb_arrived = region(sizeof(uint32_t) * p.max_tokens);
+  p.off_counts_all = region(sizeof(uint32_t) * 2 * p.world * p.num_experts);
+  p.off_arrived_e = region(sizeof(uint32_t) * 2 * p.nle);
+  p.off_disp_stage = region(static_cast<size_t>(p.world) * p.region_slots * p.slot_bytes);
+  p.off_comb_stage = region(static_cast<size_t>(p.max_tokens) * p.topk * p.hidden_dim * 4);
+  p.off_ll_disp_stage = region(static_cast<size_t>(p.world) * p.region_slots * p.ll_slot_bytes);
+  p.off_ll_comb_stage = region(static_cast<size_t>(p.max_tokens) * p.topk * p.ll_comb_slot_bytes);
   p.arena_bytes = off;
   return p;
 }
@@ -128,7 +142,7 @@ size_t AllToAll::arena_bytes(const A2AConfig& cfg) {
 AllToAll::AllToAll(const A2AConfig& cfg, std::shared_ptr<SymmetricAllocation> arena)
     : cfg_(cfg), arena_(std::move(arena)) {
   validate(cfg_);
-  params_ = make_layout(cfg_);
+  params_ = make_layout(cfg_, &canaries_);
   PPLX_CHECK(arena_ && arena_->world() == cfg_.world_size && arena_->rank() == cfg_.rank,
              "arena does not match the configuration");
   PPLX_CHECK(arena_->bytes() >= params_.arena_bytes, "arena too small");
@@ -138,6 +152,12 @@ AllToAll::AllToAll(const A2AConfig& cfg, std::shared_ptr<SymmetricAllocation> ar
   recv_count_ = DeviceBuffer<uint32_t>(params_.nle);
   row_src_ = DeviceBuffer<uint2>(static_cast<size_t>(params_.nle) * params_.cap);
   status_ = DeviceBuffer<Status>(1);
+  status_host_ = HostBuffer<Status>(1, /*mapped=*/true);
+  {
+    Status init{};
+    init.mirror = reinterpret_cast<unsigned long long>(status_host_.device_ptr());
+    status_.copy_from_host(&init, 1);
+  }
   trace_ = DeviceBuffer<uint64_t>(kTraceSlots);
   params_.trace = nullptr;
   params_.iter = iter_.get();
@@ -145,10 +165,37 @@ AllToAll::AllToAll(const A2AConfig& cfg, std::shared_ptr<SymmetricAllocation> ar
   params_.recv_count = recv_count_.get();
   params_.row_src = row_src_.get();
   params_.status = status_.get();
-  params_.timeout_ns = static_cast<uint64_t>(env_long("PPLX_B200_TIMEOUT_MS", 20000)) * 1000000ull;
+  params_.timeout_ns = static_cast<uint64_t>(env_long("PPLX_B200_TIMEOUT_MS", 10000)) * 1000000ull;
   params_.debug_checks = env_long("PPLX_B200_DEBUG_CHECKS", 0) != 0 ? 1 : 0;
+  // Flag-in-data lines for the plain dispatch and combine, unless switched off or the
+  // object is larger than PPLX_B200_LL_MAX_TOKENS (0 = no limit).  All ranks read the
+  // same environment, so they agree.
+  const long ll_limit = env_long("PPLX_B200_LL_MAX_TOKENS", 0);
+  params_.ll = env_long("PPLX_B200_LL", 1) != 0 &&
+                       (ll_limit <= 0 || cfg_.max_num_tokens <= ll_limit)
+                   ? 1
+                   : 0;
   num_sms_ = get_sm_count();
   max_blocks_ = static_cast<int>(env_long("PPLX_B200_NUM_SMS", 0));
+  {
+    int smem_limit = 0;
+    CUDA_CHECK(cudaDeviceGetAttribute(&smem_limit, cudaDevAttrMaxSharedMemoryPerBlockOptin,
+                                      current_device()));
+    PPLX_CHECK(dispatch_smem_bytes(params_) <= static_cast<size_t>(smem_limit),
+               "num_experts " << cfg_.num_experts << " with world_size " << cfg_.world_size
+                              << " needs " << dispatch_smem_bytes(params_)
+                              << " bytes of shared memory per block for the dispatch histogram; "
+                                 "the device offers "
+                              << smem_limit);
+  }
+  // Guards after every region of this rank's arena (peers never write there).
+  {
+    std::vector<uint32_t> pattern(kCanaryBytes / sizeof(uint32_t), kCanaryWord);
+    for (size_t at : canaries_) {
+      CUDA_CHECK(cudaMemcpy(params_.peer[cfg_.rank] + at, pattern.data(), kCanaryBytes,
+                            cudaMemcpyHostToDevice));
+    }
+  }
   CUDA_CHECK(cudaDeviceSynchronize());
 }
 
@@ -182,6 +229,70 @@ std::vector<std::unique_ptr<AllToAll>> AllToAll::create_local_world(const A2ACon
   return out;
 }
 
+void AllToAll::verify_canaries() const {
+  std::vector<uint32_t> got(kCanaryBytes / sizeof(uint32_t));
+  for (size_t n = 0; n < canaries_.size(); ++n) {
+    CUDA_CHECK(cudaMemcpy(got.data(), params_.peer[cfg_.rank] + canaries_[n], kCanaryBytes,
+                          cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < got.size(); ++i) {
+      PPLX_CHECK(got[i] == kCanaryWord, "arena guard " << n << " of rank " << cfg_.rank
+                                                       << " was overwritten at byte " << 4 * i
+                                                       << " (offset " << canaries_[n]
+                                                       << "): some store ran past its region");
+    }
+  }
+}
+
+void AllToAll::check_alive() const {
+  const Status s = status_host_[0];
+  if (s.code != kOk) {
+    throw Error("pplx_kernels_b200: this AllToAll object recorded a failure earlier and must be "
+                "destroyed or reset() on every rank before it is used again: " +
+                describe_status(s));
+  }
+}
+
+void AllToAll::advance(Step step) {
+  auto name = [](Step s) {
+    switch (s) {
+      case Step::kDispatchSend: return "the send half of dispatch";
+      case Step::kDispatchRecv: return "the receive half of dispatch";
+      case Step::kCombineSend: return "the send half of combine";
+      case Step::kCombineRecv: return "the receive half of combine";
+    }
+    return "?";
+  };
+  PPLX_CHECK(step == next_, "dispatch and combine must alternate on one object (each as one call "
+                            "or as its send half followed by its receive half): this call is "
+                                << name(step) << ", the object expects " << name(next_));
+  next_ = static_cast<Step>((static_cast<int>(step) + 1) % 4);
+}
+
+void AllToAll::begin(Step first, bool both) {
+  check_alive();
+  advance(first);
+  if (both) advance(static_cast<Step>(static_cast<int>(first) + 1));
+}
+
+void AllToAll::reset() {
+  CUDA_CHECK(cudaDeviceSynchronize());
+  uint8_t* mine = params_.peer[cfg_.rank];
+  CUDA_CHECK(cudaMemset(mine, 0, params_.arena_bytes));
+  {
+    std::vector<uint32_t> pattern(kCanaryBytes / sizeof(uint32_t), kCanaryWord);
+    for (size_t at : canaries_)
+      CUDA_CHECK(cudaMemcpy(mine + at, pattern.data(), kCanaryBytes, cudaMemcpyHostToDevice));
+  }
+  CUDA_CHECK(cudaMemset(iter_.get(), 0, iter_.bytes()));
+  CUDA_CHECK(cudaMemset(recv_count_.get(), 0, recv_count_.bytes()));
+  Status init{};
+  init.mirror = reinterpret_cast<unsigned long long>(status_host_.device_ptr());
+  status_.copy_from_host(&init, 1);
+  status_host_[0] = Status{};
+  next_ = Step::kDispatchSend;
+  CUDA_CHECK(cudaDeviceSynchronize());
+}
+
 void AllToAll::set_combine_units(int units) {
   PPLX_CHECK(units > 0 && units % 16 == 0, "combine units must be a positive multiple of 16");
   params_.comb_units = units;
@@ -201,6 +312,8 @@ int AllToAll::dispatch_grid(int num_tokens) const {
   const int units = std::max(1, num_tokens) * cfg_.experts_per_token;
   return std::clamp(ceil_div(units, 4), std::min(4, limit), limit);
 }
+
+bool AllToAll::dispatch_uses_lines(bool quantize) const { return params_.ll != 0 && !quantize; }
 
 int AllToAll::combine_grid(int num_tokens) const {
   const int limit = max_blocks_ > 0 ? std::min(max_blocks_, num_sms_) : num_sms_;
@@ -256,6 +369,7 @@ DispatchArgs AllToAll::make_dispatch_args(const DispatchCall& c) const {
   a.bound_m = c.bound_m;
   a.num_tokens = c.num_tokens;
   a.quantize = c.quantize ? 1 : 0;
+  a.x_on_host = c.x_on_host ? 1 : 0;
   return a;
 }
 
@@ -284,26 +398,24 @@ CombineArgs AllToAll::make_combine_args(const CombineCall& c) const {
   a.y_stride_row = c.y_stride_row;
   a.bound_m = c.bound_m;
   a.num_tokens = c.num_tokens;
+  a.ll = params_.ll;
   return a;
 }
 
 namespace {
 
-template <typename Args>
-struct StagedArgs {
-  Args* dev = nullptr;
-  explicit StagedArgs(const std::vector<Args>& host) {
-    CUDA_CHECK(cudaMalloc(&dev, host.size() * sizeof(Args)));
-    CUDA_CHECK(cudaMemcpy(dev, host.data(), host.size() * sizeof(Args), cudaMemcpyHostToDevice));
-  }
-  ~StagedArgs() { cudaFree(dev); }
-};
+void check_local_ranks(size_t n) {
+  PPLX_CHECK(n >= 1 && n <= static_cast<size_t>(kMaxLocalRanks),
+             "a group launch drives between 1 and " << kMaxLocalRanks
+                                                    << " ranks of one device, got " << n);
+}
 
 }  // namespace
 
 void AllToAll::dispatch_send_packed(const DispatchCall& call, cudaStream_t stream) {
   NvtxRange range("dispatch_send_packed");
   const DispatchArgs a = make_packed_send_args(call);
+  begin(Step::kDispatchSend, false);
   CUDA_CHECK(launch_dispatch(a, true, false, dispatch_grid(call.num_tokens), stream));
 }
 
@@ -333,6 +445,7 @@ void AllToAll::dispatch_send_packed_group(const std::vector<AllToAll*>& ranks,
                                           const std::vector<DispatchCall>& calls,
                                           cudaStream_t stream) {
   PPLX_CHECK(!ranks.empty() && ranks.size() == calls.size(), "dispatch group: size mismatch");
+  check_local_ranks(ranks.size());
   std::vector<DispatchArgs> args;
   int max_tokens = 0;
   for (size_t r = 0; r < ranks.size(); ++r) {
@@ -341,28 +454,36 @@ void AllToAll::dispatch_send_packed_group(const std::vector<AllToAll*>& ranks,
   }
   const int n = static_cast<int>(ranks.size());
   const int grid = std::min(ranks[0]->dispatch_grid(max_tokens), std::max(1, ranks[0]->num_sms_ / n));
-  StagedArgs<DispatchArgs> staged(args);
-  CUDA_CHECK(launch_dispatch_multi(staged.dev, n, ranks[0]->params_, true, false, grid, stream));
-  CUDA_CHECK(cudaStreamSynchronize(stream));
+  for (AllToAll* r : ranks) r->begin(Step::kDispatchSend, false);
+  DispatchMulti multi{};
+  for (int r = 0; r < n; ++r) multi.r[r] = args[r];
+  CUDA_CHECK(launch_dispatch_multi(multi, n, true, false, grid, stream));
 }
 
 void AllToAll::dispatch(const DispatchCall& call, SplitMode mode, cudaStream_t stream) {
   NvtxRange range("dispatch");
   const DispatchArgs a = make_dispatch_args(call);
   const bool send = mode != SplitMode::kRecv, recv = mode != SplitMode::kSend;
+  begin(send ? Step::kDispatchSend : Step::kDispatchRecv, send && recv);
   CUDA_CHECK(launch_dispatch(a, send, recv, dispatch_grid(call.num_tokens), stream));
 }
 
 void AllToAll::combine(const CombineCall& call, SplitMode mode, cudaStream_t stream) {
   NvtxRange range("combine");
-  const CombineArgs a = make_combine_args(call);
+  CombineArgs a = make_combine_args(call);
   const bool send = mode != SplitMode::kRecv, recv = mode != SplitMode::kSend;
+  begin(send ? Step::kCombineSend : Step::kCombineRecv, send && recv);
+  // The receive half follows whatever its send half used: lines for a send of this class,
+  // counters after the GEMM-epilogue send of the fused MoE path.
+  if (send) combine_send_used_lines_ = a.ll != 0;
+  else a.ll = combine_send_used_lines_ ? 1 : 0;
   CUDA_CHECK(launch_combine(a, call.in, call.out, send, recv, combine_grid(call.num_tokens),
                             stream));
 }
 
 void AllToAll::fused_up(const FusedFfnCall& f, cudaStream_t stream) {
   NvtxRange range("moe_fused_up");
+  begin(Step::kDispatchRecv, false);
   GroupedGemmCall c;
   c.w = f.w;
   c.w_stride_e = f.w_stride_e;
@@ -383,6 +504,8 @@ void AllToAll::fused_up(const FusedFfnCall& f, cudaStream_t stream) {
 
 void AllToAll::fused_down(const FusedFfnCall& f, cudaStream_t stream) {
   NvtxRange range("moe_fused_down");
+  begin(Step::kCombineSend, false);
+  combine_send_used_lines_ = false;
   GroupedGemmCall c;
   c.x = f.h;
   c.x_stride_e = f.h_stride_e;
@@ -407,6 +530,7 @@ void AllToAll::dispatch_group(const std::vector<AllToAll*>& ranks,
                               const std::vector<DispatchCall>& calls, SplitMode mode,
                               cudaStream_t stream) {
   PPLX_CHECK(!ranks.empty() && ranks.size() == calls.size(), "dispatch_group: size mismatch");
+  check_local_ranks(ranks.size());
   std::vector<DispatchArgs> args;
   int grid = 1, max_tokens = 0;
   for (size_t r = 0; r < ranks.size(); ++r) {
@@ -416,16 +540,18 @@ void AllToAll::dispatch_group(const std::vector<AllToAll*>& ranks,
   const int n = static_cast<int>(ranks.size());
   const int per_rank_limit = std::max(1, ranks[0]->num_sms_ / n);
   grid = std::min(ranks[0]->dispatch_grid(max_tokens), per_rank_limit);
-  StagedArgs<DispatchArgs> staged(args);
   const bool send = mode != SplitMode::kRecv, recv = mode != SplitMode::kSend;
-  CUDA_CHECK(launch_dispatch_multi(staged.dev, n, ranks[0]->params_, send, recv, grid, stream));
-  CUDA_CHECK(cudaStreamSynchronize(stream));
+  for (AllToAll* r : ranks) r->begin(send ? Step::kDispatchSend : Step::kDispatchRecv, send && recv);
+  DispatchMulti multi{};
+  for (int r = 0; r < n; ++r) multi.r[r] = args[r];
+  CUDA_CHECK(launch_dispatch_multi(multi, n, send, recv, grid, stream));
 }
 
 void AllToAll::combine_group(const std::vector<AllToAll*>& ranks,
                              const std::vector<CombineCall>& calls, SplitMode mode,
                              cudaStream_t stream) {
   PPLX_CHECK(!ranks.empty() && ranks.size() == calls.size(), "combine_group: size mismatch");
+  check_local_ranks(ranks.size());
   std::vector<CombineArgs> args;
   int max_tokens = 0;
   for (size_t r = 0; r < ranks.size(); ++r) {
@@ -437,22 +563,34 @@ void AllToAll::combine_group(const std::vector<AllToAll*>& ranks,
   const int n = static_cast<int>(ranks.size());
   const int per_rank_limit = std::max(1, ranks[0]->num_sms_ / n);
   const int grid = std::min(ranks[0]->combine_grid(max_tokens), per_rank_limit);
-  StagedArgs<CombineArgs> staged(args);
   const bool send = mode != SplitMode::kRecv, recv = mode != SplitMode::kSend;
-  CUDA_CHECK(launch_combine_multi(staged.dev, n, ranks[0]->params_, calls[0].in, calls[0].out,
-                                  send, recv, grid, stream));
-  CUDA_CHECK(cudaStreamSynchronize(stream));
+  for (size_t r = 0; r < ranks.size(); ++r) {
+    ranks[r]->begin(send ? Step::kCombineSend : Step::kCombineRecv, send && recv);
+    if (send) ranks[r]->combine_send_used_lines_ = args[r].ll != 0;
+    else args[r].ll = ranks[r]->combine_send_used_lines_ ? 1 : 0;
+  }
+  CombineMulti multi{};
+  for (int r = 0; r < n; ++r) multi.r[r] = args[r];
+  CUDA_CHECK(launch_combine_multi(multi, n, calls[0].in, calls[0].out, send, recv, grid, stream));
 }
 
 Status AllToAll::read_status() const {
   Status s{};
   CUDA_CHECK(cudaMemcpy(&s, status_.get(), sizeof(Status), cudaMemcpyDeviceToHost));
+  s.mirror = 0;
+  return s;
+}
+
+Status AllToAll::peek_status() const {
+  Status s = status_host_[0];
+  s.mirror = 0;
   return s;
 }
 
 void AllToAll::check_status() const {
-  const Status s = read_status();
+  const Status s = peek_status();
   if (s.code != kOk) throw Error("pplx_kernels_b200: " + describe_status(s));
+  if (params_.debug_checks) verify_canaries();
 }
 
 }  // namespace pplx

@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 
 #include "../core/buffer.h"
+#include "../core/ll128_layout.h"
 #include "../core/status.h"
 #include "../kernels/a2a_kernels.h"
 #include "../kernels/a2a_params.h"
@@ -63,6 +64,9 @@ struct DispatchCall {
   // x holds bf16 values (hidden_dim_bytes of them per row) that the send quantises to
   // e4m3 + fp32 scale per 128 columns; x_scale is then unused.
   bool quantize = false;
+  // x, x_scale and indices are device aliases of mapped pinned host memory: the send reads
+  // the tokens across PCIe itself and no upload precedes the call.
+  bool x_on_host = false;
 };
 
 struct CombineCall {
@@ -138,9 +142,23 @@ class AllToAll {
                             const std::vector<CombineCall>& calls, SplitMode mode,
                             cudaStream_t stream);
 
-  // Reads the device status block (synchronises the device); throws on failure.
+  // Failure record.  The kernels keep it in device memory and mirror the first failure
+  // into mapped pinned host memory.  read_status() copies the device block (synchronises
+  // the device, has the exact failure count); peek_status() reads the host mirror without
+  // touching the device, so it also works while kernels are still waiting.
   Status read_status() const;
+  Status peek_status() const;
+  // Throws if the mirror holds a failure (no synchronisation: call it after the caller's own
+  // stream synchronisation to cover the kernels launched so far).  With debug checks on it
+  // also verifies the guard words behind every arena region (that part synchronises).
   void check_status() const;
+  void verify_canaries() const;
+  // After a failure the flags and counters of the protocol are in an unknown state and
+  // every later dispatch() / combine() throws.  reset() clears this rank's arena, counters
+  // and failure record.  It is collective by contract: every rank of the object calls it
+  // once no kernel of the object is in flight anywhere, and the ranks meet at a barrier of
+  // the caller's (a host barrier is enough) before the next dispatch.
+  void reset();
 
   // Tunables (also settable through PPLX_B200_* environment variables at creation).
   void set_timeout_ms(double ms);
@@ -164,8 +182,17 @@ class AllToAll {
   CombineArgs make_combine_args(const CombineCall& call) const;
   int dispatch_grid(int num_tokens) const;
   int combine_grid(int num_tokens) const;
+  // Whether a dispatch of this object moves its rows as flag-in-data lines.
+  bool dispatch_uses_lines(bool quantize) const;
 
  private:
+  // The four half-operations in the only order the protocol supports.
+  enum class Step { kDispatchSend = 0, kDispatchRecv = 1, kCombineSend = 2, kCombineRecv = 3 };
+  void check_alive() const;
+  void advance(Step step);
+  // Entry of every operation: refuses a failed object, then checks and records the order.
+  void begin(Step first, bool both);
+
   A2AConfig cfg_;
   A2AParams params_{};
   std::shared_ptr<SymmetricAllocation> arena_;
@@ -173,6 +200,10 @@ class AllToAll {
   DeviceBuffer<uint32_t> recv_count_;
   DeviceBuffer<uint2> row_src_;
   DeviceBuffer<Status> status_;
+  HostBuffer<Status> status_host_;
+  std::vector<size_t> canaries_;
+  Step next_ = Step::kDispatchSend;
+  bool combine_send_used_lines_ = false;
   DeviceBuffer<uint64_t> trace_;
   int num_sms_ = 0;
   int max_blocks_ = 0;

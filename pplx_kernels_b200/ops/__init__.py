@@ -6,6 +6,11 @@ falls back to an empty namespace when loading fails.  Here a missing library is
 built on the spot when a compiler is present, and a failure on a machine that
 has a GPU is an error rather than a silent fallback: nothing in this package has
 a Python implementation of the GPU kernels.
+
+The library is loaded on the first use of an operator, not on import: helpers of
+this package that are plain PyTorch (synthetic data, clock sampling, CPU
+placement, the oracle) can then be imported by a process that must not map the
+native library -- the benchmark arm that times the unmodified reference is one.
 """
 
 from __future__ import annotations
@@ -43,7 +48,26 @@ def _load() -> object:
         return types.SimpleNamespace()
 
 
-_ops = _load()
+class _LazyOps:
+    """Stands for ``torch.ops.pplx_kernels_b200``; loads the library on first attribute use."""
+
+    _namespace: object | None = None
+
+    def _resolve(self) -> object:
+        if _LazyOps._namespace is None:
+            _LazyOps._namespace = _load()
+        return _LazyOps._namespace
+
+    def __getattr__(self, name: str) -> object:
+        return getattr(self._resolve(), name)
+
+
+_ops = _LazyOps()
+
+
+def is_loaded() -> bool:
+    """True once the native library has been mapped into this process."""
+    return _LazyOps._namespace is not None
 
 
 def library_path() -> Path:

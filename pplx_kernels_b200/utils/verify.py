@@ -1,4 +1,5 @@
-"""Shared verification logic for the GPU all-to-all tests.
+"""Verification of dispatch / combine results against the pure-PyTorch oracle (used by the
+GPU tests, the smoke run and the benchmarks that check their output before timing).
 
 Follows the reference's checks (tests/test_all_to_all.py:195-286): per-expert
 counts equal the expectation computed from the routing tables, received rows

@@ -17,7 +17,7 @@ import pplx_kernels_b200 as pk
 from pplx_kernels_b200.ops import _ops
 from pplx_kernels_b200.utils.testing import MoEConfig, as_index_tensor
 
-from .a2a_harness import (
+from pplx_kernels_b200.utils.verify import (
     RankBuffers,
     run_local_world,
     verify_combine,
@@ -407,6 +407,253 @@ def test_combine_writes_into_pinned_host_memory():
     _combine(ata, buf)
     torch.cuda.synchronize()
     ata.destroy()
+
+
+def test_dispatch_reads_its_inputs_from_pinned_host_memory():
+    """dp_x, dp_x_scale and indices in pinned host memory: the send reads them across PCIe
+    itself; counts and rows equal those of the device-input path, and combine takes its weights
+    from pinned memory too."""
+    cfg = small(torch.float8_e4m3fn, num_experts=16, experts_per_token=4, hidden_dim=1024,
+                max_num_tokens=32)
+    ata, inputs, buf = _single_rank(cfg, seed=74)
+    h_x = buf.x.cpu().pin_memory()
+    h_scale = buf.x_scale.cpu().pin_memory()
+    h_idx = buf.indices.cpu().pin_memory()
+    h_w = buf.weights.cpu().pin_memory()
+    for _ in range(2):
+        buf.counts.fill_(-1)
+        buf.expert_x.view(torch.uint8).zero_()
+        ata.dispatch(buf.counts, buf.expert_x, buf.expert_scale, h_x, h_scale, h_idx, buf.bound_m)
+        torch.cuda.synchronize()
+        ata.check_status()
+        verify_dispatch(cfg, inputs, 1, 0, buf)
+        buf.make_expert_y()
+        buf.out.fill_(float("nan"))
+        ata.combine(buf.out, h_idx, h_w, buf.expert_y, buf.bound_m)
+        torch.cuda.synchronize()
+        ata.check_status()
+        verify_combine(cfg, inputs, 0, buf)
+    # memory kinds must not be mixed, and pageable memory is refused
+    with pytest.raises(RuntimeError, match="same kind of memory"):
+        ata.dispatch(buf.counts, buf.expert_x, buf.expert_scale, h_x, h_scale, buf.indices,
+                     buf.bound_m)
+    with pytest.raises(RuntimeError, match="pinned host"):
+        ata.dispatch(buf.counts, buf.expert_x, buf.expert_scale, buf.x.cpu(), h_scale, h_idx,
+                     buf.bound_m)
+    ata.destroy()
+
+
+# ----------------------------------------------------------- both wire protocols ----
+
+
+def test_flag_in_data_lines_are_the_default_and_can_be_switched_off(monkeypatch):
+    cfg = small()
+    args = (cfg.max_num_tokens, cfg.num_experts, cfg.experts_per_token, 0, 1, 1, cfg.hidden_dim,
+            cfg.hidden_dim_bytes, cfg.hidden_dim_scale_bytes)
+    ata = pk.AllToAll.intranode(*args)
+    assert ata.layout()["flag_in_data"] == 1
+    ata.destroy()
+    monkeypatch.setenv("PPLX_B200_LL", "0")
+    ata = pk.AllToAll.intranode(*args)
+    assert ata.layout()["flag_in_data"] == 0
+    ata.destroy()
+    monkeypatch.delenv("PPLX_B200_LL")
+    monkeypatch.setenv("PPLX_B200_LL_MAX_TOKENS", str(cfg.max_num_tokens - 1))
+    ata = pk.AllToAll.intranode(*args)
+    assert ata.layout()["flag_in_data"] == 0
+    ata.destroy()
+
+
+@pytest.mark.parametrize("in_dtype", [torch.bfloat16, torch.float8_e4m3fn])
+@pytest.mark.parametrize("split", [False, True])
+def test_counter_protocol(monkeypatch, in_dtype, split):
+    """The store / fence / counter protocol (the one the fused MoE path and the quantising
+    send always use) serves the plain calls when the flag-in-data lines are switched off."""
+    monkeypatch.setenv("PPLX_B200_LL", "0")
+    run_local_world(small(in_dtype), world=4, dp_size=2, seed=81, iterations=3, split=split)
+    run_local_world(small(in_dtype), world=8, dp_size=1, seed=82, iterations=2, split=split)
+
+
+def test_counter_protocol_deepseek_rows(monkeypatch):
+    monkeypatch.setenv("PPLX_B200_LL", "0")
+    cfg = MoEConfig(num_experts=256, experts_per_token=8, hidden_dim=7168, max_num_tokens=16,
+                    in_dtype=torch.float8_e4m3fn)
+    run_local_world(cfg, world=8, dp_size=1, seed=83, num_tokens=16)
+
+
+@pytest.mark.parametrize("hidden", [16, 120, 136, 1016, 2048, 4096])
+@pytest.mark.parametrize("in_dtype", [torch.float8_e4m3fn, torch.float32])
+def test_row_lengths_around_the_line_size(hidden, in_dtype):
+    """Rows that end inside a line, on a line boundary and one chunk past it (a line carries
+    120 payload bytes), with the scales spilling into a second meta line at the largest."""
+    if in_dtype == torch.float8_e4m3fn and hidden % 16:
+        pytest.skip("hidden_dim_bytes must be a multiple of 16")
+    cfg = small(in_dtype, hidden_dim=hidden, num_experts=8, experts_per_token=2, max_num_tokens=9)
+    run_local_world(cfg, world=2, dp_size=1, seed=84, iterations=2)
+    run_local_world(cfg, world=4, dp_size=2, seed=85, split=True, y_dtype=torch.float32)
+
+
+def test_many_tokens_per_rank_through_lines():
+    cfg = MoEConfig(num_experts=32, experts_per_token=4, hidden_dim=2048, max_num_tokens=600,
+                    in_dtype=torch.float8_e4m3fn)
+    run_local_world(cfg, world=4, dp_size=1, seed=86, iterations=2)
+
+
+# ------------------------------------------------------- misuse and dead objects ----
+
+
+def test_two_dispatches_in_a_row_are_refused_on_the_host():
+    cfg = small()
+    ata, inputs, buf = _single_rank(cfg, seed=87)
+    _dispatch(ata, buf)
+    with pytest.raises(RuntimeError, match="must alternate"):
+        _dispatch(ata, buf)
+    buf.make_expert_y()
+    with pytest.raises(RuntimeError, match="must alternate"):
+        _combine(ata, buf, do_send=False, do_recv=True)
+    _combine(ata, buf)
+    with pytest.raises(RuntimeError, match="must alternate"):
+        _combine(ata, buf)
+    torch.cuda.synchronize()
+    ata.check_status()
+    verify_dispatch(cfg, inputs, 1, 0, buf)
+    verify_combine(cfg, inputs, 0, buf)
+    ata.destroy()
+
+
+def test_an_object_refuses_work_after_a_failure_until_it_is_reset():
+    """A timed-out wait leaves flags and counters in an unknown state: later calls raise
+    instead of returning incomplete data.  The host sees the failure in the pinned mirror of
+    the status block without synchronising; reset() on every rank revives the object."""
+    cfg = small(torch.bfloat16, hidden_dim=64)
+    device = torch.device("cuda", 0)
+    ranks = pk.AllToAll.local_world(cfg.max_num_tokens, cfg.num_experts, cfg.experts_per_token,
+                                    2, 1, cfg.hidden_dim, cfg.hidden_dim_bytes, 0)
+    inputs = world_inputs(cfg, 2, 1, seed=88)
+    bufs = [RankBuffers(cfg, 2, 1, inputs[r], device) for r in range(2)]
+    ranks[0].set_timeout_ms(100)
+
+    def dispatch(who):
+        pk.dispatch_group([ranks[r] for r in who], [bufs[r].counts for r in who],
+                          [bufs[r].expert_x for r in who], [None for _ in who],
+                          [bufs[r].x for r in who], [None for _ in who],
+                          [bufs[r].indices for r in who], [bufs[r].bound_m for r in who])
+
+    assert ranks[0].peek_status()["code"] == 0
+    dispatch([0])  # rank 1 never joins: rank 0's wait for its counts runs out
+    torch.cuda.synchronize()
+    peek = ranks[0].peek_status()
+    assert peek["code"] == 1 and peek["phase"] == 1 and peek["peer"] == 1
+    with pytest.raises(RuntimeError, match="recorded a failure earlier"):
+        dispatch([0])
+    with pytest.raises(RuntimeError, match="recorded a failure earlier"):
+        pk.combine_group([ranks[0]], [bufs[0].out], [bufs[0].indices], [bufs[0].weights],
+                         [bufs[0].make_expert_y()], [bufs[0].bound_m])
+    for r in ranks:
+        r.reset()
+        r.set_timeout_ms(3000)
+        r.set_debug_checks(True)
+    assert ranks[0].peek_status()["code"] == 0
+    for it in range(2):
+        dispatch([0, 1])
+        torch.cuda.synchronize()
+        for r in range(2):
+            ranks[r].check_status()
+            verify_dispatch(cfg, inputs, 1, r, bufs[r])
+        pk.combine_group(ranks, [b.out for b in bufs], [b.indices for b in bufs],
+                         [b.weights for b in bufs], [b.make_expert_y() for b in bufs],
+                         [b.bound_m for b in bufs])
+        torch.cuda.synchronize()
+        for r in range(2):
+            ranks[r].check_status()
+            verify_combine(cfg, inputs, r, bufs[r])
+    for r in ranks:
+        r.destroy()
+
+
+def test_duplicate_experts_in_a_token_are_reported_not_written_past_the_region():
+    """The staging region of a source is sized for distinct experts per token.  A token that
+    names one expert top-k times on a rank that owns fewer experts than top-k overflows it; the
+    send drops the surplus rows and records the overflow whether or not debug checks are on."""
+    cfg = small(torch.bfloat16, num_experts=4, experts_per_token=3, hidden_dim=64,
+                max_num_tokens=4)
+    device = torch.device("cuda", 0)
+    ranks = pk.AllToAll.local_world(cfg.max_num_tokens, cfg.num_experts, cfg.experts_per_token,
+                                    2, 1, cfg.hidden_dim, cfg.hidden_dim_bytes, 0)
+    inputs = world_inputs(cfg, 2, 1, seed=89, num_tokens=4)
+    bufs = [RankBuffers(cfg, 2, 1, inputs[r], device) for r in range(2)]
+    bad = torch.zeros(4, 3, dtype=torch.int32, device=device)  # every entry names expert 0
+    bufs[0].indices = bad.view(torch.uint32)
+    for r in ranks:
+        r.set_timeout_ms(300)
+    pk.dispatch_group(ranks, [b.counts for b in bufs], [b.expert_x for b in bufs], [None, None],
+                      [b.x for b in bufs], [None, None], [b.indices for b in bufs],
+                      [b.bound_m for b in bufs])
+    torch.cuda.synchronize()
+    st = ranks[0].status()
+    # kSlotOverflow from the sender, or kRowOverflow from a receiving block that saw the
+    # oversized count first
+    assert st["code"] in (3, 4), st
+    ranks[0].verify_canaries()
+    ranks[1].verify_canaries()
+    for r in ranks:
+        r.destroy()
+
+
+def test_world_graph_replayed_with_a_changing_bound_m():
+    """All ranks of an emulated world inside one CUDA graph (dispatch, expert, combine),
+    replayed many times; bound_m of one DP group changes between replays.  Graph replay across
+    ranks is what leans hardest on the iteration-numbered flags."""
+    cfg = small(torch.float8_e4m3fn, num_experts=16, experts_per_token=4, hidden_dim=1024,
+                max_num_tokens=24)
+    world, dp_size = 4, 1
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    ranks = pk.AllToAll.local_world(cfg.max_num_tokens, cfg.num_experts, cfg.experts_per_token,
+                                    world, dp_size, cfg.hidden_dim, cfg.hidden_dim_bytes,
+                                    cfg.hidden_dim_scale_bytes)
+    for r in ranks:
+        r.set_timeout_ms(3000)
+    inputs = world_inputs(cfg, world, dp_size, seed=90, num_tokens=24)
+    bufs = [RankBuffers(cfg, world, dp_size, inputs[r], device) for r in range(world)]
+    for b in bufs:
+        b.make_expert_y()
+
+    def step():
+        pk.dispatch_group(ranks, [b.counts for b in bufs], [b.expert_x for b in bufs],
+                          [b.expert_scale for b in bufs], [b.x for b in bufs],
+                          [b.x_scale for b in bufs], [b.indices for b in bufs],
+                          [b.bound_m for b in bufs])
+        for b in bufs:
+            b.expert_y.copy_((b.expert_x.to(torch.float32) * 1.5).to(cfg.out_dtype))
+        pk.combine_group(ranks, [b.out for b in bufs], [b.indices for b in bufs],
+                         [b.weights for b in bufs], [b.expert_y for b in bufs],
+                         [b.bound_m for b in bufs])
+
+    step()
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+    try:
+        for replays, m1 in ((1000, 24), (3, 7), (50, 0), (5, 19)):
+            bufs[1].bound_m.view(torch.int32).fill_(m1)
+            inputs[1].num_tokens = m1
+            for b in bufs:
+                b.out.fill_(float("nan"))
+                b.counts.fill_(-1)
+            for _ in range(replays):
+                graph.replay()
+            torch.cuda.synchronize()
+            for r in range(world):
+                ranks[r].check_status()
+                verify_dispatch(cfg, inputs, dp_size, r, bufs[r])
+                verify_combine(cfg, inputs, r, bufs[r])
+    finally:
+        for r in ranks:
+            r.destroy()
 
 
 def test_a_rank_may_run_one_dispatch_ahead_of_a_peer():

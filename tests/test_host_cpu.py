@@ -154,8 +154,42 @@ def test_bench_end_to_end_entry_picks_the_best_supported_mode():
     spec = importlib.util.spec_from_file_location("bench_module", os.path.join(root, "bench.py"))
     bench = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(bench)
-    e = bench._e2e_entry(8, 128, {"eager": 250.0, "graph": None, "host": 200.0}, 10, 20, "")
+    res = {"e2e_modes_us_per_step": {"eager": 250.0, "graph": None, "host": 200.0},
+           "h2d_bytes": 10, "d2h_bytes": 20, "e2e_note": ""}
+    e = bench.e2e_entry(8, 128, res)
     assert e["mode"] == "host" and e["us_per_step"] == 200.0
     assert abs(e["value"] - 8 * 128 / 200e-6) < 1e-3
     assert e["modes_us_per_step"]["graph"] is None
     assert e["h2d_bytes_per_step"] == 10 and e["d2h_bytes_per_step"] == 20
+
+
+def test_bench_compares_with_the_published_numbers_only_at_their_world_size():
+    import importlib.util
+    import os
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_module2", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert bench.vs_published(1, 128, 1e6) is None
+    assert bench.vs_published(8, 7, 1e6) is None
+    pub = 8 * 128 / ((83.6 + 102.3) * 1e-6)
+    assert abs(bench.vs_published(8, 128, 2 * pub) - 2.0) < 1e-9
+
+
+def test_helpers_of_the_package_import_without_the_native_library():
+    """The benchmark arm that times the unmodified reference imports the package's data and
+    clock helpers; that must not map this repository's shared object."""
+    import os
+    import subprocess
+    import sys
+
+    code = ("import pplx_kernels_b200, pplx_kernels_b200.utils.testing, "
+            "pplx_kernels_b200.utils.clocks, pplx_kernels_b200.parallel.affinity\n"
+            "from pplx_kernels_b200.ops import is_loaded\n"
+            "assert not is_loaded()\n"
+            "assert 'libpplx_kernels_b200' not in open('/proc/self/maps').read()\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=root,
+                         timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]

@@ -13,7 +13,7 @@ import torch
 import pplx_kernels_b200 as pk
 from pplx_kernels_b200.utils.testing import MoEConfig, ProcessGroupInfo, parallel_launch
 
-from .a2a_harness import RankBuffers, verify_combine, verify_dispatch, world_inputs
+from pplx_kernels_b200.utils.verify import RankBuffers, verify_combine, verify_dispatch, world_inputs
 
 pytestmark = pytest.mark.gpu
 
@@ -24,9 +24,9 @@ def _need(n: int) -> None:
 
 
 def _init_runtime(pgi: ProcessGroupInfo) -> None:
-    uid = pk.nvshmem_get_unique_id() if pgi.rank == 0 else pk.nvshmem_alloc_empty_unique_id()
-    torch.distributed.broadcast(uid, src=0)
-    pk.nvshmem_init(uid, pgi.rank, pgi.world_size)
+    from pplx_kernels_b200.parallel.runtime import init_runtime_from_torch
+
+    assert init_runtime_from_torch() == (pgi.rank, pgi.world_size)
 
 
 def _make(pgi: ProcessGroupInfo, cfg: MoEConfig, dp_size: int, internode: bool) -> pk.AllToAll:
@@ -40,30 +40,34 @@ def _make(pgi: ProcessGroupInfo, cfg: MoEConfig, dp_size: int, internode: bool) 
 
 
 def _worker_all_to_all(pgi: ProcessGroupInfo, cfg: MoEConfig, dp_size: int, internode: bool,
-                       iterations: int, split: bool) -> None:
+                       iterations: int, split: bool, use_compile: bool = False) -> None:
     if internode:
         _init_runtime(pgi)
     ata = _make(pgi, cfg, dp_size, internode)
+    # As in the reference's test (tests/test_all_to_all.py:178, 262): the calls go through
+    # torch.compile, which works because the operators have schemas and Meta kernels.
+    dispatch = torch.compile(ata.dispatch) if use_compile else ata.dispatch
+    combine = torch.compile(ata.combine) if use_compile else ata.combine
     for it in range(iterations):
         inputs = world_inputs(cfg, pgi.world_size, dp_size, seed=100 + it)
         buf = RankBuffers(cfg, pgi.world_size, dp_size, inputs[pgi.rank], pgi.device)
         d = (buf.counts, buf.expert_x, buf.expert_scale, buf.x, buf.x_scale, buf.indices,
              buf.bound_m)
         if split:
-            ata.dispatch(*d, do_send=True, do_recv=False)
-            ata.dispatch(*d, do_send=False, do_recv=True)
+            dispatch(*d, do_send=True, do_recv=False)
+            dispatch(*d, do_send=False, do_recv=True)
         else:
-            ata.dispatch(*d)
+            dispatch(*d)
         torch.cuda.synchronize()
         ata.check_status()
         verify_dispatch(cfg, inputs, dp_size, pgi.rank, buf)
         buf.make_expert_y()
         c = (buf.out, buf.indices, buf.weights, buf.expert_y, buf.bound_m)
         if split:
-            ata.combine(*c, do_send=True, do_recv=False)
-            ata.combine(*c, do_send=False, do_recv=True)
+            combine(*c, do_send=True, do_recv=False)
+            combine(*c, do_send=False, do_recv=True)
         else:
-            ata.combine(*c)
+            combine(*c)
         torch.cuda.synchronize()
         ata.check_status()
         verify_combine(cfg, inputs, pgi.rank, buf)
@@ -81,6 +85,12 @@ def test_all_to_all_2_gpu(in_dtype, internode):
     parallel_launch(2, _worker_all_to_all, cfg, 1, internode, 4, False)
 
 
+def test_all_to_all_2_gpu_through_torch_compile():
+    _need(2)
+    cfg = MoEConfig(8, 3, 512, 10, in_dtype=torch.float8_e4m3fn)
+    parallel_launch(2, _worker_all_to_all, cfg, 1, False, 3, False, True)
+
+
 def test_all_to_all_2_gpu_split_mode():
     _need(2)
     cfg = MoEConfig(8, 3, 512, 10, in_dtype=torch.float8_e4m3fn)
@@ -96,10 +106,13 @@ def test_all_to_all_2_gpu_replicated_tokens():
 @pytest.mark.parametrize("in_dtype", [torch.bfloat16, torch.float8_e4m3fn, torch.float16])
 @pytest.mark.parametrize("out_dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("internode", [True, False])
-def test_all_to_all_4_gpu(in_dtype, out_dtype, internode):
+@pytest.mark.parametrize("use_compile", [False, True])
+def test_all_to_all_4_gpu(in_dtype, out_dtype, internode, use_compile):
+    """The reference's own matrix (tests/test_all_to_all.py:313-332): world 4, dp 2, three
+    input and two output dtypes, both constructors, with and without torch.compile."""
     _need(4)
     cfg = MoEConfig(8, 3, 512, 10, in_dtype=in_dtype, out_dtype=out_dtype)
-    parallel_launch(4, _worker_all_to_all, cfg, 2, internode, 2, False)
+    parallel_launch(4, _worker_all_to_all, cfg, 2, internode, 2, False, use_compile)
 
 
 def test_all_to_all_8_gpu_deepseek_shape():

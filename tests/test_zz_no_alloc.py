@@ -24,9 +24,9 @@ import torch
 
 import pplx_kernels_b200 as pk
 from pplx_kernels_b200.ops import library_path
+from pplx_kernels_b200.ops.reference import simulate_dispatch
 from pplx_kernels_b200.utils.testing import MoEConfig, as_index_tensor, make_rank_inputs
-
-from .a2a_harness import _joined_rows, _sorted_rows
+from pplx_kernels_b200.utils.verify import _joined_rows, _sorted_rows
 
 pytestmark = pytest.mark.gpu
 
@@ -118,6 +118,17 @@ def test_matches_regular_dispatch_on_two_calls_in_a_row(in_dtype):
         torch.cuda.synchronize()
         assert int(status.item()) == 0, f"call {call}: the kernel reported a timed-out wait"
         _assert_same_dispatch(cfg, got, want)
+        # ... and what the pure-PyTorch oracle says a one-rank dispatch delivers.
+        oracle = simulate_dispatch([inp], cfg.num_experts, 1)[0]
+        assert got[0].cpu().tolist() == oracle.counts()
+        for e, rows in enumerate(oracle.rows):
+            if not rows:
+                continue
+            w_x = torch.stack([inp.x[i] for _, i, _ in rows])
+            w_s = torch.stack([inp.x_scale[i] for _, i, _ in rows]) if inp.x_scale is not None else None
+            g_s = got[2][e, :len(rows)].cpu() if got[2] is not None else None
+            assert torch.equal(_sorted_rows(_joined_rows(got[1][e, :len(rows)].cpu(), g_s)),
+                               _sorted_rows(_joined_rows(w_x, w_s))), f"expert {e}: rows differ from the oracle"
         # The regular path must be left in a state from which combine works: finish the round.
         out = torch.empty(cfg.max_num_tokens, cfg.hidden_dim, dtype=torch.bfloat16, device=device)
         ata.combine(out, indices, inp.weights.to(device), want[1].to(torch.bfloat16),
