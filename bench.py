@@ -47,6 +47,10 @@ PUBLISHED_WORLD = 8
 # NVSwitch-connected B200.
 NVLINK_GBS_DEFAULT = 770.0
 
+# The two model shapes of the reference's benchmark (tests/bench_all_to_all.py:244-262):
+# (experts, top-k, hidden); fp8 e4m3 tokens with one fp32 scale per 128 columns, bf16 results.
+SHAPES = {"r1": (256, 8, 7168), "v2lite": (64, 6, 2048)}
+
 METRIC = ("MoE dispatch+combine tokens/s (DeepSeek-V3 shape: 256 experts, top-8, hidden 7168, "
           "fp8 dispatch + bf16 combine)")
 DTYPE = "fp8_e4m3 dispatch (fp32 scale per 128) / bf16 combine"
@@ -103,6 +107,7 @@ class PackedInputs:
         for o, t in zip(offs, parts):
             self.host[o:o + t.numel()].copy_(t)
         self.dev = self.host.to(dev)
+        self._routing_from = offs[2]
         m, hidden = inp.x.shape
 
         def view(buf: torch.Tensor, i: int, t: torch.Tensor, dtype: torch.dtype, shape) -> torch.Tensor:
@@ -120,6 +125,10 @@ class PackedInputs:
     def upload(self) -> None:
         self.dev.copy_(self.host, non_blocking=True)
 
+    def upload_routing(self) -> None:
+        """Copies only indices and weights (a few KiB, adjacent in the buffer)."""
+        self.dev[self._routing_from:].copy_(self.host[self._routing_from:], non_blocking=True)
+
     def nbytes(self) -> int:
         return self.host.numel()
 
@@ -131,17 +140,19 @@ class Arm:
     of ``self.ata`` is the same for all three.
     """
 
-    def __init__(self, kind: str, tokens: int, rank: int, world: int, dev: torch.device) -> None:
+    def __init__(self, kind: str, tokens: int, rank: int, world: int, dev: torch.device,
+                 shape: str = "r1", zipf: float = 0.0) -> None:
         from pplx_kernels_b200.utils.testing import MoEConfig, make_rank_inputs
 
         self.kind, self.rank, self.world, self.device, self.tokens = kind, rank, world, dev, tokens
-        cfg = MoEConfig(num_experts=256, experts_per_token=8, hidden_dim=7168,
+        experts, topk, hidden = SHAPES[shape]
+        cfg = MoEConfig(num_experts=experts, experts_per_token=topk, hidden_dim=hidden,
                         max_num_tokens=tokens, in_dtype=torch.float8_e4m3fn,
                         out_dtype=torch.bfloat16)
         self.cfg = cfg
         nle = cfg.num_experts // world
         inp = make_rank_inputs(cfg, torch.Generator().manual_seed(1000 + rank), num_tokens=tokens,
-                               softmax_weights=True)
+                               softmax_weights=True, zipf=zipf)
         self.packed = PackedInputs(inp, dev)
         self.x, self.x_scale = self.packed.x, self.packed.x_scale
         self.indices, self.weights = self.packed.indices, self.packed.weights
@@ -173,10 +184,11 @@ class Arm:
                           self.indices, self.bound_m)
 
     def dispatch_from_host(self) -> None:
-        """dispatch whose send reads tokens, scales and routing from pinned host memory."""
+        """dispatch whose send reads tokens and scales from pinned host memory; the routing
+        table (every block reads all of it) has been copied to the device."""
         p = self.packed
         self.ata.dispatch(self.counts, self.expert_x, self.expert_scale, p.h_x, p.h_x_scale,
-                          p.h_indices, self.bound_m)
+                          self.indices, self.bound_m)
 
     def combine(self) -> None:
         self.ata.combine(self.out, self.indices, self.weights, self.expert_y, self.bound_m)
@@ -185,10 +197,6 @@ class Arm:
         """combine whose reduction writes the tokens straight into the pinned host buffer."""
         self.ata.combine(self.h_out, self.indices, self.weights, self.expert_y, self.bound_m)
 
-    def combine_host_both(self) -> None:
-        """combine that reads the weights from, and writes the tokens to, pinned host memory."""
-        self.ata.combine(self.h_out, self.packed.h_indices, self.packed.h_weights, self.expert_y,
-                         self.bound_m)
 
     def upload(self) -> None:
         self.packed.upload()
@@ -331,17 +339,18 @@ def measure_arm(kind: str, h: Harness, tokens: int, rank: int, world: int, no_gr
             arm.combine_to_host()
 
         def step_host_both() -> None:
+            arm.packed.upload_routing()
             arm.dispatch_from_host()
-            arm.combine_host_both()
+            arm.combine_to_host()
 
         modes["eager calls, combine writes the tokens to pinned host memory"] = float(
             h.time_step(step_host_out).mean())
         try:
-            modes["eager calls, dispatch reads its inputs from and combine writes the tokens to "
-                  "pinned host memory"] = float(h.time_step(step_host_both).mean())
+            modes["eager calls, dispatch reads the tokens from and combine writes the tokens to "
+                  "pinned host memory (routing table copied)"] = float(h.time_step(step_host_both).mean())
             if not no_graph:
-                modes["one CUDA graph replay per step, inputs read from and tokens written to "
-                      "pinned host memory"], _ = h.time_graph(step_host_both)
+                modes["one CUDA graph replay per step, tokens read from and written to pinned "
+                      "host memory (routing table copied)"], _ = h.time_graph(step_host_both)
         except RuntimeError as exn:  # an older native library without host-input support
             graph_why = (graph_why + "; " if graph_why else "") + f"host-input mode: {str(exn)[:100]}"
     res = {
@@ -633,9 +642,10 @@ def own_arm(args: argparse.Namespace) -> None:
     comb_bytes = rows * cfg.hidden_dim * 2
     if world > 1:
         remote = (world - 1) / world
-        floor_us = {"dispatch": disp_bytes * remote / link_gbs / 1e3,
-                    "combine": comb_bytes * remote / link_gbs / 1e3}
-        bound = f"NVLink {link_gbs:.0f} GB/s per direction ({link_how})"
+        floor_us = {"dispatch": disp_bytes * remote / NVLINK_GBS_DEFAULT / 1e3,
+                    "combine": comb_bytes * remote / NVLINK_GBS_DEFAULT / 1e3}
+        bound = (f"NVLink {NVLINK_GBS_DEFAULT:.0f} GB/s per direction (peer copy); this run's own "
+                 f"copy kernel reached {link_gbs:.0f} GB/s ({link_how})")
     else:
         # single GPU: staging write + staging read + output write per row (dispatch);
         # staging write + staging read per row plus the token write (combine)
@@ -663,6 +673,58 @@ def own_arm(args: argparse.Namespace) -> None:
         torch.distributed.destroy_process_group()
 
 
+def sweep(args: argparse.Namespace) -> None:
+    """One JSON line per (shape, tokens per GPU): dispatch / combine / step p50 of the chosen arm
+    (max over ranks, L2 flushed, same harness as the headline run) and, in the own arm, torch's
+    NCCL all_to_all_single on the reference's dense shape.  Serves the measurement tables."""
+    rank, world, local_rank = _env_rank()
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    init_distributed(world, local_rank)
+    kind = "ours"
+    if args.impl == "reference":
+        sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+        kind = "ref-internode" if args.ref_sub == "internode" else "ref-intranode"
+        if kind == "ref-internode":
+            from pplx_kernels import nvshmem as ref_nvshmem
+
+            uid = (ref_nvshmem.nvshmem_get_unique_id() if rank == 0
+                   else ref_nvshmem.nvshmem_alloc_empty_unique_id())
+            torch.distributed.broadcast(uid, src=0)
+            ref_nvshmem.nvshmem_init(uid, rank, world)
+    h = Harness(world, dev, args.steps, max(args.warmup, 3))
+    for shape in args.shapes.split(","):
+        for tokens in (int(t) for t in args.sweep.split(",")):
+            if SHAPES[shape][0] % world:
+                continue
+            arm = Arm(kind, tokens, rank, world, dev, shape=shape, zipf=args.zipf)
+            t = h.time_pair(arm.dispatch, arm.combine)
+            row = {"impl": kind, "shape": shape, "ep": world, "tokens": tokens, "zipf": args.zipf,
+                   "dispatch_us_p50": float(t[:, 0].median()),
+                   "combine_us_p50": float(t[:, 1].median()),
+                   "step_us_p50": float(t[:, 2].median()), "steps": h.steps}
+            if kind == "ours":
+                row["nccl_all_to_all_single_us_p50"] = (
+                    nccl_baseline(h, arm.cfg, tokens)
+                    if tokens * (arm.cfg.hidden_dim_bytes + arm.cfg.hidden_dim_scale_bytes)
+                    * arm.cfg.num_experts <= (2 << 30) else None)
+                link = NVLINK_GBS_DEFAULT
+                remote = (world - 1) / world
+                rows = tokens * arm.cfg.experts_per_token
+                slot = arm.cfg.hidden_dim_bytes + arm.cfg.hidden_dim_scale_bytes + 16
+                if world > 1:
+                    row["dispatch_frac_of_nvlink_floor"] = (
+                        rows * slot * remote / link / 1e3 / row["dispatch_us_p50"])
+                    row["combine_frac_of_nvlink_floor"] = (
+                        rows * arm.cfg.hidden_dim * 2 * remote / link / 1e3 / row["combine_us_p50"])
+            arm.close()
+            if rank == 0:
+                _emit(row)
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -678,11 +740,17 @@ def main() -> None:
     ap.add_argument("--ref-child-timeout", type=int, default=300,
                     help="seconds the NVSHMEM sub-arm's child processes may take")
     ap.add_argument("--out-file", default="", help=argparse.SUPPRESS)
+    ap.add_argument("--sweep", default="", help="comma list of tokens per GPU: print one JSON "
+                    "line per size instead of the headline line")
+    ap.add_argument("--shapes", default="r1", help="sweep: comma list of r1, v2lite")
+    ap.add_argument("--zipf", type=float, default=0.0, help="sweep: routing skew, 0 = uniform")
     args = ap.parse_args()
     global _RESULT_FD
     sys.stdout.flush()
     _RESULT_FD = os.dup(1)
     os.dup2(2, 1)
+    if args.sweep:
+        return sweep(args)
     if args.impl == "reference":
         try:
             reference_arm(args)

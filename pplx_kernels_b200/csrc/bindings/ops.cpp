@@ -215,11 +215,13 @@ DispatchCall make_dispatch_call(const AllToAll& ata, at::Tensor& out_expert_num_
     TORCH_CHECK(dp_x.size(1) * static_cast<int64_t>(dp_x.element_size()) == p.hidden_bytes,
                 "dp_x rows must be hidden_dim_bytes long");
   }
-  TORCH_CHECK((host_in ? on_pinned_host(indices) : indices.is_cuda()) && indices.dim() == 2 &&
+  // Every block reads the whole routing table, so with the tokens in host memory it is
+  // cheaper to keep `indices` (a few KiB) on the device; both are accepted.
+  TORCH_CHECK((indices.is_cuda() || (host_in && on_pinned_host(indices))) && indices.dim() == 2 &&
                   indices.is_contiguous() && indices.element_size() == 4 &&
                   indices.size(1) == p.topk,
-              "indices must be a contiguous 32-bit tensor of [num_tokens, experts_per_token] in "
-              "the same kind of memory as dp_x");
+              "indices must be a contiguous 32-bit tensor of [num_tokens, experts_per_token] on "
+              "the device (or, with dp_x in pinned host memory, in pinned host memory too)");
   TORCH_CHECK(indices.size(0) == dp_x.size(0), "indices and dp_x disagree on the token count");
 
   DispatchCall c;

@@ -92,9 +92,19 @@ struct Poll {
   }
 };
 
+// Where the sender's copy of a row lives: global memory (device or mapped host memory,
+// read through the non-coherent path) or this block's shared memory.
+enum class Src { kGlobal, kShared };
+
+template <Src S>
+__device__ __forceinline__ uint64_t ld_row8(const uint8_t* p) {
+  if constexpr (S == Src::kGlobal) return ld_src8(p);
+  else return *reinterpret_cast<const uint64_t*>(p);
+}
+
 // Sends bytes of `src` as lines [l0, l1) of `slot`: line L carries src[L*120, L*120+120),
 // zero beyond `nbytes` (a multiple of 8).  One warp, all lanes.
-template <int kBatch = 4>
+template <Src S = Src::kGlobal, int kBatch = 4>
 __device__ __forceinline__ void warp_send_lines(uint8_t* slot, const uint8_t* src, int nbytes,
                                                 int l0, int l1, uint64_t flag, int lane) {
   const int j = lane & 7, g = lane >> 3;
@@ -107,8 +117,8 @@ __device__ __forceinline__ void warp_send_lines(uint8_t* slot, const uint8_t* sr
       b[u] = 0;
       if (line < l1) {
         const int o = line * kLineData + j * 16;
-        if (o + 8 <= nbytes) a[u] = ld_src8(src + o);
-        if (j < 7 && o + 16 <= nbytes) b[u] = ld_src8(src + o + 8);
+        if (o + 8 <= nbytes) a[u] = ld_row8<S>(src + o);
+        if (j < 7 && o + 16 <= nbytes) b[u] = ld_row8<S>(src + o + 8);
       }
     }
 #pragma unroll
@@ -161,13 +171,18 @@ __device__ __forceinline__ bool warp_recv_lines(uint8_t* dst, const uint8_t* slo
 // ---- word-granular lines: a short stream of 32-bit words (trailer, strided scales) ----
 
 // Word `idx` of the meta stream of a dispatch row: 4 trailer words, then the fp32 scales.
+template <Src S>
 __device__ __forceinline__ uint32_t meta_word(int idx, const uint32_t (&trailer)[4],
                                               const float* scales, int64_t stride, int nscale) {
   if (idx < 4) return trailer[idx];
-  if (idx - 4 < nscale) return __float_as_uint(__ldg(scales + static_cast<int64_t>(idx - 4) * stride));
+  if (idx - 4 < nscale) {
+    const float* at = scales + static_cast<int64_t>(idx - 4) * stride;
+    return __float_as_uint(S == Src::kGlobal ? __ldg(at) : *at);
+  }
   return 0u;
 }
 
+template <Src S = Src::kGlobal>
 __device__ __forceinline__ void warp_send_meta(uint8_t* meta, int nlines,
                                                const uint32_t (&trailer)[4], const float* scales,
                                                int64_t stride, int nscale, uint64_t flag, int lane) {
@@ -176,12 +191,12 @@ __device__ __forceinline__ void warp_send_meta(uint8_t* meta, int nlines,
     const int line = lb + g;
     if (line < nlines) {
       const int w0 = (line * kLineData + j * 16) >> 2;
-      const uint32_t x0 = meta_word(w0, trailer, scales, stride, nscale);
-      const uint32_t x1 = meta_word(w0 + 1, trailer, scales, stride, nscale);
+      const uint32_t x0 = meta_word<S>(w0, trailer, scales, stride, nscale);
+      const uint32_t x1 = meta_word<S>(w0 + 1, trailer, scales, stride, nscale);
       uint64_t b = flag;
       if (j < 7) {
-        const uint32_t x2 = meta_word(w0 + 2, trailer, scales, stride, nscale);
-        const uint32_t x3 = meta_word(w0 + 3, trailer, scales, stride, nscale);
+        const uint32_t x2 = meta_word<S>(w0 + 2, trailer, scales, stride, nscale);
+        const uint32_t x3 = meta_word<S>(w0 + 3, trailer, scales, stride, nscale);
         b = static_cast<uint64_t>(x2) | (static_cast<uint64_t>(x3) << 32);
       }
       st16(meta + line * kLineBytes + j * 16,

@@ -15,7 +15,10 @@ enum class DType : int { kF32 = 0, kF16 = 1, kBF16 = 2 };
 
 inline size_t dtype_size(DType t) { return t == DType::kF32 ? 4 : 2; }
 
-size_t dispatch_smem_bytes(const A2AParams& p);
+// `stage_tokens`: token rows a block fetches into shared memory per round (DispatchArgs).
+size_t dispatch_smem_bytes(const A2AParams& p, int stage_tokens = 0);
+// Rows per round that fit the staging budget for this geometry (0: rows too long to stage).
+int dispatch_stage_tokens(const A2AParams& p);
 int dispatch_threads();
 
 // One rank per device (production path).

@@ -143,7 +143,9 @@ struct DispatchArgs {
                              // e4m3 + one fp32 scale per 128 columns on the fly
   int packed;                // send only: two-hop protocol, rows land at their final,
                              // expert-major position in the destination's staging
-  int x_on_host;             // x / x_scale / indices live in mapped pinned host memory
+  int x_on_host;             // x / x_scale live in mapped pinned host memory
+  int stage_tokens;          // x_on_host with the flag-in-data send: token rows a block
+                             // fetches into shared memory per round (0: read rows in place)
 };
 
 struct CombineArgs {

@@ -32,9 +32,23 @@ __global__ void alltoall_copy_kernel(const __grid_constant__ AllToAllCopyParams 
   const size_t nvec = a.chunk_bytes >> 4;
   const int4* src = reinterpret_cast<const int4*>(a.src + dst_rank * a.chunk_bytes);
   int4* dst = reinterpret_cast<int4*>(a.peer_dst[dst_rank] + a.rank * a.chunk_bytes);
-  for (size_t v = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v < nvec;
-       v += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    dst[v] = src[v];
+  // Eight 16-byte loads in flight per thread before the first store, so that the copy is
+  // bound by the link and not by one memory latency per vector.
+  constexpr int kBatch = 8;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t v0 = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; v0 < nvec;
+       v0 += stride * kBatch) {
+    int4 r[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const size_t v = v0 + u * stride;
+      if (v < nvec) r[u] = ptx::ld_nc_v4(src + v);
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const size_t v = v0 + u * stride;
+      if (v < nvec) ptx::st_v4(dst + v, r[u]);
+    }
   }
 }
 

@@ -54,6 +54,8 @@
 // waits at all, so the kernel needs no cooperative launch.  In fused mode a
 // block may sit in a receive wait while a peer still has blocks to schedule, so
 // the host keeps the grid within what is resident at once.
+#include <algorithm>
+
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
@@ -93,6 +95,7 @@ struct DispatchSmem {
   uint32_t* rbase;   // [P]
   uint32_t* sent;    // [kMaxWorld]
   uint32_t* rowpos;  // [kRowCap] staging slot of each row this block sends
+  uint8_t* xstage;   // token rows fetched from host memory before they are sent (optional)
 };
 
 __device__ __forceinline__ DispatchSmem carve(uint32_t* s, int E, int P) {
@@ -105,6 +108,11 @@ __device__ __forceinline__ DispatchSmem carve(uint32_t* s, int E, int P) {
   m.rbase = m.fstart + P + 1;
   m.sent = m.rbase + P;
   m.rowpos = m.sent + kMaxWorld;
+  // The word arrays before it have an odd total in general; rows are moved with 16-byte
+  // accesses, so the staging starts on the next 16-byte boundary of the (16-byte aligned)
+  // dynamic shared memory.
+  const size_t words = static_cast<size_t>(m.rowpos + kRowCap - s);
+  m.xstage = reinterpret_cast<uint8_t*>(s) + round_up<size_t>(words * sizeof(uint32_t), 16);
   return m;
 }
 
@@ -348,87 +356,134 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
   }
   trace(p, kTrDispatchPosted);
 
-  const int n_units = rows_here * split;
-  for (int unit = warp; unit < n_units; unit += nwarps) {
-    const int r = unit / split;
-    const int c = unit - r * split;
-    const int u = u_begin + r;
-    const int o = u / topk;
-    const int k = u - o * topk;
-    const int i = o * p.dp_size + dp_rank;
-    const uint32_t e = __ldg(a.indices + static_cast<size_t>(i) * topk + k);
-    if (e >= static_cast<uint32_t>(E)) continue;
-    const int dst = e / p.nle;
-    const int le = e - dst * p.nle;
-    uint32_t pos;
-    if (precomputed) {
-      pos = sm.rowpos[r];
-      if (pos == kNoSlot) continue;
-    } else {
-      pos = 0;
-      if (lane == 0) pos = atomicAdd(&sm.base[e], 1u);
-      pos = __shfl_sync(0xffffffffu, pos, 0);
-      if (pos >= slot_limit) {
-        if (lane == 0)
-          report_failure(p.status, kSlotOverflow, kPhaseDispatchPayload, dst, slot_limit, pos,
-                         p.rank);
-        continue;
+  // Tokens whose rows this block sends, taken in chunks.  With the tokens in host memory a
+  // chunk is first fetched into shared memory (every byte crosses PCIe once, however many
+  // experts the token goes to) and sent from there; otherwise there is one chunk and the
+  // rows are read where they are.
+  const int stage_tokens = (ll && a.x_on_host) ? a.stage_tokens : 0;
+  const int row_smem = round_up<int>(p.hidden_bytes + p.scale_bytes, 16);
+  const int o_first = u_begin / topk;
+  const int o_end = rows_here > 0 ? (u_end - 1) / topk + 1 : o_first;
+  const int o_step = stage_tokens > 0 ? stage_tokens : max(1, o_end - o_first);
+  for (int o0 = o_first; o0 < o_end; o0 += o_step) {
+    const int o1 = min(o0 + o_step, o_end);
+    if (stage_tokens > 0) {
+      const int per_row = nvec + nscale;  // 16-byte vectors of payload, then single scales
+      for (int idx = tid; idx < (o1 - o0) * per_row; idx += blockDim.x) {
+        const int t = idx / per_row;
+        const int v = idx - t * per_row;
+        const int i = (o0 + t) * p.dp_size + dp_rank;
+        uint8_t* row = sm.xstage + static_cast<size_t>(t) * row_smem;
+        if (v < nvec) {
+          *reinterpret_cast<int4*>(row + (static_cast<size_t>(v) << 4)) =
+              ptx::ld_nc_v4(a.x + static_cast<int64_t>(i) * a.x_stride_row + (static_cast<size_t>(v) << 4));
+        } else {
+          const int j = v - nvec;
+          reinterpret_cast<float*>(row + p.hidden_bytes)[j] =
+              __ldg(a.x_scale + static_cast<int64_t>(i) * a.x_scale_stride_row +
+                    static_cast<int64_t>(j) * a.x_scale_stride_col);
+        }
       }
-      if (lane == 0) {
-        atomicAdd(&sm.sent[dst], 1u);
-        if (packed) atomicAdd(&sm.hist[e], 1u);
-      }
+      __syncthreads();
     }
+    const int ua = max(u_begin, o0 * topk);
+    const int ub = min(u_end, o1 * topk);
+    const int n_units = (ub - ua) * split;
+    for (int unit = warp; unit < n_units; unit += nwarps) {
+      const int r = (ua - u_begin) + unit / split;
+      const int c = unit % split;
+      const int u = u_begin + r;
+      const int o = u / topk;
+      const int k = u - o * topk;
+      const int i = o * p.dp_size + dp_rank;
+      const uint32_t e = __ldg(a.indices + static_cast<size_t>(i) * topk + k);
+      if (e >= static_cast<uint32_t>(E)) continue;
+      const int dst = e / p.nle;
+      const int le = e - dst * p.nle;
+      uint32_t pos;
+      if (precomputed) {
+        pos = sm.rowpos[r];
+        if (pos == kNoSlot) continue;
+      } else {
+        pos = 0;
+        if (lane == 0) pos = atomicAdd(&sm.base[e], 1u);
+        pos = __shfl_sync(0xffffffffu, pos, 0);
+        if (pos >= slot_limit) {
+          if (lane == 0)
+            report_failure(p.status, kSlotOverflow, kPhaseDispatchPayload, dst, slot_limit, pos,
+                           p.rank);
+          continue;
+        }
+        if (lane == 0) {
+          atomicAdd(&sm.sent[dst], 1u);
+          if (packed) atomicAdd(&sm.hist[e], 1u);
+        }
+      }
 
-    const uint8_t* src = a.x + static_cast<int64_t>(i) * a.x_stride_row;
-    if (ll) {
-      uint8_t* slot =
-          p.peer[dst] + p.off_ll_disp_stage + (region_first + pos) * p.ll_slot_bytes;
-      const int l0 = (c * p.ll_x_lines) / split;
-      const int l1 = ((c + 1) * p.ll_x_lines) / split;
-      ll::warp_send_lines(slot, src, p.hidden_bytes, l0, l1, flag, lane);
-      if (c == split - 1) {
+      const uint8_t* src = a.x + static_cast<int64_t>(i) * a.x_stride_row;
+      if (ll) {
+        uint8_t* slot =
+            p.peer[dst] + p.off_ll_disp_stage + (region_first + pos) * p.ll_slot_bytes;
+        const int l0 = (c * p.ll_x_lines) / split;
+        const int l1 = ((c + 1) * p.ll_x_lines) / split;
         const uint32_t trailer[4] = {static_cast<uint32_t>(i), static_cast<uint32_t>(k),
                                      static_cast<uint32_t>(le), static_cast<uint32_t>(p.rank)};
-        const float* ssrc =
-            nscale > 0 ? a.x_scale + static_cast<int64_t>(i) * a.x_scale_stride_row : nullptr;
-        ll::warp_send_meta(slot + p.ll_x_lines * ll::kLineBytes, p.ll_meta_lines, trailer, ssrc,
-                           a.x_scale_stride_col, nscale, flag, lane);
+        uint8_t* meta = slot + p.ll_x_lines * ll::kLineBytes;
+        if (stage_tokens > 0) {
+          const uint8_t* row = sm.xstage + static_cast<size_t>(o - o0) * row_smem;
+          ll::warp_send_lines<ll::Src::kShared>(slot, row, p.hidden_bytes, l0, l1, flag, lane);
+          if (c == split - 1)
+            ll::warp_send_meta<ll::Src::kShared>(
+                meta, p.ll_meta_lines, trailer, reinterpret_cast<const float*>(row + p.hidden_bytes),
+                1, nscale, flag, lane);
+        } else {
+          ll::warp_send_lines(slot, src, p.hidden_bytes, l0, l1, flag, lane);
+          if (c == split - 1) {
+            const float* ssrc =
+                nscale > 0 ? a.x_scale + static_cast<int64_t>(i) * a.x_scale_stride_row : nullptr;
+            ll::warp_send_meta(meta, p.ll_meta_lines, trailer, ssrc, a.x_scale_stride_col, nscale,
+                               flag, lane);
+          }
+        }
+        continue;
       }
-      continue;
-    }
-    uint8_t* slot = p.peer[dst] + p.off_disp_stage + (region_first + pos) * p.slot_bytes;
-    if (a.quantize) {
-      // Parts are cut at multiples of 32 output vectors (512 columns).
-      const int groups = ceil_div<int>(nvec, 32);
-      const int v0 = ((c * groups) / split) * 32;
-      const int v1 = min((((c + 1) * groups) / split) * 32, nvec);
-      warp_quantize_row(slot, reinterpret_cast<float*>(slot + p.hidden_bytes),
-                        reinterpret_cast<const __nv_bfloat16*>(src), v0, v1, nvec, lane);
-    } else {
-      const int v0 = (c * nvec) / split;
-      const int v1 = ((c + 1) * nvec) / split;
-      ptx::warp_copy_v4<ptx::LoadKind::kNonCoherent>(slot + (static_cast<size_t>(v0) << 4),
-                                                     src + (static_cast<size_t>(v0) << 4),
-                                                     v1 - v0, lane);
-    }
-    if (c == split - 1) {
-      if (nscale > 0 && !a.quantize) {
-        float* sdst = reinterpret_cast<float*>(slot + p.hidden_bytes);
-        const float* ssrc = a.x_scale + static_cast<int64_t>(i) * a.x_scale_stride_row;
-        for (int j = lane; j < nscale; j += 32) sdst[j] = __ldg(ssrc + j * a.x_scale_stride_col);
+      uint8_t* slot = p.peer[dst] + p.off_disp_stage + (region_first + pos) * p.slot_bytes;
+      if (a.quantize) {
+        // Parts are cut at multiples of 32 output vectors (512 columns).
+        const int groups = ceil_div<int>(nvec, 32);
+        const int v0 = ((c * groups) / split) * 32;
+        const int v1 = min((((c + 1) * groups) / split) * 32, nvec);
+        warp_quantize_row(slot, reinterpret_cast<float*>(slot + p.hidden_bytes),
+                          reinterpret_cast<const __nv_bfloat16*>(src), v0, v1, nvec, lane);
+      } else {
+        const int v0 = (c * nvec) / split;
+        const int v1 = ((c + 1) * nvec) / split;
+        ptx::warp_copy_v4<ptx::LoadKind::kNonCoherent>(slot + (static_cast<size_t>(v0) << 4),
+                                                       src + (static_cast<size_t>(v0) << 4),
+                                                       v1 - v0, lane);
       }
-      if (lane == 0) {
-        int4 t;
-        t.x = i;
-        t.y = k;
-        t.z = le;
-        t.w = p.rank;
-        ptx::st_v4(slot + p.trailer_off, t);
+      if (c == split - 1) {
+        if (nscale > 0 && !a.quantize) {
+          float* sdst = reinterpret_cast<float*>(slot + p.hidden_bytes);
+          const float* ssrc = a.x_scale + static_cast<int64_t>(i) * a.x_scale_stride_row;
+          for (int j = lane; j < nscale; j += 32) sdst[j] = __ldg(ssrc + j * a.x_scale_stride_col);
+        }
+        if (lane == 0) {
+          int4 t;
+          t.x = i;
+          t.y = k;
+          t.z = le;
+          t.w = p.rank;
+          ptx::st_v4(slot + p.trailer_off, t);
+        }
       }
     }
+    if (stage_tokens > 0) __syncthreads();  // the next chunk overwrites the staged rows
   }
   trace(p, kTrDispatchStored);
+  // (Also in flag-in-data mode, where nothing is signalled: warps that ran ahead into the
+  // receive phase would poll for counts next to warps that are still storing, and measurably
+  // slow them down.)
   __syncthreads();
   if (ll) {
     // Nothing to signal: every line carries its own flag.
@@ -647,9 +702,17 @@ __global__ void __launch_bounds__(kDispatchThreads, 1)
 
 }  // namespace
 
-size_t dispatch_smem_bytes(const A2AParams& p) {
+size_t dispatch_smem_bytes(const A2AParams& p, int stage_tokens) {
   const size_t E = p.num_experts, P = static_cast<size_t>(p.world) * p.nle;
-  return sizeof(uint32_t) * (4 * E + (P + 1) + P + kMaxWorld + kRowCap);
+  const size_t words = 4 * E + (P + 1) + P + kMaxWorld + kRowCap;
+  const size_t row = round_up<size_t>(static_cast<size_t>(p.hidden_bytes) + p.scale_bytes, 16);
+  return round_up<size_t>(sizeof(uint32_t) * words, 16) + static_cast<size_t>(stage_tokens) * row;
+}
+
+int dispatch_stage_tokens(const A2AParams& p) {
+  // Rows fetched from host memory per round: as many as fit into 64 KiB, at most 8.
+  const size_t row = round_up<size_t>(static_cast<size_t>(p.hidden_bytes) + p.scale_bytes, 16);
+  return static_cast<int>(std::min<size_t>(8, (64 * 1024) / row));
 }
 
 int dispatch_threads() { return kDispatchThreads; }
@@ -668,7 +731,7 @@ cudaError_t allow_smem(Kernel kernel, size_t smem) {
 
 cudaError_t launch_dispatch(const DispatchArgs& a, bool send, bool recv, int grid,
                             cudaStream_t stream) {
-  const size_t smem = dispatch_smem_bytes(a.p);
+  const size_t smem = dispatch_smem_bytes(a.p, a.stage_tokens);
   cudaError_t err = cudaSuccess;
   if (send && recv) {
     if ((err = allow_smem(dispatch_kernel<true, true>, smem)) != cudaSuccess) return err;
@@ -686,7 +749,9 @@ cudaError_t launch_dispatch(const DispatchArgs& a, bool send, bool recv, int gri
 cudaError_t launch_dispatch_multi(const DispatchMulti& args, int nranks, bool send, bool recv,
                                   int grid, cudaStream_t stream) {
   if (nranks < 1 || nranks > kMaxLocalRanks) return cudaErrorInvalidValue;
-  const size_t smem = dispatch_smem_bytes(args.r[0].p);
+  int stage_tokens = 0;
+  for (int r = 0; r < nranks; ++r) stage_tokens = std::max(stage_tokens, args.r[r].stage_tokens);
+  const size_t smem = dispatch_smem_bytes(args.r[0].p, stage_tokens);
   void* params[] = {const_cast<DispatchMulti*>(&args)};
   const dim3 g(grid, nranks);
   const void* fn = nullptr;

@@ -370,6 +370,7 @@ DispatchArgs AllToAll::make_dispatch_args(const DispatchCall& c) const {
   a.num_tokens = c.num_tokens;
   a.quantize = c.quantize ? 1 : 0;
   a.x_on_host = c.x_on_host ? 1 : 0;
+  a.stage_tokens = (c.x_on_host && params_.ll != 0 && !c.quantize) ? dispatch_stage_tokens(p) : 0;
   return a;
 }
 

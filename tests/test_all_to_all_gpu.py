@@ -420,10 +420,10 @@ def test_dispatch_reads_its_inputs_from_pinned_host_memory():
     h_scale = buf.x_scale.cpu().pin_memory()
     h_idx = buf.indices.cpu().pin_memory()
     h_w = buf.weights.cpu().pin_memory()
-    for _ in range(2):
+    for idx in (h_idx, buf.indices):  # the routing table may stay on the device
         buf.counts.fill_(-1)
         buf.expert_x.view(torch.uint8).zero_()
-        ata.dispatch(buf.counts, buf.expert_x, buf.expert_scale, h_x, h_scale, h_idx, buf.bound_m)
+        ata.dispatch(buf.counts, buf.expert_x, buf.expert_scale, h_x, h_scale, idx, buf.bound_m)
         torch.cuda.synchronize()
         ata.check_status()
         verify_dispatch(cfg, inputs, 1, 0, buf)
@@ -435,11 +435,30 @@ def test_dispatch_reads_its_inputs_from_pinned_host_memory():
         verify_combine(cfg, inputs, 0, buf)
     # memory kinds must not be mixed, and pageable memory is refused
     with pytest.raises(RuntimeError, match="same kind of memory"):
-        ata.dispatch(buf.counts, buf.expert_x, buf.expert_scale, h_x, h_scale, buf.indices,
+        ata.dispatch(buf.counts, buf.expert_x, buf.expert_scale, h_x, buf.x_scale, h_idx,
                      buf.bound_m)
     with pytest.raises(RuntimeError, match="pinned host"):
         ata.dispatch(buf.counts, buf.expert_x, buf.expert_scale, buf.x.cpu(), h_scale, h_idx,
                      buf.bound_m)
+    ata.destroy()
+
+
+def test_host_inputs_with_more_tokens_than_fit_one_staging_round():
+    """Blocks that own many tokens fetch them from host memory in several rounds."""
+    cfg = MoEConfig(num_experts=8, experts_per_token=2, hidden_dim=4096, max_num_tokens=300,
+                    in_dtype=torch.float8_e4m3fn)
+    ata, inputs, buf = _single_rank(cfg, seed=75)
+    ata.set_max_blocks(3)
+    h_x = buf.x.cpu().pin_memory()
+    h_scale = buf.x_scale.cpu().pin_memory()
+    ata.dispatch(buf.counts, buf.expert_x, buf.expert_scale, h_x, h_scale, buf.indices, buf.bound_m)
+    torch.cuda.synchronize()
+    ata.check_status()
+    verify_dispatch(cfg, inputs, 1, 0, buf)
+    buf.make_expert_y()
+    _combine(ata, buf)
+    torch.cuda.synchronize()
+    verify_combine(cfg, inputs, 0, buf)
     ata.destroy()
 
 
