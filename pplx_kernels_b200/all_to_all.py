@@ -203,15 +203,34 @@ class AllToAll:
         _ops.all_to_all_set_combine_units(self._ptr, int(units))
 
     def fused_dispatch(self, dp_x: torch.Tensor, indices: torch.Tensor,
-                       bound_m: torch.Tensor | None = None) -> None:
-        """Send half of the fused MoE dispatch (bf16 tokens, no scales).
+                       bound_m: torch.Tensor | None = None, quantize: bool = False) -> None:
+        """Send half of the fused MoE dispatch (bf16 tokens).
 
         Two-hop protocol: ranks first exchange their per-expert histograms, then store
         every row at its final, expert-major position in the destination's staging, so
         that ``fused_up`` can read dense 128-row tiles by TMA.  Follow it with
         ``fused_up``, ``fused_down`` and ``combine(..., do_send=False)``.
+
+        With ``quantize`` (object created with ``hidden_dim_bytes = hidden`` and
+        ``hidden_dim_scale_bytes = ceil(hidden / 128) * 4``) the rows travel as e4m3 with one
+        fp32 scale per 128 columns, converted while they are sent; follow it with
+        ``fused_up_fp8`` and ``fused_down_fp8``.
         """
-        _ops.moe_dispatch_send(self._ptr, dp_x, indices, bound_m)
+        _ops.moe_dispatch_send(self._ptr, dp_x, indices, bound_m, quantize)
+
+    def fused_up_fp8(self, w13: torch.Tensor, w13_scale: torch.Tensor, h: torch.Tensor,
+                     h_scale: torch.Tensor, out_expert_num_tokens: torch.Tensor | None = None,
+                     status: torch.Tensor | None = None) -> None:
+        """Block-scaled fp8 SwiGLU up projection that reads rows and their scales out of the
+        dispatch staging arena as peers fill it; writes the re-quantised intermediate
+        (``h`` e4m3, ``h_scale`` one fp32 per row and 128 columns)."""
+        _ops.moe_fused_up_fp8(self._ptr, w13, w13_scale, h, h_scale, out_expert_num_tokens, status)
+
+    def fused_down_fp8(self, h: torch.Tensor, h_scale: torch.Tensor, w2: torch.Tensor,
+                       w2_scale: torch.Tensor, status: torch.Tensor | None = None) -> None:
+        """Block-scaled fp8 down projection whose epilogue stores each bf16 row to its token's
+        home rank(s); call before ``combine(..., do_send=False, do_recv=True)``."""
+        _ops.moe_fused_down_fp8(self._ptr, h, h_scale, w2, w2_scale, status)
 
     def fused_up(self, w13: torch.Tensor, h: torch.Tensor,
                  out_expert_num_tokens: torch.Tensor | None = None,
@@ -432,9 +451,11 @@ def fused_dispatch_group(
     dp_x: Sequence[torch.Tensor],
     indices: Sequence[torch.Tensor],
     bound_m: Sequence[torch.Tensor | None],
+    quantize: bool = False,
 ) -> None:
     """``fused_dispatch`` of every rank of a local world, as a single cooperative launch."""
     dev = dp_x[0].device
     _ops.moe_dispatch_send_group(
-        [r._ptr for r in ranks], list(dp_x), list(indices), [_or_empty(t, dev) for t in bound_m]
+        [r._ptr for r in ranks], list(dp_x), list(indices), [_or_empty(t, dev) for t in bound_m],
+        quantize,
     )

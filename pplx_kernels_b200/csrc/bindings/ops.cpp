@@ -509,7 +509,7 @@ void check_bf16_3d(const at::Tensor& t, const char* name) {
 
 DispatchCall make_packed_call(const AllToAll& ata, const at::Tensor& dp_x,
                               const at::Tensor& indices,
-                              const std::optional<at::Tensor>& bound_m) {
+                              const std::optional<at::Tensor>& bound_m, bool quantize = false) {
   const A2AParams& p = ata.params();
   TORCH_CHECK(dp_x.is_cuda() && dp_x.dim() == 2 && dp_x.is_contiguous() &&
                   dp_x.scalar_type() == at::kBFloat16 && dp_x.size(1) == p.hidden_dim,
@@ -528,25 +528,28 @@ DispatchCall make_packed_call(const AllToAll& ata, const at::Tensor& dp_x,
     c.bound_m = static_cast<const uint32_t*>(bound_m->data_ptr());
   }
   c.num_tokens = static_cast<int>(indices.size(0));
+  c.quantize = quantize;
   return c;
 }
 
 // Send half of the fused MoE dispatch: rows land in the peers' staging grouped by expert.
+// With `quantize` the bf16 tokens travel as e4m3 + one fp32 scale per 128 columns.
 void moe_dispatch_send_op(int64_t ptr, const at::Tensor& dp_x, const at::Tensor& indices,
-                          const std::optional<at::Tensor>& bound_m) {
+                          const std::optional<at::Tensor>& bound_m, bool quantize) {
   AllToAll* ata = lookup(ptr);
   const c10::cuda::OptionalCUDAGuard guard(dp_x.device());
   guarded([&] {
-    ata->dispatch_send_packed(make_packed_call(*ata, dp_x, indices, bound_m),
+    ata->dispatch_send_packed(make_packed_call(*ata, dp_x, indices, bound_m, quantize),
                               at::cuda::getCurrentCUDAStream());
   });
 }
 
 void fake_moe_dispatch_send(int64_t, const at::Tensor&, const at::Tensor&,
-                            const std::optional<at::Tensor>&) {}
+                            const std::optional<at::Tensor>&, bool) {}
 
 void moe_dispatch_send_group_op(std::vector<int64_t> ptrs, std::vector<at::Tensor> dp_x,
-                                std::vector<at::Tensor> indices, std::vector<at::Tensor> bound_m) {
+                                std::vector<at::Tensor> indices, std::vector<at::Tensor> bound_m,
+                                bool quantize) {
   const size_t n = ptrs.size();
   TORCH_CHECK(n > 0 && dp_x.size() == n && indices.size() == n && bound_m.size() == n,
               "moe_dispatch_send_group: list lengths differ");
@@ -555,7 +558,7 @@ void moe_dispatch_send_group_op(std::vector<int64_t> ptrs, std::vector<at::Tenso
     std::vector<DispatchCall> calls;
     for (size_t r = 0; r < n; ++r) {
       ranks.push_back(lookup(ptrs[r]));
-      calls.push_back(make_packed_call(*ranks[r], dp_x[r], indices[r], opt(bound_m[r])));
+      calls.push_back(make_packed_call(*ranks[r], dp_x[r], indices[r], opt(bound_m[r]), quantize));
     }
     const c10::cuda::OptionalCUDAGuard guard(dp_x[0].device());
     AllToAll::dispatch_send_packed_group(ranks, calls, at::cuda::getCurrentCUDAStream());
@@ -618,6 +621,87 @@ void moe_fused_down_op(int64_t ptr, const at::Tensor& h, const at::Tensor& w2,
   const c10::cuda::OptionalCUDAGuard guard(h.device());
   guarded([&] { ata->fused_down(f, at::cuda::getCurrentCUDAStream()); });
 }
+
+void check_fp8_3d(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.dim() == 3 && t.element_size() == 1 && t.stride(2) == 1, name,
+              " must be a 3-D one-byte (e4m3) CUDA tensor with a contiguous last dimension");
+}
+
+void check_scale_3d(const at::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.dim() == 3 && t.scalar_type() == at::kFloat && t.stride(2) == 1,
+              name, " must be a 3-D float32 CUDA tensor with a contiguous last dimension");
+}
+
+FusedFfnFp8Call make_fp8_ffn_call(const AllToAll& ata, const at::Tensor& w, const at::Tensor& sw,
+                                  const at::Tensor& h, const at::Tensor& h_scale, bool up,
+                                  const std::optional<at::Tensor>& status) {
+  const A2AParams& p = ata.params();
+  check_fp8_3d(w, "w");
+  check_fp8_3d(h, "h");
+  check_scale_3d(sw, "w_scale");
+  check_scale_3d(h_scale, "h_scale");
+  const int64_t inter = h.size(2);
+  const int64_t w_rows = up ? 2 * inter : p.hidden_dim;
+  const int64_t k = up ? p.hidden_dim : inter;
+  TORCH_CHECK(w.size(0) == p.nle && w.size(1) == w_rows && w.size(2) == k,
+              "w must be [num_local_experts, ", up ? "2 * intermediate, hidden]" : "hidden, intermediate]");
+  TORCH_CHECK(sw.size(0) == p.nle && sw.size(1) == (w_rows + 127) / 128 && sw.size(2) == (k + 127) / 128,
+              "w_scale must hold one value per 128 x 128 block of w");
+  TORCH_CHECK(h.size(0) == p.nle && h.size(1) >= p.cap && inter % 128 == 0,
+              "h must be [num_local_experts, rows, intermediate] with intermediate % 128 == 0");
+  TORCH_CHECK(h_scale.size(0) == p.nle && h_scale.size(1) == h.size(1) && h_scale.size(2) == inter / 128,
+              "h_scale must be [num_local_experts, rows, intermediate / 128]");
+  FusedFfnFp8Call f;
+  f.w = w.data_ptr();
+  f.w_stride_e = w.stride(0);
+  f.w_stride_row = w.stride(1);
+  f.sw = sw.data_ptr<float>();
+  f.sw_stride_e = sw.stride(0);
+  f.sw_stride_row = sw.stride(1);
+  f.h = h.data_ptr();
+  f.h_stride_e = h.stride(0);
+  f.h_stride_row = h.stride(1);
+  f.h_scale = h_scale.data_ptr<float>();
+  f.hs_stride_e = h_scale.stride(0);
+  f.hs_stride_row = h_scale.stride(1);
+  f.rows_per_expert = static_cast<int>(h.size(1));
+  f.inter_dim = static_cast<int>(inter);
+  f.status = status_word(status);
+  return f;
+}
+
+// fp8 SwiGLU up projection fed from the staging arena (after moe_dispatch_send with quantize).
+void moe_fused_up_fp8_op(int64_t ptr, const at::Tensor& w13, const at::Tensor& w13_scale,
+                         at::Tensor& h, at::Tensor& h_scale,
+                         const std::optional<at::Tensor>& out_expert_num_tokens,
+                         const std::optional<at::Tensor>& status) {
+  AllToAll* ata = lookup(ptr);
+  FusedFfnFp8Call f = make_fp8_ffn_call(*ata, w13, w13_scale, h, h_scale, true, status);
+  if (out_expert_num_tokens.has_value()) {
+    TORCH_CHECK(out_expert_num_tokens->is_cuda() && out_expert_num_tokens->scalar_type() == at::kInt &&
+                    out_expert_num_tokens->numel() == ata->params().nle &&
+                    out_expert_num_tokens->is_contiguous(),
+                "out_expert_num_tokens must be a contiguous int32 CUDA tensor of [num_local_experts]");
+    f.out_num_tokens = out_expert_num_tokens->data_ptr<int32_t>();
+  }
+  const c10::cuda::OptionalCUDAGuard guard(h.device());
+  guarded([&] { ata->fused_up_fp8(f, at::cuda::getCurrentCUDAStream()); });
+}
+
+// fp8 down projection whose epilogue stores the bf16 rows to the tokens' home ranks.
+void moe_fused_down_fp8_op(int64_t ptr, const at::Tensor& h, const at::Tensor& h_scale,
+                           const at::Tensor& w2, const at::Tensor& w2_scale,
+                           const std::optional<at::Tensor>& status) {
+  AllToAll* ata = lookup(ptr);
+  const FusedFfnFp8Call f = make_fp8_ffn_call(*ata, w2, w2_scale, h, h_scale, false, status);
+  const c10::cuda::OptionalCUDAGuard guard(h.device());
+  guarded([&] { ata->fused_down_fp8(f, at::cuda::getCurrentCUDAStream()); });
+}
+
+void fake_moe_fused_up_fp8(int64_t, const at::Tensor&, const at::Tensor&, at::Tensor&, at::Tensor&,
+                           const std::optional<at::Tensor>&, const std::optional<at::Tensor>&) {}
+void fake_moe_fused_down_fp8(int64_t, const at::Tensor&, const at::Tensor&, const at::Tensor&,
+                             const at::Tensor&, const std::optional<at::Tensor>&) {}
 
 void fake_moe_fused_up(int64_t, const at::Tensor&, at::Tensor&, const std::optional<at::Tensor>&,
                        const std::optional<at::Tensor>&, int64_t) {}
@@ -821,12 +905,21 @@ void register_all_to_all_ops(torch::Library& m) {
   m.def("all_to_all_layout(int ptr) -> int[]", &layout_op);
   m.def("all_to_all_set_trace(int ptr, bool on) -> ()", &set_trace_op);
   m.def("all_to_all_set_combine_units(int ptr, int units) -> ()", &set_combine_units_op);
-  m.def("moe_dispatch_send(int ptr, Tensor dp_x, Tensor indices, Tensor? bound_m) -> ()");
+  m.def("moe_dispatch_send(int ptr, Tensor dp_x, Tensor indices, Tensor? bound_m, "
+        "bool quantize=False) -> ()");
   m.impl("moe_dispatch_send", c10::kCUDA, &moe_dispatch_send_op);
   m.impl("moe_dispatch_send", c10::kMeta, &fake_moe_dispatch_send);
   m.def("moe_dispatch_send_group(int[] ptrs, Tensor[] dp_x, Tensor[] indices, "
-        "Tensor[] bound_m) -> ()",
+        "Tensor[] bound_m, bool quantize=False) -> ()",
         &moe_dispatch_send_group_op);
+  m.def("moe_fused_up_fp8(int ptr, Tensor w13, Tensor w13_scale, Tensor! h, Tensor! h_scale, "
+        "Tensor!? out_expert_num_tokens, Tensor!? status) -> ()");
+  m.impl("moe_fused_up_fp8", c10::kCUDA, &moe_fused_up_fp8_op);
+  m.impl("moe_fused_up_fp8", c10::kMeta, &fake_moe_fused_up_fp8);
+  m.def("moe_fused_down_fp8(int ptr, Tensor h, Tensor h_scale, Tensor w2, Tensor w2_scale, "
+        "Tensor!? status) -> ()");
+  m.impl("moe_fused_down_fp8", c10::kCUDA, &moe_fused_down_fp8_op);
+  m.impl("moe_fused_down_fp8", c10::kMeta, &fake_moe_fused_down_fp8);
   m.def("moe_fused_up(int ptr, Tensor w13, Tensor! h, Tensor!? out_expert_num_tokens, "
         "Tensor!? status, int expected_rows=0) -> ()");
   m.impl("moe_fused_up", c10::kCUDA, &moe_fused_up_op);

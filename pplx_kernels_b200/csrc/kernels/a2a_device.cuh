@@ -11,8 +11,8 @@ __device__ __forceinline__ void reset_packed_flags(const A2AParams& p, int parit
                   static_cast<size_t>(parity) * p.world * p.num_experts;
   for (int i = threadIdx.x; i < p.world * p.num_experts; i += blockDim.x) all[i] = 0;
   uint32_t* arrived_e = reinterpret_cast<uint32_t*>(p.peer[p.rank] + p.off_arrived_e) +
-                        parity * p.nle;
-  for (int i = threadIdx.x; i < p.nle; i += blockDim.x) arrived_e[i] = 0;
+                        static_cast<size_t>(parity) * p.nle * p.world;
+  for (int i = threadIdx.x; i < p.nle * p.world; i += blockDim.x) arrived_e[i] = 0;
 }
 
 }  // namespace pplx

@@ -24,6 +24,8 @@
 //    staging, grouped by local expert and then by source.  It costs one more
 //    flag round trip before the payload moves, and gives the expert GEMM dense
 //    128-row tiles that it can read with TMA without any receive-side copy.
+//    Arrival is counted per (local expert, source), so the GEMM can start a tile
+//    as soon as the sources whose rows it covers have landed.
 //  * Resets ride on the strict dispatch/combine alternation: a combine clears the
 //    flag set of the dispatch before it and bumps the iteration counter.  The
 //    combine's per-token arrival counters are never cleared: every combine adds
@@ -74,7 +76,8 @@ struct A2AParams {
   size_t off_comb_arrived;  // u32 [max_tokens]      running total, 16 units per expert output
   size_t off_counts_all;    // u32 [2][world][num_experts]  packed mode: every source's full
                             //                       histogram, value = count + 1
-  size_t off_arrived_e;     // u32 [2][nle]          packed mode: rows landed per local expert
+  size_t off_arrived_e;     // u32 [2][nle][world]   packed mode: rows landed per local expert
+                            //                       and source rank
   size_t off_disp_stage;    // u8  [world][region_slots][slot_bytes]; in packed mode the same
                             //     memory is one array of world * region_slots slots with
                             //     rows grouped by local expert, then by source rank

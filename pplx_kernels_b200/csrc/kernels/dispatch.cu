@@ -31,7 +31,7 @@
 // histogram to every peer, every block then waits for all peers' histograms and
 // places each row at its final position in the destination's staging -- grouped
 // by local expert, then by source rank -- and step 4 signals per (destination,
-// expert) instead of per destination.
+// expert, source) instead of per destination.
 //
 // Quantising send (a.quantize): the caller's tokens are bf16 and the wire format
 // is fp8 e4m3 with one fp32 scale per 128 columns.  The warp that copies a row
@@ -502,8 +502,9 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
         if (n == 0) continue;
         const int dst = e / p.nle;
         const int le = e - dst * p.nle;
-        ptx::red_add_relaxed_sys(
-            reinterpret_cast<uint32_t*>(p.peer[dst] + p.off_arrived_e) + parity * p.nle + le, n);
+        ptx::red_add_relaxed_sys(reinterpret_cast<uint32_t*>(p.peer[dst] + p.off_arrived_e) +
+                                     (static_cast<size_t>(parity) * p.nle + le) * p.world + p.rank,
+                                 n);
       }
     }
   }

@@ -28,6 +28,8 @@ struct GroupedGemmArgs {
                                // in columns); 0 = not available.  Chosen on the device.
   // Only read by the kernels fused with the all-to-all:
   int32_t* out_num_tokens;          // optional [nle]: per-expert totals for the caller
+  int src_table;                    // staging-fed form: keep rows per (expert, source) in
+                                    // shared memory (set by the launcher when it fits)
   A2AParams a2a;
 };
 
@@ -103,5 +105,15 @@ struct Fp8GemmCall {
 };
 
 void launch_grouped_gemm_fp8(const Fp8GemmCall& call, cudaStream_t stream);
+
+// The fp8 forms of the two expert GEMMs of the fused MoE layer (see the bf16 functions
+// above for the protocol).  from_staging: A and its scales are read from the dispatch
+// staging arena after a packed, quantising send (call.x / sa / counts are ignored); the
+// result is the SwiGLU-ed, re-quantised intermediate.  to_peers: the bf16 rows of the down
+// projection are stored to the tokens' home ranks (call.out is ignored, call.counts must be
+// p.recv_count).
+void launch_gemm_fp8_from_staging(const Fp8GemmCall& call, const A2AParams& p,
+                                  int32_t* out_num_tokens, cudaStream_t stream);
+void launch_gemm_fp8_to_peers(const Fp8GemmCall& call, const A2AParams& p, cudaStream_t stream);
 
 }  // namespace pplx

@@ -37,6 +37,8 @@
 #include "../core/ptx.cuh"
 #include "../core/tcgen05.cuh"
 #include "../core/utils.h"
+#include "../core/wait.cuh"
+#include "a2a_device.cuh"
 #include "grouped_gemm.h"
 
 namespace pplx {
@@ -63,7 +65,11 @@ struct SharedControl {
   uint32_t tmem_base;
   uint32_t abort_flag;
   float row_amax[2][kBlockM];  // SwiGLU epilogue: per-row maxima of the two column halves
+  uint32_t sig_token[kBlockM];  // peer-storing epilogue: token of each tile row
+  uint32_t sig_group[kBlockM];  //                        first rank of the token's DP group
 };
+
+constexpr uint32_t kNoSignalFp8 = 0xffffffffu;
 
 __device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
 
@@ -82,11 +88,11 @@ struct Fp8Tile {
   int expert, m_blk, n_blk, rows;
 };
 
-__device__ __forceinline__ Fp8Tile locate(const uint32_t* tile_start, const int32_t* counts,
-                                          int num_experts, int capacity, uint32_t t) {
+__device__ __forceinline__ Fp8Tile locate(const uint32_t* tile_start, const uint32_t* rows_of,
+                                          int num_experts, uint32_t t) {
   Fp8Tile c;
   c.expert = find_group(tile_start, num_experts, t);
-  c.rows = min(max(counts[c.expert], 0), capacity);
+  c.rows = static_cast<int>(rows_of[c.expert]);
   const int m_tiles = ceil_div<int>(c.rows, kBlockM);
   const uint32_t rem = t - tile_start[c.expert];
   c.n_blk = static_cast<int>(rem / m_tiles);
@@ -143,20 +149,29 @@ CUtensorMap make_byte_map(const void* base, int64_t experts, int64_t rows, int64
 
 }  // namespace
 
-void launch_grouped_gemm_fp8(const Fp8GemmCall& c, cudaStream_t stream) {
+namespace {
+
+constexpr size_t kMaxSrcEntriesFp8 = 2048;
+
+size_t fp8_smem_bytes(size_t experts, size_t src_entries) {
+  return 1024 + kStages * kStageBytes + sizeof(SharedControl) +
+         sizeof(uint32_t) * (3 * experts + 1 + src_entries);
+}
+
+void check_fp8_call(const Fp8GemmCall& c, bool need_x, bool need_out) {
   PPLX_CHECK(c.num_experts > 0 && c.num_experts <= kMaxExperts, "num_experts out of range");
   PPLX_CHECK(c.k > 0 && c.k % 16 == 0, "K must be a positive multiple of 16");
   PPLX_CHECK(c.n_out > 0 && c.n_out % 16 == 0, "the output width must be a multiple of 16");
   PPLX_CHECK(!c.swiglu_quant || c.n_out % 128 == 0,
              "the SwiGLU + quantise epilogue needs an intermediate size that is a multiple of 128");
-  PPLX_CHECK(c.x && c.w && c.sa && c.sw && c.out && c.counts, "missing tensor");
+  PPLX_CHECK(c.w && c.sw, "missing weight tensor");
+  PPLX_CHECK(!need_x || (c.x && c.sa && c.counts), "missing activation tensor");
+  PPLX_CHECK(!need_out || c.out, "missing output tensor");
   PPLX_CHECK(!c.swiglu_quant || c.out_scale != nullptr, "out_scale is required");
   PPLX_CHECK(reinterpret_cast<uintptr_t>(c.out) % 16 == 0, "the output must be 16-byte aligned");
-  const int64_t w_rows = c.swiglu_quant ? 2 * static_cast<int64_t>(c.n_out) : c.n_out;
-  const CUtensorMap tmap_a =
-      make_byte_map(c.x, c.num_experts, c.rows_per_expert, c.k, c.x_stride_row, c.x_stride_e);
-  const CUtensorMap tmap_b =
-      make_byte_map(c.w, c.num_experts, w_rows, c.k, c.w_stride_row, c.w_stride_e);
+}
+
+Fp8GemmArgs fp8_args(const Fp8GemmCall& c) {
   Fp8GemmArgs g{};
   g.counts = c.counts;
   g.sa = c.sa;
@@ -176,23 +191,80 @@ void launch_grouped_gemm_fp8(const Fp8GemmCall& c, cudaStream_t stream) {
   g.rows_per_expert = c.rows_per_expert;
   g.n_out = c.n_out;
   g.k = c.k;
-  const size_t smem = 1024 + kStages * kStageBytes + sizeof(SharedControl) +
-                      sizeof(uint32_t) * (static_cast<size_t>(c.num_experts) + 1);
-  const size_t smem_max = 1024 + kStages * kStageBytes + sizeof(SharedControl) +
-                          sizeof(uint32_t) * (kMaxExperts + 1);
-  const int grid = c.num_sms > 0 ? c.num_sms : get_sm_count();
-  if (c.swiglu_quant) {
-    CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_fp8_kernel<true>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(smem_max)));
-    grouped_gemm_fp8_kernel<true><<<grid, kThreads, smem, stream>>>(tmap_a, tmap_b, g);
-  } else {
-    CUDA_CHECK(cudaFuncSetAttribute(grouped_gemm_fp8_kernel<false>,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(smem_max)));
-    grouped_gemm_fp8_kernel<false><<<grid, kThreads, smem, stream>>>(tmap_a, tmap_b, g);
-  }
+  return g;
+}
+
+template <bool kSwiGLUQuant, bool kFromStaging, bool kToPeers>
+void launch_fp8(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const Fp8GemmArgs& g,
+                int num_sms, cudaStream_t stream) {
+  auto* kernel = grouped_gemm_fp8_kernel<kSwiGLUQuant, kFromStaging, kToPeers>;
+  const size_t src_entries =
+      (kFromStaging && g.src_table != 0) ? static_cast<size_t>(g.num_experts) * g.a2a.world : 0;
+  const size_t smem = fp8_smem_bytes(g.num_experts, src_entries);
+  PPLX_CHECK(smem <= 227 * 1024, "the tile tables of " << g.num_experts << " experts need "
+                                                       << smem << " bytes of shared memory");
+  CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(smem)));
+  const int grid = num_sms > 0 ? num_sms : get_sm_count();
+  kernel<<<grid, kThreads, smem, stream>>>(tmap_a, tmap_b, g);
   CUDA_CHECK(cudaGetLastError());
+}
+
+}  // namespace
+
+void launch_grouped_gemm_fp8(const Fp8GemmCall& c, cudaStream_t stream) {
+  check_fp8_call(c, true, true);
+  const int64_t w_rows = c.swiglu_quant ? 2 * static_cast<int64_t>(c.n_out) : c.n_out;
+  const CUtensorMap tmap_a =
+      make_byte_map(c.x, c.num_experts, c.rows_per_expert, c.k, c.x_stride_row, c.x_stride_e);
+  const CUtensorMap tmap_b =
+      make_byte_map(c.w, c.num_experts, w_rows, c.k, c.w_stride_row, c.w_stride_e);
+  const Fp8GemmArgs g = fp8_args(c);
+  if (c.swiglu_quant) launch_fp8<true, false, false>(tmap_a, tmap_b, g, c.num_sms, stream);
+  else launch_fp8<false, false, false>(tmap_a, tmap_b, g, c.num_sms, stream);
+}
+
+void launch_gemm_fp8_from_staging(const Fp8GemmCall& c, const A2AParams& p,
+                                  int32_t* out_num_tokens, cudaStream_t stream) {
+  check_fp8_call(c, false, true);
+  PPLX_CHECK(c.swiglu_quant, "the staging-fed fp8 GEMM is the SwiGLU up projection");
+  PPLX_CHECK(p.hidden_bytes == p.hidden_dim && p.scale_bytes == ceil_div(p.hidden_dim, 128) * 4,
+             "the staging-fed fp8 GEMM needs an object created for a 1-byte payload with one "
+             "fp32 scale per 128 columns");
+  PPLX_CHECK(c.k == p.hidden_dim && c.num_experts == p.nle && c.rows_per_expert >= p.cap,
+             "shape mismatch between the GEMM and the all-to-all");
+  // A: [1][world * region_slots][hidden] e4m3 view of this rank's packed staging.
+  const int64_t slots = static_cast<int64_t>(p.world) * p.region_slots;
+  const CUtensorMap tmap_a = make_byte_map(p.peer[p.rank] + p.off_disp_stage, 1, slots,
+                                           p.hidden_dim, p.slot_bytes, slots * p.slot_bytes);
+  const CUtensorMap tmap_b = make_byte_map(c.w, c.num_experts, 2 * static_cast<int64_t>(c.n_out),
+                                           c.k, c.w_stride_row, c.w_stride_e);
+  Fp8GemmArgs g = fp8_args(c);
+  g.out_num_tokens = out_num_tokens;
+  g.a2a = p;
+  g.src_table = static_cast<size_t>(p.nle) * p.world <= kMaxSrcEntriesFp8 ? 1 : 0;
+  launch_fp8<true, true, false>(tmap_a, tmap_b, g, c.num_sms, stream);
+}
+
+void launch_gemm_fp8_to_peers(const Fp8GemmCall& c, const A2AParams& p, cudaStream_t stream) {
+  check_fp8_call(c, true, false);
+  PPLX_CHECK(!c.swiglu_quant, "the peer-storing fp8 GEMM is the plain down projection");
+  PPLX_CHECK(c.n_out == p.hidden_dim && c.num_experts == p.nle && c.rows_per_expert >= p.cap,
+             "shape mismatch between the GEMM and the all-to-all");
+  PPLX_CHECK(c.counts == reinterpret_cast<const int32_t*>(p.recv_count),
+             "counts must be the all-to-all's received-row counts");
+  PPLX_CHECK(p.dp_size <= 8, "at most 8 replicas per DP group");
+  PPLX_CHECK(p.comb_units % ceil_div(c.n_out, kTileN) == 0,
+             "the arrival units of a row (" << p.comb_units << ") must be a multiple of the "
+             "output's 256-column blocks (" << ceil_div(c.n_out, kTileN) << ")");
+  const CUtensorMap tmap_a =
+      make_byte_map(c.x, c.num_experts, c.rows_per_expert, c.k, c.x_stride_row, c.x_stride_e);
+  const CUtensorMap tmap_b =
+      make_byte_map(c.w, c.num_experts, c.n_out, c.k, c.w_stride_row, c.w_stride_e);
+  Fp8GemmArgs g = fp8_args(c);
+  g.out = nullptr;
+  g.a2a = p;
+  launch_fp8<false, false, true>(tmap_a, tmap_b, g, c.num_sms, stream);
 }
 
 }  // namespace pplx

@@ -36,12 +36,13 @@
 //
 //   kFromStaging   the A operand is read by TMA straight out of the dispatch
 //                  staging arena that PEERS fill with P2P stores (packed send:
-//                  rows grouped by local expert, dense).  The producer warp waits
-//                  on the expert's arrival counter (ld.acquire.sys, then
-//                  fence.proxy.async) before the expert's first tile, so the
-//                  expert GEMM starts expert by expert as tokens land and the
-//                  receive-side copy of dispatch disappears.  The epilogue also
-//                  records (source, token, k) of every row for combine.
+//                  rows grouped by local expert, then by source rank, dense).
+//                  Arrival is counted per (expert, source): before a tile the
+//                  producer warp waits (ld.acquire.sys, then fence.proxy.async)
+//                  only for the sources whose rows the tile covers, so the expert
+//                  GEMM starts tile by tile as tokens land and the receive-side
+//                  copy of dispatch disappears.  The epilogue also records
+//                  (source, token, k) of every row for combine.
 //   kToPeers       the epilogue does not write a local result: every output row
 //                  is stored into the combine staging of the token's home rank(s)
 //                  over NVLink, followed once per tile by one system-scope fence
@@ -112,6 +113,9 @@ struct GroupTable {
   uint32_t* rows;        // [G] valid rows
   uint32_t* a_row0;      // [G] first row inside the A plane
   uint32_t* out_row0;    // [G] first row inside the output plane
+  uint32_t* src_rows;    // kFromStaging: [G][world] rows that each source sends to the group,
+                         // or null when the table does not fit (then a tile waits for all
+                         // sources of its expert)
 };
 
 struct TileCoord {
@@ -176,6 +180,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   gt.rows = gt.tile_start + num_groups + 1;
   gt.a_row0 = gt.rows + num_groups;
   gt.out_row0 = gt.a_row0 + num_groups;
+  gt.src_rows = (kFromStaging && g.src_table != 0) ? gt.out_row0 + num_groups : nullptr;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -204,6 +209,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                                  PredNonZero{}, v, w, kPhaseDispatchCounts, src, 1u);
       if (!ok) ctl->abort_flag = 1;
       if (ok && v > 1u) atomicAdd(&gt.rows[le], v - 1u);
+      if (gt.src_rows != nullptr) gt.src_rows[le * p.world + src] = (ok && v > 1u) ? v - 1u : 0u;
     }
     __syncthreads();
     for (int le = tid; le < num_groups; le += blockDim.x) {
@@ -317,28 +323,53 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t pending = 0;        // stages that have been filled at least once
       uint32_t pending_phase = 0;  // parity of the phase each stage was last filled in
       bool ok = *abort_flag == 0u;
-      int last_group = -1;  // expert whose rows are known to have landed
+      int last_group = -1;     // expert that `landed` refers to
+      uint32_t landed = 0;     // bit s: the rows of source s for that expert have landed
       for (uint32_t t = worker; t < total_tiles && ok; t += workers) {
         const TileCoord c = locate_tile<kFromStaging>(gt, num_groups, p, t, tile_m);
         if constexpr (kFromStaging) {
+          // The tile's rows were stored by peers.  Wait for the arrival counters of the
+          // sources it covers (rows of an expert are grouped by source rank), then order
+          // the peers' (generic-proxy) stores before the TMA (async-proxy) reads.
           if (c.group != last_group) {
-            // The expert's rows were stored by peers: wait for its arrival counter,
-            // then order the peers' (generic-proxy) stores before the TMA
-            // (async-proxy) reads that follow.
-            const WaitCtx w{p.status, p.timeout_ns, static_cast<uint32_t>(p.rank)};
-            const uint32_t* arrived =
-                reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.off_arrived_e) +
-                parity * p.nle + c.group;
-            uint32_t seen;
-            ok = wait_until(arrived, PredGe{static_cast<uint32_t>(c.rows)}, seen, w,
-                            kPhaseFusedGemm, c.group, c.rows);
-            if (!ok) {
-              *abort_flag = 1u;
-              break;
-            }
-            ptx::fence_proxy_async();
             last_group = c.group;
+            landed = 0;
           }
+          const WaitCtx w{p.status, p.timeout_ns, static_cast<uint32_t>(p.rank)};
+          const uint32_t* arrived =
+              reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.off_arrived_e) +
+              (static_cast<size_t>(parity) * p.nle + c.group) * p.world;
+          const uint32_t r0 = static_cast<uint32_t>(c.m_blk * tile_m);
+          const uint32_t r1 = min(r0 + static_cast<uint32_t>(tile_m), static_cast<uint32_t>(c.rows));
+          uint32_t first = 0;  // first row of source s inside the expert
+          bool waited = false;
+          for (int s = 0; s < p.world && ok; ++s) {
+            uint32_t n;
+            if (gt.src_rows != nullptr) {
+              n = gt.src_rows[c.group * p.world + s];
+            } else {
+              // No per-source table: counts straight from the posted histograms.
+              const uint32_t v = ptx::ld_relaxed_sys(
+                  reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.off_counts_all) +
+                  (static_cast<size_t>(parity) * p.world + s) * p.num_experts + p.rank * p.nle +
+                  c.group);
+              n = v > 1u ? v - 1u : 0u;
+            }
+            const bool overlaps = n > 0 && first < r1 && first + n > r0;
+            if (overlaps && !((landed >> s) & 1u)) {
+              uint32_t seen;
+              ok = wait_until(arrived + s, PredGe{n}, seen, w, kPhaseFusedGemm,
+                              static_cast<uint32_t>(s), n);
+              landed |= 1u << s;
+              waited = true;
+            }
+            first += n;
+          }
+          if (!ok) {
+            *abort_flag = 1u;
+            break;
+          }
+          if (waited) ptx::fence_proxy_async();
         }
         for (int kb = 0; kb < num_kb; ++kb) {
           ok = tc::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, kWaitLimitNs);
@@ -631,22 +662,31 @@ CUtensorMap make_operand_map(const void* base, int64_t experts, int64_t rows, in
   return map;
 }
 
-size_t smem_bytes(int num_groups) {
+// `src_entries`: entries of the per-source row table of the staging-fed form (0: none).
+size_t smem_bytes(int num_groups, size_t src_entries = 0) {
   static_assert(kStages * kStageBytes == kStages2 * kStageBytes2, "both rings use 192 KiB");
   return 1024 + kStages * kStageBytes + sizeof(SharedControl) +
-         sizeof(uint32_t) * (4 * static_cast<size_t>(num_groups) + 1);
+         sizeof(uint32_t) * (4 * static_cast<size_t>(num_groups) + 1 + src_entries);
 }
+
+// The per-source table is kept in shared memory when it is at most this many entries.
+constexpr size_t kMaxSrcEntries = 2048;
 
 template <bool SWIGLU, bool kFromStaging, bool kToPeers, bool kTwoCta>
 void launch_one(const CUtensorMap& tmap_a, const WeightMaps& tmap_b, const GroupedGemmArgs& g,
                 int num_groups, int grid, cudaStream_t stream) {
   auto* kernel = grouped_gemm_kernel<SWIGLU, kFromStaging, kToPeers, kTwoCta>;
+  const size_t src_entries =
+      (kFromStaging && g.src_table != 0) ? static_cast<size_t>(num_groups) * g.a2a.world : 0;
+  const size_t smem = smem_bytes(num_groups, src_entries);
+  PPLX_CHECK(smem <= 227 * 1024, "the tile tables of " << num_groups << " experts need " << smem
+                                                       << " bytes of shared memory");
   CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  static_cast<int>(smem_bytes(kMaxExperts))));
+                                  static_cast<int>(smem)));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(kTwoCta ? (grid & ~1) : grid);
   cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = smem_bytes(num_groups);
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr{};
   attr.id = cudaLaunchAttributeClusterDimension;
@@ -764,6 +804,7 @@ void launch_gemm_from_staging(const GroupedGemmCall& c, const A2AParams& p,
   const WeightMaps tmap_b = weight_maps(c, g, 0);
   g.out_num_tokens = out_num_tokens;
   g.a2a = p;
+  g.src_table = static_cast<size_t>(p.nle) * p.world <= kMaxSrcEntries ? 1 : 0;
   launch_variant<true, true, false>(tmap_a, tmap_b, g, p.nle, grid, two_cta, stream);
 }
 

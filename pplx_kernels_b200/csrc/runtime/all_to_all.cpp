@@ -123,7 +123,7 @@ A2AParams make_layout(const A2AConfig& c, std::vector<size_t>* canaries = nullpt
   p.off_arrived = region(sizeof(uint32_t) * 2 * p.world);
   p.off_comb_arrived = region(sizeof(uint32_t) * p.max_tokens);
   p.off_counts_all = region(sizeof(uint32_t) * 2 * p.world * p.num_experts);
-  p.off_arrived_e = region(sizeof(uint32_t) * 2 * p.nle);
+  p.off_arrived_e = region(sizeof(uint32_t) * 2 * p.nle * p.world);
   p.off_disp_stage = region(static_cast<size_t>(p.world) * p.region_slots * p.slot_bytes);
   p.off_comb_stage = region(static_cast<size_t>(p.max_tokens) * p.topk * p.hidden_dim * 4);
   p.off_ll_disp_stage = region(static_cast<size_t>(p.world) * p.region_slots * p.ll_slot_bytes);
@@ -424,7 +424,13 @@ DispatchArgs AllToAll::make_packed_send_args(const DispatchCall& c) const {
   const A2AParams& p = params_;
   PPLX_CHECK(c.num_tokens == 0 || (c.x.data != nullptr && c.indices != nullptr),
              "packed dispatch: missing tensor");
-  PPLX_CHECK(p.scale_bytes == 0, "packed dispatch carries no scales");
+  if (c.quantize) {
+    PPLX_CHECK(p.hidden_bytes == p.hidden_dim && p.scale_bytes == ceil_div(p.hidden_dim, 128) * 4,
+               "the quantising packed dispatch needs an object created for a 1-byte payload "
+               "with one fp32 scale per 128 columns");
+  } else {
+    PPLX_CHECK(p.scale_bytes == 0, "the packed dispatch carries scales only when it quantises");
+  }
   PPLX_CHECK(c.num_tokens >= 0 && c.num_tokens <= p.max_tokens,
              "dispatch: " << c.num_tokens << " tokens exceed max_num_tokens " << p.max_tokens);
   PPLX_CHECK(reinterpret_cast<uintptr_t>(c.x.data) % 16 == 0 && c.x.stride_row % 16 == 0,
@@ -439,6 +445,7 @@ DispatchArgs AllToAll::make_packed_send_args(const DispatchCall& c) const {
   a.bound_m = c.bound_m;
   a.num_tokens = c.num_tokens;
   a.packed = 1;
+  a.quantize = c.quantize ? 1 : 0;
   return a;
 }
 
@@ -501,6 +508,60 @@ void AllToAll::fused_up(const FusedFfnCall& f, cudaStream_t stream) {
   c.expected_total_rows = f.expected_total_rows;
   c.num_sms = max_blocks_ > 0 ? std::min(max_blocks_, num_sms_) : num_sms_;
   launch_gemm_from_staging(c, params_, f.out_num_tokens, stream);
+}
+
+void AllToAll::fused_up_fp8(const FusedFfnFp8Call& f, cudaStream_t stream) {
+  NvtxRange range("moe_fused_up_fp8");
+  begin(Step::kDispatchRecv, false);
+  Fp8GemmCall c;
+  c.w = f.w;
+  c.w_stride_e = f.w_stride_e;
+  c.w_stride_row = f.w_stride_row;
+  c.sw = f.sw;
+  c.sw_stride_e = f.sw_stride_e;
+  c.sw_stride_row = f.sw_stride_row;
+  c.out = f.h;
+  c.out_stride_e = f.h_stride_e;
+  c.out_stride_row = f.h_stride_row;
+  c.out_scale = f.h_scale;
+  c.os_stride_e = f.hs_stride_e;
+  c.os_stride_row = f.hs_stride_row;
+  c.status = f.status;
+  c.num_experts = params_.nle;
+  c.rows_per_expert = f.rows_per_expert;
+  c.n_out = f.inter_dim;
+  c.k = params_.hidden_dim;
+  c.swiglu_quant = true;
+  c.num_sms = max_blocks_ > 0 ? std::min(max_blocks_, num_sms_) : num_sms_;
+  launch_gemm_fp8_from_staging(c, params_, f.out_num_tokens, stream);
+}
+
+void AllToAll::fused_down_fp8(const FusedFfnFp8Call& f, cudaStream_t stream) {
+  NvtxRange range("moe_fused_down_fp8");
+  begin(Step::kCombineSend, false);
+  combine_send_used_lines_ = false;
+  Fp8GemmCall c;
+  c.x = f.h;
+  c.x_stride_e = f.h_stride_e;
+  c.x_stride_row = f.h_stride_row;
+  c.sa = f.h_scale;
+  c.sa_stride_e = f.hs_stride_e;
+  c.sa_stride_row = f.hs_stride_row;
+  c.w = f.w;
+  c.w_stride_e = f.w_stride_e;
+  c.w_stride_row = f.w_stride_row;
+  c.sw = f.sw;
+  c.sw_stride_e = f.sw_stride_e;
+  c.sw_stride_row = f.sw_stride_row;
+  c.counts = reinterpret_cast<const int32_t*>(params_.recv_count);
+  c.status = f.status;
+  c.num_experts = params_.nle;
+  c.rows_per_expert = f.rows_per_expert;
+  c.n_out = params_.hidden_dim;
+  c.k = f.inter_dim;
+  c.swiglu_quant = false;
+  c.num_sms = max_blocks_ > 0 ? std::min(max_blocks_, num_sms_) : num_sms_;
+  launch_gemm_fp8_to_peers(c, params_, stream);
 }
 
 void AllToAll::fused_down(const FusedFfnCall& f, cudaStream_t stream) {

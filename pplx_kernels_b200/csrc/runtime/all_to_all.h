@@ -98,6 +98,24 @@ struct FusedFfnCall {
   int64_t expected_total_rows = 0;    // hint for the tile shape choice, 0 = capacity
 };
 
+// The same for the block-scaled fp8 layer: e4m3 weights with one fp32 scale per 128 x 128
+// block, an e4m3 intermediate with one fp32 scale per row and 128 columns.  Payload strides
+// in bytes (= elements), scale strides in floats.
+struct FusedFfnFp8Call {
+  const void* w = nullptr;    // up: [nle][2 * inter][hidden]; down: [nle][hidden][inter]
+  int64_t w_stride_e = 0, w_stride_row = 0;
+  const float* sw = nullptr;  // [nle][ceil(w rows / 128)][ceil(k / 128)]
+  int64_t sw_stride_e = 0, sw_stride_row = 0;
+  void* h = nullptr;          // e4m3 [nle][rows_per_expert][inter]: written by up, read by down
+  int64_t h_stride_e = 0, h_stride_row = 0;
+  float* h_scale = nullptr;   // [nle][rows_per_expert][inter / 128]
+  int64_t hs_stride_e = 0, hs_stride_row = 0;
+  int rows_per_expert = 0;
+  int inter_dim = 0;
+  int32_t* out_num_tokens = nullptr;  // up only, optional
+  uint32_t* status = nullptr;
+};
+
 class AllToAll {
  public:
   AllToAll(const A2AConfig& cfg, std::shared_ptr<SymmetricAllocation> arena);
@@ -118,9 +136,11 @@ class AllToAll {
   void dispatch(const DispatchCall& call, SplitMode mode, cudaStream_t stream);
   void combine(const CombineCall& call, SplitMode mode, cudaStream_t stream);
 
-  // Send half of the two-hop "packed" dispatch (bf16 payload, no scales): rows land
-  // in the destination's staging grouped by local expert, ready for fused_up.  Only
-  // x, indices, bound_m and num_tokens of the call are used.
+  // Send half of the two-hop "packed" dispatch: rows land in the destination's staging
+  // grouped by local expert, ready for fused_up.  The payload is bf16 without scales, or
+  // (call.quantize, on an object created for a 1-byte payload with scales) bf16 tokens
+  // converted to e4m3 + one fp32 scale per 128 columns on the way.  Only x, indices,
+  // bound_m, num_tokens and quantize of the call are used.
   void dispatch_send_packed(const DispatchCall& call, cudaStream_t stream);
   static void dispatch_send_packed_group(const std::vector<AllToAll*>& ranks,
                                          const std::vector<DispatchCall>& calls,
@@ -133,6 +153,10 @@ class AllToAll {
   // (the GEMM epilogue stores to the tokens' home ranks).
   void fused_up(const FusedFfnCall& call, cudaStream_t stream);
   void fused_down(const FusedFfnCall& call, cudaStream_t stream);
+  // fp8 forms: after dispatch_send_packed with call.quantize (bf16 tokens quantised to e4m3
+  // + fp32 scale per 128 columns while they are sent).
+  void fused_up_fp8(const FusedFfnFp8Call& call, cudaStream_t stream);
+  void fused_down_fp8(const FusedFfnFp8Call& call, cudaStream_t stream);
 
   // All ranks of a local world in one cooperative launch per operation.
   static void dispatch_group(const std::vector<AllToAll*>& ranks,

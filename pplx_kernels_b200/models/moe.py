@@ -151,7 +151,8 @@ class MoELayerFP8:
 
     def __init__(self, cfg: MoEModelConfig, max_num_tokens: int, rank: int = 0,
                  world_size: int = 1, dp_size: int = 1, device: torch.device | None = None,
-                 seed: int = 0, group_name: str = "default", init_std: float = 0.02) -> None:
+                 seed: int = 0, group_name: str = "default", init_std: float = 0.02,
+                 ata: AllToAll | None = None) -> None:
         from ..ops.grouped_gemm import quantize_weight_blocks
 
         assert cfg.num_experts % world_size == 0 and cfg.intermediate_dim % 128 == 0
@@ -163,9 +164,11 @@ class MoELayerFP8:
         self.rows = max_num_tokens * (world_size // dp_size)
         H, I = cfg.hidden_dim, cfg.intermediate_dim
         nscale = (H + 127) // 128
-        self.ata = AllToAll.intranode(max_num_tokens, cfg.num_experts, cfg.experts_per_token,
-                                      rank, world_size, dp_size, H, H, nscale * 4,
-                                      group_name=group_name)
+        self.ata = ata or AllToAll.intranode(
+            max_num_tokens, cfg.num_experts, cfg.experts_per_token, rank, world_size, dp_size,
+            H, H, nscale * 4, group_name=group_name)
+        # The fused down projection signals once per 256-column block of the output.
+        self.ata.set_combine_units(math.lcm(16, (H + 255) // 256))
         dev = self.device
         w13, w2 = _random_expert_weights(cfg, rank * self.nle, self.nle, seed, init_std, dev)
         self.w13_q, self.w13_s = quantize_weight_blocks(w13)
@@ -182,13 +185,25 @@ class MoELayerFP8:
         self.gemm_status = torch.zeros(1, dtype=torch.int32, device=dev)
 
     def forward(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
-                out: torch.Tensor | None = None,
-                bound_m: torch.Tensor | None = None) -> torch.Tensor:
+                out: torch.Tensor | None = None, bound_m: torch.Tensor | None = None,
+                fused: bool = False) -> torch.Tensor:
+        """``fused=True``: quantising packed send, fp8 up projection fed from the staging
+        arena (rows and scales) as tokens land, fp8 down projection whose epilogue stores to
+        the tokens' home ranks, combine reduction -- four kernels.  ``fused=False``: the
+        composition dispatch_quant -> GEMM -> GEMM -> combine."""
         from ..ops.grouped_gemm import grouped_gemm_fp8
 
         if out is None:
             out = torch.empty(self.max_num_tokens, self.cfg.hidden_dim, dtype=torch.bfloat16,
                               device=self.device)
+        if fused:
+            self.ata.fused_dispatch(x, indices, bound_m, quantize=True)
+            self.ata.fused_up_fp8(self.w13_q, self.w13_s, self.h, self.h_scale, self.counts,
+                                  self.gemm_status)
+            self.ata.fused_down_fp8(self.h, self.h_scale, self.w2_q, self.w2_s, self.gemm_status)
+            self.ata.combine(out, indices, weights, self.expert_y, bound_m,
+                             do_send=False, do_recv=True)
+            return out
         self.ata.dispatch_quant(self.counts, self.expert_x, self.expert_scale, x, indices, bound_m)
         grouped_gemm_fp8(self.expert_x, self.expert_scale, self.w13_q, self.w13_s, self.counts,
                          swiglu_quant=True, out=self.h, out_scale=self.h_scale,

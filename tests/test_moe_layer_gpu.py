@@ -133,6 +133,83 @@ def test_fp8_layer_matches_reference():
     layer.destroy()
 
 
+@pytest.mark.parametrize("cfg,m", [(MoEModelConfig("q", 8, 2, 512, 256), 96),
+                                   (MoEModelConfig("q3", 16, 4, 1024, 384), 300)])
+def test_fused_fp8_layer_matches_reference(cfg, m):
+    """One rank: quantising packed send -> fp8 up projection fed from the staging arena (rows
+    and scales) -> fp8 down projection storing into the combine staging -> reduction."""
+    from pplx_kernels_b200.models.moe import MoELayerFP8, moe_reference_fp8
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    layer = MoELayerFP8(cfg, max_num_tokens=m, init_std=0.05)
+    x, idx, w = _inputs(cfg, m, seed=23, dev=dev)
+    want = moe_reference_fp8(x, idx.to(dev), w, *layer.dequantized_weights())
+    idx_dev = as_index_tensor(idx, dev)
+    composed = layer(x, idx_dev, w).clone()
+    for _ in range(3):
+        out = layer(x, idx_dev, w, fused=True)
+        torch.cuda.synchronize()
+        layer.check_status()
+        err = (out[:m].float() - want).abs()
+        assert (err <= 0.06 * want.abs() + 0.03 * want.abs().amax()).all(), err.max()
+        # same arithmetic as the composed path: the two must agree to rounding of the sums
+        torch.testing.assert_close(out[:m].float(), composed[:m].float(), rtol=2e-2, atol=2e-3)
+    assert int(layer.counts.sum()) == m * cfg.experts_per_token
+    layer.destroy()
+
+
+@pytest.mark.parametrize("world,dp_size,m", [(2, 1, 24), (4, 2, 40), (8, 1, 64)])
+def test_fused_fp8_layer_in_an_emulated_world(world, dp_size, m):
+    """All ranks on one GPU, each step launched for all ranks before the next one."""
+    import pplx_kernels_b200 as pk
+    from pplx_kernels_b200.models.moe import MoELayerFP8, moe_reference_fp8
+
+    cfg = MoEModelConfig("q4", 16, 4, 512, 256)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    nscale = (cfg.hidden_dim + 127) // 128
+    atas = pk.AllToAll.local_world(m, cfg.num_experts, cfg.experts_per_token, world, dp_size,
+                                   cfg.hidden_dim, cfg.hidden_dim, nscale * 4)
+    layers = [MoELayerFP8(cfg, m, rank=r, world_size=world, dp_size=dp_size, device=dev,
+                          ata=atas[r], init_std=0.05) for r in range(world)]
+    for a in atas:
+        a.set_debug_checks(True)
+        a.set_timeout_ms(2000)
+    groups = world // dp_size
+    data = [_inputs(cfg, m, seed=30 + g, dev=dev) for g in range(groups)]
+    per_rank = [data[r // dp_size] for r in range(world)]
+    idx_dev = [as_index_tensor(d[1], dev) for d in per_rank]
+    outs = [torch.full((m, cfg.hidden_dim), float("nan"), dtype=torch.bfloat16, device=dev)
+            for _ in range(world)]
+    deq = [l.dequantized_weights() for l in layers]
+    w13 = torch.cat([d[0] for d in deq])
+    w2 = torch.cat([d[1] for d in deq])
+    for _ in range(3):
+        for o in outs:
+            o.fill_(float("nan"))
+        pk.fused_dispatch_group(atas, [d[0] for d in per_rank], idx_dev, [None] * world,
+                                quantize=True)
+        for l in layers:
+            l.ata.fused_up_fp8(l.w13_q, l.w13_s, l.h, l.h_scale, l.counts, l.gemm_status)
+        for l in layers:
+            l.ata.fused_down_fp8(l.h, l.h_scale, l.w2_q, l.w2_s, l.gemm_status)
+        pk.combine_group(atas, outs, idx_dev, [d[2] for d in per_rank],
+                         [l.expert_y for l in layers], [None] * world,
+                         do_send=False, do_recv=True)
+        torch.cuda.synchronize()
+        for r, l in enumerate(layers):
+            l.check_status()
+            x, idx, w = per_rank[r]
+            want = moe_reference_fp8(x, idx.to(dev), w, w13, w2)
+            err = (outs[r].float() - want).abs()
+            assert (err <= 0.06 * want.abs() + 0.03 * want.abs().amax()).all(), err.max()
+    total = sum(int(l.counts.sum()) for l in layers)
+    assert total == groups * m * cfg.experts_per_token
+    for l in layers:
+        l.destroy()
+
+
 def test_fp8_layer_graph_replayed_1000_times():
     from pplx_kernels_b200.models.moe import MoELayerFP8, moe_reference_fp8
 

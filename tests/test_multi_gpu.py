@@ -239,3 +239,39 @@ def _worker_moe_layer(pgi: ProcessGroupInfo, model: str, tokens: int) -> None:
 def test_moe_layer_fused_and_composed_multi_gpu(world):
     _need(world)
     parallel_launch(world, _worker_moe_layer, "tiny", 48)
+
+
+def _worker_moe_layer_fp8(pgi: ProcessGroupInfo, tokens: int) -> None:
+    from pplx_kernels_b200.models.configs import MoEModelConfig
+    from pplx_kernels_b200.models.moe import MoELayerFP8, moe_reference_fp8
+    from pplx_kernels_b200.utils.testing import as_index_tensor, routing
+
+    cfg = MoEModelConfig("q-multi", 16, 4, 512, 256)
+    dev = pgi.device
+    layer = MoELayerFP8(cfg, max_num_tokens=tokens, rank=pgi.rank, world_size=pgi.world_size,
+                        device=dev, init_std=0.05)
+    layer.ata.set_timeout_ms(5000)
+    gen = torch.Generator().manual_seed(60 + pgi.rank)
+    x = torch.randn(tokens, cfg.hidden_dim, generator=gen).to(torch.bfloat16).to(dev)
+    idx = routing(tokens, cfg.num_experts, cfg.experts_per_token, gen)
+    w = torch.softmax(torch.randn(tokens, cfg.experts_per_token, generator=gen), dim=-1).to(dev)
+    w13, w2 = layer.dequantized_weights()
+    w13_all = [torch.empty_like(w13) for _ in range(pgi.world_size)]
+    w2_all = [torch.empty_like(w2) for _ in range(pgi.world_size)]
+    torch.distributed.all_gather(w13_all, w13)
+    torch.distributed.all_gather(w2_all, w2)
+    want = moe_reference_fp8(x, idx.to(dev), w, torch.cat(w13_all), torch.cat(w2_all))
+    for fused in (True, False, True):
+        out = layer(x, as_index_tensor(idx, dev), w, fused=fused)
+        torch.cuda.synchronize()
+        layer.check_status()
+        err = (out[:tokens].float() - want).abs()
+        assert (err <= 0.06 * want.abs() + 0.03 * want.abs().amax()).all(), err.max()
+    torch.distributed.barrier()
+    layer.destroy()
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_fp8_moe_layer_fused_and_composed_multi_gpu(world):
+    _need(world)
+    parallel_launch(world, _worker_moe_layer_fp8, 48)
