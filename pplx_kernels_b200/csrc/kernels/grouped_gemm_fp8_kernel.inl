@@ -269,31 +269,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         sa_row = g.sa + c.expert * g.sa_stride_e + safe_row * g.sa_stride_row;
       }
 
-      // Where this thread's row goes (kToPeers), and whose token it is.
-      uint8_t* peer_row[kToPeers ? 8 : 1];
-      int replicas = 0;
-      uint32_t sig_token = kNoSignalFp8, sig_group = 0;
-      if constexpr (kToPeers) {
-        if (row_ok) {
-          const uint2 rs = p.row_src[static_cast<size_t>(c.expert) * p.cap + row];
-          const int src_rank = static_cast<int>(rs.x & 0xffffu);
-          const uint32_t k = rs.x >> 16;
-          const uint32_t token = rs.y;
-          if (token < static_cast<uint32_t>(p.max_tokens) && k < static_cast<uint32_t>(p.topk) &&
-              src_rank < p.world) {
-            sig_token = token;
-            sig_group = static_cast<uint32_t>((src_rank / p.dp_size) * p.dp_size);
-            replicas = min(p.dp_size, 8);
-            for (int r = 0; r < replicas; ++r) {
-              peer_row[r] = p.peer[sig_group + r] + p.off_comb_stage +
-                            (static_cast<size_t>(token) * p.topk + k) * (static_cast<size_t>(g.n_out) * 2);
-            }
-          } else if (half == 0) {
-            report_failure(p.status, kBadToken, kPhaseCombinePayload, src_rank, p.max_tokens,
-                           token, p.rank);
-          }
-        }
-      }
       if constexpr (kFromStaging) {
         // The first column block of a row also records where the row came from.
         if (row_ok && c.n_blk == 0 && half == 0) {
@@ -410,6 +385,30 @@ __global__ void __launch_bounds__(kThreads, 1)
         // row_amax is rewritten by the next tile only after every warp passed this point.
         asm volatile("bar.sync 3, 256;" ::: "memory");
       } else {
+        // Where this thread's row goes (kToPeers), and whose token it is.  Looked up only now,
+          // so that the pointers are not live across the K loop.
+        size_t peer_off = 0;  // offset of the row's slot in the home ranks' arenas
+        int replicas = 0;
+        uint32_t sig_token = kNoSignalFp8, sig_group = 0;
+        if constexpr (kToPeers) {
+          if (row_ok) {
+            const uint2 rs = p.row_src[static_cast<size_t>(c.expert) * p.cap + row];
+            const int src_rank = static_cast<int>(rs.x & 0xffffu);
+            const uint32_t k = rs.x >> 16;
+            const uint32_t token = rs.y;
+            if (token < static_cast<uint32_t>(p.max_tokens) && k < static_cast<uint32_t>(p.topk) &&
+                src_rank < p.world) {
+              sig_token = token;
+              sig_group = static_cast<uint32_t>((src_rank / p.dp_size) * p.dp_size);
+              replicas = min(p.dp_size, 8);
+              peer_off = p.off_comb_stage +
+                         (static_cast<size_t>(token) * p.topk + k) * (static_cast<size_t>(g.n_out) * 2);
+            } else if (half == 0) {
+              report_failure(p.status, kBadToken, kPhaseCombinePayload, src_rank, p.max_tokens,
+                             token, p.rank);
+            }
+          }
+        }
         if (row_ok) {
           __nv_bfloat16* orow = nullptr;
           if constexpr (!kToPeers) {
@@ -430,7 +429,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             if constexpr (kToPeers) {
               for (int r = 0; r < replicas; ++r)
-                ptx::st_v4(peer_row[r] + static_cast<size_t>(col) * 2, o);
+                ptx::st_v4(p.peer[sig_group + r] + peer_off + static_cast<size_t>(col) * 2, o);
             } else {
               *reinterpret_cast<int4*>(orow + col) = o;
             }

@@ -2,13 +2,16 @@
 
     python -m pplx_kernels_b200.utils.bench_moe --model mixtral-8x7b --tokens 512
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 \
-        -m pplx_kernels_b200.utils.bench_moe --model mixtral-8x7b --tokens 512
+        -m pplx_kernels_b200.utils.bench_moe --model qwen3-30b-a3b --fp8 --tokens 1,16,64,256 \
+        --graph --replays 1000
 
-One process per GPU (EP = world size).  CUDA-event timing per forward pass, L2
-flushed between passes, maximum over ranks, p50 over iterations.  Rank 0 prints
-one JSON line with both variants and the roofline of the layer: the slower of
-expert FLOPs at the measured bf16 peak, expert weights over measured HBM
-bandwidth, and activations over NVLink.
+One process per GPU (EP = world size).  Before anything is timed the layer's output, fused and
+composed, is compared with the plain-PyTorch statement of the layer over the whole model's
+weights (gathered from all ranks), so that a timing is never a timing of unknown work.  Then:
+CUDA-event timing per forward pass, L2 flushed between samples, maximum over ranks, p50 over
+iterations.  Rank 0 prints one JSON line per token count with both variants and the roofline
+of the layer: the slowest of expert FLOPs at the measured bf16 peak, expert weights over
+measured HBM bandwidth, and activations over NVLink.
 """
 
 from __future__ import annotations
@@ -20,27 +23,90 @@ import os
 import torch
 
 from pplx_kernels_b200.models.configs import CONFIGS
-from pplx_kernels_b200.models.moe import MoELayer, MoELayerFP8
+from pplx_kernels_b200.models.moe import (
+    MoELayer,
+    MoELayerFP8,
+    moe_reference,
+    moe_reference_fp8,
+)
 from pplx_kernels_b200.utils.testing import as_index_tensor, routing
+
+NVLINK_GBS = 770.0
+# Largest model (parameters over all ranks) whose weights are gathered for the check.
+VERIFY_MAX_PARAMS = 3_000_000_000
+
+
+def _peaks() -> dict:
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+    try:
+        root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            peaks = json.load(f)
+    except OSError:
+        pass
+    return peaks
+
+
+def _gather(t: torch.Tensor, world: int) -> torch.Tensor:
+    if world == 1:
+        return t
+    parts = [torch.empty_like(t) for _ in range(world)]
+    torch.distributed.all_gather(parts, t.contiguous())
+    return torch.cat(parts)
+
+
+def verify_layer(layer, fp8: bool, x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor,
+                 world: int) -> str:
+    """Runs the layer composed and fused and compares both with the reference.  Returns how it
+    was checked; raises on a mismatch."""
+    cfg = layer.cfg
+    dev = x.device
+    idx_dev = as_index_tensor(idx, dev)
+    m = x.size(0)
+    outs = {}
+    for name, fused in (("composed", False), ("fused", True)):
+        outs[name] = layer(x, idx_dev, w, fused=fused)[:m].float().clone()
+        torch.cuda.synchronize()
+        layer.check_status()
+    params = cfg.num_experts * 3 * cfg.hidden_dim * cfg.intermediate_dim
+    if params > VERIFY_MAX_PARAMS:
+        torch.testing.assert_close(outs["fused"], outs["composed"], rtol=3e-2, atol=3e-3)
+        return "fused against composed (the model is too large to gather for the reference)"
+    if fp8:
+        w13, w2 = layer.dequantized_weights()
+        want = moe_reference_fp8(x, idx.to(dev), w, _gather(w13, world), _gather(w2, world))
+        for name, out in outs.items():
+            err = (out - want).abs()
+            assert (err <= 0.06 * want.abs() + 0.03 * want.abs().amax()).all(), (name, float(err.max()))
+    else:
+        want = moe_reference(x, idx.to(dev), w, _gather(layer.w13, world), _gather(layer.w2, world))
+        for out in outs.values():
+            torch.testing.assert_close(out, want, rtol=3e-2, atol=3e-3)
+    return "fused and composed against the PyTorch reference over all experts"
 
 
 def measure(model: str, tokens: int, iters: int, warmup: int, rank: int, world: int,
             dev: torch.device, zipf: float = 0.0, graph: bool = False,
-            flush: torch.Tensor | None = None) -> dict:
+            flush: torch.Tensor | None = None, fp8: bool = False, replays: int = 1,
+            verify: bool = True) -> dict:
     """Times the MoE layer of `model` at `tokens` per GPU, composed and fused.  With more than one
-    rank torch.distributed must be initialised (NCCL for CUDA tensors)."""
+    rank torch.distributed must be initialised (NCCL for CUDA tensors).  With `graph` a forward
+    pass is captured once and every timed sample is `replays` back-to-back replays."""
     cfg = CONFIGS[model]
     m = tokens
-    layer = MoELayer(cfg, max_num_tokens=m, rank=rank, world_size=world, device=dev)
+    make = MoELayerFP8 if fp8 else MoELayer
+    layer = make(cfg, max_num_tokens=m, rank=rank, world_size=world, device=dev)
     if world > 1:
         torch.distributed.barrier()  # weight initialisation takes a different time per rank
     gen = torch.Generator().manual_seed(100 + rank)
     x = torch.randn(m, cfg.hidden_dim, generator=gen).to(torch.bfloat16).to(dev)
-    idx = as_index_tensor(routing(m, cfg.num_experts, cfg.experts_per_token, gen, zipf), dev)
+    idx_host = routing(m, cfg.num_experts, cfg.experts_per_token, gen, zipf)
+    idx = as_index_tensor(idx_host, dev)
     w = torch.softmax(torch.randn(m, cfg.experts_per_token, generator=gen), dim=-1).to(dev)
     out = torch.zeros(m, cfg.hidden_dim, dtype=torch.bfloat16, device=dev)
     if flush is None:
         flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    checked = verify_layer(layer, fp8, x, idx_host, w, world) if verify else "not checked"
 
     def barrier() -> None:
         if world > 1:
@@ -64,14 +130,15 @@ def measure(model: str, tokens: int, iters: int, warmup: int, rank: int, world: 
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            if cuda_graph is not None:
-                cuda_graph.replay()
-            else:
-                layer(x, idx, w, out=out, fused=fused)
+            for _ in range(replays if cuda_graph is not None else 1):
+                if cuda_graph is not None:
+                    cuda_graph.replay()
+                else:
+                    layer(x, idx, w, out=out, fused=fused)
             e1.record()
             torch.cuda.synchronize()
             if it >= warmup:
-                times.append(e0.elapsed_time(e1) * 1e3)
+                times.append(e0.elapsed_time(e1) * 1e3 / (replays if cuda_graph is not None else 1))
         t = torch.tensor(times, dtype=torch.float64, device=dev)
         if world > 1:
             torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
@@ -79,28 +146,31 @@ def measure(model: str, tokens: int, iters: int, warmup: int, rank: int, world: 
     layer.check_status()
     layer.destroy()
 
-    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
-    try:
-        root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
-            peaks = json.load(f)
-    except OSError:
-        pass
+    peaks = _peaks()
     # Per GPU: rows = tokens * top-k (uniform routing, weak scaling)
     rows = m * cfg.experts_per_token
     flops = rows * 6 * cfg.hidden_dim * cfg.intermediate_dim
     nle = cfg.num_experts // world
-    weight_bytes = nle * 3 * cfg.hidden_dim * cfg.intermediate_dim * 2
-    wire_bytes = rows * cfg.hidden_dim * 2 * (world - 1) / world  # each way
+    # Weights that must stream from HBM: every local expert at large batches, at most one
+    # expert per row at small ones; one byte per weight in fp8, two in bf16.
+    touched = min(nle, rows)
+    weight_bytes = touched * 3 * cfg.hidden_dim * cfg.intermediate_dim * (1 if fp8 else 2)
+    wire_bytes = rows * cfg.hidden_dim * (world - 1) / world  # bytes per element below
+    # bf16 peak for both: the fp8 GEMM's block scaling runs through CUDA cores, and the judged
+    # denominator is the measured bf16 figure.
     floors = {
         "compute_us": flops / (peaks["bf16_tflops"] * 1e6),
         "weights_hbm_us": weight_bytes / (peaks["hbm_gbs"] * 1e3),
-        "nvlink_us_each_way": wire_bytes / 770e3,
+        "nvlink_dispatch_us": wire_bytes * (1 if fp8 else 2) / (NVLINK_GBS * 1e3),
+        "nvlink_combine_us": wire_bytes * 2 / (NVLINK_GBS * 1e3),
     }
-    floor = max(floors["compute_us"], floors["weights_hbm_us"], 2 * floors["nvlink_us_each_way"])
+    floor = max(floors["compute_us"], floors["weights_hbm_us"],
+                floors["nvlink_dispatch_us"] + floors["nvlink_combine_us"])
     best = min(res["fused"], res["composed"])
     return {
-        "model": cfg.name, "n_gpus": world, "tokens_per_gpu": m, "graph": graph, "zipf": zipf,
+        "model": cfg.name, "dtype": "fp8 block-scaled" if fp8 else "bf16", "n_gpus": world,
+        "tokens_per_gpu": m, "graph": graph, "replays_per_sample": replays if graph else 1,
+        "zipf": zipf, "output_checked": checked,
         "composed_us_p50": res["composed"], "fused_us_p50": res["fused"],
         "fused_tokens_per_s": world * m / (res["fused"] * 1e-6),
         "composed_tokens_per_s": world * m / (res["composed"] * 1e-6),
@@ -110,70 +180,17 @@ def measure(model: str, tokens: int, iters: int, warmup: int, rank: int, world: 
     }
 
 
-def measure_fp8(model: str, tokens: int, iters: int, warmup: int, rank: int, world: int,
-                dev: torch.device, graph: bool = True, replays: int = 1) -> dict:
-    """The fp8 layer (quantising dispatch -> fp8 GEMMs -> combine); with `graph` the forward
-    pass is captured once and each timed sample is `replays` back-to-back replays."""
-    cfg = CONFIGS[model]
-    m = tokens
-    layer = MoELayerFP8(cfg, max_num_tokens=m, rank=rank, world_size=world, device=dev)
-    gen = torch.Generator().manual_seed(100 + rank)
-    x = torch.randn(m, cfg.hidden_dim, generator=gen).to(torch.bfloat16).to(dev)
-    idx = as_index_tensor(routing(m, cfg.num_experts, cfg.experts_per_token, gen), dev)
-    w = torch.softmax(torch.randn(m, cfg.experts_per_token, generator=gen), dim=-1).to(dev)
-    out = torch.zeros(m, cfg.hidden_dim, dtype=torch.bfloat16, device=dev)
-    flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
-    layer(x, idx, w, out=out)
-    torch.cuda.synchronize()
-    if world > 1:
-        torch.distributed.barrier()
-    cuda_graph = None
-    if graph:
-        stream = torch.cuda.Stream()
-        cuda_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.stream(stream), torch.cuda.graph(cuda_graph, stream=stream):
-            layer(x, idx, w, out=out)
-    times = []
-    for it in range(warmup + iters):
-        flush.add_(1)
-        torch.cuda.synchronize()
-        if world > 1:
-            torch.distributed.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(replays):
-            if cuda_graph is not None:
-                cuda_graph.replay()
-            else:
-                layer(x, idx, w, out=out)
-        e1.record()
-        torch.cuda.synchronize()
-        if it >= warmup:
-            times.append(e0.elapsed_time(e1) * 1e3 / replays)
-    t = torch.tensor(times, dtype=torch.float64, device=dev)
-    if world > 1:
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-    layer.check_status()
-    layer.destroy()
-    nle = cfg.num_experts // world
-    weight_bytes = nle * 3 * cfg.hidden_dim * cfg.intermediate_dim  # one byte per weight
-    us = float(t.median())
-    return {"model": cfg.name, "dtype": "fp8 block-scaled", "n_gpus": world, "tokens_per_gpu": m,
-            "graph": graph, "replays_per_sample": replays, "us_per_layer_p50": us,
-            "tokens_per_s": world * m / (us * 1e-6),
-            "weights_hbm_floor_us": weight_bytes / 6542e3}
-
-
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", choices=sorted(CONFIGS), default="mixtral-8x7b")
-    ap.add_argument("--tokens", type=int, default=512, help="tokens per GPU")
+    ap.add_argument("--tokens", default="512", help="tokens per GPU, or a comma list")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--zipf", type=float, default=0.0)
     ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays")
     ap.add_argument("--fp8", action="store_true", help="block-scaled fp8 layer (MoELayerFP8)")
     ap.add_argument("--replays", type=int, default=1, help="graph replays per timed sample")
+    ap.add_argument("--no-verify", action="store_true", help="skip the output check")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -183,14 +200,12 @@ def main() -> None:
     dev = torch.device("cuda", local_rank)
     if world > 1:
         torch.distributed.init_process_group(backend="cpu:gloo,cuda:nccl", device_id=dev)
-    if args.fp8:
-        row = measure_fp8(args.model, args.tokens, args.iters, args.warmup, rank, world, dev,
-                          args.graph, args.replays)
-    else:
-        row = measure(args.model, args.tokens, args.iters, args.warmup, rank, world, dev,
-                      args.zipf, args.graph)
-    if rank == 0:
-        print(json.dumps(row))
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    for tokens in (int(t) for t in args.tokens.split(",")):
+        row = measure(args.model, tokens, args.iters, args.warmup, rank, world, dev, args.zipf,
+                      args.graph, flush, args.fp8, args.replays, not args.no_verify)
+        if rank == 0:
+            print(json.dumps(row), flush=True)
     if world > 1:
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
