@@ -66,7 +66,9 @@ struct CombineSmem {
   uint32_t* estart;   // [nle + 1]
   uint32_t* sig_tok;  // [nwarps] token whose part a warp stored in the current pass, or kNoSignal
   uint32_t* sig_grp;  // [nwarps] first rank of the token's DP group
+  uint8_t* outbuf;    // [nwarps][512] reduced results of one warp unit, before they are stored
 };
+constexpr int kOutBufBytes = 512;
 constexpr uint32_t kNoSignal = 0xffffffffu;
 
 __device__ __forceinline__ CombineSmem carve(uint32_t* s, int nle) {
@@ -74,6 +76,8 @@ __device__ __forceinline__ CombineSmem carve(uint32_t* s, int nle) {
   m.estart = s;
   m.sig_tok = m.estart + nle + 1;
   m.sig_grp = m.sig_tok + kCombineThreads / 32;
+  const size_t words = static_cast<size_t>(m.sig_grp + kCombineThreads / 32 - s);
+  m.outbuf = reinterpret_cast<uint8_t*>(s) + round_up<size_t>(words * sizeof(uint32_t), 16);
   return m;
 }
 
@@ -326,23 +330,27 @@ __device__ __forceinline__ uint32_t pack2(float a, float b, __nv_bfloat16*) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-// Stores kPer consecutive results (2 or 4) starting at element `e0` of the output row.
+// Puts kPer consecutive results (2 or 4), converted to U, at `dst` in shared memory.
 template <int kPer, typename U>
-__device__ __forceinline__ void store_results(U* out_row, int e0, const float* acc) {
+__device__ __forceinline__ void stage_results(uint8_t* dst, const float* acc) {
   if constexpr (kPer == 4) {
-    const uint64_t v = static_cast<uint64_t>(pack2(acc[0], acc[1], static_cast<U*>(nullptr))) |
-                       (static_cast<uint64_t>(pack2(acc[2], acc[3], static_cast<U*>(nullptr))) << 32);
-    ll::st8(out_row + e0, v);
+    uint2 v;
+    v.x = pack2(acc[0], acc[1], static_cast<U*>(nullptr));
+    v.y = pack2(acc[2], acc[3], static_cast<U*>(nullptr));
+    *reinterpret_cast<uint2*>(dst) = v;
   } else {
-    ll::st4(out_row + e0, pack2(acc[0], acc[1], static_cast<U*>(nullptr)));
+    *reinterpret_cast<uint32_t*>(dst) = pack2(acc[0], acc[1], static_cast<U*>(nullptr));
   }
 }
 
 // Reduction of the flag-in-data mode.  A warp unit is (token, group of four lines): lane
 // (g, j) owns the 16 bytes at line 4c + g, offset 16 j of each of the token's top-k rows,
-// polls until all of them carry this combine's flag, and reduces them.
+// polls until all of them carry this combine's flag, and reduces them.  The unit's results
+// (480 bytes of 16-bit values, 240 for fp32 inputs: a multiple of 16 at a multiple of 16) pass
+// through shared memory so that they leave as aligned 16-byte stores, whole lines at a time --
+// which matters most when out_tokens is pinned host memory and every store crosses PCIe.
 template <typename T, typename U>
-__device__ __forceinline__ void recv_phase_ll(const CombineArgs& a, int m) {
+__device__ __forceinline__ void recv_phase_ll(const CombineArgs& a, const CombineSmem& sm, int m) {
   const A2AParams& p = a.p;
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -418,11 +426,22 @@ __device__ __forceinline__ void recv_phase_ll(const CombineArgs& a, int m) {
         }
       }
     }
-    if (!ok || !live) continue;
-    U* out_row = out + static_cast<int64_t>(i) * a.out_stride_row;
-    const int e0 = o / static_cast<int>(sizeof(T));
-    if (o + 8 <= row_bytes) store_results<kPer>(out_row, e0, acc);
-    if (j < 7 && o + 16 <= row_bytes) store_results<kPer>(out_row, e0 + kPer, acc + kPer);
+    if (!ok) continue;
+    // Bytes of output per byte of input: 1 for 16-bit inputs, 1/2 for fp32.
+    constexpr int kIn = static_cast<int>(sizeof(T)), kOut = static_cast<int>(sizeof(U));
+    uint8_t* wbuf = sm.outbuf + warp * kOutBufBytes;
+    const int in_unit = g * ll::kLineData + j * 16;  // this lane's byte offset inside the unit
+    if (live && o + 8 <= row_bytes) stage_results<kPer, U>(wbuf + in_unit / kIn * kOut, acc);
+    if (live && j < 7 && o + 16 <= row_bytes)
+      stage_results<kPer, U>(wbuf + (in_unit + 8) / kIn * kOut, acc + kPer);
+    __syncwarp();
+    const int unit_in0 = 4 * c * ll::kLineData;  // first input byte of the unit in its row
+    const int out_bytes = (min(row_bytes - unit_in0, 4 * ll::kLineData) / kIn) * kOut;
+    uint8_t* out_at = reinterpret_cast<uint8_t*>(out + static_cast<int64_t>(i) * a.out_stride_row) +
+                      unit_in0 / kIn * kOut;
+    if (lane * 16 < out_bytes)
+      ptx::st_v4(out_at + lane * 16, *reinterpret_cast<const int4*>(wbuf + lane * 16));
+    __syncwarp();  // the buffer is rewritten by the warp's next unit
   }
   trace(p, kTrCombineReduced);
 }
@@ -512,7 +531,7 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a, uint32_t* sme
   trace(p, kTrCombineSent);
   if constexpr (SEND && RECV) __syncthreads();
   if constexpr (RECV) {
-    if (a.ll) recv_phase_ll<T, U>(a, m);
+    if (a.ll) recv_phase_ll<T, U>(a, sm, m);
     else recv_phase<T, U>(a, sm, m);
   }
   trace(p, kTrCombineEnd);
@@ -581,7 +600,8 @@ cudaError_t dispatch_types(DType in, DType out, F&& fn) {
 }  // namespace
 
 size_t combine_smem_bytes(const A2AParams& p) {
-  return sizeof(uint32_t) * (static_cast<size_t>(p.nle) + 1 + 2 * (kCombineThreads / 32));
+  const size_t words = static_cast<size_t>(p.nle) + 1 + 2 * (kCombineThreads / 32);
+  return round_up<size_t>(sizeof(uint32_t) * words, 16) + (kCombineThreads / 32) * kOutBufBytes;
 }
 
 int combine_threads() { return kCombineThreads; }

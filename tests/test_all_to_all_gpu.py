@@ -512,7 +512,8 @@ def test_row_lengths_around_the_line_size(hidden, in_dtype):
     run_local_world(cfg, world=4, dp_size=2, seed=85, split=True, y_dtype=torch.float32)
 
 
-def test_many_tokens_per_rank_through_lines():
+def test_many_tokens_per_rank_through_lines(monkeypatch):
+    monkeypatch.setenv("PPLX_B200_LL_MAX_TOKENS", "0")  # lines at any size
     cfg = MoEConfig(num_experts=32, experts_per_token=4, hidden_dim=2048, max_num_tokens=600,
                     in_dtype=torch.float8_e4m3fn)
     run_local_world(cfg, world=4, dp_size=1, seed=86, iterations=2)
