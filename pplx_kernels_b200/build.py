@@ -31,6 +31,11 @@ BUILD_DIR = PKG_DIR / "_build"
 LIB_NAME = "libpplx_kernels_b200.so"
 LIB_PATH = PKG_DIR / LIB_NAME
 
+# Experiments: a library under another name (PPLX_B200_LIB_OUT, loaded through
+# PPLX_B200_LIBRARY) built with extra nvcc flags (PPLX_B200_EXTRA_NVCC_FLAGS).
+LIB_PATH = Path(os.environ.get("PPLX_B200_LIB_OUT", str(LIB_PATH)))
+EXTRA_NVCC_FLAGS = shlex.split(os.environ.get("PPLX_B200_EXTRA_NVCC_FLAGS", ""))
+
 CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
 NVCC = str(CUDA_HOME / "bin" / "nvcc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
@@ -85,7 +90,7 @@ def _compile_cmd(src: Path, obj: Path, ptxas_info: bool) -> list[str]:
     if src.suffix == ".cu":
         cmd = [NVCC, "-std=c++20", "-O3", *ARCH_FLAGS, "-lineinfo", "--expt-relaxed-constexpr",
                "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
-               *includes, *defines]
+               *includes, *defines, *EXTRA_NVCC_FLAGS]
         if ptxas_info:
             cmd += ["-Xptxas", "-v"]
         cmd += ["-c", str(src), "-o", str(obj)]
@@ -128,7 +133,7 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
                 if log:
                     print(log, flush=True)
 
-    stamp = BUILD_DIR / "link.stamp"
+    stamp = BUILD_DIR / f"link.{LIB_PATH.name}.stamp"
     link_tag = hashlib.sha256(" ".join(sorted(o.name for o in objs)).encode()).hexdigest()
     if jobs or force or not LIB_PATH.exists() or not stamp.exists() or stamp.read_text() != link_tag:
         _, tlib = _torch_paths()

@@ -74,6 +74,11 @@ struct Poll {
   // Call after an unsuccessful poll (all 32 lanes).  False: give up.
   __device__ __forceinline__ bool again(int lane, uint64_t expected, uint64_t observed) {
     if (++spins < 64u) return true;
+    return patient(lane, expected, observed);
+  }
+
+  // The patient part (see PPLX_COLD_PATH in wait.cuh).
+  __device__ PPLX_COLD_PATH bool patient(int lane, uint64_t expected, uint64_t observed) {
     ptx::nanosleep(40);
     if ((spins & 15u) != 0u) return true;
     int go = 1;

@@ -153,7 +153,7 @@ __device__ __forceinline__ int4 pack8(const float (&acc)[8], __nv_bfloat16*) {
 
 // ---- phases --------------------------------------------------------------------
 
-template <typename T>
+template <typename T, bool kLines>
 __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSmem& sm) {
   const A2AParams& p = a.p;
   const int tid = threadIdx.x;
@@ -200,7 +200,7 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
   const uint32_t n_units = total_rows * split;
   const uint32_t arrival_units = static_cast<uint32_t>(p.comb_units) / split;
 
-  if (a.ll) {
+  if constexpr (kLines) {
     const int nlines = ll::lines_for(row_bytes);
     const uint64_t flag = ll::kCombineTag | static_cast<uint64_t>(ptx::ld_volatile(p.comb_iter));
     for (uint32_t unit = gwarp; unit < n_units; unit += gwarps) {
@@ -518,7 +518,9 @@ __device__ __forceinline__ void recv_phase(const CombineArgs& a, const CombineSm
   trace(p, kTrCombineReduced);
 }
 
-template <typename T, typename U, bool SEND, bool RECV>
+// kLines: flag-in-data lines, else counters.  Separate instantiations keep each kernel's code
+// small, which counts at decode sizes where the instructions are fetched from DRAM too.
+template <typename T, typename U, bool SEND, bool RECV, bool kLines>
 __device__ __forceinline__ void combine_body(const CombineArgs& a, uint32_t* smem) {
   const A2AParams& p = a.p;
   const CombineSmem sm = carve(smem, p.nle);
@@ -527,11 +529,11 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a, uint32_t* sme
   m = min(m, p.max_tokens);
   trace(p, kTrCombineStart);
   trace_block(p, kTrBlockCombineStart);
-  if constexpr (SEND) send_phase<T>(a, sm);
+  if constexpr (SEND) send_phase<T, kLines>(a, sm);
   trace(p, kTrCombineSent);
   if constexpr (SEND && RECV) __syncthreads();
   if constexpr (RECV) {
-    if (a.ll) recv_phase_ll<T, U>(a, sm, m);
+    if constexpr (kLines) recv_phase_ll<T, U>(a, sm, m);
     else recv_phase<T, U>(a, sm, m);
   }
   trace(p, kTrCombineEnd);
@@ -539,41 +541,52 @@ __device__ __forceinline__ void combine_body(const CombineArgs& a, uint32_t* sme
   trace_block(p, kTrBlockCombineEnd);
 }
 
-template <typename T, typename U, bool SEND, bool RECV>
+template <typename T, typename U, bool SEND, bool RECV, bool kLines>
 __global__ void __launch_bounds__(kCombineThreads, 1)
     combine_kernel(const __grid_constant__ CombineArgs a) {
   extern __shared__ __align__(16) uint32_t dyn_smem[];
-  combine_body<T, U, SEND, RECV>(a, dyn_smem);
+  combine_body<T, U, SEND, RECV, kLines>(a, dyn_smem);
 }
 
-template <typename T, typename U, bool SEND, bool RECV>
+template <typename T, typename U, bool SEND, bool RECV, bool kLines>
 __global__ void __launch_bounds__(kCombineThreads, 1)
     combine_kernel_multi(const __grid_constant__ CombineMulti m) {
   extern __shared__ __align__(16) uint32_t dyn_smem[];
-  combine_body<T, U, SEND, RECV>(m.r[blockIdx.y], dyn_smem);
+  combine_body<T, U, SEND, RECV, kLines>(m.r[blockIdx.y], dyn_smem);
+}
+
+template <typename T, typename U, bool kLines, bool kMulti>
+const void* combine_fn(bool send, bool recv) {
+  if constexpr (kMulti) {
+    if (send && recv) return reinterpret_cast<const void*>(&combine_kernel_multi<T, U, true, true, kLines>);
+    if (send) return reinterpret_cast<const void*>(&combine_kernel_multi<T, U, true, false, kLines>);
+    return reinterpret_cast<const void*>(&combine_kernel_multi<T, U, false, true, kLines>);
+  } else {
+    if (send && recv) return reinterpret_cast<const void*>(&combine_kernel<T, U, true, true, kLines>);
+    if (send) return reinterpret_cast<const void*>(&combine_kernel<T, U, true, false, kLines>);
+    return reinterpret_cast<const void*>(&combine_kernel<T, U, false, true, kLines>);
+  }
 }
 
 template <typename T, typename U>
 cudaError_t launch_typed(const CombineArgs& a, bool send, bool recv, int grid, size_t smem,
                          cudaStream_t stream) {
-  if (send && recv) {
-    combine_kernel<T, U, true, true><<<grid, kCombineThreads, smem, stream>>>(a);
-  } else if (send) {
-    combine_kernel<T, U, true, false><<<grid, kCombineThreads, smem, stream>>>(a);
-  } else {
-    combine_kernel<T, U, false, true><<<grid, kCombineThreads, smem, stream>>>(a);
-  }
-  return cudaGetLastError();
+  const void* fn = a.ll ? combine_fn<T, U, true, false>(send, recv)
+                        : combine_fn<T, U, false, false>(send, recv);
+  void* params[] = {const_cast<CombineArgs*>(&a)};
+  return cudaLaunchKernel(fn, dim3(grid), dim3(kCombineThreads), params, smem, stream);
 }
 
 template <typename T, typename U>
 cudaError_t launch_typed_multi(const CombineMulti& args, int nranks, bool send, bool recv,
                                int grid, size_t smem, cudaStream_t stream) {
+  // All ranks of an emulated world run one instantiation.
+  for (int r = 1; r < nranks; ++r) {
+    if ((args.r[r].ll != 0) != (args.r[0].ll != 0)) return cudaErrorInvalidValue;
+  }
   void* params[] = {const_cast<CombineMulti*>(&args)};
-  const void* fn = nullptr;
-  if (send && recv) fn = reinterpret_cast<const void*>(&combine_kernel_multi<T, U, true, true>);
-  else if (send) fn = reinterpret_cast<const void*>(&combine_kernel_multi<T, U, true, false>);
-  else fn = reinterpret_cast<const void*>(&combine_kernel_multi<T, U, false, true>);
+  const void* fn = args.r[0].ll ? combine_fn<T, U, true, true>(send, recv)
+                                : combine_fn<T, U, false, true>(send, recv);
   return cudaLaunchCooperativeKernel(fn, dim3(grid, nranks), dim3(kCombineThreads), params, smem,
                                      stream);
 }

@@ -75,6 +75,25 @@ constexpr int kDispatchThreads = 512;
 constexpr int kRowCap = 512;           // rows per block whose slots are precomputed
 constexpr uint32_t kNoSlot = 0xffffffffu;
 
+// The wire protocol and payload treatment of a launch.  Each is its own kernel instantiation:
+// a decode-sized launch after an L2 flush also fetches its instructions from DRAM, and a
+// kernel that carries every variant pays for all of them (3 µs at one token).
+enum Mode : int {
+  kModeLines = 0,        // flag-in-data lines, rows read where they are
+  kModeLinesStaged = 1,  // ... rows fetched from host memory into shared memory first
+  kModeCounters = 2,     // stores, barrier, arrival counters
+  kModeQuant = 3,        // counters; bf16 -> e4m3 + scales inside the send
+  kModePacked = 4,       // counters; two-hop expert-major placement (fused MoE layer)
+  kModePackedQuant = 5,  // ... with the quantisation
+};
+template <int kMode>
+struct ModeOf {
+  static constexpr bool ll = kMode == kModeLines || kMode == kModeLinesStaged;
+  static constexpr bool staged = kMode == kModeLinesStaged;
+  static constexpr bool quantize = kMode == kModeQuant || kMode == kModePackedQuant;
+  static constexpr bool packed = kMode == kModePacked || kMode == kModePackedQuant;
+};
+
 // Number of warps that share one row: the largest power of two that keeps every
 // warp busy, at most 16, and never so many that a warp gets under 32 vectors.
 __device__ __forceinline__ int split_factor(uint32_t rows, uint32_t warps, int nvec) {
@@ -189,8 +208,10 @@ __device__ __forceinline__ void warp_quantize_row(uint8_t* slot, float* slot_sca
   }
 }
 
+template <int kMode>
 __device__ __forceinline__ void send_phase(const DispatchArgs& a, const DispatchSmem& sm,
                                            int parity, int m, uint32_t iter_now) {
+  using M = ModeOf<kMode>;
   const A2AParams& p = a.p;
   const int tid = threadIdx.x;
   const int lane = tid & 31;
@@ -212,7 +233,7 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
   // for them now, so that they arrive in L2 while the histogram is built.
   {
     const int rows_here = u_end - u_begin;
-    const int src_bytes = a.quantize ? 2 * p.hidden_bytes : p.hidden_bytes;
+    const int src_bytes = M::quantize ? 2 * p.hidden_bytes : p.hidden_bytes;
     if (rows_here > 0 && rows_here <= kRowCap && !a.x_on_host) {
       const int parts = split_factor(rows_here, nwarps, p.hidden_bytes >> 4);
       for (int unit = warp; unit < rows_here * parts; unit += nwarps) {
@@ -262,8 +283,8 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
   __syncthreads();
   trace(p, kTrDispatchHist);
 
-  const bool packed = a.packed != 0;
-  const bool ll = p.ll != 0 && !packed && !a.quantize;
+  constexpr bool packed = M::packed;
+  constexpr bool ll = M::ll;
   const uint64_t flag = ll::kDispatchTag | static_cast<uint64_t>(iter_now + 1u);
   if (!packed) {
     if (blockIdx.x == 0) {
@@ -360,14 +381,14 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
   // chunk is first fetched into shared memory (every byte crosses PCIe once, however many
   // experts the token goes to) and sent from there; otherwise there is one chunk and the
   // rows are read where they are.
-  const int stage_tokens = (ll && a.x_on_host) ? a.stage_tokens : 0;
+  const int stage_tokens = M::staged ? max(a.stage_tokens, 1) : 0;
   const int row_smem = round_up<int>(p.hidden_bytes + p.scale_bytes, 16);
   const int o_first = u_begin / topk;
   const int o_end = rows_here > 0 ? (u_end - 1) / topk + 1 : o_first;
   const int o_step = stage_tokens > 0 ? stage_tokens : max(1, o_end - o_first);
   for (int o0 = o_first; o0 < o_end; o0 += o_step) {
     const int o1 = min(o0 + o_step, o_end);
-    if (stage_tokens > 0) {
+    if constexpr (M::staged) {
       const int per_row = nvec + nscale;  // 16-byte vectors of payload, then single scales
       for (int idx = tid; idx < (o1 - o0) * per_row; idx += blockDim.x) {
         const int t = idx / per_row;
@@ -429,7 +450,7 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
         const uint32_t trailer[4] = {static_cast<uint32_t>(i), static_cast<uint32_t>(k),
                                      static_cast<uint32_t>(le), static_cast<uint32_t>(p.rank)};
         uint8_t* meta = slot + p.ll_x_lines * ll::kLineBytes;
-        if (stage_tokens > 0) {
+        if constexpr (M::staged) {
           const uint8_t* row = sm.xstage + static_cast<size_t>(o - o0) * row_smem;
           ll::warp_send_lines<ll::Src::kShared>(slot, row, p.hidden_bytes, l0, l1, flag, lane);
           if (c == split - 1)
@@ -448,7 +469,7 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
         continue;
       }
       uint8_t* slot = p.peer[dst] + p.off_disp_stage + (region_first + pos) * p.slot_bytes;
-      if (a.quantize) {
+      if constexpr (M::quantize) {
         // Parts are cut at multiples of 32 output vectors (512 columns).
         const int groups = ceil_div<int>(nvec, 32);
         const int v0 = ((c * groups) / split) * 32;
@@ -463,7 +484,7 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
                                                        v1 - v0, lane);
       }
       if (c == split - 1) {
-        if (nscale > 0 && !a.quantize) {
+        if (nscale > 0 && !M::quantize) {
           float* sdst = reinterpret_cast<float*>(slot + p.hidden_bytes);
           const float* ssrc = a.x_scale + static_cast<int64_t>(i) * a.x_scale_stride_row;
           for (int j = lane; j < nscale; j += 32) sdst[j] = __ldg(ssrc + j * a.x_scale_stride_col);
@@ -478,7 +499,7 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
         }
       }
     }
-    if (stage_tokens > 0) __syncthreads();  // the next chunk overwrites the staged rows
+    if constexpr (M::staged) __syncthreads();  // the next chunk overwrites the staged rows
   }
   trace(p, kTrDispatchStored);
   // (Also in flag-in-data mode, where nothing is signalled: warps that ran ahead into the
@@ -511,6 +532,7 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
   trace(p, kTrDispatchSignalled);
 }
 
+template <int kMode>
 __device__ __forceinline__ void recv_phase(const DispatchArgs& a, const DispatchSmem& sm,
                                            int parity, uint32_t iter_now) {
   const A2AParams& p = a.p;
@@ -520,7 +542,7 @@ __device__ __forceinline__ void recv_phase(const DispatchArgs& a, const Dispatch
   const int nwarps = blockDim.x >> 5;
   const int P = p.world * p.nle;
   const WaitCtx w{p.status, p.timeout_ns, static_cast<uint32_t>(p.rank)};
-  const bool ll = p.ll != 0 && !a.quantize;
+  constexpr bool ll = ModeOf<kMode>::ll;
   const uint64_t flag = ll::kDispatchTag | static_cast<uint64_t>(iter_now + 1u);
 
   uint32_t* counts = reinterpret_cast<uint32_t*>(p.peer[p.rank] + p.off_counts) +
@@ -666,7 +688,7 @@ __device__ __forceinline__ void recv_phase(const DispatchArgs& a, const Dispatch
   trace(p, kTrDispatchEnd);
 }
 
-template <bool SEND, bool RECV>
+template <bool SEND, bool RECV, int kMode>
 __device__ __forceinline__ void dispatch_body(const DispatchArgs& a, uint32_t* smem) {
   const A2AParams& p = a.p;
   const DispatchSmem sm = carve(smem, p.num_experts, p.world * p.nle);
@@ -677,28 +699,28 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs& a, uint32_t* s
   m = min(m, p.max_tokens);
   trace(p, kTrDispatchStart);
   trace_block(p, kTrBlockDispatchStart);
-  if constexpr (SEND) send_phase(a, sm, parity, m, iter_now);
+  if constexpr (SEND) send_phase<kMode>(a, sm, parity, m, iter_now);
   if constexpr (SEND && RECV) __syncthreads();
-  if constexpr (RECV) recv_phase(a, sm, parity, iter_now);
+  if constexpr (RECV) recv_phase<kMode>(a, sm, parity, iter_now);
   __syncthreads();
   trace_block(p, kTrBlockDispatchEnd);
 }
 
-template <bool SEND, bool RECV>
+template <bool SEND, bool RECV, int kMode>
 __global__ void __launch_bounds__(kDispatchThreads, 1)
     dispatch_kernel(const __grid_constant__ DispatchArgs a) {
   extern __shared__ __align__(16) uint32_t dyn_smem[];
-  dispatch_body<SEND, RECV>(a, dyn_smem);
+  dispatch_body<SEND, RECV, kMode>(a, dyn_smem);
 }
 
 // Several ranks that live on one device, run as one grid: blockIdx.y picks the
 // rank.  Blocks of different ranks wait on one another, so the launch is
 // cooperative to have them all resident.
-template <bool SEND, bool RECV>
+template <bool SEND, bool RECV, int kMode>
 __global__ void __launch_bounds__(kDispatchThreads, 1)
     dispatch_kernel_multi(const __grid_constant__ DispatchMulti m) {
   extern __shared__ __align__(16) uint32_t dyn_smem[];
-  dispatch_body<SEND, RECV>(m.r[blockIdx.y], dyn_smem);
+  dispatch_body<SEND, RECV, kMode>(m.r[blockIdx.y], dyn_smem);
 }
 
 }  // namespace
@@ -720,9 +742,60 @@ int dispatch_threads() { return kDispatchThreads; }
 
 namespace {
 
-// Histograms of many experts need more dynamic shared memory than a kernel gets by default.
-template <typename Kernel>
-cudaError_t allow_smem(Kernel kernel, size_t smem) {
+// The instantiation that serves a launch.  The receive half only distinguishes lines from
+// counters: the packed sends have no receive half of this kernel, and a quantised row is
+// received like any other.
+int mode_of(const DispatchArgs& a, bool send) {
+  if (a.packed) return a.quantize ? kModePackedQuant : kModePacked;
+  if (a.quantize) return send ? kModeQuant : kModeCounters;
+  if (a.p.ll == 0) return kModeCounters;
+  return (send && a.stage_tokens > 0) ? kModeLinesStaged : kModeLines;
+}
+
+template <template <bool, bool, int> class Pick>
+const void* pick_kernel(bool send, bool recv, int mode) {
+  // Only the combinations that exist are instantiated.
+  if (send && recv) {
+    switch (mode) {
+      case kModeLines: return Pick<true, true, kModeLines>::fn();
+      case kModeLinesStaged: return Pick<true, true, kModeLinesStaged>::fn();
+      case kModeCounters: return Pick<true, true, kModeCounters>::fn();
+      case kModeQuant: return Pick<true, true, kModeQuant>::fn();
+      default: return nullptr;
+    }
+  }
+  if (send) {
+    switch (mode) {
+      case kModeLines: return Pick<true, false, kModeLines>::fn();
+      case kModeLinesStaged: return Pick<true, false, kModeLinesStaged>::fn();
+      case kModeCounters: return Pick<true, false, kModeCounters>::fn();
+      case kModeQuant: return Pick<true, false, kModeQuant>::fn();
+      case kModePacked: return Pick<true, false, kModePacked>::fn();
+      case kModePackedQuant: return Pick<true, false, kModePackedQuant>::fn();
+      default: return nullptr;
+    }
+  }
+  switch (mode) {
+    case kModeLines: return Pick<false, true, kModeLines>::fn();
+    case kModeCounters: return Pick<false, true, kModeCounters>::fn();
+    default: return nullptr;
+  }
+}
+
+template <bool SEND, bool RECV, int kMode>
+struct SingleKernel {
+  static const void* fn() { return reinterpret_cast<const void*>(&dispatch_kernel<SEND, RECV, kMode>); }
+};
+template <bool SEND, bool RECV, int kMode>
+struct MultiKernel {
+  static const void* fn() {
+    return reinterpret_cast<const void*>(&dispatch_kernel_multi<SEND, RECV, kMode>);
+  }
+};
+
+// Histograms of many experts and staged rows need more dynamic shared memory than a kernel
+// gets by default.
+cudaError_t allow_smem(const void* kernel, size_t smem) {
   if (smem <= 48 * 1024) return cudaSuccess;
   return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               static_cast<int>(smem));
@@ -732,39 +805,35 @@ cudaError_t allow_smem(Kernel kernel, size_t smem) {
 
 cudaError_t launch_dispatch(const DispatchArgs& a, bool send, bool recv, int grid,
                             cudaStream_t stream) {
-  const size_t smem = dispatch_smem_bytes(a.p, a.stage_tokens);
-  cudaError_t err = cudaSuccess;
-  if (send && recv) {
-    if ((err = allow_smem(dispatch_kernel<true, true>, smem)) != cudaSuccess) return err;
-    dispatch_kernel<true, true><<<grid, kDispatchThreads, smem, stream>>>(a);
-  } else if (send) {
-    if ((err = allow_smem(dispatch_kernel<true, false>, smem)) != cudaSuccess) return err;
-    dispatch_kernel<true, false><<<grid, kDispatchThreads, smem, stream>>>(a);
-  } else {
-    if ((err = allow_smem(dispatch_kernel<false, true>, smem)) != cudaSuccess) return err;
-    dispatch_kernel<false, true><<<grid, kDispatchThreads, smem, stream>>>(a);
-  }
-  return cudaGetLastError();
+  const int mode = mode_of(a, send);
+  const void* fn = pick_kernel<SingleKernel>(send, recv, mode);
+  if (fn == nullptr) return cudaErrorInvalidValue;
+  const size_t smem = dispatch_smem_bytes(a.p, mode == kModeLinesStaged ? a.stage_tokens : 0);
+  const cudaError_t err = allow_smem(fn, smem);
+  if (err != cudaSuccess) return err;
+  void* params[] = {const_cast<DispatchArgs*>(&a)};
+  return cudaLaunchKernel(fn, dim3(grid), dim3(kDispatchThreads), params, smem, stream);
 }
 
 cudaError_t launch_dispatch_multi(const DispatchMulti& args, int nranks, bool send, bool recv,
                                   int grid, cudaStream_t stream) {
   if (nranks < 1 || nranks > kMaxLocalRanks) return cudaErrorInvalidValue;
+  // All ranks of an emulated world run one instantiation: the mode of rank 0, which the
+  // others must share.
+  const int mode = mode_of(args.r[0], send);
   int stage_tokens = 0;
-  for (int r = 0; r < nranks; ++r) stage_tokens = std::max(stage_tokens, args.r[r].stage_tokens);
-  const size_t smem = dispatch_smem_bytes(args.r[0].p, stage_tokens);
-  void* params[] = {const_cast<DispatchMulti*>(&args)};
-  const dim3 g(grid, nranks);
-  const void* fn = nullptr;
-  if (send && recv) fn = reinterpret_cast<const void*>(&dispatch_kernel_multi<true, true>);
-  else if (send) fn = reinterpret_cast<const void*>(&dispatch_kernel_multi<true, false>);
-  else fn = reinterpret_cast<const void*>(&dispatch_kernel_multi<false, true>);
-  if (smem > 48 * 1024) {
-    const cudaError_t err = cudaFuncSetAttribute(
-        fn, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (err != cudaSuccess) return err;
+  for (int r = 0; r < nranks; ++r) {
+    if (mode_of(args.r[r], send) != mode) return cudaErrorInvalidValue;
+    stage_tokens = std::max(stage_tokens, args.r[r].stage_tokens);
   }
-  return cudaLaunchCooperativeKernel(fn, g, dim3(kDispatchThreads), params, smem, stream);
+  const void* fn = pick_kernel<MultiKernel>(send, recv, mode);
+  if (fn == nullptr) return cudaErrorInvalidValue;
+  const size_t smem = dispatch_smem_bytes(args.r[0].p, mode == kModeLinesStaged ? stage_tokens : 0);
+  const cudaError_t err = allow_smem(fn, smem);
+  if (err != cudaSuccess) return err;
+  void* params[] = {const_cast<DispatchMulti*>(&args)};
+  return cudaLaunchCooperativeKernel(fn, dim3(grid, nranks), dim3(kDispatchThreads), params, smem,
+                                     stream);
 }
 
 }  // namespace pplx

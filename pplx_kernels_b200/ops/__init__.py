@@ -24,7 +24,9 @@ import torch
 
 logger = logging.getLogger(__name__)
 
-_LIB = Path(__file__).resolve().parent.parent / "libpplx_kernels_b200.so"
+# PPLX_B200_LIBRARY points at another build of the library (an experiment, a debug build).
+_LIB = Path(os.environ.get("PPLX_B200_LIBRARY") or
+            Path(__file__).resolve().parent.parent / "libpplx_kernels_b200.so")
 
 
 def _load() -> object:
