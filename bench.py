@@ -28,6 +28,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import logging
 import os
 import subprocess
 import sys
@@ -38,6 +39,7 @@ import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+_LOG = logging.getLogger("pplx_kernels_b200.bench")
 
 # Published EP8 NVLink numbers of the reference (its README.md:60-81), in microseconds.
 PUBLISHED_US = {1: {"dispatch": 41.6, "combine": 41.7}, 128: {"dispatch": 83.6, "combine": 102.3}}
@@ -153,6 +155,11 @@ class Arm:
         nle = cfg.num_experts // world
         inp = make_rank_inputs(cfg, torch.Generator().manual_seed(1000 + rank), num_tokens=tokens,
                                softmax_weights=True, zipf=zipf)
+        if rank == 0 and _LOG.isEnabledFor(logging.DEBUG):
+            from pplx_kernels_b200.utils.logging_utils import describe_routing
+
+            _LOG.debug("%s, %d tokens: rank 0 routes\n%s", kind, tokens,
+                       describe_routing(inp.indices, cfg.num_experts, world))
         self.packed = PackedInputs(inp, dev)
         self.x, self.x_scale = self.packed.x, self.packed.x_scale
         self.indices, self.weights = self.packed.indices, self.packed.weights
@@ -749,6 +756,9 @@ def main() -> None:
     sys.stdout.flush()
     _RESULT_FD = os.dup(1)
     os.dup2(2, 1)
+    from pplx_kernels_b200.utils.logging_utils import init_logging
+
+    init_logging()  # per-rank prefix on standard error; level from PPLX_B200_LOG_LEVEL
     if args.sweep:
         return sweep(args)
     if args.impl == "reference":

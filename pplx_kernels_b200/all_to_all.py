@@ -195,11 +195,8 @@ class AllToAll:
         _ops.all_to_all_set_max_blocks(self._ptr, int(n))
 
     def set_combine_units(self, units: int) -> None:
-        """Arrival units a complete expert-output row is worth (multiple of 16, default 16).
-
-        Must be the same on all ranks.  The fused down projection needs a multiple of its
-        number of 256-column output blocks.
-        """
+        """No effect, kept for callers of earlier versions: arrival of expert outputs is
+        counted in columns, so senders need not agree on a unit."""
         _ops.all_to_all_set_combine_units(self._ptr, int(units))
 
     def fused_dispatch(self, dp_x: torch.Tensor, indices: torch.Tensor,

@@ -29,9 +29,9 @@
 //  * Resets ride on the strict dispatch/combine alternation: a combine clears the
 //    flag set of the dispatch before it and bumps the iteration counter.  The
 //    combine's per-token arrival counters are never cleared: every combine adds
-//    16 * topk to each of them (peers for live tokens, the owner itself for
-//    tokens at or beyond bound_m), so the n-th combine waits for n * 16 * topk
-//    modulo 2^32.
+//    hidden_dim * topk to each of them (one unit per column that landed: peers for
+//    live tokens, the owner itself for tokens at or beyond bound_m), so the n-th
+//    combine waits for n * hidden_dim * topk modulo 2^32.
 #pragma once
 
 #include <cstddef>
@@ -62,7 +62,7 @@ struct A2AParams {
   int region_slots;  // dispatch staging slots per source rank
   int cap;           // rows per local expert in out_expert_x / expert_y
   int debug_checks;  // non-zero: bounds checks that record instead of corrupting
-  int comb_units;    // arrival units one complete expert output row is worth (multiple of 16)
+  int comb_units;    // arrival units one complete expert output row is worth: its columns
   // Flag-in-data protocol (core/ll128.cuh) for the plain dispatch and combine.
   int ll;                  // non-zero: in use
   int ll_x_lines;          // 128-byte lines that carry a dispatch row's token payload

@@ -16,9 +16,9 @@
 //    single token still uses many warps, and a unit starts as soon as its own
 //    token is complete.
 //  * A row is split over several warps when there are fewer rows than warps.
-//    A complete row is worth `comb_units` arrival units (a multiple of 16) and
-//    each part adds comb_units/parts, so a token is complete at comb_units *
-//    top-k whatever split the senders chose.
+//    Arrival is counted in columns: each part adds the columns it carries, so a
+//    token is complete at hidden_dim * top-k whatever split the senders chose (and
+//    whatever column blocks a GEMM epilogue sends instead).
 //  * Signals are issued once per block and round: all warps store their parts,
 //    the block synchronises, and one warp executes a single system-scope fence
 //    followed by relaxed adds.  (A fence per warp serialises inside an SM and
@@ -198,7 +198,6 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
   const uint32_t gwarps = gridDim.x * nwarps;
   const int split = split_factor(total_rows, gwarps, nvec);
   const uint32_t n_units = total_rows * split;
-  const uint32_t arrival_units = static_cast<uint32_t>(p.comb_units) / split;
 
   if constexpr (kLines) {
     const int nlines = ll::lines_for(row_bytes);
@@ -240,6 +239,7 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
     const uint32_t unit = round * gwarps + gwarp;
     uint32_t sig_token = kNoSignal;
     uint32_t sig_group = 0;
+    uint32_t sig_units = 0;  // columns this warp's part carries
     if (unit < n_units) {
       const uint32_t f = unit / split;
       const int c = static_cast<int>(unit - f * split);
@@ -269,16 +269,19 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
         }
         sig_token = token;
         sig_group = static_cast<uint32_t>(group_first);
+        sig_units = static_cast<uint32_t>(nv) * (16u / static_cast<uint32_t>(sizeof(T)));
       }
     }
     if (lane == 0) {
       sm.sig_tok[warp] = sig_token;
-      sm.sig_grp[warp] = sig_group;
+      sm.sig_grp[warp] = sig_group | (sig_units << 8);  // ranks fit in 8 bits
     }
     __syncthreads();
     if (warp == 0) {
       const uint32_t tok = lane < nwarps ? sm.sig_tok[lane] : kNoSignal;
-      const uint32_t grp = lane < nwarps ? sm.sig_grp[lane] : 0u;
+      const uint32_t packed_grp = lane < nwarps ? sm.sig_grp[lane] : 0u;
+      const uint32_t grp = packed_grp & 0xffu;
+      const uint32_t arrival_units = packed_grp >> 8;
       if (__any_sync(0xffffffffu, tok != kNoSignal)) ptx::fence_acq_rel_sys();
       if (tok != kNoSignal) {
         for (int r = 0; r < p.dp_size; ++r) {

@@ -73,8 +73,8 @@ void launch_gemm_from_staging(const GroupedGemmCall& call, const A2AParams& p,
 // Second expert GEMM of the fused MoE layer.  Takes the place of the combine send
 // phase: every output row x[le, r] @ w[le]^T goes to the combine staging of the
 // token's home rank(s); call.out is ignored, call.counts must be p.recv_count and
-// call.n_out the hidden size of `p`.  p.comb_units must be a multiple of the
-// number of 256-column blocks of the output.
+// call.n_out the hidden size of `p`.  Every column block adds its columns to the tokens'
+// arrival counters, so any tile width can be chosen.
 void launch_gemm_to_peers(const GroupedGemmCall& call, const A2AParams& p, cudaStream_t stream);
 
 }  // namespace pplx

@@ -21,6 +21,22 @@ struct Fp8GemmArgs {
   A2AParams a2a;
 };
 
+// One system-scope fence, then the queued adds on the tokens' arrival counters (one warp).
+__device__ __forceinline__ void flush_signals(const A2AParams& p, const Fp8PeerStage* stage,
+                                              uint32_t count, int lane) {
+  ptx::fence_acq_rel_sys();
+  for (uint32_t i = lane; i < count; i += 32) {
+    const uint32_t tok = stage->q_token[i];
+    const uint32_t grp = stage->q_group_units[i] & 0xffu;
+    const uint32_t units = stage->q_group_units[i] >> 8;
+    for (int r = 0; r < min(p.dp_size, 8); ++r) {
+      ptx::red_add_relaxed_sys(
+          reinterpret_cast<uint32_t*>(p.peer[grp + r] + p.off_comb_arrived) + tok, units);
+    }
+  }
+  __syncwarp();
+}
+
 // kFromStaging: the A operand and its scales are read out of the dispatch staging arena
 // that peers fill (packed, quantising send); tiles wait for the sources they cover.
 // kToPeers: the bf16 result rows go to the combine staging of the tokens' home ranks.
@@ -40,6 +56,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint32_t* a_row0 = rows_of + g.num_experts;                     // [E] first row in the A plane
   uint32_t* src_rows =                                            // [E][world] or null
       (kFromStaging && g.src_table != 0) ? a_row0 + g.num_experts : nullptr;
+  // (kToPeers only) staging of the peer-storing epilogue, behind the tables, 16-byte aligned.
+  Fp8PeerStage* peer_stage = reinterpret_cast<Fp8PeerStage*>(
+      (reinterpret_cast<uintptr_t>(a_row0 + g.num_experts) + 15) & ~static_cast<uintptr_t>(15));
   const A2AParams& p = g.a2a;
   int parity = 0;
   if constexpr (kFromStaging || kToPeers) parity = static_cast<int>(ptx::ld_volatile(p.iter) & 1u);
@@ -252,6 +271,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int half = (warp - 4) >> 2;   // columns [64 * half, +64) of each 128-column half
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(ew * 32) << 16);
     uint32_t round = 0;
+    uint32_t pending_signals = 0;  // kToPeers, warp 4: queued arrival adds
     bool ok = *abort_flag == 0u;
     for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const Fp8Tile c = locate(tile_start, rows_of, g.num_experts, t);
@@ -388,7 +408,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         // Where this thread's row goes (kToPeers), and whose token it is.  Looked up only now,
           // so that the pointers are not live across the K loop.
         size_t peer_off = 0;  // offset of the row's slot in the home ranks' arenas
-        int replicas = 0;
+        const int replicas = kToPeers ? min(p.dp_size, 8) : 0;
         uint32_t sig_token = kNoSignalFp8, sig_group = 0;
         if constexpr (kToPeers) {
           if (row_ok) {
@@ -400,7 +420,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                 src_rank < p.world) {
               sig_token = token;
               sig_group = static_cast<uint32_t>((src_rank / p.dp_size) * p.dp_size);
-              replicas = min(p.dp_size, 8);
               peer_off = p.off_comb_stage +
                          (static_cast<size_t>(token) * p.topk + k) * (static_cast<size_t>(g.n_out) * 2);
             } else if (half == 0) {
@@ -409,12 +428,52 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
         }
-        if (row_ok) {
-          __nv_bfloat16* orow = nullptr;
-          if constexpr (!kToPeers) {
-            orow = static_cast<__nv_bfloat16*>(g.out) + c.expert * g.out_stride_e +
-                   static_cast<int64_t>(row) * g.out_stride_row;
+        if constexpr (kToPeers) {
+          // A thread owns one row; stored straight from registers its 16-byte pieces would
+          // cross NVLink one by one.  Each warp passes 32 columns at a time through shared
+          // memory and writes them out as 64-byte row segments (four lanes per row).
+          if (half == 0) {
+            ctl->sig_token[tile_row] = sig_token;
+            ctl->sig_group[tile_row] = sig_group;
+            peer_stage->row_off[tile_row] = peer_off;
           }
+          asm volatile("bar.sync 2, 256;" ::: "memory");
+          uint8_t* stg = &peer_stage->rows[warp - 4][0][0];
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {  // 32 columns of this thread's 128
+#pragma unroll
+            for (int v4 = 0; v4 < 4; ++v4) {
+              const int v = q4 * 4 + v4;
+              int4 o;
+              uint32_t* w = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat162 b =
+                    __floats2bfloat162_rn(acc[v * 8 + 2 * j], acc[v * 8 + 2 * j + 1]);
+                w[j] = *reinterpret_cast<const uint32_t*>(&b);
+              }
+              *reinterpret_cast<int4*>(stg + lane * kFp8StageRowBytes + v4 * 16) = o;
+            }
+            __syncwarp();
+            const int seg = lane & 3;
+            const int col = c.n_blk * kTileN + (q4 >> 1) * 128 + half * 64 + (q4 & 1) * 32 + seg * 8;
+#pragma unroll 2
+            for (int it = 0; it < 4; ++it) {
+              const int rr = it * 8 + (lane >> 2);
+              const int trow = ew * 32 + rr;
+              const uint32_t tok = ctl->sig_token[trow];
+              if (tok != kNoSignalFp8 && col + 8 <= g.n_out) {
+                const int4 o = *reinterpret_cast<const int4*>(stg + rr * kFp8StageRowBytes + seg * 16);
+                const uint32_t grp = ctl->sig_group[trow];
+                const size_t off = peer_stage->row_off[trow] + static_cast<size_t>(col) * 2;
+                for (int r = 0; r < replicas; ++r) ptx::st_v4(p.peer[grp + r] + off, o);
+              }
+            }
+            __syncwarp();
+          }
+        } else if (row_ok) {
+          __nv_bfloat16* orow = static_cast<__nv_bfloat16*>(g.out) + c.expert * g.out_stride_e +
+                                static_cast<int64_t>(row) * g.out_stride_row;
 #pragma unroll
           for (int v = 0; v < 16; ++v) {  // 16 vectors of 8 columns
             const int col = c.n_blk * kTileN + (v >> 3) * 128 + half * 64 + (v & 7) * 8;
@@ -427,38 +486,44 @@ __global__ void __launch_bounds__(kThreads, 1)
                   __floats2bfloat162_rn(acc[v * 8 + 2 * j], acc[v * 8 + 2 * j + 1]);
               w[j] = *reinterpret_cast<const uint32_t*>(&b);
             }
-            if constexpr (kToPeers) {
-              for (int r = 0; r < replicas; ++r)
-                ptx::st_v4(p.peer[sig_group + r] + peer_off + static_cast<size_t>(col) * 2, o);
-            } else {
-              *reinterpret_cast<int4*>(orow + col) = o;
-            }
+            *reinterpret_cast<int4*>(orow + col) = o;
           }
         }
         if constexpr (kToPeers) {
           // One fence for the whole tile, then the adds on the tokens' arrival counters.
           // (All eight warps meet at the barrier at the top of the next tile's epilogue
           // before anyone rewrites the sig arrays.)
-          if (half == 0) {
-            ctl->sig_token[tile_row] = sig_token;
-            ctl->sig_group[tile_row] = sig_group;
-          }
-          asm volatile("bar.sync 2, 256;" ::: "memory");
+          asm volatile("bar.sync 3, 256;" ::: "memory");
           if (warp == 4) {
-            ptx::fence_acq_rel_sys();
-            const uint32_t units = static_cast<uint32_t>(p.comb_units / n_blocks);
-            for (int j = lane; j < kBlockM; j += 32) {
+            // Arrival is counted in columns: this tile's share of the row.  The adds are
+            // queued and flushed behind ONE system-scope fence for as many tiles as the queue
+            // holds: with a handful of rows per expert (decode) a fence per tile would cost
+            // more than the tile.
+            const uint32_t units =
+                static_cast<uint32_t>(min(kTileN, g.n_out - c.n_blk * kTileN));
+            if (pending_signals + kBlockM > kSignalQueue) {
+              flush_signals(p, peer_stage, pending_signals, lane);
+              pending_signals = 0;
+            }
+            for (int j0 = 0; j0 < kBlockM; j0 += 32) {
+              const int j = j0 + lane;
               const uint32_t tok = ctl->sig_token[j];
-              if (tok == kNoSignalFp8) continue;
-              const uint32_t grp = ctl->sig_group[j];
-              for (int r = 0; r < min(p.dp_size, 8); ++r) {
-                ptx::red_add_relaxed_sys(
-                    reinterpret_cast<uint32_t*>(p.peer[grp + r] + p.off_comb_arrived) + tok, units);
+              const bool live = tok != kNoSignalFp8;
+              const uint32_t mask = __ballot_sync(0xffffffffu, live);
+              if (live) {
+                const uint32_t at = pending_signals + __popc(mask & ((1u << lane) - 1u));
+                peer_stage->q_token[at] = tok;
+                peer_stage->q_group_units[at] = ctl->sig_group[j] | (units << 8);
               }
+              pending_signals += __popc(mask);
             }
           }
         }
       }
+    }
+    if constexpr (kToPeers) {
+      // What is still queued (also after a failed wait: rows that were stored are announced).
+      if (warp == 4 && pending_signals > 0) flush_signals(p, peer_stage, pending_signals, lane);
     }
   }
 

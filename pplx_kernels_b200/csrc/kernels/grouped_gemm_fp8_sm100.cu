@@ -71,6 +71,16 @@ struct SharedControl {
 
 constexpr uint32_t kNoSignalFp8 = 0xffffffffu;
 
+// Staging of the peer-storing epilogue: per fold warp 32 rows x (64 B + 16 B pad).
+constexpr int kFp8StageRowBytes = 80;
+constexpr uint32_t kSignalQueue = 512;
+struct Fp8PeerStage {
+  uint8_t rows[8][32][kFp8StageRowBytes];
+  unsigned long long row_off[kBlockM];  // arena offset of each tile row's combine slot
+  uint32_t q_token[kSignalQueue];        // queued arrival adds: token ...
+  uint32_t q_group_units[kSignalQueue];  // ... first rank of its DP group | columns << 8
+};
+
 __device__ __forceinline__ float silu(float v) { return v / (1.0f + __expf(-v)); }
 
 // 32 lanes x 16 consecutive columns.
@@ -153,9 +163,10 @@ namespace {
 
 constexpr size_t kMaxSrcEntriesFp8 = 2048;
 
-size_t fp8_smem_bytes(size_t experts, size_t src_entries) {
+size_t fp8_smem_bytes(size_t experts, size_t src_entries, bool to_peers) {
   return 1024 + kStages * kStageBytes + sizeof(SharedControl) +
-         sizeof(uint32_t) * (3 * experts + 1 + src_entries);
+         sizeof(uint32_t) * (3 * experts + 1 + src_entries) +
+         (to_peers ? sizeof(Fp8PeerStage) + 16 : 0);
 }
 
 void check_fp8_call(const Fp8GemmCall& c, bool need_x, bool need_out) {
@@ -200,7 +211,7 @@ void launch_fp8(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const Fp8G
   auto* kernel = grouped_gemm_fp8_kernel<kSwiGLUQuant, kFromStaging, kToPeers>;
   const size_t src_entries =
       (kFromStaging && g.src_table != 0) ? static_cast<size_t>(g.num_experts) * g.a2a.world : 0;
-  const size_t smem = fp8_smem_bytes(g.num_experts, src_entries);
+  const size_t smem = fp8_smem_bytes(g.num_experts, src_entries, kToPeers);
   PPLX_CHECK(smem <= 227 * 1024, "the tile tables of " << g.num_experts << " experts need "
                                                        << smem << " bytes of shared memory");
   CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -254,9 +265,6 @@ void launch_gemm_fp8_to_peers(const Fp8GemmCall& c, const A2AParams& p, cudaStre
   PPLX_CHECK(c.counts == reinterpret_cast<const int32_t*>(p.recv_count),
              "counts must be the all-to-all's received-row counts");
   PPLX_CHECK(p.dp_size <= 8, "at most 8 replicas per DP group");
-  PPLX_CHECK(p.comb_units % ceil_div(c.n_out, kTileN) == 0,
-             "the arrival units of a row (" << p.comb_units << ") must be a multiple of the "
-             "output's 256-column blocks (" << ceil_div(c.n_out, kTileN) << ")");
   const CUtensorMap tmap_a =
       make_byte_map(c.x, c.num_experts, c.rows_per_expert, c.k, c.x_stride_row, c.x_stride_e);
   const CUtensorMap tmap_b =

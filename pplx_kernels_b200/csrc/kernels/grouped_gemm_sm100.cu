@@ -87,6 +87,16 @@ constexpr int kMaxExperts = 1024;
 
 constexpr uint32_t kNoSignal = 0xffffffffu;
 
+// Peer-storing epilogue: an epilogue thread owns one ROW of the tile, so storing straight from
+// registers would send 32 separate 16-byte pieces per instruction over NVLink.  Each epilogue
+// warp therefore passes 64 columns at a time through a [32 rows][128 B + 16 B pad] buffer in
+// shared memory and writes them out as 128-byte row segments (eight lanes per row).
+constexpr int kOutStageRowBytes = 144;
+struct PeerStage {
+  uint8_t rows[4][32][kOutStageRowBytes];   // one buffer per epilogue warp
+  unsigned long long row_off[2][kBlockM];   // arena offset of each tile row's combine slot
+};
+
 // One tensor map of the weights per candidate tile width (the TMA box height is
 // fixed in the map); the kernel picks the width once it knows the real row counts.
 struct WeightMaps {
@@ -181,6 +191,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   gt.a_row0 = gt.rows + num_groups;
   gt.out_row0 = gt.a_row0 + num_groups;
   gt.src_rows = (kFromStaging && g.src_table != 0) ? gt.out_row0 + num_groups : nullptr;
+  // (kToPeers only) staging of the peer-storing epilogue, behind the tables, 16-byte aligned.
+  PeerStage* peer_stage = reinterpret_cast<PeerStage*>(
+      (reinterpret_cast<uintptr_t>(gt.out_row0 + num_groups) + 15) & ~static_cast<uintptr_t>(15));
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
@@ -493,8 +506,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 
       // Where this thread's row goes.
       __nv_bfloat16* local_row = nullptr;
-      uint8_t* peer_row[kToPeers ? 8 : 1];
-      int replicas = 0;
+      size_t peer_off = 0;
+      const int replicas = kToPeers ? min(p.dp_size, 8) : 0;
       uint32_t sig_token = kNoSignal, sig_group = 0;
       if constexpr (kToPeers) {
         if (row_ok) {
@@ -506,11 +519,7 @@ __global__ void __launch_bounds__(kThreads, 1)
               src_rank < p.world) {
             sig_token = token;
             sig_group = static_cast<uint32_t>((src_rank / p.dp_size) * p.dp_size);
-            replicas = min(p.dp_size, 8);
-            for (int r = 0; r < replicas; ++r) {
-              peer_row[r] = p.peer[sig_group + r] + p.off_comb_stage +
-                            (static_cast<size_t>(token) * p.topk + k) * row_bytes_out;
-            }
+            peer_off = p.off_comb_stage + (static_cast<size_t>(token) * p.topk + k) * row_bytes_out;
           } else if (p.debug_checks) {
             report_failure(p.status, kBadToken, kPhaseCombinePayload, src_rank, p.max_tokens,
                            token, p.rank);
@@ -533,6 +542,15 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
 
+      if constexpr (kToPeers) {
+        // The rows' destinations, for the lanes that will store other rows' segments and for
+        // the signalling below.  (Double buffered by accumulator; the barrier at the end of
+        // every tile keeps the epilogue warps within one tile of each other.)
+        ctl->sig_token[buf][tile_row] = sig_token;
+        ctl->sig_group[buf][tile_row] = sig_group;
+        peer_stage->row_off[buf][tile_row] = peer_off;
+        __syncwarp();
+      }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(ew * 32) << 16) + buf * kBlockN;
       const int col0 = c.n_blk * out_cols_per_tile;
 #pragma unroll 1
@@ -558,19 +576,47 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         const int col = col0 + chunk * 32;
+        if constexpr (kToPeers) {
+          uint8_t* stg = &peer_stage->rows[ew][0][0];
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          if (chunk * 32 + v * 8 + 8 > out_cols_per_tile || col + v * 8 + 8 > g.n_out) continue;
-          int4 q;
-          q.x = packed[4 * v];
-          q.y = packed[4 * v + 1];
-          q.z = packed[4 * v + 2];
-          q.w = packed[4 * v + 3];
-          if constexpr (kToPeers) {
-            for (int r = 0; r < replicas; ++r) {
-              ptx::st_v4(peer_row[r] + static_cast<size_t>(col + v * 8) * 2, q);
+          for (int v = 0; v < 4; ++v) {
+            int4 q;
+            q.x = packed[4 * v];
+            q.y = packed[4 * v + 1];
+            q.z = packed[4 * v + 2];
+            q.w = packed[4 * v + 3];
+            *reinterpret_cast<int4*>(stg + lane * kOutStageRowBytes + (chunk & 1) * 64 + v * 16) = q;
+          }
+          const bool last_chunk = (chunk + 1) * 32 >= out_cols_per_tile;
+          if ((chunk & 1) == 1 || last_chunk) {
+            __syncwarp();
+            const int pair0 = (chunk & ~1) * 32;  // first tile column of the staged pair
+            const int seg = lane & 7;             // 16-byte piece of the row's 128 bytes
+            const int tcol = pair0 + seg * 8;
+            const bool seg_ok = seg * 8 < ((chunk & 1) + 1) * 32 && tcol + 8 <= out_cols_per_tile &&
+                                col0 + tcol + 8 <= g.n_out;
+#pragma unroll 2
+            for (int it = 0; it < 8; ++it) {
+              const int rr = it * 4 + (lane >> 3);
+              const int trow = ew * 32 + rr;
+              if (seg_ok && ctl->sig_token[buf][trow] != kNoSignal) {
+                const int4 q = *reinterpret_cast<const int4*>(stg + rr * kOutStageRowBytes + seg * 16);
+                const uint32_t grp = ctl->sig_group[buf][trow];
+                const size_t off = peer_stage->row_off[buf][trow] + static_cast<size_t>(col0 + tcol) * 2;
+                for (int r = 0; r < replicas; ++r) ptx::st_v4(p.peer[grp + r] + off, q);
+              }
             }
-          } else {
+            __syncwarp();
+          }
+        } else {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (chunk * 32 + v * 8 + 8 > out_cols_per_tile || col + v * 8 + 8 > g.n_out) continue;
+            int4 q;
+            q.x = packed[4 * v];
+            q.y = packed[4 * v + 1];
+            q.z = packed[4 * v + 2];
+            q.w = packed[4 * v + 3];
             if (row_ok) *reinterpret_cast<int4*>(local_row + col + v * 8) = q;
           }
         }
@@ -584,15 +630,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
 
       if constexpr (kToPeers) {
-        // One fence for the whole tile, then the adds.  The sig arrays are double
-        // buffered by accumulator; the barrier below keeps the epilogue warps
-        // within one tile of each other.
-        ctl->sig_token[buf][tile_row] = sig_token;
-        ctl->sig_group[buf][tile_row] = sig_group;
+        // One fence for the whole tile, then the adds.
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (ew == 0) {
           ptx::fence_acq_rel_sys();
-          const uint32_t units = static_cast<uint32_t>(p.comb_units / n_blocks);
+          // Arrival is counted in columns: this tile's share of the row.
+          const uint32_t units = static_cast<uint32_t>(min(out_cols_per_tile, g.n_out - col0));
           for (int j = lane; j < kBlockM; j += 32) {
             const uint32_t tok = ctl->sig_token[buf][j];
             if (tok == kNoSignal) continue;
@@ -662,11 +705,13 @@ CUtensorMap make_operand_map(const void* base, int64_t experts, int64_t rows, in
   return map;
 }
 
-// `src_entries`: entries of the per-source row table of the staging-fed form (0: none).
-size_t smem_bytes(int num_groups, size_t src_entries = 0) {
+// `src_entries`: entries of the per-source row table of the staging-fed form (0: none);
+// `to_peers`: room for the peer-storing epilogue's staging.
+size_t smem_bytes(int num_groups, size_t src_entries = 0, bool to_peers = false) {
   static_assert(kStages * kStageBytes == kStages2 * kStageBytes2, "both rings use 192 KiB");
   return 1024 + kStages * kStageBytes + sizeof(SharedControl) +
-         sizeof(uint32_t) * (4 * static_cast<size_t>(num_groups) + 1 + src_entries);
+         sizeof(uint32_t) * (4 * static_cast<size_t>(num_groups) + 1 + src_entries) +
+         (to_peers ? sizeof(PeerStage) + 16 : 0);
 }
 
 // The per-source table is kept in shared memory when it is at most this many entries.
@@ -678,7 +723,7 @@ void launch_one(const CUtensorMap& tmap_a, const WeightMaps& tmap_b, const Group
   auto* kernel = grouped_gemm_kernel<SWIGLU, kFromStaging, kToPeers, kTwoCta>;
   const size_t src_entries =
       (kFromStaging && g.src_table != 0) ? static_cast<size_t>(num_groups) * g.a2a.world : 0;
-  const size_t smem = smem_bytes(num_groups, src_entries);
+  const size_t smem = smem_bytes(num_groups, src_entries, kToPeers);
   PPLX_CHECK(smem <= 227 * 1024, "the tile tables of " << num_groups << " experts need " << smem
                                                        << " bytes of shared memory");
   CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -821,7 +866,7 @@ void launch_gemm_to_peers(const GroupedGemmCall& c, const A2AParams& p, cudaStre
   const CUtensorMap tmap_a = make_operand_map(c.x, c.num_experts, c.rows_per_expert, c.k,
                                               c.x_stride_row, c.x_stride_e);
   GroupedGemmArgs g = base_args(c);
-  const WeightMaps tmap_b = weight_maps(c, g, p.comb_units);
+  const WeightMaps tmap_b = weight_maps(c, g, 0);
   g.out = nullptr;
   g.a2a = p;
   launch_variant<false, false, true>(tmap_a, tmap_b, g, c.num_experts, grid, two_cta, stream);

@@ -102,7 +102,7 @@ A2AParams make_layout(const A2AConfig& c, std::vector<size_t>* canaries = nullpt
   const int tokens_per_sender = ceil_div(c.max_num_tokens, c.dp_size);
   p.region_slots = tokens_per_sender * std::min(c.experts_per_token, p.nle);
   p.cap = c.max_num_tokens * p.num_dp_groups;
-  p.comb_units = 16;
+  p.comb_units = c.hidden_dim;  // one arrival unit per column of an expert output row
   // Flag-in-data staging: a dispatch row is its payload lines followed by the lines of
   // its meta stream (4 trailer words, then the scales); a combine row is sized for fp32.
   p.ll_x_lines = ll::lines_for(c.hidden_dim_bytes);
@@ -294,9 +294,10 @@ void AllToAll::reset() {
   CUDA_CHECK(cudaDeviceSynchronize());
 }
 
-void AllToAll::set_combine_units(int units) {
-  PPLX_CHECK(units > 0 && units % 16 == 0, "combine units must be a positive multiple of 16");
-  params_.comb_units = units;
+void AllToAll::set_combine_units(int) {
+  // Kept for callers of earlier versions: arrival is counted in columns now, so any sender
+  // (a row part of the combine kernel, a column block of a GEMM epilogue) adds what it covers
+  // and nothing has to be agreed beforehand.
 }
 
 void AllToAll::set_trace(bool on) { params_.trace = on ? trace_.get() : nullptr; }

@@ -188,9 +188,7 @@ class AllToAll {
   void set_timeout_ms(double ms);
   void set_debug_checks(bool on) { params_.debug_checks = on ? 1 : 0; }
   void set_max_blocks(int n) { max_blocks_ = n; }
-  // Arrival units one complete expert-output row is worth (default 16).  All ranks
-  // must agree; the GEMM whose epilogue stores to peers needs a multiple of its
-  // number of column blocks.  Change only between a combine and the next dispatch.
+  // No effect (arrival is counted in columns of the row); kept for source compatibility.
   void set_combine_units(int units);
   // Per-phase %globaltimer stamps of block 0 (see TraceSlot); synchronises on read.
   void set_trace(bool on);

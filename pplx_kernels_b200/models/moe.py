@@ -20,8 +20,6 @@ pass can be captured in a CUDA graph.
 
 from __future__ import annotations
 
-import math
-
 import torch
 
 from ..all_to_all import AllToAll
@@ -71,8 +69,6 @@ class MoELayer:
         self.h = torch.zeros(self.nle, self.rows, I, dtype=torch.bfloat16, device=dev)
         self.expert_y = torch.zeros(self.nle, self.rows, H, dtype=torch.bfloat16, device=dev)
         self.gemm_status = torch.zeros(1, dtype=torch.int32, device=dev)
-        # The fused down projection signals once per 256-column block of the output.
-        self.ata.set_combine_units(math.lcm(16, (H + 255) // 256))
 
     def forward(self, x: torch.Tensor, indices: torch.Tensor, weights: torch.Tensor,
                 out: torch.Tensor | None = None, bound_m: torch.Tensor | None = None,
@@ -167,8 +163,6 @@ class MoELayerFP8:
         self.ata = ata or AllToAll.intranode(
             max_num_tokens, cfg.num_experts, cfg.experts_per_token, rank, world_size, dp_size,
             H, H, nscale * 4, group_name=group_name)
-        # The fused down projection signals once per 256-column block of the output.
-        self.ata.set_combine_units(math.lcm(16, (H + 255) // 256))
         dev = self.device
         w13, w2 = _random_expert_weights(cfg, rank * self.nle, self.nle, seed, init_std, dev)
         self.w13_q, self.w13_s = quantize_weight_blocks(w13)

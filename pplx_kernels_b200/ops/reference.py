@@ -69,16 +69,20 @@ def simulate_dispatch(
     inputs: Sequence[RankInputs], num_experts: int, dp_size: int
 ) -> list[ExpectedDispatch]:
     """``inputs[r]`` is rank r's data; ranks of one DP group must hold equal data."""
+    from ..parallel.placement import EPLayout
+
     world = len(inputs)
-    nle = -(-num_experts // world)  # blocks of ceil(E / W); the last rank(s) own fewer
-    out = [ExpectedDispatch([[] for _ in range(nle)]) for _ in range(world)]
+    layout = EPLayout(num_experts, world, dp_size)  # who owns an expert, who sends a token
+    out = [ExpectedDispatch([[] for _ in range(layout.num_local_experts)]) for _ in range(world)]
     for src in range(world):
-        dp_rank = src % dp_size
+        group = layout.dp_group(src)
         idx = inputs[src].indices.cpu().to(torch.int64)
-        for i in range(dp_rank, inputs[src].num_tokens, dp_size):
+        for i in range(inputs[src].num_tokens):
+            if layout.sender_of(group, i) != src:
+                continue
             for k in range(idx.size(1)):
                 e = int(idx[i, k])
-                out[e // nle].rows[e % nle].append((src, i, k))
+                out[layout.owner(e)].rows[layout.local_index(e)].append((src, i, k))
     return out
 
 

@@ -69,20 +69,29 @@ def verify_layer(layer, fp8: bool, x: torch.Tensor, idx: torch.Tensor, w: torch.
         torch.cuda.synchronize()
         layer.check_status()
     params = cfg.num_experts * 3 * cfg.hidden_dim * cfg.intermediate_dim
+    def close(got: torch.Tensor, want: torch.Tensor, rel: float, of_max: float, what: str) -> None:
+        # Elementwise: a share of the value plus a share of the largest value (a rounding of
+        # an intermediate moves a small output by an amount that scales with the row).
+        err = (got - want).abs()
+        bound = rel * want.abs() + of_max * want.abs().amax()
+        assert (err <= bound).all(), (
+            f"{what}: largest error {float(err.max()):.4g} where {float(bound[err.argmax()] if err.dim() == 1 else bound.flatten()[err.argmax()]):.4g} "
+            f"is allowed (largest value {float(want.abs().amax()):.4g})")
+
+    # The two paths do the same arithmetic; they may differ by roundings of the top-k sums only.
+    close(outs["fused"], outs["composed"], 2e-2, 5e-3, "fused against composed")
     if params > VERIFY_MAX_PARAMS:
-        torch.testing.assert_close(outs["fused"], outs["composed"], rtol=3e-2, atol=3e-3)
         return "fused against composed (the model is too large to gather for the reference)"
     if fp8:
         w13, w2 = layer.dequantized_weights()
         want = moe_reference_fp8(x, idx.to(dev), w, _gather(w13, world), _gather(w2, world))
         for name, out in outs.items():
-            err = (out - want).abs()
-            assert (err <= 0.06 * want.abs() + 0.03 * want.abs().amax()).all(), (name, float(err.max()))
+            close(out, want, 0.06, 0.04, f"{name} against the fp8 reference")
     else:
         want = moe_reference(x, idx.to(dev), w, _gather(layer.w13, world), _gather(layer.w2, world))
-        for out in outs.values():
-            torch.testing.assert_close(out, want, rtol=3e-2, atol=3e-3)
-    return "fused and composed against the PyTorch reference over all experts"
+        for name, out in outs.items():
+            close(out, want, 3e-2, 1e-2, f"{name} against the reference")
+    return "fused and composed against the PyTorch reference over all experts, and against each other"
 
 
 def measure(model: str, tokens: int, iters: int, warmup: int, rank: int, world: int,
@@ -180,6 +189,82 @@ def measure(model: str, tokens: int, iters: int, warmup: int, rank: int, world: 
     }
 
 
+def breakdown(model: str, tokens: int, iters: int, warmup: int, rank: int, world: int,
+              dev: torch.device, fp8: bool = False) -> dict:
+    """p50 microseconds of each of the four kernels of the layer, composed and fused (CUDA events
+    between the calls, L2 flushed before each pass, max over ranks).  The events add a few
+    microseconds per kernel; the figures are for comparing the kernels, not for the totals."""
+    from pplx_kernels_b200.ops.grouped_gemm import grouped_gemm, grouped_gemm_fp8
+
+    cfg = CONFIGS[model]
+    m = tokens
+    layer = (MoELayerFP8 if fp8 else MoELayer)(cfg, max_num_tokens=m, rank=rank, world_size=world,
+                                               device=dev)
+    gen = torch.Generator().manual_seed(100 + rank)
+    x = torch.randn(m, cfg.hidden_dim, generator=gen).to(torch.bfloat16).to(dev)
+    idx = as_index_tensor(routing(m, cfg.num_experts, cfg.experts_per_token, gen), dev)
+    w = torch.softmax(torch.randn(m, cfg.experts_per_token, generator=gen), dim=-1).to(dev)
+    out = torch.zeros(m, cfg.hidden_dim, dtype=torch.bfloat16, device=dev)
+    flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    a, L = layer.ata, layer
+    expect = m * cfg.experts_per_token
+    if fp8:
+        steps = {
+            "composed": [
+                ("dispatch_quant", lambda: a.dispatch_quant(L.counts, L.expert_x, L.expert_scale, x, idx, None)),
+                ("up", lambda: grouped_gemm_fp8(L.expert_x, L.expert_scale, L.w13_q, L.w13_s, L.counts,
+                                                swiglu_quant=True, out=L.h, out_scale=L.h_scale,
+                                                status=L.gemm_status)),
+                ("down", lambda: grouped_gemm_fp8(L.h, L.h_scale, L.w2_q, L.w2_s, L.counts,
+                                                  out=L.expert_y, status=L.gemm_status)),
+                ("combine", lambda: a.combine(out, idx, w, L.expert_y, None))],
+            "fused": [
+                ("fused_dispatch", lambda: a.fused_dispatch(x, idx, None, quantize=True)),
+                ("fused_up", lambda: a.fused_up_fp8(L.w13_q, L.w13_s, L.h, L.h_scale, L.counts, L.gemm_status)),
+                ("fused_down", lambda: a.fused_down_fp8(L.h, L.h_scale, L.w2_q, L.w2_s, L.gemm_status)),
+                ("combine_recv", lambda: a.combine(out, idx, w, L.expert_y, None, do_send=False))]}
+    else:
+        steps = {
+            "composed": [
+                ("dispatch", lambda: a.dispatch(L.counts, L.expert_x, None, x, None, idx, None)),
+                ("up", lambda: grouped_gemm(L.expert_x, L.w13, L.counts, out=L.h, swiglu=True,
+                                            status=L.gemm_status, expected_rows=expect)),
+                ("down", lambda: grouped_gemm(L.h, L.w2, L.counts, out=L.expert_y, swiglu=False,
+                                              status=L.gemm_status, expected_rows=expect)),
+                ("combine", lambda: a.combine(out, idx, w, L.expert_y, None))],
+            "fused": [
+                ("fused_dispatch", lambda: a.fused_dispatch(x, idx, None)),
+                ("fused_up", lambda: a.fused_up(L.w13, L.h, L.counts, L.gemm_status, expect)),
+                ("fused_down", lambda: a.fused_down(L.h, L.w2, L.gemm_status, expect)),
+                ("combine_recv", lambda: a.combine(out, idx, w, L.expert_y, None, do_send=False))]}
+    report: dict = {"model": cfg.name, "n_gpus": world, "tokens_per_gpu": m, "fp8": fp8}
+    for variant, calls in steps.items():
+        samples = []
+        for it in range(warmup + iters):
+            flush.add_(1)
+            torch.cuda.synchronize()
+            if world > 1:
+                torch.distributed.barrier()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(len(calls) + 1)]
+            ev[0].record()
+            for k, (_, fn) in enumerate(calls):
+                fn()
+                ev[k + 1].record()
+            torch.cuda.synchronize()
+            if it >= warmup:
+                samples.append([ev[k].elapsed_time(ev[k + 1]) * 1e3 for k in range(len(calls))]
+                               + [ev[0].elapsed_time(ev[-1]) * 1e3])
+        t = torch.tensor(samples, dtype=torch.float64, device=dev)
+        if world > 1:
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        med = t.median(dim=0).values.tolist()
+        report[variant] = {name: med[k] for k, (name, _) in enumerate(calls)}
+        report[variant]["total"] = med[-1]
+    layer.check_status()
+    layer.destroy()
+    return report
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", choices=sorted(CONFIGS), default="mixtral-8x7b")
@@ -191,6 +276,8 @@ def main() -> None:
     ap.add_argument("--fp8", action="store_true", help="block-scaled fp8 layer (MoELayerFP8)")
     ap.add_argument("--replays", type=int, default=1, help="graph replays per timed sample")
     ap.add_argument("--no-verify", action="store_true", help="skip the output check")
+    ap.add_argument("--breakdown", action="store_true",
+                    help="time each of the layer's four kernels instead of the layer")
     args = ap.parse_args()
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -202,6 +289,11 @@ def main() -> None:
         torch.distributed.init_process_group(backend="cpu:gloo,cuda:nccl", device_id=dev)
     flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
     for tokens in (int(t) for t in args.tokens.split(",")):
+        if args.breakdown:
+            row = breakdown(args.model, tokens, args.iters, args.warmup, rank, world, dev, args.fp8)
+            if rank == 0:
+                print(json.dumps(row), flush=True)
+            continue
         row = measure(args.model, tokens, args.iters, args.warmup, rank, world, dev, args.zipf,
                       args.graph, flush, args.fp8, args.replays, not args.no_verify)
         if rank == 0:

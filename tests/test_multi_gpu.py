@@ -261,12 +261,18 @@ def _worker_moe_layer_fp8(pgi: ProcessGroupInfo, tokens: int) -> None:
     torch.distributed.all_gather(w13_all, w13)
     torch.distributed.all_gather(w2_all, w2)
     want = moe_reference_fp8(x, idx.to(dev), w, torch.cat(w13_all), torch.cat(w2_all))
+    outs = {}
     for fused in (True, False, True):
         out = layer(x, as_index_tensor(idx, dev), w, fused=fused)
         torch.cuda.synchronize()
         layer.check_status()
-        err = (out[:tokens].float() - want).abs()
-        assert (err <= 0.06 * want.abs() + 0.03 * want.abs().amax()).all(), err.max()
+        got = out[:tokens].float().clone()
+        err = (got - want).abs()
+        # two e4m3 roundings of the activations on top of bf16
+        assert (err <= 0.06 * want.abs() + 0.04 * want.abs().amax()).all(), (fused, err.max())
+        outs.setdefault(fused, got)
+    # the fused and the composed path do the same arithmetic
+    torch.testing.assert_close(outs[True], outs[False], rtol=2e-2, atol=2e-3)
     torch.distributed.barrier()
     layer.destroy()
 
