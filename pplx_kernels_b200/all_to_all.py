@@ -275,7 +275,7 @@ class AllToAll:
     def layout(self) -> dict[str, int]:
         keys = ("num_local_experts", "num_dp_groups", "rows_per_expert", "region_slots",
                 "slot_bytes", "arena_bytes", "flag_in_data", "line_slot_bytes",
-                "line_combine_slot_bytes")
+                "line_combine_slot_bytes", "decode_sized_dispatch")
         return dict(zip(keys, _ops.all_to_all_layout(self._ptr), strict=True))
 
     # ------------------------------------------------------------ constructors --

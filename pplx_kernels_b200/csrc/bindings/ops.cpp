@@ -718,7 +718,8 @@ std::vector<int64_t> read_trace_op(int64_t ptr) {
 std::vector<int64_t> layout_op(int64_t ptr) {
   const A2AParams& p = lookup(ptr)->params();
   return {p.nle, p.num_dp_groups, p.cap, p.region_slots, p.slot_bytes,
-          static_cast<int64_t>(p.arena_bytes), p.ll, p.ll_slot_bytes, p.ll_comb_slot_bytes};
+          static_cast<int64_t>(p.arena_bytes), p.ll, p.ll_slot_bytes, p.ll_comb_slot_bytes,
+          p.tiny};
 }
 
 // -------------------------------------------------------- symmetric memory ----

@@ -30,6 +30,14 @@ cudaError_t launch_dispatch(const DispatchArgs& a, bool send, bool recv, int gri
 cudaError_t launch_dispatch_multi(const DispatchMulti& args, int nranks, bool send, bool recv,
                                   int grid, cudaStream_t stream);
 
+// Decode-sized dispatch (dispatch_tiny.cu): objects of a few tokens per rank, lines only.
+bool dispatch_tiny_supports(const A2AParams& p);
+int dispatch_tiny_grid(const A2AParams& p, int limit);
+cudaError_t launch_dispatch_tiny(const DispatchArgs& a, bool send, bool recv, int grid,
+                                 cudaStream_t stream);
+cudaError_t launch_dispatch_tiny_multi(const DispatchMulti& args, int nranks, bool send, bool recv,
+                                       int grid, cudaStream_t stream);
+
 size_t combine_smem_bytes(const A2AParams& p);
 int combine_threads();
 

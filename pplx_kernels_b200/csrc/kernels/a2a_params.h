@@ -69,6 +69,7 @@ struct A2AParams {
   int ll_meta_lines;       // lines that carry its trailer and scales
   int ll_slot_bytes;       // (ll_x_lines + ll_meta_lines) * 128
   int ll_comb_slot_bytes;  // lines of one fp32 expert output row * 128
+  int tiny;                // non-zero: the plain dispatch runs the decode-sized kernel
 
   // offsets into the symmetric arena (bytes, 256-aligned)
   size_t off_counts;        // u32 [2][world][nle]   value = count + 1, 0 = not posted
@@ -84,6 +85,8 @@ struct A2AParams {
   size_t off_comb_stage;    // u8  [max_tokens*topk][hidden_dim*4]
   size_t off_ll_disp_stage; // u8  [world][region_slots][ll_slot_bytes], written only as lines
   size_t off_ll_comb_stage; // u8  [max_tokens*topk][ll_comb_slot_bytes], written only as lines
+  size_t off_tiny_hdr;      // u8  [2][world][ceil(max_tokens/dp_size)][128]: decode-sized dispatch,
+                            //     one header line per (parity, source, token)
   size_t arena_bytes;
 
   uint8_t* peer[kMaxWorld];  // arena base of every rank as mapped in this process

@@ -128,6 +128,7 @@ A2AParams make_layout(const A2AConfig& c, std::vector<size_t>* canaries = nullpt
   p.off_comb_stage = region(static_cast<size_t>(p.max_tokens) * p.topk * p.hidden_dim * 4);
   p.off_ll_disp_stage = region(static_cast<size_t>(p.world) * p.region_slots * p.ll_slot_bytes);
   p.off_ll_comb_stage = region(static_cast<size_t>(p.max_tokens) * p.topk * p.ll_comb_slot_bytes);
+  p.off_tiny_hdr = region(static_cast<size_t>(2) * p.world * tokens_per_sender * ll::kLineBytes);
   p.arena_bytes = off;
   return p;
 }
@@ -176,6 +177,14 @@ AllToAll::AllToAll(const A2AConfig& cfg, std::shared_ptr<SymmetricAllocation> ar
                        (ll_limit <= 0 || cfg_.max_num_tokens <= ll_limit)
                    ? 1
                    : 0;
+  // Decode-sized objects (PPLX_B200_TINY_MAX_TOKENS, default 8, 0 = never) run the plain
+  // dispatch as the header-line kernel of dispatch_tiny.cu: about 2 us faster than the general
+  // kernel at one token per rank, level with it from four tokens on.
+  const long tiny_limit = env_long("PPLX_B200_TINY_MAX_TOKENS", 8);
+  params_.tiny = params_.ll != 0 && tiny_limit > 0 && cfg_.max_num_tokens <= tiny_limit &&
+                         dispatch_tiny_supports(params_)
+                     ? 1
+                     : 0;
   num_sms_ = get_sm_count();
   max_blocks_ = static_cast<int>(env_long("PPLX_B200_NUM_SMS", 0));
   {
@@ -475,6 +484,11 @@ void AllToAll::dispatch(const DispatchCall& call, SplitMode mode, cudaStream_t s
   const DispatchArgs a = make_dispatch_args(call);
   const bool send = mode != SplitMode::kRecv, recv = mode != SplitMode::kSend;
   begin(send ? Step::kDispatchSend : Step::kDispatchRecv, send && recv);
+  if (params_.tiny != 0 && !call.quantize) {
+    const int limit = max_blocks_ > 0 ? std::min(max_blocks_, num_sms_) : num_sms_;
+    CUDA_CHECK(launch_dispatch_tiny(a, send, recv, dispatch_tiny_grid(params_, limit), stream));
+    return;
+  }
   CUDA_CHECK(launch_dispatch(a, send, recv, dispatch_grid(call.num_tokens), stream));
 }
 
@@ -608,6 +622,13 @@ void AllToAll::dispatch_group(const std::vector<AllToAll*>& ranks,
   for (AllToAll* r : ranks) r->begin(send ? Step::kDispatchSend : Step::kDispatchRecv, send && recv);
   DispatchMulti multi{};
   for (int r = 0; r < n; ++r) multi.r[r] = args[r];
+  if (ranks[0]->params_.tiny != 0 && !calls[0].quantize) {
+    const int limit = ranks[0]->max_blocks_ > 0 ? std::min(ranks[0]->max_blocks_, per_rank_limit)
+                                                 : per_rank_limit;
+    CUDA_CHECK(launch_dispatch_tiny_multi(multi, n, send, recv,
+                                          dispatch_tiny_grid(ranks[0]->params_, limit), stream));
+    return;
+  }
   CUDA_CHECK(launch_dispatch_multi(multi, n, send, recv, grid, stream));
 }
 

@@ -34,14 +34,23 @@ def small(in_dtype=torch.bfloat16, out_dtype=torch.bfloat16, **kw) -> MoEConfig:
     return MoEConfig(in_dtype=in_dtype, out_dtype=out_dtype, **base)
 
 
+@pytest.fixture(params=["decode-sized kernel", "general kernel"])
+def dispatch_kernel_kind(request, monkeypatch):
+    """Small objects run the decode-sized dispatch; the same cases must pass on the general
+    kernel, which larger objects use."""
+    monkeypatch.setenv("PPLX_B200_TINY_MAX_TOKENS",
+                       "0" if request.param == "general kernel" else "64")
+    return request.param
+
+
 @pytest.mark.parametrize("in_dtype", [torch.bfloat16, torch.float8_e4m3fn, torch.float16])
 @pytest.mark.parametrize("out_dtype", [torch.float16, torch.bfloat16])
-def test_world4_dp2_dtype_matrix(in_dtype, out_dtype):
+def test_world4_dp2_dtype_matrix(in_dtype, out_dtype, dispatch_kernel_kind):
     run_local_world(small(in_dtype, out_dtype), world=4, dp_size=2, seed=123)
 
 
 @pytest.mark.parametrize("world,dp_size", [(1, 1), (2, 1), (2, 2), (4, 1), (4, 4), (8, 1), (8, 2)])
-def test_expert_parallel_sizes(world, dp_size):
+def test_expert_parallel_sizes(world, dp_size, dispatch_kernel_kind):
     cfg = small(torch.float8_e4m3fn, num_experts=16, experts_per_token=4, hidden_dim=256,
                 max_num_tokens=12)
     run_local_world(cfg, world=world, dp_size=dp_size, seed=5)
@@ -57,7 +66,7 @@ def test_expert_count_that_does_not_divide_evenly(world, dp_size, num_experts):
 
 @pytest.mark.parametrize("use_bound_m", [True, False])
 @pytest.mark.parametrize("counts", [[0, 5, 0, 12], [0, 0, 0, 0], [1, 0, 0, 0]])
-def test_ranks_without_tokens(counts, use_bound_m):
+def test_ranks_without_tokens(counts, use_bound_m, dispatch_kernel_kind):
     """bound_m = 0 on some or all ranks: they still post counts, forward what they receive
     and keep their arrival counters in step."""
     cfg = small(torch.float8_e4m3fn, num_experts=16, experts_per_token=4, hidden_dim=256,
@@ -82,7 +91,7 @@ def test_tiny_hidden_dim():
 
 
 @pytest.mark.parametrize("in_dtype", [torch.bfloat16, torch.float8_e4m3fn])
-def test_split_send_recv(in_dtype):
+def test_split_send_recv(in_dtype, dispatch_kernel_kind):
     run_local_world(small(in_dtype), world=4, dp_size=2, seed=11, split=True, iterations=2)
 
 
@@ -90,11 +99,11 @@ def test_without_bound_m():
     run_local_world(small(torch.float8_e4m3fn), world=4, dp_size=1, seed=12, use_bound_m=False)
 
 
-def test_strided_scales():
+def test_strided_scales(dispatch_kernel_kind):
     run_local_world(small(torch.float8_e4m3fn), world=2, dp_size=1, seed=13, strided_scale=True)
 
 
-def test_many_iterations_on_one_object():
+def test_many_iterations_on_one_object(dispatch_kernel_kind):
     # Exercises both parities of the flag sets and the self-reset of all counters.
     run_local_world(small(torch.float8_e4m3fn), world=4, dp_size=2, seed=21, iterations=7)
 
@@ -469,8 +478,13 @@ def test_flag_in_data_lines_are_the_default_and_can_be_switched_off(monkeypatch)
     cfg = small()
     args = (cfg.max_num_tokens, cfg.num_experts, cfg.experts_per_token, 0, 1, 1, cfg.hidden_dim,
             cfg.hidden_dim_bytes, cfg.hidden_dim_scale_bytes)
+    monkeypatch.setenv("PPLX_B200_TINY_MAX_TOKENS", str(cfg.max_num_tokens))
     ata = pk.AllToAll.intranode(*args)
-    assert ata.layout()["flag_in_data"] == 1
+    assert ata.layout()["flag_in_data"] == 1 and ata.layout()["decode_sized_dispatch"] == 1
+    ata.destroy()
+    monkeypatch.setenv("PPLX_B200_TINY_MAX_TOKENS", str(cfg.max_num_tokens - 1))
+    ata = pk.AllToAll.intranode(*args)
+    assert ata.layout()["flag_in_data"] == 1 and ata.layout()["decode_sized_dispatch"] == 0
     ata.destroy()
     monkeypatch.setenv("PPLX_B200_LL", "0")
     ata = pk.AllToAll.intranode(*args)
@@ -620,7 +634,7 @@ def test_duplicate_experts_in_a_token_are_reported_not_written_past_the_region()
         r.destroy()
 
 
-def test_world_graph_replayed_with_a_changing_bound_m():
+def test_world_graph_replayed_with_a_changing_bound_m(dispatch_kernel_kind):
     """All ranks of an emulated world inside one CUDA graph (dispatch, expert, combine),
     replayed many times; bound_m of one DP group changes between replays.  Graph replay across
     ranks is what leans hardest on the iteration-numbered flags."""
@@ -676,7 +690,7 @@ def test_world_graph_replayed_with_a_changing_bound_m():
             r.destroy()
 
 
-def test_a_rank_may_run_one_dispatch_ahead_of_a_peer():
+def test_a_rank_may_run_one_dispatch_ahead_of_a_peer(dispatch_kernel_kind):
     """Rank S, whose tokens of step n use none of rank A's experts, finishes its combine
     without waiting for A and sends the rows of dispatch n + 1 to A before A has read the
     rows of dispatch n.  Flags and staging are kept per parity, so A still receives step n
