@@ -275,8 +275,13 @@ class AllToAll:
     def layout(self) -> dict[str, int]:
         keys = ("num_local_experts", "num_dp_groups", "rows_per_expert", "region_slots",
                 "slot_bytes", "arena_bytes", "flag_in_data", "line_slot_bytes",
-                "line_combine_slot_bytes", "decode_sized_dispatch")
+                "line_combine_slot_bytes", "decode_sized_dispatch", "vmm_arena", "multicast")
         return dict(zip(keys, _ops.all_to_all_layout(self._ptr), strict=True))
+
+    def multicast_note(self) -> str:
+        """Why NVLink multicast was asked for (``PPLX_B200_MULTIMEM=1``) but is not in use;
+        empty when it is in use or was not asked for."""
+        return _ops.all_to_all_multicast_note(self._ptr)
 
     # ------------------------------------------------------------ constructors --
 

@@ -10,6 +10,9 @@
 #include <mutex>
 #include <unordered_map>
 
+#include <sys/mman.h>
+#include <unistd.h>
+
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/csrc/distributed/c10d/GroupRegistry.hpp>
@@ -21,6 +24,7 @@
 #include "../runtime/all_to_all.h"
 #include "../runtime/bootstrap.h"
 #include "../runtime/runtime.h"
+#include "../runtime/vmm.h"
 #include "registration.h"
 
 namespace pplx {
@@ -719,7 +723,10 @@ std::vector<int64_t> layout_op(int64_t ptr) {
   const A2AParams& p = lookup(ptr)->params();
   return {p.nle, p.num_dp_groups, p.cap, p.region_slots, p.slot_bytes,
           static_cast<int64_t>(p.arena_bytes), p.ll, p.ll_slot_bytes, p.ll_comb_slot_bytes,
-          p.tiny};
+          p.tiny, lookup(ptr)->arena().from_vmm() ? 1 : 0, p.mc != nullptr ? 1 : 0};
+}
+
+std::string multicast_note_op(int64_t ptr) { return lookup(ptr)->arena().multicast_note();
 }
 
 // -------------------------------------------------------- symmetric memory ----
@@ -824,6 +831,43 @@ at::Tensor bootstrap_selftest_op(const at::Tensor& uid, int64_t rank, int64_t wo
   });
 }
 
+// Host-only exercise of the descriptor exchange that the VMM arena uses: every rank puts a
+// word into an anonymous file and passes the descriptor to all peers (the last rank of a
+// world of three or more passes none); returns what was read through the received
+// descriptors, -1 where none came, -2 at the caller's own index.
+at::Tensor fd_exchange_selftest_op(const at::Tensor& uid, int64_t rank, int64_t world_size,
+                                   int64_t timeout_ms) {
+  TORCH_CHECK(uid.device().is_cpu() && uid.scalar_type() == at::kByte &&
+                  uid.numel() == static_cast<int64_t>(kUniqueIdBytes),
+              "uid must be a CPU uint8 tensor of ", kUniqueIdBytes, " bytes");
+  return guarded([&] {
+    UniqueId id{};
+    std::memcpy(id.bytes, uid.contiguous().data_ptr(), kUniqueIdBytes);
+    SocketBootstrap bs(id, static_cast<int>(rank), static_cast<int>(world_size),
+                       static_cast<int>(timeout_ms));
+    int mine = -1;
+    if (!(world_size >= 3 && rank == world_size - 1)) {
+      mine = ::memfd_create("pplx-fd-selftest", MFD_CLOEXEC);
+      PPLX_CHECK(mine >= 0, "memfd_create failed");
+      const int64_t word = 7000 + rank;
+      PPLX_CHECK(::pwrite(mine, &word, sizeof(word), 0) == sizeof(word), "pwrite failed");
+    }
+    const std::vector<int> fds = exchange_fds(bs, mine, static_cast<int>(timeout_ms));
+    if (mine >= 0) ::close(mine);
+    at::Tensor out = at::full({world_size}, -1, at::TensorOptions().dtype(at::kLong));
+    int64_t* o = out.data_ptr<int64_t>();
+    o[rank] = -2;
+    for (int64_t r = 0; r < world_size; ++r) {
+      if (fds[r] < 0) continue;
+      int64_t word = 0;
+      PPLX_CHECK(::pread(fds[r], &word, sizeof(word), 0) == sizeof(word), "pread failed");
+      o[r] = word;
+      ::close(fds[r]);
+    }
+    return out;
+  });
+}
+
 void sleep_on_stream_op(double seconds) {
   CUDA_CHECK(launch_sleep(static_cast<uint64_t>(seconds * 1e9), at::cuda::getCurrentCUDAStream()));
 }
@@ -904,6 +948,7 @@ void register_all_to_all_ops(torch::Library& m) {
   m.def("all_to_all_set_debug_checks(int ptr, bool on) -> ()", &set_debug_checks_op);
   m.def("all_to_all_set_max_blocks(int ptr, int n) -> ()", &set_max_blocks_op);
   m.def("all_to_all_layout(int ptr) -> int[]", &layout_op);
+  m.def("all_to_all_multicast_note(int ptr) -> str", &multicast_note_op);
   m.def("all_to_all_set_trace(int ptr, bool on) -> ()", &set_trace_op);
   m.def("all_to_all_set_combine_units(int ptr, int units) -> ()", &set_combine_units_op);
   m.def("moe_dispatch_send(int ptr, Tensor dp_x, Tensor indices, Tensor? bound_m, "
@@ -948,6 +993,8 @@ void register_symmetric_memory_ops(torch::Library& m) {
 
   m.def("bootstrap_selftest(Tensor uid, int rank, int world_size, int timeout_ms) -> Tensor",
         &bootstrap_selftest_op);
+  m.def("fd_exchange_selftest(Tensor uid, int rank, int world_size, int timeout_ms) -> Tensor",
+        &fd_exchange_selftest_op);
   m.def("sleep_on_stream(float seconds) -> ()", &sleep_on_stream_op);
   m.def("wait_probe(Tensor flag, float timeout_ms) -> int[]", &wait_probe_op);
 }

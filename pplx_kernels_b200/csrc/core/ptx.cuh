@@ -42,6 +42,16 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+// Stores and reductions through an NVLink multicast mapping: the NVSwitch applies them to the
+// same offset of every GPU bound to the multicast object.
+__device__ __forceinline__ void multimem_st_relaxed_sys(void* mc, uint32_t v) {
+  asm volatile("multimem.st.relaxed.sys.global.b32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void multimem_red_add_release_sys(void* mc, uint32_t v) {
+  asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
+
 __device__ __forceinline__ void st_volatile(uint32_t* p, uint32_t v) {
   asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }

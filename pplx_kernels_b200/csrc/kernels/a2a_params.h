@@ -90,6 +90,7 @@ struct A2AParams {
   size_t arena_bytes;
 
   uint8_t* peer[kMaxWorld];  // arena base of every rank as mapped in this process
+  uint8_t* mc;  // NVLink multicast alias of the arenas (same offsets on all ranks), or nullptr
 
   // rank-local state (plain device memory)
   uint32_t* iter;         // dispatch iteration counter; its parity selects the flag set

@@ -10,17 +10,26 @@ __global__ void barrier_kernel(const __grid_constant__ BarrierParams b) {
   const int tid = threadIdx.x;
   const uint32_t target = ptx::ld_volatile(b.epoch) + 1u;
   __syncthreads();
-  if (tid < b.world) {
+  // Epochs only grow; compare modulo 2^32.
+  struct Reached {
+    uint32_t t;
+    __device__ bool operator()(uint32_t v) const { return static_cast<int32_t>(v - t) >= 0; }
+  };
+  if (b.mc != nullptr) {
+    if (tid == 0) {
+      ptx::multimem_red_add_release_sys(reinterpret_cast<uint32_t*>(b.mc) + kBarrierMcWord, 1u);
+      const uint32_t* mine = reinterpret_cast<const uint32_t*>(b.peer[b.rank]) + kBarrierMcWord;
+      const WaitCtx w{b.status, b.timeout_ns, static_cast<uint32_t>(b.rank)};
+      const uint32_t want = target * static_cast<uint32_t>(b.world);
+      uint32_t seen;
+      wait_until(mine, Reached{want}, seen, w, kPhaseBarrier, 0u, want);
+    }
+  } else if (tid < b.world) {
     uint32_t* remote = reinterpret_cast<uint32_t*>(b.peer[tid]) + b.rank;
     ptx::st_release_sys(remote, target);
     const uint32_t* mine = reinterpret_cast<const uint32_t*>(b.peer[b.rank]) + tid;
     const WaitCtx w{b.status, b.timeout_ns, static_cast<uint32_t>(b.rank)};
     uint32_t seen;
-    // Epochs only grow; compare modulo 2^32.
-    struct Reached {
-      uint32_t t;
-      __device__ bool operator()(uint32_t v) const { return static_cast<int32_t>(v - t) >= 0; }
-    };
     wait_until(mine, Reached{target}, seen, w, kPhaseBarrier, tid, target);
   }
   __syncthreads();

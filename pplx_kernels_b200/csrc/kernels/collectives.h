@@ -16,7 +16,8 @@
 namespace pplx {
 
 struct BarrierParams {
-  uint8_t* peer[kMaxWorld];  // base of every rank's flag array: u32 [world]
+  uint8_t* peer[kMaxWorld];  // base of every rank's flag array: u32 [world], then counters
+  uint8_t* mc;               // multicast alias of the flag arrays, or nullptr
   uint32_t* epoch;           // local device word, last completed epoch
   Status* status;
   uint64_t timeout_ns;
@@ -25,7 +26,10 @@ struct BarrierParams {
 };
 
 // flags[rank] on every peer <- epoch + 1 (release), then wait until every local
-// flag reached it.
+// flag reached it.  With a multicast alias: one `multimem.red` adds 1 to word
+// kBarrierMcWord of every rank, and the wait is for world * (epoch + 1) there.
+constexpr int kBarrierMcWord = 32;
+constexpr size_t kBarrierFlagBytes = 256;
 cudaError_t launch_barrier(const BarrierParams& b, cudaStream_t stream);
 
 struct AllToAllCopyParams {

@@ -298,7 +298,13 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
   } else {
     // Hop 1: everybody learns everybody's histogram.
     const int WE = p.world * E;
-    if (blockIdx.x == 0) {
+    if (blockIdx.x == 0 && p.mc != nullptr) {
+      // The same words go to the same place on every rank: one multicast store each, and
+      // the NVSwitch replicates them.
+      uint32_t* dstp = reinterpret_cast<uint32_t*>(p.mc + p.off_counts_all) +
+                       (static_cast<size_t>(parity) * p.world + p.rank) * E;
+      for (int e = tid; e < E; e += blockDim.x) ptx::multimem_st_relaxed_sys(dstp + e, sm.hist[e] + 1u);
+    } else if (blockIdx.x == 0) {
       for (int idx = tid; idx < WE; idx += blockDim.x) {
         const int d = idx / E;
         const int e = idx - d * E;

@@ -148,6 +148,7 @@ AllToAll::AllToAll(const A2AConfig& cfg, std::shared_ptr<SymmetricAllocation> ar
              "arena does not match the configuration");
   PPLX_CHECK(arena_->bytes() >= params_.arena_bytes, "arena too small");
   for (int r = 0; r < cfg_.world_size; ++r) params_.peer[r] = static_cast<uint8_t*>(arena_->peer(r));
+  params_.mc = static_cast<uint8_t*>(arena_->multicast());
 
   iter_ = DeviceBuffer<uint32_t>(2);
   recv_count_ = DeviceBuffer<uint32_t>(params_.nle);

@@ -195,6 +195,7 @@ class AllToAll {
   std::vector<uint64_t> read_trace() const;
 
   const A2AParams& params() const { return params_; }
+  const SymmetricAllocation& arena() const { return *arena_; }
   const A2AConfig& config() const { return cfg_; }
   int num_local_experts() const { return params_.nle; }
   int num_dp_groups() const { return params_.num_dp_groups; }

@@ -76,6 +76,15 @@ std::shared_ptr<SymmetricAllocation> SymmetricAllocation::create(Bootstrap& bs, 
   alloc->device_ = current_device();
   alloc->peers_.assign(world, nullptr);
   alloc->ipc_opened_.assign(world, false);
+  const bool want_multicast = env_long("PPLX_B200_MULTIMEM", 0) != 0;
+  if (world > 1 && (want_multicast || env_long("PPLX_B200_VMM", 0) != 0)) {
+    // All ranks read the same environment, so they take this branch together.
+    alloc->vmm_ = std::make_unique<VmmArena>();
+    alloc->vmm_->create(bs, bytes, want_multicast);
+    for (int r = 0; r < world; ++r) alloc->peers_[r] = alloc->vmm_->peer(r);
+    bs.barrier();
+    return alloc;
+  }
   alloc->local_owner_ = alloc_zeroed(bytes);
   alloc->peers_[rank] = alloc->local_owner_.get();
   if (world == 1) return alloc;
@@ -135,7 +144,10 @@ std::vector<std::shared_ptr<SymmetricAllocation>> SymmetricAllocation::create_lo
 }
 
 StreamBarrier::StreamBarrier(Bootstrap& bs) {
-  flags_ = SymmetricAllocation::create(bs, round_up<size_t>(sizeof(uint32_t) * bs.world(), 256));
+  static_assert(sizeof(uint32_t) * (kBarrierMcWord + 1) <= kBarrierFlagBytes &&
+                    sizeof(uint32_t) * kMaxWorld <= sizeof(uint32_t) * kBarrierMcWord,
+                "barrier flag layout");
+  flags_ = SymmetricAllocation::create(bs, kBarrierFlagBytes);
   CUDA_CHECK(cudaMalloc(&epoch_, sizeof(uint32_t)));
   CUDA_CHECK(cudaMemset(epoch_, 0, sizeof(uint32_t)));
   CUDA_CHECK(cudaMalloc(&status_, sizeof(Status)));
@@ -152,6 +164,7 @@ void StreamBarrier::run(cudaStream_t stream) {
   BarrierParams b{};
   PPLX_CHECK(flags_->world() <= kMaxWorld, "world too large");
   for (int r = 0; r < flags_->world(); ++r) b.peer[r] = static_cast<uint8_t*>(flags_->peer(r));
+  b.mc = static_cast<uint8_t*>(flags_->multicast());
   b.epoch = epoch_;
   b.status = status_;
   b.timeout_ns = timeout_ns_;

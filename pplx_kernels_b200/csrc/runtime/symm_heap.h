@@ -9,6 +9,14 @@
 // peers are reachable by load/store, so one implementation serves both API
 // flavours.  Handles are exchanged through a `Bootstrap`.
 //
+// With PPLX_B200_VMM=1 the buffers come from the driver's virtual memory management API
+// instead (runtime/vmm.h): file-descriptor handles passed between the ranks over unix
+// sockets, and -- with PPLX_B200_MULTIMEM=1 on NVSwitch systems -- one multicast mapping of
+// the whole allocation, through which a kernel reaches the same offset on ALL ranks with
+// one `multimem` instruction.  Both are off by default: a process that dies while its
+// memory is bound to a multicast object can raise NVLink errors on its peers' GPUs, so jobs
+// that must survive the loss of a rank leave them off.
+//
 // A second construction path, `SymmetricAllocation::create_local_world`, places
 // several ranks' buffers on ONE device inside one process.  It exists so that
 // the multi-rank protocol can be exercised where fewer GPUs than ranks are
@@ -18,11 +26,13 @@
 #include <cstddef>
 #include <memory>
 #include <mutex>
+#include <string>
 #include <vector>
 
 #include <cuda_runtime.h>
 
 #include "bootstrap.h"
+#include "vmm.h"
 
 namespace pplx {
 
@@ -38,6 +48,11 @@ class SymmetricAllocation {
   size_t bytes() const { return bytes_; }
   int rank() const { return rank_; }
   int world() const { return static_cast<int>(peers_.size()); }
+  // The multicast alias of the allocation (same offsets), or nullptr.
+  void* multicast() const { return vmm_ ? vmm_->multicast() : nullptr; }
+  bool from_vmm() const { return vmm_ != nullptr; }
+  // Why multicast was asked for but is not there (empty otherwise).
+  std::string multicast_note() const { return vmm_ ? vmm_->multicast_note() : std::string(); }
 
   // Collective over `bs`: allocates `bytes` zero-filled bytes on the current
   // device and maps every peer's buffer.
@@ -51,6 +66,7 @@ class SymmetricAllocation {
   std::vector<void*> peers_;
   std::vector<bool> ipc_opened_;
   std::shared_ptr<void> local_owner_;  // frees the local buffer
+  std::unique_ptr<VmmArena> vmm_;      // owns everything instead, when in use
   size_t bytes_ = 0;
   int rank_ = 0;
   int device_ = 0;

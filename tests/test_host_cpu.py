@@ -95,6 +95,39 @@ def test_socket_bootstrap_gathers_and_exchanges(world):
         assert results[r][world:] == [src * 100 + r for src in range(world)]
 
 
+def _fd_exchange_rank(uid_bytes: bytes, rank: int, world: int, q) -> None:
+    import torch as t
+
+    from pplx_kernels_b200.ops import _ops as ops
+
+    uid = t.tensor(list(uid_bytes), dtype=t.uint8)
+    q.put((rank, ops.fd_exchange_selftest(uid, rank, world, 20000).tolist()))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_file_descriptors_travel_between_the_ranks_of_a_box(world):
+    """The VMM arena hands its allocations to the peers as file descriptors over unix
+    sockets (SCM_RIGHTS); here the descriptors are anonymous files holding one word each."""
+    uid = pk.nvshmem_get_unique_id()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_fd_exchange_rank, args=(bytes(uid.tolist()), r, world, q))
+             for r in range(1, world)]
+    for p in procs:
+        p.start()
+    results = {0: _ops.fd_exchange_selftest(uid, 0, world, 20000).tolist()}
+    for _ in procs:
+        r, out = q.get(timeout=60)
+        results[r] = out
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    silent = world - 1 if world >= 3 else -1   # this rank passes no descriptor
+    for r in range(world):
+        want = [-2 if s == r else (-1 if s == silent else 7000 + s) for s in range(world)]
+        assert results[r] == want
+
+
 def test_socket_bootstrap_reports_a_missing_peer():
     # A world of two in which rank 1 never shows up: rank 0 gives up with an error.
     uid = pk.nvshmem_get_unique_id()

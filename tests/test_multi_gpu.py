@@ -168,6 +168,40 @@ def test_runtime_alltoall_multi_gpu(world):
     parallel_launch(world, _worker_runtime)
 
 
+# ------------------------------------------- driver-allocated arena, multicast ----
+
+
+def _worker_vmm(pgi: ProcessGroupInfo, cfg: MoEConfig, want_multicast: bool) -> None:
+    ata = _make(pgi, cfg, 1, False)
+    lay = ata.layout()
+    note = ata.multicast_note()
+    ata.destroy()
+    assert lay["vmm_arena"] == 1, lay
+    if want_multicast and pgi.rank == 0:
+        print(f"MULTICAST in use: {lay['multicast']} {note!r}", flush=True)
+    if not want_multicast:
+        assert lay["multicast"] == 0 and note == ""
+    # Plain dispatch / combine over the mapped peers, the stream barrier and the dense
+    # all-to-all of the runtime, then the fused layer, whose packed send broadcasts its
+    # histogram (one multicast store per word where multicast is in use).
+    _worker_all_to_all(pgi, cfg, 1, False, 2, False)
+    _worker_runtime(pgi)
+    _worker_moe_layer(pgi, "tiny", 48)
+
+
+@pytest.mark.parametrize("want_multicast", [False, True])
+def test_vmm_arena_2_gpu(want_multicast, monkeypatch):
+    """The arena as driver allocations passed between the processes as file descriptors
+    (PPLX_B200_VMM=1) and, on top, bound to an NVLink multicast object (PPLX_B200_MULTIMEM=1).
+    Every rank stays to the end and unbinds before it exits."""
+    _need(2)
+    monkeypatch.setenv("PPLX_B200_VMM", "1")
+    monkeypatch.setenv("PPLX_B200_MULTIMEM", "1" if want_multicast else "0")
+    monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
+    parallel_launch(2, _worker_vmm, MoEConfig(16, 4, 512, 24, in_dtype=torch.bfloat16),
+                    want_multicast)
+
+
 # ---------------------------------------------------------------- lost peer ----
 
 
