@@ -700,33 +700,35 @@ def sweep(args: argparse.Namespace) -> None:
             torch.distributed.broadcast(uid, src=0)
             ref_nvshmem.nvshmem_init(uid, rank, world)
     h = Harness(world, dev, args.steps, max(args.warmup, 3))
-    for shape in args.shapes.split(","):
-        for tokens in (int(t) for t in args.sweep.split(",")):
-            if SHAPES[shape][0] % world:
-                continue
-            arm = Arm(kind, tokens, rank, world, dev, shape=shape, zipf=args.zipf)
-            t = h.time_pair(arm.dispatch, arm.combine)
-            row = {"impl": kind, "shape": shape, "ep": world, "tokens": tokens, "zipf": args.zipf,
-                   "dispatch_us_p50": float(t[:, 0].median()),
-                   "combine_us_p50": float(t[:, 1].median()),
-                   "step_us_p50": float(t[:, 2].median()), "steps": h.steps}
-            if kind == "ours":
-                row["nccl_all_to_all_single_us_p50"] = (
-                    nccl_baseline(h, arm.cfg, tokens)
-                    if tokens * (arm.cfg.hidden_dim_bytes + arm.cfg.hidden_dim_scale_bytes)
-                    * arm.cfg.num_experts <= (2 << 30) else None)
-                link = NVLINK_GBS_DEFAULT
-                remote = (world - 1) / world
-                rows = tokens * arm.cfg.experts_per_token
-                slot = arm.cfg.hidden_dim_bytes + arm.cfg.hidden_dim_scale_bytes + 16
-                if world > 1:
-                    row["dispatch_frac_of_nvlink_floor"] = (
-                        rows * slot * remote / link / 1e3 / row["dispatch_us_p50"])
-                    row["combine_frac_of_nvlink_floor"] = (
-                        rows * arm.cfg.hidden_dim * 2 * remote / link / 1e3 / row["combine_us_p50"])
-            arm.close()
-            if rank == 0:
-                _emit(row)
+    cases = [(shape, zipf, tokens) for shape in args.shapes.split(",")
+             for zipf in (float(z) for z in str(args.zipf).split(","))
+             for tokens in (int(t) for t in args.sweep.split(","))]
+    for shape, zipf, tokens in cases:
+        if SHAPES[shape][0] % world:
+            continue
+        arm = Arm(kind, tokens, rank, world, dev, shape=shape, zipf=zipf)
+        t = h.time_pair(arm.dispatch, arm.combine)
+        row = {"impl": kind, "shape": shape, "ep": world, "tokens": tokens, "zipf": zipf,
+               "dispatch_us_p50": float(t[:, 0].median()),
+               "combine_us_p50": float(t[:, 1].median()),
+               "step_us_p50": float(t[:, 2].median()), "steps": h.steps}
+        if kind == "ours":
+            row["nccl_all_to_all_single_us_p50"] = (
+                nccl_baseline(h, arm.cfg, tokens)
+                if tokens * (arm.cfg.hidden_dim_bytes + arm.cfg.hidden_dim_scale_bytes)
+                * arm.cfg.num_experts <= (2 << 30) else None)
+            link = NVLINK_GBS_DEFAULT
+            remote = (world - 1) / world
+            rows = tokens * arm.cfg.experts_per_token
+            slot = arm.cfg.hidden_dim_bytes + arm.cfg.hidden_dim_scale_bytes + 16
+            if world > 1:
+                row["dispatch_frac_of_nvlink_floor"] = (
+                    rows * slot * remote / link / 1e3 / row["dispatch_us_p50"])
+                row["combine_frac_of_nvlink_floor"] = (
+                    rows * arm.cfg.hidden_dim * 2 * remote / link / 1e3 / row["combine_us_p50"])
+        arm.close()
+        if rank == 0:
+            _emit(row)
     if world > 1:
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
@@ -750,7 +752,7 @@ def main() -> None:
     ap.add_argument("--sweep", default="", help="comma list of tokens per GPU: print one JSON "
                     "line per size instead of the headline line")
     ap.add_argument("--shapes", default="r1", help="sweep: comma list of r1, v2lite")
-    ap.add_argument("--zipf", type=float, default=0.0, help="sweep: routing skew, 0 = uniform")
+    ap.add_argument("--zipf", default="0", help="sweep: routing skew(s), comma list; 0 = uniform")
     args = ap.parse_args()
     global _RESULT_FD
     sys.stdout.flush()

@@ -52,6 +52,13 @@ __device__ __forceinline__ void multimem_red_add_release_sys(void* mc, uint32_t 
   asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
 }
 
+__device__ __forceinline__ void multimem_st_v4(void* mc, const int4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc),
+               "f"(__int_as_float(v.x)), "f"(__int_as_float(v.y)), "f"(__int_as_float(v.z)),
+               "f"(__int_as_float(v.w))
+               : "memory");
+}
+
 __device__ __forceinline__ void st_volatile(uint32_t* p, uint32_t v) {
   asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -153,6 +160,28 @@ __device__ __forceinline__ void warp_copy_v4(void* dst, const void* src, int nve
     for (int u = 0; u < kBatch; ++u) {
       const int v = v0 + 32 * u;
       if (v < nvec) st_v4(d + (static_cast<size_t>(v) << 4), r[u]);
+    }
+  }
+}
+
+// The same copy with the stores going through a multicast mapping: every rank bound to it
+// receives the vectors at the same offset.
+template <int kBatch = 8>
+__device__ __forceinline__ void warp_copy_v4_multicast(void* dst_mc, const void* src, int nvec,
+                                                       int lane) {
+  uint8_t* d = static_cast<uint8_t*>(dst_mc);
+  const uint8_t* s = static_cast<const uint8_t*>(src);
+  for (int v0 = lane; v0 < nvec; v0 += 32 * kBatch) {
+    int4 r[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int v = v0 + 32 * u;
+      if (v < nvec) r[u] = ld_nc_v4(s + (static_cast<size_t>(v) << 4));
+    }
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int v = v0 + 32 * u;
+      if (v < nvec) multimem_st_v4(d + (static_cast<size_t>(v) << 4), r[u]);
     }
   }
 }

@@ -232,6 +232,9 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
     return;
   }
 
+  // With the tokens replicated on all ranks and a multicast mapping of the arena, rows and
+  // arrival counts are multicast instead of being sent once per rank.
+  const bool to_all = p.mc != nullptr && p.dp_size == p.world;
   // Rounds: in each, every warp stores at most one part; then one fence and the
   // adds for the whole block.  All warps take part in every round's barriers.
   const uint32_t rounds = ceil_div<uint32_t>(n_units, gwarps);
@@ -260,12 +263,20 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
         const size_t v0 = static_cast<size_t>((c * nvec) / split);
         const int nv = ((c + 1) * nvec) / split - static_cast<int>(v0);
         const int group_first = (src_rank / p.dp_size) * p.dp_size;
-        for (int r = 0; r < p.dp_size; ++r) {
-          uint8_t* slot = p.peer[group_first + r] + p.off_comb_stage +
+        if (to_all) {
+          // Every rank holds the token: the row leaves this GPU once and the NVSwitch
+          // delivers it to all of them.
+          uint8_t* slot = p.mc + p.off_comb_stage +
                           (static_cast<size_t>(token) * p.topk + k) * row_bytes;
-          // 16 loads in flight per lane: half of a 14 KiB bf16 row in one round trip.
-          ptx::warp_copy_v4<ptx::LoadKind::kNonCoherent, 16>(slot + (v0 << 4), src + (v0 << 4),
-                                                             nv, lane);
+          ptx::warp_copy_v4_multicast<16>(slot + (v0 << 4), src + (v0 << 4), nv, lane);
+        } else {
+          for (int r = 0; r < p.dp_size; ++r) {
+            uint8_t* slot = p.peer[group_first + r] + p.off_comb_stage +
+                            (static_cast<size_t>(token) * p.topk + k) * row_bytes;
+            // 16 loads in flight per lane: half of a 14 KiB bf16 row in one round trip.
+            ptx::warp_copy_v4<ptx::LoadKind::kNonCoherent, 16>(slot + (v0 << 4), src + (v0 << 4),
+                                                               nv, lane);
+          }
         }
         sig_token = token;
         sig_group = static_cast<uint32_t>(group_first);
@@ -283,7 +294,10 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
       const uint32_t grp = packed_grp & 0xffu;
       const uint32_t arrival_units = packed_grp >> 8;
       if (__any_sync(0xffffffffu, tok != kNoSignal)) ptx::fence_acq_rel_sys();
-      if (tok != kNoSignal) {
+      if (tok != kNoSignal && to_all) {
+        ptx::multimem_red_add_release_sys(
+            reinterpret_cast<uint32_t*>(p.mc + p.off_comb_arrived) + tok, arrival_units);
+      } else if (tok != kNoSignal) {
         for (int r = 0; r < p.dp_size; ++r) {
           ptx::red_add_relaxed_sys(
               reinterpret_cast<uint32_t*>(p.peer[grp + r] + p.off_comb_arrived) + tok,

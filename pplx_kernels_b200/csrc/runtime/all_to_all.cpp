@@ -411,7 +411,8 @@ CombineArgs AllToAll::make_combine_args(const CombineCall& c) const {
   a.y_stride_row = c.y_stride_row;
   a.bound_m = c.bound_m;
   a.num_tokens = c.num_tokens;
-  a.ll = params_.ll;
+  // Replicated tokens with a multicast mapping: the counter form, whose send multicasts rows.
+  a.ll = params_.ll != 0 && !(params_.mc != nullptr && params_.dp_size == params_.world) ? 1 : 0;
   return a;
 }
 

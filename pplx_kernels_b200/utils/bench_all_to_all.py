@@ -38,13 +38,16 @@ def _max_over_ranks(t: torch.Tensor, world: int) -> torch.Tensor:
 
 
 def bench_config(cfg: MoEConfig, rank: int, world: int, dev: torch.device, zipf: float,
-                 repeat: int, samples: int, warmup: int, flush: torch.Tensor | None) -> dict:
+                 repeat: int, samples: int, warmup: int, flush: torch.Tensor | None,
+                 dp_size: int = 1) -> dict:
     nle = cfg.num_experts // world
-    gen = torch.Generator().manual_seed(7 + rank)
+    # The ranks of one DP group hold the same tokens.
+    gen = torch.Generator().manual_seed(7 + rank // dp_size)
     inp = make_rank_inputs(cfg, gen, num_tokens=cfg.max_num_tokens, zipf=zipf)
     ata = pk.AllToAll.internode(cfg.max_num_tokens, cfg.num_experts, cfg.experts_per_token, rank,
-                                world, 1, cfg.hidden_dim, cfg.hidden_dim_bytes,
+                                world, dp_size, cfg.hidden_dim, cfg.hidden_dim_bytes,
                                 cfg.hidden_dim_scale_bytes)
+    layout = ata.layout()
     rows = cfg.max_num_tokens * world
     counts = torch.empty(nle, dtype=torch.int32, device=dev)
     expert_x = torch.empty(nle, rows, cfg.hidden_dim, dtype=torch.uint8 if cfg.in_dtype.itemsize == 1
@@ -104,7 +107,8 @@ def bench_config(cfg: MoEConfig, rank: int, world: int, dev: torch.device, zipf:
     t = _max_over_ranks(torch.tensor(all_times, dtype=torch.float64, device=dev), world).cpu()
     row = {
         "experts": cfg.num_experts, "topk": cfg.experts_per_token, "hidden": cfg.hidden_dim,
-        "tokens": cfg.max_num_tokens, "zipf": zipf, "ep": world,
+        "tokens": cfg.max_num_tokens, "zipf": zipf, "ep": world, "dp_size": dp_size,
+        "multicast": layout["multicast"],
     }
     disp_bytes = cfg.max_num_tokens * cfg.experts_per_token * per_token
     comb_bytes = cfg.max_num_tokens * cfg.experts_per_token * cfg.hidden_dim * cfg.out_dtype.itemsize
@@ -143,6 +147,8 @@ def main() -> None:
     ap.add_argument("--samples", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--flush-l2", action="store_true")
+    ap.add_argument("--dp-size", type=int, default=1,
+                    help="ranks that hold the same tokens (0: all of them)")
     ap.add_argument("--out-dir", default="data")
     args = ap.parse_args()
 
@@ -169,7 +175,7 @@ def main() -> None:
         for tok in (int(t) for t in args.tokens.split(",")):
             cfg = MoEConfig(experts, topk, hidden, tok, in_dtype, out_dtype)
             row = bench_config(cfg, rank, world, dev, args.zipf, args.repeat, args.samples,
-                               args.warmup, flush)
+                               args.warmup, flush, args.dp_size or world)
             row["shape"] = name
             rows.append(row)
             if rank == 0:

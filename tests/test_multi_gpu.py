@@ -185,6 +185,8 @@ def _worker_vmm(pgi: ProcessGroupInfo, cfg: MoEConfig, want_multicast: bool) -> 
     # all-to-all of the runtime, then the fused layer, whose packed send broadcasts its
     # histogram (one multicast store per word where multicast is in use).
     _worker_all_to_all(pgi, cfg, 1, False, 2, False)
+    # Tokens replicated on all ranks: with multicast the combine sends every row once.
+    _worker_all_to_all(pgi, cfg, pgi.world_size, False, 2, False)
     _worker_runtime(pgi)
     _worker_moe_layer(pgi, "tiny", 48)
 
