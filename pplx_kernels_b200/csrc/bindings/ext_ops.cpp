@@ -72,7 +72,7 @@ void fake_grouped_gemm(const at::Tensor&, const at::Tensor&, const at::Tensor&, 
 void grouped_gemm_fp8_op(const at::Tensor& xq, const at::Tensor& sa, const at::Tensor& wq,
                          const at::Tensor& sw, const at::Tensor& counts, at::Tensor& out,
                          const std::optional<at::Tensor>& out_scale, bool swiglu_quant,
-                         const std::optional<at::Tensor>& status) {
+                         const std::optional<at::Tensor>& status, bool pow2_scales) {
   TORCH_CHECK(xq.is_cuda() && wq.is_cuda() && sa.is_cuda() && sw.is_cuda() && out.is_cuda(),
               "grouped_gemm_fp8: all tensors must be CUDA tensors");
   TORCH_CHECK(xq.element_size() == 1 && wq.element_size() == 1, "xq and wq must be 1-byte (e4m3)");
@@ -134,6 +134,7 @@ void grouped_gemm_fp8_op(const at::Tensor& xq, const at::Tensor& sa, const at::T
   c.n_out = static_cast<int>(n_out);
   c.k = static_cast<int>(K);
   c.swiglu_quant = swiglu_quant;
+  c.pow2_scales = pow2_scales;
   try {
     launch_grouped_gemm_fp8(c, at::cuda::getCurrentCUDAStream());
   } catch (const Error& e) {
@@ -144,7 +145,7 @@ void grouped_gemm_fp8_op(const at::Tensor& xq, const at::Tensor& sa, const at::T
 void fake_grouped_gemm_fp8(const at::Tensor&, const at::Tensor&, const at::Tensor&,
                            const at::Tensor&, const at::Tensor&, at::Tensor&,
                            const std::optional<at::Tensor>&, bool,
-                           const std::optional<at::Tensor>&) {}
+                           const std::optional<at::Tensor>&, bool) {}
 
 }  // namespace
 
@@ -154,7 +155,7 @@ void register_extension_ops(torch::Library& m) {
   m.impl("grouped_gemm", c10::kCUDA, &grouped_gemm_op);
   m.impl("grouped_gemm", c10::kMeta, &fake_grouped_gemm);
   m.def("grouped_gemm_fp8(Tensor xq, Tensor sa, Tensor wq, Tensor sw, Tensor counts, Tensor! out, "
-        "Tensor!? out_scale, bool swiglu_quant, Tensor!? status) -> ()");
+        "Tensor!? out_scale, bool swiglu_quant, Tensor!? status, bool pow2_scales=False) -> ()");
   m.impl("grouped_gemm_fp8", c10::kCUDA, &grouped_gemm_fp8_op);
   m.impl("grouped_gemm_fp8", c10::kMeta, &fake_grouped_gemm_fp8);
 }

@@ -222,6 +222,56 @@ __host__ __device__ constexpr uint32_t make_instr_desc(uint32_t ab_format, int m
          | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
+// ---- hardware block scaling (kind::mxf8f6f4.block_scale) ----
+//
+// Every 32 K-elements of a row of A and of a column of B carry one power-of-two scale (E8M0:
+// value 2^(byte - 127)).  The scales of one MMA sit in tensor memory: for M (or N) = 128 rows
+// the byte of row r0 + 32 * r1 is byte `id` of the 32-bit cell at lane r0 (replicated in all
+// four lane quarters), column base + r1; `id` (0..3) selects one of four K = 32 steps, so one
+// copy serves a 128-wide K block.  tcgen05.cp brings them there from shared memory, where the
+// same 128 x 4 bytes are laid out as 32 rows of 16 bytes: byte 16 * r0 + 4 * r1 + id.
+
+// Instruction descriptor: e4m3 x e4m3, E8M0 scales, both operands K-major.
+__host__ __device__ constexpr uint32_t make_instr_desc_mxf8(int m, int n, uint32_t sf_id) {
+  return (sf_id << 4)                               // B scale id
+         | (static_cast<uint32_t>(n >> 3) << 17)
+         | (1u << 23)                               // scale format: E8M0
+         | (static_cast<uint32_t>(m >> 4) << 24)
+         | (sf_id << 29);                           // A scale id
+}
+
+// Descriptor of 32 rows x 16 bytes stored contiguously without swizzle (8-row core matrices of
+// 128 bytes, one after the other).
+__device__ __forceinline__ uint64_t make_smem_desc_rows16(const void* smem) {
+  uint64_t desc = (smem_u32(smem) & 0x3ffffu) >> 4;
+  desc |= static_cast<uint64_t>(128 >> 4) << 32;    // SBO: next group of 8 rows
+  desc |= static_cast<uint64_t>(1) << 46;           // version
+  return desc;                                      // layout type 0: no swizzle
+}
+
+// 32 rows x 128 bits of shared memory -> tensor-memory lanes 0..31 of all four lane quarters,
+// four consecutive columns at `taddr`.  Issued by one thread; ordered with the tcgen05.mma
+// instructions the same thread issues before and after it.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc)
+               : "memory");
+}
+
+__device__ __forceinline__ void mma_mxf8_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                            uint32_t idesc, uint32_t tmem_sfa, uint32_t tmem_sfb,
+                                            bool accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t"
+      "}\n"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate ? 1u : 0u),
+        "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+
 // -------------------------------------------------------------- mma etc. ----
 
 // D[tmem] (+)= A[smem] * B[smem]^T, issued by one thread.

@@ -101,6 +101,10 @@ struct Fp8GemmCall {
   uint32_t* status = nullptr;
   int num_experts = 0, rows_per_expert = 0, n_out = 0, k = 0;
   bool swiglu_quant = false;    // w = [gate; up]; result silu(gate) * up quantised to e4m3
+  // Every scale in sa and sw is a power of two (the caller's promise; mantissa bits would be
+  // ignored): the tensor cores apply them (kind::mxf8f6f4.block_scale) instead of the CUDA
+  // cores, and the swiglu_quant epilogue emits power-of-two scales in turn.
+  bool pow2_scales = false;
   int num_sms = 0;
 };
 

@@ -41,12 +41,25 @@ __device__ __forceinline__ void flush_signals(const A2AParams& p, const Fp8PeerS
 // that peers fill (packed, quantising send); tiles wait for the sources they cover.
 // kToPeers: the bf16 result rows go to the combine staging of the tokens' home ranks.
 // Same protocol as the bf16 kernel's forms of the same names (grouped_gemm_sm100.cu).
-template <bool kSwiGLUQuant, bool kFromStaging, bool kToPeers>
+// E8M0 byte of a power-of-two fp32 scale (its exponent field).
+__device__ __forceinline__ uint32_t e8m0_of(float scale) {
+  return (__float_as_uint(scale) >> 23) & 0xffu;
+}
+
+// The smallest power of two that is not below v (v > 0, finite).
+__device__ __forceinline__ float pow2_not_below(float v) {
+  const uint32_t bits = __float_as_uint(v);
+  const uint32_t exp = (bits >> 23) + ((bits & 0x7fffffu) != 0u ? 1u : 0u);
+  return __uint_as_float(exp << 23);
+}
+
+template <bool kSwiGLUQuant, bool kFromStaging, bool kToPeers, bool kPow2>
 __global__ void __launch_bounds__(kThreads, 1)
     grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             const __grid_constant__ CUtensorMap tmap_b,
                             const __grid_constant__ Fp8GemmArgs g) {
   static_assert(!(kFromStaging && kToPeers) && !(kToPeers && kSwiGLUQuant), "unsupported form");
+  static_assert(!(kPow2 && kFromStaging), "the staging-fed form folds its scales on CUDA cores");
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* stages = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -128,9 +141,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
   if (tid == 0) {
     for (int s = 0; s < kStages; ++s) {
-      tc::mbar_init(&ctl->full[s], 1);
+      tc::mbar_init(&ctl->full[s], kPow2 ? 2 : 1);  // the tiles, and (kPow2) the scales
       tc::mbar_init(&ctl->empty[s], 1);
     }
+    tc::mbar_init(&ctl->acc_full, 1);
+    tc::mbar_init(&ctl->acc_empty, 8);
     for (int b = 0; b < 2; ++b) {
       tc::mbar_init(&ctl->part_full[b], 1);
       tc::mbar_init(&ctl->part_empty[b], 8);
@@ -238,7 +253,42 @@ __global__ void __launch_bounds__(kThreads, 1)
       const uint32_t idesc = tc::make_instr_desc(0u, kBlockM, kTileN);
       uint32_t stage = 0, phase = 0, round = 0;
       bool ok = *abort_flag == 0u;
-      for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      if constexpr (kPow2) {
+        uint32_t tile_it = 0;
+        for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_it) {
+          // The fold warps have read the previous tile out of the accumulator.
+          ok = tc::mbar_wait(&ctl->acc_empty, (tile_it & 1u) ^ 1u, abort_flag, kWaitLimitNs);
+          for (int kb = 0; kb < num_kb && ok; ++kb) {
+            ok = tc::mbar_wait(&ctl->full[stage], phase, abort_flag, kWaitLimitNs);
+            if (!ok) break;
+            tc::tc_fence_after_sync();
+            const uint8_t* a_src = stages + stage * kStageBytes;
+            const uint64_t a_desc = tc::make_smem_desc_sw128(a_src);
+            const uint64_t b_desc = tc::make_smem_desc_sw128(a_src + kABytes);
+            const uint8_t* sf = ctl->sf[stage];
+            tc::tmem_cp_32x128b_warpx4(tmem_base + kSfaCol, tc::make_smem_desc_rows16(sf));
+            tc::tmem_cp_32x128b_warpx4(tmem_base + kSfbCol,
+                                       tc::make_smem_desc_rows16(sf + kSfAtomBytes));
+            tc::tmem_cp_32x128b_warpx4(tmem_base + kSfbCol + 4,
+                                       tc::make_smem_desc_rows16(sf + 2 * kSfAtomBytes));
+#pragma unroll
+            for (uint32_t k = 0; k < kBlockKBytes / kUmmaKBytes; ++k) {
+              tc::mma_mxf8_ss(tmem_base, tc::advance_smem_desc(a_desc, k * kUmmaKBytes),
+                              tc::advance_smem_desc(b_desc, k * kUmmaKBytes),
+                              tc::make_instr_desc_mxf8(kBlockM, kTileN, k),
+                              (tmem_base + kSfaCol) | (k << 30), (tmem_base + kSfbCol) | (k << 30),
+                              kb != 0 || k != 0);
+            }
+            tc::mma_commit(&ctl->empty[stage]);
+            if (kb == num_kb - 1) tc::mma_commit(&ctl->acc_full);
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+      for (uint32_t t = blockIdx.x; !kPow2 && t < total_tiles && ok; t += gridDim.x) {
         for (int kb = 0; kb < num_kb && ok; ++kb, ++round) {
           // K blocks alternate between the two scratch accumulators.
           const uint32_t buf = round & 1u;
@@ -266,11 +316,73 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
     __syncwarp();
+  } else if (kPow2 && warp == 3) {
+    // The scales of each K block as E8M0 bytes, where tcgen05.cp finds them.  Lane l owns
+    // rows l, l + 32, l + 64, l + 96 of the tile: exactly one 16-byte row of the A atom.
+    uint32_t stage = 0, phase = 0;
+    bool ok = *abort_flag == 0u;
+    constexpr int kChunk = 8;  // K blocks whose scales are fetched together
+    for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const Fp8Tile c = locate(tile_start, rows_of, g.num_experts, t);
+      const float* sa_rows[4];
+      bool live[4];
+#pragma unroll
+      for (int r1 = 0; r1 < 4; ++r1) {
+        const int row = c.m_blk * kBlockM + lane + 32 * r1;
+        live[r1] = row < c.rows;
+        sa_rows[r1] = g.sa + c.expert * g.sa_stride_e + (live[r1] ? row : 0) * g.sa_stride_row;
+      }
+      const int wrow0 = kSwiGLUQuant ? c.n_blk * (kTileN / 2) : c.n_blk * kTileN;
+      const int wrow1 = kSwiGLUQuant ? g.n_out + wrow0 : wrow0 + kTileN / 2;
+      const int last_block = (((kSwiGLUQuant ? 2 : 1) * g.n_out) - 1) / 128;
+      const float* sw0 =
+          g.sw + c.expert * g.sw_stride_e + min(wrow0 / 128, last_block) * g.sw_stride_row;
+      const float* sw1 =
+          g.sw + c.expert * g.sw_stride_e + min(wrow1 / 128, last_block) * g.sw_stride_row;
+      for (int kb0 = 0; kb0 < num_kb && ok; kb0 += kChunk) {
+        uint32_t ea[kChunk], eb[kChunk];  // four row bytes, two column-half bytes per K block
+#pragma unroll
+        for (int u = 0; u < kChunk; ++u) {
+          const int kb = min(kb0 + u, num_kb - 1);
+          uint32_t v = 0;
+#pragma unroll
+          for (int r1 = 0; r1 < 4; ++r1)
+            v |= (live[r1] ? e8m0_of(__ldg(sa_rows[r1] + kb)) : 127u) << (8 * r1);
+          ea[u] = v;
+          eb[u] = e8m0_of(__ldg(sw0 + kb)) | (e8m0_of(__ldg(sw1 + kb)) << 8);
+        }
+#pragma unroll
+        for (int u = 0; u < kChunk; ++u) {
+          if (kb0 + u >= num_kb || !ok) continue;
+          ok = tc::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag, kWaitLimitNs);
+          if (!ok) continue;
+          uint8_t* sf = ctl->sf[stage];
+          uint4 a;
+          a.x = (ea[u] & 0xffu) * 0x01010101u;
+          a.y = ((ea[u] >> 8) & 0xffu) * 0x01010101u;
+          a.z = ((ea[u] >> 16) & 0xffu) * 0x01010101u;
+          a.w = (ea[u] >> 24) * 0x01010101u;
+          *reinterpret_cast<uint4*>(sf + 16 * lane) = a;
+          const uint32_t b0 = (eb[u] & 0xffu) * 0x01010101u;
+          const uint32_t b1 = (eb[u] >> 8) * 0x01010101u;
+          *reinterpret_cast<uint4*>(sf + kSfAtomBytes + 16 * lane) = make_uint4(b0, b0, b0, b0);
+          *reinterpret_cast<uint4*>(sf + 2 * kSfAtomBytes + 16 * lane) = make_uint4(b1, b1, b1, b1);
+          ptx::fence_proxy_async_smem();  // these writes, before tcgen05.cp reads them
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(&ctl->full[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
   } else if (warp >= 4) {
     const int ew = (warp - 4) & 3;      // tensor-memory lanes [32 * ew, +32)
     const int half = (warp - 4) >> 2;   // columns [64 * half, +64) of each 128-column half
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(ew * 32) << 16);
     uint32_t round = 0;
+    uint32_t tile_it = 0;          // kPow2: tiles this CTA has finished
     uint32_t pending_signals = 0;  // kToPeers, warp 4: queued arrival adds
     bool ok = *abort_flag == 0u;
     for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -315,7 +427,31 @@ __global__ void __launch_bounds__(kThreads, 1)
       float acc[128];
 #pragma unroll
       for (int j = 0; j < 128; ++j) acc[j] = 0.f;
-      for (int kb = 0; kb < num_kb && ok; ++kb, ++round) {
+      if constexpr (kPow2) {
+        // The tensor cores applied the scales: take the finished tile out of tensor memory
+        // and hand the accumulator back before converting and storing.
+        ok = tc::mbar_wait(&ctl->acc_full, tile_it & 1u, abort_flag, kWaitLimitNs);
+        ++tile_it;
+        if (ok) {
+          tc::tc_fence_after_sync();
+          // Four loads of 32 columns in flight, one wait: the accumulator is free again
+          // after a single tensor-memory round trip.
+          const uint32_t t_acc = t_lane + half * 64;
+          uint32_t raw[4][32];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) tc::tmem_ld_32x32(t_acc + (q >> 1) * 128 + (q & 1) * 32, raw[q]);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[q * 32 + j] = __uint_as_float(raw[q][j]);
+          }
+          tc::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) tc::mbar_arrive(&ctl->acc_empty);
+        }
+      }
+      for (int kb = 0; !kPow2 && kb < num_kb && ok; ++kb, ++round) {
         // Staging memory is rewritten by peers every step: read it from L2, never through
         // the non-coherent path.
         const float a_scale = kFromStaging ? __ldcg(sa_row + kb) : __ldg(sa_row + kb);
@@ -372,7 +508,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         ctl->row_amax[half][tile_row] = amax;
         asm volatile("bar.sync 2, 256;" ::: "memory");
         amax = fmaxf(fmaxf(ctl->row_amax[0][tile_row], ctl->row_amax[1][tile_row]), 1e-4f);
-        const float inv = 448.0f / amax;
+        // The scale of the row's 128 outputs: amax / 448, or the next power of two above it
+        // where the consumer wants hardware scales.
+        const float out_scale = kPow2 ? pow2_not_below(amax / 448.0f) : amax / 448.0f;
+        const float inv = 1.0f / out_scale;
         if (row_ok) {
           const int col0 = c.n_blk * 128 + half * 64;
           uint8_t* orow = static_cast<uint8_t*>(g.out) + c.expert * g.out_stride_e +
@@ -399,7 +538,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           if (half == 0) {
             g.out_scale[c.expert * g.os_stride_e + static_cast<int64_t>(row) * g.os_stride_row +
-                        c.n_blk] = amax / 448.0f;
+                        c.n_blk] = out_scale;
           }
         }
         // row_amax is rewritten by the next tile only after every warp passed this point.

@@ -17,6 +17,13 @@
 // only reads tensor memory (tcgen05.ld), while the MMAs of the next K block fill
 // the other scratch accumulator.
 //
+// With power-of-two scales (`pow2_scales`) the tensor cores apply them themselves
+// (kind::mxf8f6f4.block_scale): warp 3 turns the fp32 scales of each K block into E8M0 bytes in
+// the layout tcgen05.cp takes, the MMA thread copies them into tensor memory in front of the
+// block's four MMAs, the whole K range accumulates in ONE tensor-memory accumulator, and the
+// fold warps only read the finished tile (and free the accumulator before they convert and
+// store, so that the next tile's MMAs run under the epilogue).
+//
 // Epilogues:  kBf16   plain down projection, bf16 result, 256 columns per tile
 //             kSwiGLUQuant   w stacks gate and up rows; the tile is 128 gate + 128 up
 //                     rows, the result silu(gate) * up is 128 columns = exactly one
@@ -54,6 +61,10 @@ constexpr int kTmemCols = 512;     // two scratch accumulators of 256 columns
 constexpr uint32_t kABytes = kBlockM * kBlockKBytes;
 constexpr uint32_t kBBytes = kTileN * kBlockKBytes;
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kSfAtomBytes = 512;
+constexpr uint32_t kSfStageBytes = 3 * kSfAtomBytes;
+constexpr uint32_t kSfaCol = 256;  // tensor-memory columns of the scales, behind the accumulator
+constexpr uint32_t kSfbCol = 260;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 constexpr int kMaxExperts = 1024;
 
@@ -62,11 +73,16 @@ struct SharedControl {
   uint64_t empty[kStages];
   uint64_t part_full[2];   // scratch accumulator holds a finished K block
   uint64_t part_empty[2];  // scratch accumulator may be overwritten
+  uint64_t acc_full;       // hardware-scaled form: the tile's accumulator is complete
+  uint64_t acc_empty;      //                       ... has been read out by all fold warps
   uint32_t tmem_base;
   uint32_t abort_flag;
   float row_amax[2][kBlockM];  // SwiGLU epilogue: per-row maxima of the two column halves
   uint32_t sig_token[kBlockM];  // peer-storing epilogue: token of each tile row
   uint32_t sig_group[kBlockM];  //                        first rank of the token's DP group
+  // Hardware-scaled form: per stage the E8M0 scales of the K block in the layout tcgen05.cp
+  // takes (32 rows of 16 bytes per 128 rows or columns): A rows, B columns 0-127, 128-255.
+  alignas(128) uint8_t sf[kStages][kSfStageBytes];
 };
 
 constexpr uint32_t kNoSignalFp8 = 0xffffffffu;
@@ -205,10 +221,10 @@ Fp8GemmArgs fp8_args(const Fp8GemmCall& c) {
   return g;
 }
 
-template <bool kSwiGLUQuant, bool kFromStaging, bool kToPeers>
+template <bool kSwiGLUQuant, bool kFromStaging, bool kToPeers, bool kPow2 = false>
 void launch_fp8(const CUtensorMap& tmap_a, const CUtensorMap& tmap_b, const Fp8GemmArgs& g,
                 int num_sms, cudaStream_t stream) {
-  auto* kernel = grouped_gemm_fp8_kernel<kSwiGLUQuant, kFromStaging, kToPeers>;
+  auto* kernel = grouped_gemm_fp8_kernel<kSwiGLUQuant, kFromStaging, kToPeers, kPow2>;
   const size_t src_entries =
       (kFromStaging && g.src_table != 0) ? static_cast<size_t>(g.num_experts) * g.a2a.world : 0;
   const size_t smem = fp8_smem_bytes(g.num_experts, src_entries, kToPeers);
@@ -231,8 +247,14 @@ void launch_grouped_gemm_fp8(const Fp8GemmCall& c, cudaStream_t stream) {
   const CUtensorMap tmap_b =
       make_byte_map(c.w, c.num_experts, w_rows, c.k, c.w_stride_row, c.w_stride_e);
   const Fp8GemmArgs g = fp8_args(c);
-  if (c.swiglu_quant) launch_fp8<true, false, false>(tmap_a, tmap_b, g, c.num_sms, stream);
-  else launch_fp8<false, false, false>(tmap_a, tmap_b, g, c.num_sms, stream);
+  if (c.pow2_scales) {
+    if (c.swiglu_quant) launch_fp8<true, false, false, true>(tmap_a, tmap_b, g, c.num_sms, stream);
+    else launch_fp8<false, false, false, true>(tmap_a, tmap_b, g, c.num_sms, stream);
+  } else if (c.swiglu_quant) {
+    launch_fp8<true, false, false>(tmap_a, tmap_b, g, c.num_sms, stream);
+  } else {
+    launch_fp8<false, false, false>(tmap_a, tmap_b, g, c.num_sms, stream);
+  }
 }
 
 void launch_gemm_fp8_from_staging(const Fp8GemmCall& c, const A2AParams& p,
@@ -272,7 +294,8 @@ void launch_gemm_fp8_to_peers(const Fp8GemmCall& c, const A2AParams& p, cudaStre
   Fp8GemmArgs g = fp8_args(c);
   g.out = nullptr;
   g.a2a = p;
-  launch_fp8<false, false, true>(tmap_a, tmap_b, g, c.num_sms, stream);
+  if (c.pow2_scales) launch_fp8<false, false, true, true>(tmap_a, tmap_b, g, c.num_sms, stream);
+  else launch_fp8<false, false, true>(tmap_a, tmap_b, g, c.num_sms, stream);
 }
 
 }  // namespace pplx

@@ -55,8 +55,9 @@ def grouped_gemm_reference(x: torch.Tensor, w: torch.Tensor, counts: torch.Tenso
 def grouped_gemm_fp8(xq: torch.Tensor, sa: torch.Tensor, wq: torch.Tensor, sw: torch.Tensor,
                      counts: torch.Tensor, swiglu_quant: bool = False,
                      out: torch.Tensor | None = None, out_scale: torch.Tensor | None = None,
-                     status: torch.Tensor | None = None):
-    """Block-scaled fp8 grouped GEMM (tcgen05 ``kind::f8f6f4``).
+                     status: torch.Tensor | None = None, pow2_scales: bool = False):
+    """Block-scaled fp8 grouped GEMM (tcgen05 ``kind::f8f6f4``, or with ``pow2_scales``
+    ``kind::mxf8f6f4.block_scale``).
 
     ``xq`` [E, rows, K] and ``wq`` [E, N (or 2N), K] are ``float8_e4m3fn``; ``sa`` [E, rows,
     K/128] holds one fp32 scale per row and 128 columns, ``sw`` [E, ceil(w rows/128), K/128]
@@ -64,6 +65,12 @@ def grouped_gemm_fp8(xq: torch.Tensor, sa: torch.Tensor, wq: torch.Tensor, sw: t
     ``swiglu_quant`` (``wq`` stacks gate and up rows): returns ``(hq, hs)`` -- silu(gate) * up
     quantised to e4m3 with one fp32 scale per row and 128 columns, the input format of the
     next GEMM.
+
+    ``pow2_scales=True`` is the caller's promise that every scale in ``sa`` and ``sw`` is a power
+    of two (``per_token_block_quant(..., pow2=True)``, ``quantize_weight_blocks(..., pow2=True)``,
+    ``dispatch_quant(..., pow2=True)``): the tensor cores then apply the scales themselves and the
+    whole K range accumulates in tensor memory; the ``swiglu_quant`` epilogue emits power-of-two
+    scales in turn.  Mantissa bits of a scale that is not a power of two would be ignored.
     """
     E, rows, _ = xq.shape
     n_out = wq.size(1) // 2 if swiglu_quant else wq.size(1)
@@ -74,20 +81,25 @@ def grouped_gemm_fp8(xq: torch.Tensor, sa: torch.Tensor, wq: torch.Tensor, sw: t
             out_scale = torch.empty(E, rows, n_out // 128, dtype=torch.float32, device=xq.device)
     elif out is None:
         out = torch.empty(E, rows, n_out, dtype=torch.bfloat16, device=xq.device)
-    _ops.grouped_gemm_fp8(xq, sa, wq, sw, counts, out, out_scale, swiglu_quant, status)
+    _ops.grouped_gemm_fp8(xq, sa, wq, sw, counts, out, out_scale, swiglu_quant, status,
+                          pow2_scales)
     return (out, out_scale) if swiglu_quant else out
 
 
-def quantize_weight_blocks(w: torch.Tensor, block: int = 128) -> tuple[torch.Tensor, torch.Tensor]:
-    """w: [E, N, K] -> (e4m3 [E, N, K], fp32 scales [E, ceil(N/block), ceil(K/block)])."""
+def quantize_weight_blocks(w: torch.Tensor, block: int = 128,
+                           pow2: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """w: [E, N, K] -> (e4m3 [E, N, K], fp32 scales [E, ceil(N/block), ceil(K/block)]).
+    With ``pow2`` every scale is rounded up to a power of two (hardware block scaling)."""
     E, N, K = w.shape
     nb, kb = (N + block - 1) // block, (K + block - 1) // block
     wf = torch.nn.functional.pad(w.to(torch.float32), (0, kb * block - K, 0, nb * block - N))
     v = wf.view(E, nb, block, kb, block)
-    amax = v.abs().amax(dim=(2, 4)).clamp(min=1e-4)
-    q = (v * (448.0 / amax)[:, :, None, :, None]).clamp(-448.0, 448.0)
+    scale = v.abs().amax(dim=(2, 4)).clamp(min=1e-4) / 448.0
+    if pow2:
+        scale = torch.exp2(torch.ceil(torch.log2(scale)))
+    q = (v / scale[:, :, None, :, None]).clamp(-448.0, 448.0)
     q = q.view(E, nb * block, kb * block)[:, :N, :K].to(torch.float8_e4m3fn).contiguous()
-    return q, (amax / 448.0).contiguous()
+    return q, scale.contiguous()
 
 
 def grouped_gemm_fp8_reference(xq: torch.Tensor, sa: torch.Tensor, wq: torch.Tensor,

@@ -52,6 +52,8 @@ def main() -> None:
     ap.add_argument("--cta-pair", type=int, default=-1, help="1 = CTA pair, 0 = single, -1 = choose")
     ap.add_argument("--fp8", action="store_true",
                     help="block-scaled e4m3 kernel (with --swiglu its output is quantised too)")
+    ap.add_argument("--pow2", action="store_true",
+                    help="with --fp8: power-of-two scales, applied by the tensor cores")
     args = ap.parse_args()
     if args.shape:
         E, rows, K, N, swiglu = SHAPES[args.shape]
@@ -73,16 +75,16 @@ def main() -> None:
             torch.matmul(x[e], w[e].t())
 
     if args.fp8:
-        xq, sa = per_token_block_quant(x.view(E * rows, K))
+        xq, sa = per_token_block_quant(x.view(E * rows, K), pow2=args.pow2)
         xq, sa = xq.view(E, rows, K), sa.view(E, rows, -1)
-        wq, sw = quantize_weight_blocks(w)
+        wq, sw = quantize_weight_blocks(w, pow2=args.pow2)
         out8 = torch.empty(E, rows, N, dtype=torch.float8_e4m3fn, device=dev) if swiglu else out
         out8_scale = (torch.empty(E, rows, N // 128, dtype=torch.float32, device=dev)
                       if swiglu else None)
 
         def ours():
             grouped_gemm_fp8(xq, sa, wq, sw, counts, swiglu_quant=swiglu, out=out8,
-                             out_scale=out8_scale, status=status)
+                             out_scale=out8_scale, status=status, pow2_scales=args.pow2)
     else:
         def ours():
             grouped_gemm(x, w, counts, out=out, swiglu=swiglu, status=status,
@@ -114,7 +116,8 @@ def main() -> None:
     tf = flops / results["ours"] / 1e6
     print(json.dumps({
         "shape": {"experts": E, "rows": rows, "k": K, "n": N, "swiglu": swiglu},
-        "dtype": "fp8_e4m3 block-scaled" if args.fp8 else "bf16",
+        "dtype": ("fp8_e4m3, power-of-two block scales in hardware" if args.fp8 and args.pow2
+                  else "fp8_e4m3 block-scaled" if args.fp8 else "bf16"),
         "us_p50": results["ours"],
         "tflops": tf,
         "frac_of_measured_bf16_peak": tf / peak if peak else None,

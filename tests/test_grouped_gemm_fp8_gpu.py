@@ -13,13 +13,19 @@ from pplx_kernels_b200.ops.quant import block_dequant, per_token_block_quant
 pytestmark = pytest.mark.gpu
 
 
-def _operands(E, rows, K, w_rows, seed):
+def _operands(E, rows, K, w_rows, seed, pow2=False):
     dev = torch.device("cuda", 0)
     g = torch.Generator().manual_seed(seed)
     x = torch.randn(E, rows, K, generator=g)
     w = torch.randn(E, w_rows, K, generator=g) * K ** -0.5
-    xq, sa = per_token_block_quant(x.view(E * rows, K))
-    wq, sw = quantize_weight_blocks(w)
+    # Rows with very different magnitudes, so that the scales differ from row to row and from
+    # K block to K block (a wrong scale byte then shows as a factor of two or more).
+    x = x * torch.exp2(torch.randint(-6, 7, (E, rows, 1), generator=g).float())
+    kblocks = (K + 127) // 128
+    x = x * torch.exp2(torch.randint(-3, 4, (E, rows, kblocks), generator=g).float()
+                       ).repeat_interleave(128, dim=2)[:, :, :K]
+    xq, sa = per_token_block_quant(x.view(E * rows, K), pow2=pow2)
+    wq, sw = quantize_weight_blocks(w, pow2=pow2)
     return (xq.view(E, rows, K).to(dev), sa.view(E, rows, -1).to(dev), wq.to(dev), sw.to(dev))
 
 
@@ -29,17 +35,19 @@ def _operands(E, rows, K, w_rows, seed):
     (2, 128, 2048, 768, [100, 128]),       # Qwen3 down projection shape
     (4, 384, 384, 272, [384, 1, 129, 200]),  # column tail, 3 K blocks
 ])
-def test_plain_bf16_epilogue(E, rows, K, N, counts):
-    xq, sa, wq, sw = _operands(E, rows, K, N, seed=1)
+@pytest.mark.parametrize("pow2", [False, True], ids=["fp32 scales", "power-of-two scales"])
+def test_plain_bf16_epilogue(E, rows, K, N, counts, pow2):
+    xq, sa, wq, sw = _operands(E, rows, K, N, seed=1, pow2=pow2)
     cnt = torch.tensor(counts, dtype=torch.int32, device=xq.device)
     out = torch.full((E, rows, N), float("nan"), dtype=torch.bfloat16, device=xq.device)
     status = torch.zeros(1, dtype=torch.int32, device=xq.device)
-    grouped_gemm_fp8(xq, sa, wq, sw, cnt, out=out, status=status)
+    grouped_gemm_fp8(xq, sa, wq, sw, cnt, out=out, status=status, pow2_scales=pow2)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     want = grouped_gemm_fp8_reference(xq, sa, wq, sw, cnt)
     for e, m in enumerate(counts):
-        torch.testing.assert_close(out[e, :m].float(), want[e, :m], rtol=2e-2, atol=2e-2)
+        tol = 2e-2 * want[e, :m].abs().amax(dim=1, keepdim=True).clamp(min=1.0)
+        assert ((out[e, :m].float() - want[e, :m]).abs() <= 2e-2 * want[e, :m].abs() + tol).all()
         assert torch.isnan(out[e, m:].float()).all()
 
 
@@ -48,11 +56,13 @@ def test_plain_bf16_epilogue(E, rows, K, N, counts):
     (2, 256, 2048, 768, [256, 130]),       # Qwen3 up projection shape
     (5, 128, 512, 256, [5, 128, 0, 64, 127]),
 ])
-def test_swiglu_epilogue_quantises_its_result(E, rows, K, I, counts):
-    xq, sa, wq, sw = _operands(E, rows, K, 2 * I, seed=2)
+@pytest.mark.parametrize("pow2", [False, True], ids=["fp32 scales", "power-of-two scales"])
+def test_swiglu_epilogue_quantises_its_result(E, rows, K, I, counts, pow2):
+    xq, sa, wq, sw = _operands(E, rows, K, 2 * I, seed=2, pow2=pow2)
     cnt = torch.tensor(counts, dtype=torch.int32, device=xq.device)
     status = torch.zeros(1, dtype=torch.int32, device=xq.device)
-    hq, hs = grouped_gemm_fp8(xq, sa, wq, sw, cnt, swiglu_quant=True, status=status)
+    hq, hs = grouped_gemm_fp8(xq, sa, wq, sw, cnt, swiglu_quant=True, status=status,
+                              pow2_scales=pow2)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     want = grouped_gemm_fp8_reference(xq, sa, wq, sw, cnt, swiglu=True)
@@ -65,4 +75,11 @@ def test_swiglu_epilogue_quantises_its_result(E, rows, K, I, counts):
         assert ((got - w).abs() <= 0.07 * w.abs() + 0.02 * w.abs().amax(dim=1, keepdim=True)).all()
         # the scales are the per-block maxima of the result
         amax = w.view(m, -1, 128).abs().amax(dim=2).clamp(min=1e-4) / 448.0
-        torch.testing.assert_close(hs[e, :m].cpu(), amax, rtol=2e-2, atol=1e-6)
+        if pow2:
+            # powers of two, at or just above amax / 448 (the kernel's maximum is of its own
+            # fp32 result, which may sit on the other side of a power of two)
+            got_s = hs[e, :m].cpu()
+            assert torch.equal(got_s, torch.exp2(torch.round(torch.log2(got_s))))
+            assert ((got_s >= amax * 0.98) & (got_s <= amax * 2.05)).all()
+        else:
+            torch.testing.assert_close(hs[e, :m].cpu(), amax, rtol=2e-2, atol=1e-6)
