@@ -191,6 +191,14 @@ class AllToAll:
     def set_debug_checks(self, on: bool) -> None:
         _ops.all_to_all_set_debug_checks(self._ptr, bool(on))
 
+    def set_power_of_two_scales(self, on: bool) -> None:
+        """The quantising sends (``dispatch_quant``, ``fused_dispatch(quantize=True)``) round each
+        scale up to a power of two, and ``fused_up_fp8`` / ``fused_down_fp8`` let the tensor cores
+        apply the scales (``kind::mxf8f6f4.block_scale``) instead of the CUDA cores.  The weight
+        scales passed to those calls must then be powers of two as well
+        (``quantize_weight_blocks(..., pow2=True)``)."""
+        _ops.all_to_all_set_quant_pow2(self._ptr, bool(on))
+
     def set_max_blocks(self, n: int) -> None:
         _ops.all_to_all_set_max_blocks(self._ptr, int(n))
 

@@ -492,6 +492,7 @@ void set_timeout_ms_op(int64_t ptr, double ms) {
 }
 
 void set_debug_checks_op(int64_t ptr, bool on) { lookup(ptr)->set_debug_checks(on); }
+void set_quant_pow2_op(int64_t ptr, bool on) { lookup(ptr)->set_quant_pow2(on); }
 
 void set_max_blocks_op(int64_t ptr, int64_t n) { lookup(ptr)->set_max_blocks(static_cast<int>(n)); }
 
@@ -946,6 +947,7 @@ void register_all_to_all_ops(torch::Library& m) {
   m.def("all_to_all_verify_canaries(int ptr) -> ()", &verify_canaries_op);
   m.def("all_to_all_set_timeout_ms(int ptr, float ms) -> ()", &set_timeout_ms_op);
   m.def("all_to_all_set_debug_checks(int ptr, bool on) -> ()", &set_debug_checks_op);
+  m.def("all_to_all_set_quant_pow2(int ptr, bool on) -> ()", &set_quant_pow2_op);
   m.def("all_to_all_set_max_blocks(int ptr, int n) -> ()", &set_max_blocks_op);
   m.def("all_to_all_layout(int ptr) -> int[]", &layout_op);
   m.def("all_to_all_multicast_note(int ptr) -> str", &multicast_note_op);

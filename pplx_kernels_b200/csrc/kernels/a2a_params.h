@@ -62,6 +62,8 @@ struct A2AParams {
   int region_slots;  // dispatch staging slots per source rank
   int cap;           // rows per local expert in out_expert_x / expert_y
   int debug_checks;  // non-zero: bounds checks that record instead of corrupting
+  int quant_pow2;    // non-zero: the quantising sends emit power-of-two scales, and the fp8 expert
+                     // GEMMs of the fused path let the tensor cores apply them
   int comb_units;    // arrival units one complete expert output row is worth: its columns
   // Flag-in-data protocol (core/ll128.cuh) for the plain dispatch and combine.
   int ll;                  // non-zero: in use

@@ -159,7 +159,7 @@ __device__ __forceinline__ uint32_t* arrived_ptr(const A2AParams& p, int dst, in
 // warps) and stores payload and scales into the slot.
 __device__ __forceinline__ void warp_quantize_row(uint8_t* slot, float* slot_scales,
                                                   const __nv_bfloat16* src, int v0, int v1,
-                                                  int nvec, int lane) {
+                                                  int nvec, int lane, bool pow2) {
   for (int base = v0; base < v1; base += 32) {
     const int v = base + lane;
     const bool live = v < v1 && v < nvec;
@@ -188,7 +188,13 @@ __device__ __forceinline__ void warp_quantize_row(uint8_t* slot, float* slot_sca
     amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
     if (!live) continue;
     amax = fmaxf(amax, 1e-4f);
-    const float inv = 448.0f / amax;
+    float scale = amax / 448.0f, inv = 448.0f / amax;
+    if (pow2) {
+      // The smallest power of two that is not below amax / 448: hardware block scaling.
+      const uint32_t bits = __float_as_uint(scale);
+      scale = __uint_as_float(((bits >> 23) + ((bits & 0x7fffffu) != 0u ? 1u : 0u)) << 23);
+      inv = 1.0f / scale;
+    }
     uint32_t q[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -204,7 +210,7 @@ __device__ __forceinline__ void warp_quantize_row(uint8_t* slot, float* slot_sca
     out.z = q[2];
     out.w = q[3];
     ptx::st_v4(slot + static_cast<size_t>(v) * 16, out);
-    if ((lane & 7) == 0) slot_scales[v >> 3] = amax / 448.0f;
+    if ((lane & 7) == 0) slot_scales[v >> 3] = scale;
   }
 }
 
@@ -481,7 +487,8 @@ __device__ __forceinline__ void send_phase(const DispatchArgs& a, const Dispatch
         const int v0 = ((c * groups) / split) * 32;
         const int v1 = min((((c + 1) * groups) / split) * 32, nvec);
         warp_quantize_row(slot, reinterpret_cast<float*>(slot + p.hidden_bytes),
-                          reinterpret_cast<const __nv_bfloat16*>(src), v0, v1, nvec, lane);
+                          reinterpret_cast<const __nv_bfloat16*>(src), v0, v1, nvec, lane,
+                          p.quant_pow2 != 0);
       } else {
         const int v0 = (c * nvec) / split;
         const int v1 = ((c + 1) * nvec) / split;

@@ -41,6 +41,40 @@ __device__ __forceinline__ void flush_signals(const A2AParams& p, const Fp8PeerS
 // that peers fill (packed, quantising send); tiles wait for the sources they cover.
 // kToPeers: the bf16 result rows go to the combine staging of the tokens' home ranks.
 // Same protocol as the bf16 kernel's forms of the same names (grouped_gemm_sm100.cu).
+// Staging-fed forms: waits until the rows of tile `c` have landed, that is for the arrival
+// counters of exactly the sources whose rows the tile covers.  `landed` remembers the sources
+// of the current expert that were already waited for.  False: a wait ran out.
+__device__ __forceinline__ bool wait_tile_sources(const A2AParams& p, const Fp8Tile& c, int parity,
+                                                  const uint32_t* src_rows, uint32_t& landed) {
+  const WaitCtx w{p.status, p.timeout_ns, static_cast<uint32_t>(p.rank)};
+  const uint32_t* arrived = reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.off_arrived_e) +
+                            (static_cast<size_t>(parity) * p.nle + c.expert) * p.world;
+  const uint32_t r0 = static_cast<uint32_t>(c.m_blk * kBlockM);
+  const uint32_t r1 = min(r0 + static_cast<uint32_t>(kBlockM), static_cast<uint32_t>(c.rows));
+  uint32_t first = 0;
+  bool waited = false, ok = true;
+  for (int s = 0; s < p.world && ok; ++s) {
+    uint32_t n;
+    if (src_rows != nullptr) {
+      n = src_rows[c.expert * p.world + s];
+    } else {
+      const uint32_t v = ptx::ld_relaxed_sys(
+          reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.off_counts_all) +
+          (static_cast<size_t>(parity) * p.world + s) * p.num_experts + p.rank * p.nle + c.expert);
+      n = v > 1u ? v - 1u : 0u;
+    }
+    if (n > 0 && first < r1 && first + n > r0 && !((landed >> s) & 1u)) {
+      uint32_t seen;
+      ok = wait_until(arrived + s, PredGe{n}, seen, w, kPhaseFusedGemm, static_cast<uint32_t>(s), n);
+      landed |= 1u << s;
+      waited = true;
+    }
+    first += n;
+  }
+  if (ok && waited) ptx::fence_proxy_async();
+  return ok;
+}
+
 // E8M0 byte of a power-of-two fp32 scale (its exponent field).
 __device__ __forceinline__ uint32_t e8m0_of(float scale) {
   return (__float_as_uint(scale) >> 23) & 0xffu;
@@ -59,7 +93,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                             const __grid_constant__ CUtensorMap tmap_b,
                             const __grid_constant__ Fp8GemmArgs g) {
   static_assert(!(kFromStaging && kToPeers) && !(kToPeers && kSwiGLUQuant), "unsupported form");
-  static_assert(!(kPow2 && kFromStaging), "the staging-fed form folds its scales on CUDA cores");
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* stages = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -179,39 +212,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             last_group = c.expert;
             landed = 0;
           }
-          const WaitCtx w{p.status, p.timeout_ns, static_cast<uint32_t>(p.rank)};
-          const uint32_t* arrived =
-              reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.off_arrived_e) +
-              (static_cast<size_t>(parity) * p.nle + c.expert) * p.world;
-          const uint32_t r0 = static_cast<uint32_t>(c.m_blk * kBlockM);
-          const uint32_t r1 = min(r0 + static_cast<uint32_t>(kBlockM), static_cast<uint32_t>(c.rows));
-          uint32_t first = 0;
-          bool waited = false;
-          for (int s = 0; s < p.world && ok; ++s) {
-            uint32_t n;
-            if (src_rows != nullptr) {
-              n = src_rows[c.expert * p.world + s];
-            } else {
-              const uint32_t v = ptx::ld_relaxed_sys(
-                  reinterpret_cast<const uint32_t*>(p.peer[p.rank] + p.off_counts_all) +
-                  (static_cast<size_t>(parity) * p.world + s) * p.num_experts + p.rank * p.nle +
-                  c.expert);
-              n = v > 1u ? v - 1u : 0u;
-            }
-            if (n > 0 && first < r1 && first + n > r0 && !((landed >> s) & 1u)) {
-              uint32_t seen;
-              ok = wait_until(arrived + s, PredGe{n}, seen, w, kPhaseFusedGemm,
-                              static_cast<uint32_t>(s), n);
-              landed |= 1u << s;
-              waited = true;
-            }
-            first += n;
-          }
+          ok = wait_tile_sources(p, c, parity, src_rows, landed);
           if (!ok) {
             *abort_flag = 1u;
             break;
           }
-          if (waited) ptx::fence_proxy_async();
         }
         const int a_row = static_cast<int>(a_row0[c.expert]) + c.m_blk * kBlockM;
         const int a_plane = kFromStaging ? 0 : c.expert;
@@ -321,16 +326,42 @@ __global__ void __launch_bounds__(kThreads, 1)
     // rows l, l + 32, l + 64, l + 96 of the tile: exactly one 16-byte row of the A atom.
     uint32_t stage = 0, phase = 0;
     bool ok = *abort_flag == 0u;
+    int sf_group = -1;       // kFromStaging: expert that sf_landed refers to
+    uint32_t sf_landed = 0;  // (lane 0) sources of that expert already waited for
     constexpr int kChunk = 8;  // K blocks whose scales are fetched together
     for (uint32_t t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       const Fp8Tile c = locate(tile_start, rows_of, g.num_experts, t);
+      if constexpr (kFromStaging) {
+        // The scales sit behind the rows in the staging that peers write: wait for the same
+        // sources as the TMA producer does (lane 0 acquires, the warp follows).
+        if (c.expert != sf_group) {
+          sf_group = c.expert;
+          sf_landed = 0;
+        }
+        int good = 1;
+        if (lane == 0) good = wait_tile_sources(p, c, parity, src_rows, sf_landed) ? 1 : 0;
+        good = __shfl_sync(0xffffffffu, good, 0);
+        __syncwarp();
+        if (good == 0) {
+          if (lane == 0) *abort_flag = 1u;
+          ok = false;
+          break;
+        }
+      }
       const float* sa_rows[4];
       bool live[4];
 #pragma unroll
       for (int r1 = 0; r1 < 4; ++r1) {
         const int row = c.m_blk * kBlockM + lane + 32 * r1;
         live[r1] = row < c.rows;
-        sa_rows[r1] = g.sa + c.expert * g.sa_stride_e + (live[r1] ? row : 0) * g.sa_stride_row;
+        if constexpr (kFromStaging) {
+          sa_rows[r1] = reinterpret_cast<const float*>(
+              p.peer[p.rank] + p.off_disp_stage +
+              (static_cast<size_t>(a_row0[c.expert]) + (live[r1] ? row : 0)) * p.slot_bytes +
+              p.hidden_bytes);
+        } else {
+          sa_rows[r1] = g.sa + c.expert * g.sa_stride_e + (live[r1] ? row : 0) * g.sa_stride_row;
+        }
       }
       const int wrow0 = kSwiGLUQuant ? c.n_blk * (kTileN / 2) : c.n_blk * kTileN;
       const int wrow1 = kSwiGLUQuant ? g.n_out + wrow0 : wrow0 + kTileN / 2;
@@ -347,7 +378,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           uint32_t v = 0;
 #pragma unroll
           for (int r1 = 0; r1 < 4; ++r1)
-            v |= (live[r1] ? e8m0_of(__ldg(sa_rows[r1] + kb)) : 127u) << (8 * r1);
+            v |= (live[r1] ? e8m0_of(kFromStaging ? __ldcg(sa_rows[r1] + kb) : __ldg(sa_rows[r1] + kb))
+                           : 127u)
+                 << (8 * r1);
           ea[u] = v;
           eb[u] = e8m0_of(__ldg(sw0 + kb)) | (e8m0_of(__ldg(sw1 + kb)) << 8);
         }

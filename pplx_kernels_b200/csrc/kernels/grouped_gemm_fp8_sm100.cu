@@ -276,7 +276,8 @@ void launch_gemm_fp8_from_staging(const Fp8GemmCall& c, const A2AParams& p,
   g.out_num_tokens = out_num_tokens;
   g.a2a = p;
   g.src_table = static_cast<size_t>(p.nle) * p.world <= kMaxSrcEntriesFp8 ? 1 : 0;
-  launch_fp8<true, true, false>(tmap_a, tmap_b, g, c.num_sms, stream);
+  if (c.pow2_scales) launch_fp8<true, true, false, true>(tmap_a, tmap_b, g, c.num_sms, stream);
+  else launch_fp8<true, true, false>(tmap_a, tmap_b, g, c.num_sms, stream);
 }
 
 void launch_gemm_fp8_to_peers(const Fp8GemmCall& c, const A2AParams& p, cudaStream_t stream) {

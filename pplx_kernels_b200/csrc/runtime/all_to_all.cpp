@@ -550,6 +550,7 @@ void AllToAll::fused_up_fp8(const FusedFfnFp8Call& f, cudaStream_t stream) {
   c.n_out = f.inter_dim;
   c.k = params_.hidden_dim;
   c.swiglu_quant = true;
+  c.pow2_scales = params_.quant_pow2 != 0;
   c.num_sms = max_blocks_ > 0 ? std::min(max_blocks_, num_sms_) : num_sms_;
   launch_gemm_fp8_from_staging(c, params_, f.out_num_tokens, stream);
 }
@@ -573,6 +574,7 @@ void AllToAll::fused_down_fp8(const FusedFfnFp8Call& f, cudaStream_t stream) {
   c.sw_stride_row = f.sw_stride_row;
   c.counts = reinterpret_cast<const int32_t*>(params_.recv_count);
   c.status = f.status;
+  c.pow2_scales = params_.quant_pow2 != 0;
   c.num_experts = params_.nle;
   c.rows_per_expert = f.rows_per_expert;
   c.n_out = params_.hidden_dim;

@@ -187,6 +187,8 @@ class AllToAll {
   // Tunables (also settable through PPLX_B200_* environment variables at creation).
   void set_timeout_ms(double ms);
   void set_debug_checks(bool on) { params_.debug_checks = on ? 1 : 0; }
+  // fp8 rows of this object carry power-of-two scales (see A2AParams::quant_pow2).
+  void set_quant_pow2(bool on) { params_.quant_pow2 = on ? 1 : 0; }
   void set_max_blocks(int n) { max_blocks_ = n; }
   // No effect (arrival is counted in columns of the row); kept for source compatibility.
   void set_combine_units(int units);

@@ -55,6 +55,14 @@ def _gather(t: torch.Tensor, world: int) -> torch.Tensor:
     return torch.cat(parts)
 
 
+# fp8 layers: power-of-two scales applied by the tensor cores (--pow2).
+POW2_SCALES = False
+
+
+def _fp8_layer(cfg, **kw):
+    return MoELayerFP8(cfg, pow2_scales=POW2_SCALES, **kw)
+
+
 def verify_layer(layer, fp8: bool, x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor,
                  world: int) -> str:
     """Runs the layer composed and fused and compares both with the reference.  Returns how it
@@ -84,7 +92,8 @@ def verify_layer(layer, fp8: bool, x: torch.Tensor, idx: torch.Tensor, w: torch.
         return "fused against composed (the model is too large to gather for the reference)"
     if fp8:
         w13, w2 = layer.dequantized_weights()
-        want = moe_reference_fp8(x, idx.to(dev), w, _gather(w13, world), _gather(w2, world))
+        want = moe_reference_fp8(x, idx.to(dev), w, _gather(w13, world), _gather(w2, world),
+                                 pow2=POW2_SCALES)
         for name, out in outs.items():
             close(out, want, 0.06, 0.04, f"{name} against the fp8 reference")
     else:
@@ -103,7 +112,7 @@ def measure(model: str, tokens: int, iters: int, warmup: int, rank: int, world: 
     pass is captured once and every timed sample is `replays` back-to-back replays."""
     cfg = CONFIGS[model]
     m = tokens
-    make = MoELayerFP8 if fp8 else MoELayer
+    make = _fp8_layer if fp8 else MoELayer
     layer = make(cfg, max_num_tokens=m, rank=rank, world_size=world, device=dev)
     if world > 1:
         torch.distributed.barrier()  # weight initialisation takes a different time per rank
@@ -198,8 +207,8 @@ def breakdown(model: str, tokens: int, iters: int, warmup: int, rank: int, world
 
     cfg = CONFIGS[model]
     m = tokens
-    layer = (MoELayerFP8 if fp8 else MoELayer)(cfg, max_num_tokens=m, rank=rank, world_size=world,
-                                               device=dev)
+    layer = (_fp8_layer if fp8 else MoELayer)(cfg, max_num_tokens=m, rank=rank, world_size=world,
+                                              device=dev)
     gen = torch.Generator().manual_seed(100 + rank)
     x = torch.randn(m, cfg.hidden_dim, generator=gen).to(torch.bfloat16).to(dev)
     idx = as_index_tensor(routing(m, cfg.num_experts, cfg.experts_per_token, gen), dev)
@@ -214,9 +223,10 @@ def breakdown(model: str, tokens: int, iters: int, warmup: int, rank: int, world
                 ("dispatch_quant", lambda: a.dispatch_quant(L.counts, L.expert_x, L.expert_scale, x, idx, None)),
                 ("up", lambda: grouped_gemm_fp8(L.expert_x, L.expert_scale, L.w13_q, L.w13_s, L.counts,
                                                 swiglu_quant=True, out=L.h, out_scale=L.h_scale,
-                                                status=L.gemm_status)),
+                                                status=L.gemm_status, pow2_scales=POW2_SCALES)),
                 ("down", lambda: grouped_gemm_fp8(L.h, L.h_scale, L.w2_q, L.w2_s, L.counts,
-                                                  out=L.expert_y, status=L.gemm_status)),
+                                                  out=L.expert_y, status=L.gemm_status,
+                                                  pow2_scales=POW2_SCALES)),
                 ("combine", lambda: a.combine(out, idx, w, L.expert_y, None))],
             "fused": [
                 ("fused_dispatch", lambda: a.fused_dispatch(x, idx, None, quantize=True)),
@@ -237,7 +247,8 @@ def breakdown(model: str, tokens: int, iters: int, warmup: int, rank: int, world
                 ("fused_up", lambda: a.fused_up(L.w13, L.h, L.counts, L.gemm_status, expect)),
                 ("fused_down", lambda: a.fused_down(L.h, L.w2, L.gemm_status, expect)),
                 ("combine_recv", lambda: a.combine(out, idx, w, L.expert_y, None, do_send=False))]}
-    report: dict = {"model": cfg.name, "n_gpus": world, "tokens_per_gpu": m, "fp8": fp8}
+    report: dict = {"model": cfg.name, "n_gpus": world, "tokens_per_gpu": m, "fp8": fp8,
+                    "pow2_scales": bool(fp8 and POW2_SCALES)}
     for variant, calls in steps.items():
         samples = []
         for it in range(warmup + iters):
@@ -274,11 +285,15 @@ def main() -> None:
     ap.add_argument("--zipf", type=float, default=0.0)
     ap.add_argument("--graph", action="store_true", help="time CUDA-graph replays")
     ap.add_argument("--fp8", action="store_true", help="block-scaled fp8 layer (MoELayerFP8)")
+    ap.add_argument("--pow2", action="store_true",
+                    help="with --fp8: power-of-two scales, applied by the tensor cores")
     ap.add_argument("--replays", type=int, default=1, help="graph replays per timed sample")
     ap.add_argument("--no-verify", action="store_true", help="skip the output check")
     ap.add_argument("--breakdown", action="store_true",
                     help="time each of the layer's four kernels instead of the layer")
     args = ap.parse_args()
+    global POW2_SCALES
+    POW2_SCALES = bool(args.fp8 and args.pow2)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

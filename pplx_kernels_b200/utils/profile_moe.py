@@ -34,12 +34,15 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=2)
     ap.add_argument("--fused", action="store_true")
     ap.add_argument("--fp8", action="store_true")
+    ap.add_argument("--pow2", action="store_true", help="fp8 with power-of-two (hardware) scales")
     args = ap.parse_args()
 
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     cfg = MoEModelConfig("profile", args.experts, args.topk, args.hidden, args.inter)
-    layer = (MoELayerFP8 if args.fp8 else MoELayer)(cfg, max_num_tokens=args.tokens, device=dev)
+    extra = {"pow2_scales": True} if args.fp8 and args.pow2 else {}
+    layer = (MoELayerFP8 if args.fp8 else MoELayer)(cfg, max_num_tokens=args.tokens, device=dev,
+                                                    **extra)
     gen = torch.Generator().manual_seed(5)
     x = torch.randn(args.tokens, cfg.hidden_dim, generator=gen).to(torch.bfloat16).to(dev)
     idx = as_index_tensor(routing(args.tokens, cfg.num_experts, cfg.experts_per_token, gen), dev)

@@ -114,15 +114,16 @@ def test_fused_layer_in_an_emulated_world(world, dp_size, m):
         l.destroy()
 
 
-def test_fp8_layer_matches_reference():
+@pytest.mark.parametrize("pow2", [False, True], ids=["fp32 scales", "power-of-two scales"])
+def test_fp8_layer_matches_reference(pow2):
     from pplx_kernels_b200.models.moe import MoELayerFP8, moe_reference_fp8
 
     cfg, m = MoEModelConfig("q", 8, 2, 512, 256), 96
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    layer = MoELayerFP8(cfg, max_num_tokens=m, init_std=0.05)
+    layer = MoELayerFP8(cfg, max_num_tokens=m, init_std=0.05, pow2_scales=pow2)
     x, idx, w = _inputs(cfg, m, seed=21, dev=dev)
-    want = moe_reference_fp8(x, idx.to(dev), w, *layer.dequantized_weights())
+    want = moe_reference_fp8(x, idx.to(dev), w, *layer.dequantized_weights(), pow2=pow2)
     for _ in range(2):
         out = layer(x, as_index_tensor(idx, dev), w)
         torch.cuda.synchronize()
@@ -135,16 +136,17 @@ def test_fp8_layer_matches_reference():
 
 @pytest.mark.parametrize("cfg,m", [(MoEModelConfig("q", 8, 2, 512, 256), 96),
                                    (MoEModelConfig("q3", 16, 4, 1024, 384), 300)])
-def test_fused_fp8_layer_matches_reference(cfg, m):
+@pytest.mark.parametrize("pow2", [False, True], ids=["fp32 scales", "power-of-two scales"])
+def test_fused_fp8_layer_matches_reference(cfg, m, pow2):
     """One rank: quantising packed send -> fp8 up projection fed from the staging arena (rows
     and scales) -> fp8 down projection storing into the combine staging -> reduction."""
     from pplx_kernels_b200.models.moe import MoELayerFP8, moe_reference_fp8
 
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    layer = MoELayerFP8(cfg, max_num_tokens=m, init_std=0.05)
+    layer = MoELayerFP8(cfg, max_num_tokens=m, init_std=0.05, pow2_scales=pow2)
     x, idx, w = _inputs(cfg, m, seed=23, dev=dev)
-    want = moe_reference_fp8(x, idx.to(dev), w, *layer.dequantized_weights())
+    want = moe_reference_fp8(x, idx.to(dev), w, *layer.dequantized_weights(), pow2=pow2)
     idx_dev = as_index_tensor(idx, dev)
     composed = layer(x, idx_dev, w).clone()
     for _ in range(3):
@@ -160,7 +162,8 @@ def test_fused_fp8_layer_matches_reference(cfg, m):
 
 
 @pytest.mark.parametrize("world,dp_size,m", [(2, 1, 24), (4, 2, 40), (8, 1, 64)])
-def test_fused_fp8_layer_in_an_emulated_world(world, dp_size, m):
+@pytest.mark.parametrize("pow2", [False, True], ids=["fp32 scales", "power-of-two scales"])
+def test_fused_fp8_layer_in_an_emulated_world(world, dp_size, m, pow2):
     """All ranks on one GPU, each step launched for all ranks before the next one."""
     import pplx_kernels_b200 as pk
     from pplx_kernels_b200.models.moe import MoELayerFP8, moe_reference_fp8
@@ -172,7 +175,7 @@ def test_fused_fp8_layer_in_an_emulated_world(world, dp_size, m):
     atas = pk.AllToAll.local_world(m, cfg.num_experts, cfg.experts_per_token, world, dp_size,
                                    cfg.hidden_dim, cfg.hidden_dim, nscale * 4)
     layers = [MoELayerFP8(cfg, m, rank=r, world_size=world, dp_size=dp_size, device=dev,
-                          ata=atas[r], init_std=0.05) for r in range(world)]
+                          ata=atas[r], init_std=0.05, pow2_scales=pow2) for r in range(world)]
     for a in atas:
         a.set_debug_checks(True)
         a.set_timeout_ms(2000)
@@ -201,7 +204,7 @@ def test_fused_fp8_layer_in_an_emulated_world(world, dp_size, m):
         for r, l in enumerate(layers):
             l.check_status()
             x, idx, w = per_rank[r]
-            want = moe_reference_fp8(x, idx.to(dev), w, w13, w2)
+            want = moe_reference_fp8(x, idx.to(dev), w, w13, w2, pow2=pow2)
             err = (outs[r].float() - want).abs()
             assert (err <= 0.06 * want.abs() + 0.03 * want.abs().amax()).all(), err.max()
     total = sum(int(l.counts.sum()) for l in layers)
