@@ -178,10 +178,11 @@ AllToAll::AllToAll(const A2AConfig& cfg, std::shared_ptr<SymmetricAllocation> ar
                        (ll_limit <= 0 || cfg_.max_num_tokens <= ll_limit)
                    ? 1
                    : 0;
-  // Decode-sized objects (PPLX_B200_TINY_MAX_TOKENS, default 8, 0 = never) run the plain
+  // Decode-sized objects (PPLX_B200_TINY_MAX_TOKENS, default 2, 0 = never) run the plain
   // dispatch as the header-line kernel of dispatch_tiny.cu: about 2 us faster than the general
-  // kernel at one token per rank, level with it from four tokens on.
-  const long tiny_limit = env_long("PPLX_B200_TINY_MAX_TOKENS", 8);
+  // kernel at one token per rank on two GPUs, level with it on eight; from four tokens on the
+  // general kernel is level or ahead.
+  const long tiny_limit = env_long("PPLX_B200_TINY_MAX_TOKENS", 2);
   params_.tiny = params_.ll != 0 && tiny_limit > 0 && cfg_.max_num_tokens <= tiny_limit &&
                          dispatch_tiny_supports(params_)
                      ? 1
