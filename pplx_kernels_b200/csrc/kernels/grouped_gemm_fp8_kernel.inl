@@ -370,8 +370,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           g.sw + c.expert * g.sw_stride_e + min(wrow0 / 128, last_block) * g.sw_stride_row;
       const float* sw1 =
           g.sw + c.expert * g.sw_stride_e + min(wrow1 / 128, last_block) * g.sw_stride_row;
-      for (int kb0 = 0; kb0 < num_kb && ok; kb0 += kChunk) {
-        uint32_t ea[kChunk], eb[kChunk];  // four row bytes, two column-half bytes per K block
+      // Four row bytes and two column-half bytes per K block, fetched a chunk ahead of use.
+      uint32_t ea[kChunk], eb[kChunk], ea_next[kChunk], eb_next[kChunk];
+      auto fetch = [&](int kb0, uint32_t (&da)[kChunk], uint32_t (&db)[kChunk]) {
 #pragma unroll
         for (int u = 0; u < kChunk; ++u) {
           const int kb = min(kb0 + u, num_kb - 1);
@@ -381,9 +382,18 @@ __global__ void __launch_bounds__(kThreads, 1)
             v |= (live[r1] ? e8m0_of(kFromStaging ? __ldcg(sa_rows[r1] + kb) : __ldg(sa_rows[r1] + kb))
                            : 127u)
                  << (8 * r1);
-          ea[u] = v;
-          eb[u] = e8m0_of(__ldg(sw0 + kb)) | (e8m0_of(__ldg(sw1 + kb)) << 8);
+          da[u] = v;
+          db[u] = e8m0_of(__ldg(sw0 + kb)) | (e8m0_of(__ldg(sw1 + kb)) << 8);
         }
+      };
+      fetch(0, ea_next, eb_next);
+      for (int kb0 = 0; kb0 < num_kb && ok; kb0 += kChunk) {
+#pragma unroll
+        for (int u = 0; u < kChunk; ++u) {
+          ea[u] = ea_next[u];
+          eb[u] = eb_next[u];
+        }
+        if (kb0 + kChunk < num_kb) fetch(kb0 + kChunk, ea_next, eb_next);
 #pragma unroll
         for (int u = 0; u < kChunk; ++u) {
           if (kb0 + u >= num_kb || !ok) continue;
