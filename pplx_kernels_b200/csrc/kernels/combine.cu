@@ -268,7 +268,7 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
           // delivers it to all of them.
           uint8_t* slot = p.mc + p.off_comb_stage +
                           (static_cast<size_t>(token) * p.topk + k) * row_bytes;
-          ptx::warp_copy_v4_multicast<16>(slot + (v0 << 4), src + (v0 << 4), nv, lane);
+          ptx::warp_copy_v4_multicast<8>(slot + (v0 << 4), src + (v0 << 4), nv, lane);
         } else {
           for (int r = 0; r < p.dp_size; ++r) {
             uint8_t* slot = p.peer[group_first + r] + p.off_comb_stage +
