@@ -670,6 +670,34 @@ def own_arm(args: argparse.Namespace) -> None:
     line = base_line(world, args.tokens, steps, warmup, numa, res)
     line.update({"roofline": roofline, "clocks": clocks, "gpu_launches": 2 * steps,
                  "moe_layer": moe, "impl": "ours"})
+    if not args.no_moe:
+        # The same layer in block-scaled fp8 with power-of-two scales, which the tensor cores
+        # apply themselves (kind::mxf8f6f4.block_scale).  Informative only: neither an error nor
+        # a rank that never comes back may cost the line above, so a timer prints the line
+        # without this entry and ends the process if the measurement has not returned in time.
+        import threading
+
+        import pplx_kernels_b200.utils.bench_moe as bench_moe_mod
+
+        def give_up() -> None:
+            if rank == 0:
+                line["moe_layer_fp8_hardware_scales"] = {"error": "did not finish in 180 s"}
+                _emit(line)
+            os._exit(0)
+
+        timer = threading.Timer(180.0, give_up)
+        timer.daemon = True
+        timer.start()
+        try:
+            bench_moe_mod.POW2_SCALES = True
+            moe_fp8 = measure_moe("mixtral-8x7b", 512, iters=10, warmup=3, rank=rank, world=world,
+                                  dev=dev, flush=h.flush, fp8=True)
+        except Exception as e:  # noqa: BLE001
+            moe_fp8 = {"error": f"{type(e).__name__}: {e}"[:300]}
+        finally:
+            bench_moe_mod.POW2_SCALES = False
+            timer.cancel()
+        line["moe_layer_fp8_hardware_scales"] = moe_fp8
     if rank == 0:
         _emit(line)
     if world > 1:

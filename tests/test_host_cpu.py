@@ -226,3 +226,27 @@ def test_helpers_of_the_package_import_without_the_native_library():
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=root,
                          timeout=300)
     assert out.returncode == 0, out.stderr[-2000:]
+
+
+def test_power_of_two_quantisation_oracles():
+    """The scales that the hardware-scaled fp8 GEMM takes: powers of two, never below amax / 448,
+    below twice that; values survive the round trip within the e4m3 step."""
+    import torch
+
+    from pplx_kernels_b200.ops.grouped_gemm import quantize_weight_blocks
+    from pplx_kernels_b200.ops.quant import block_dequant, per_token_block_quant
+
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(7, 300, generator=g) * torch.exp2(torch.randint(-8, 8, (7, 1), generator=g).float())
+    q, s = per_token_block_quant(x, pow2=True)
+    assert s.shape == (7, 3) and torch.equal(s, torch.exp2(torch.round(torch.log2(s))))
+    amax = torch.nn.functional.pad(x, (0, 84)).view(7, 3, 128).abs().amax(dim=2).clamp(min=1e-4)
+    assert ((s >= amax / 448.0) & (s < 2 * amax / 448.0 * 1.0001)).all()
+    back = block_dequant(q, s)
+    assert ((back - x).abs() <= 0.0725 * x.abs() + s.repeat_interleave(128, dim=1)[:, :300] * 2 ** -9
+            ).all()
+    w = torch.randn(2, 130, 200, generator=g)
+    wq, ws = quantize_weight_blocks(w, pow2=True)
+    assert ws.shape == (2, 2, 2) and torch.equal(ws, torch.exp2(torch.round(torch.log2(ws))))
+    full = ws.repeat_interleave(128, dim=1)[:, :130].repeat_interleave(128, dim=2)[:, :, :200]
+    assert ((wq.float() * full - w).abs() <= 0.0725 * w.abs() + full * 2 ** -9).all()
