@@ -47,6 +47,7 @@ constexpr int kTinyWarps = kTinyThreads / 32;
 constexpr int kTinyMaxTopk = 32;
 constexpr int kTinyMaxSlots = 29;      // rows of a token per destination: words 1..29 of a header
 constexpr int kTinyMaxEntries = 2048;  // world * tokens per sender * S
+constexpr int kTinyMaxLocalExperts = 1024;
 constexpr uint32_t kNoEntry = 0xffffffffu;
 
 struct TinySmem {
@@ -59,6 +60,7 @@ struct TinySmem {
   uint32_t entry[kTinyMaxEntries];  // [(source, token), j] -> k | le << 16, or kNoEntry
   uint32_t row[kTinyMaxEntries];    // output row of that entry within its expert
   uint16_t list[kTinyMaxEntries];   // the valid entries, compacted
+  uint32_t cnt[kTinyMaxLocalExperts];  // rows assigned so far per local expert
   uint32_t valid;                   // how many
 };
 
@@ -252,41 +254,49 @@ __device__ __forceinline__ void read_headers(const A2AParams& p, TinySmem& sm, i
 }
 
 // From sm.entry: the output row of every entry (the number of earlier entries of the same
-// local expert), the compacted list of valid entries, and -- block 0 -- the totals.
+// local expert, in (source, token, j) order), the compacted list of valid entries, and -- block
+// 0 -- the totals.  One warp walks the entries 32 at a time; lanes that name the same expert find
+// each other with a match instruction, so the cost does not depend on how many experts a rank
+// owns.  Block-wide call.
 __device__ __forceinline__ void assign_rows(const DispatchArgs& a, TinySmem& sm, int entries) {
   const A2AParams& p = a.p;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t lt = (1u << lane) - 1u;
-  for (int le = warp; le < p.nle; le += kTinyWarps) {
-    uint32_t base = 0;
+  for (int le = tid; le < p.nle; le += blockDim.x) sm.cnt[le] = 0;
+  __syncthreads();
+  if (warp == 0) {
+    uint32_t nvalid = 0;
     for (int e0 = 0; e0 < entries; e0 += 32) {
       const int e = e0 + lane;
       const uint32_t v = e < entries ? sm.entry[e] : kNoEntry;
-      const bool hit = v != kNoEntry && (v >> 16) == static_cast<uint32_t>(le);
-      const uint32_t mask = __ballot_sync(0xffffffffu, hit);
-      if (hit) sm.row[e] = base + __popc(mask & lt);
-      base += __popc(mask);
-    }
-    if (blockIdx.x == 0 && lane == 0) {
-      a.out_num_tokens[le] = static_cast<int32_t>(base);
-      p.recv_count[le] = min(base, static_cast<uint32_t>(p.cap));
-    }
-  }
-  if (warp == kTinyWarps - 1) {
-    uint32_t base = 0;
-    for (int e0 = 0; e0 < entries; e0 += 32) {
-      const int e = e0 + lane;
-      const uint32_t v = e < entries ? sm.entry[e] : kNoEntry;
+      const uint32_t le = v >> 16;
       // An entry that names an expert or a k this rank does not have is dropped here.
-      const bool hit = v != kNoEntry && (v >> 16) < static_cast<uint32_t>(p.nle) &&
+      const bool hit = v != kNoEntry && le < static_cast<uint32_t>(p.nle) &&
                        (v & 0xffffu) < static_cast<uint32_t>(p.topk);
       if (v != kNoEntry && !hit)
-        report_failure(p.status, kBadToken, kPhaseDispatchPayload, 0, p.nle, v >> 16, p.rank);
-      const uint32_t mask = __ballot_sync(0xffffffffu, hit);
-      if (hit) sm.list[base + __popc(mask & lt)] = static_cast<uint16_t>(e);
-      base += __popc(mask);
+        report_failure(p.status, kBadToken, kPhaseDispatchPayload, 0, p.nle, le, p.rank);
+      const uint32_t active = __ballot_sync(0xffffffffu, hit);
+      uint32_t same = 0, base = 0;
+      if (hit) {
+        same = __match_any_sync(active, le);
+        base = sm.cnt[le];
+        sm.row[e] = base + __popc(same & lt);
+        sm.list[nvalid + __popc(active & lt)] = static_cast<uint16_t>(e);
+      }
+      __syncwarp();  // every lane of a group has read the count before its first lane moves it on
+      if (hit && (same & lt) == 0u) sm.cnt[le] = base + __popc(same);
+      __syncwarp();
+      nvalid += __popc(active);
     }
-    if (lane == 0) sm.valid = base;
+    if (lane == 0) sm.valid = nvalid;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int le = tid; le < p.nle; le += blockDim.x) {
+      const uint32_t total = sm.cnt[le];
+      a.out_num_tokens[le] = static_cast<int32_t>(total);
+      p.recv_count[le] = min(total, static_cast<uint32_t>(p.cap));
+    }
   }
 }
 
@@ -399,6 +409,7 @@ bool dispatch_tiny_supports(const A2AParams& p) {
   const int S = min(p.topk, p.nle);
   const int tokens_per_sender = ceil_div<int>(p.max_tokens, p.dp_size);
   return p.topk <= kTinyMaxTopk && p.world <= kMaxWorld && S <= kTinyMaxSlots &&
+         p.nle <= kTinyMaxLocalExperts &&
          p.world * tokens_per_sender * S <= kTinyMaxEntries;
 }
 
