@@ -98,7 +98,8 @@ struct Fp8GemmCall {
   int64_t out_stride_e = 0, out_stride_row = 0;  // elements
   float* out_scale = nullptr;   // swiglu_quant: [E][rows][n_out / 128]
   int64_t os_stride_e = 0, os_stride_row = 0;
-  uint32_t* status = nullptr;
+  uint32_t* status = nullptr;   // optional device word: 1 a wait ran out, 2 (pow2_scales) a scale
+                                // was not a power of two
   int num_experts = 0, rows_per_expert = 0, n_out = 0, k = 0;
   bool swiglu_quant = false;    // w = [gate; up]; result silu(gate) * up quantised to e4m3
   // Every scale in sa and sw is a power of two (the caller's promise; mantissa bits would be

@@ -326,6 +326,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // rows l, l + 32, l + 64, l + 96 of the tile: exactly one 16-byte row of the A atom.
     uint32_t stage = 0, phase = 0;
     bool ok = *abort_flag == 0u;
+    uint32_t not_pow2 = 0;   // mantissa bits seen in any scale: the caller's promise was broken
     int sf_group = -1;       // kFromStaging: expert that sf_landed refers to
     uint32_t sf_landed = 0;  // (lane 0) sources of that expert already waited for
     constexpr int kChunk = 8;  // K blocks whose scales are fetched together
@@ -378,12 +379,19 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int kb = min(kb0 + u, num_kb - 1);
           uint32_t v = 0;
 #pragma unroll
-          for (int r1 = 0; r1 < 4; ++r1)
-            v |= (live[r1] ? e8m0_of(kFromStaging ? __ldcg(sa_rows[r1] + kb) : __ldg(sa_rows[r1] + kb))
-                           : 127u)
-                 << (8 * r1);
+          for (int r1 = 0; r1 < 4; ++r1) {
+            uint32_t byte = 127u;
+            if (live[r1]) {
+              const float sc = kFromStaging ? __ldcg(sa_rows[r1] + kb) : __ldg(sa_rows[r1] + kb);
+              not_pow2 |= __float_as_uint(sc) & 0x7fffffu;
+              byte = e8m0_of(sc);
+            }
+            v |= byte << (8 * r1);
+          }
           da[u] = v;
-          db[u] = e8m0_of(__ldg(sw0 + kb)) | (e8m0_of(__ldg(sw1 + kb)) << 8);
+          const float w0 = __ldg(sw0 + kb), w1 = __ldg(sw1 + kb);
+          not_pow2 |= (__float_as_uint(w0) | __float_as_uint(w1)) & 0x7fffffu;
+          db[u] = e8m0_of(w0) | (e8m0_of(w1) << 8);
         }
       };
       fetch(0, ea_next, eb_next);
@@ -420,6 +428,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
+    // A scale with mantissa bits would have been truncated to its exponent: report it
+    // (status 2) instead of returning plausible, wrong numbers.
+    if (__any_sync(0xffffffffu, not_pow2 != 0u) && lane == 0 && g.status != nullptr)
+      atomicMax(g.status, 2u);
   } else if (warp >= 4) {
     const int ew = (warp - 4) & 3;      // tensor-memory lanes [32 * ew, +32)
     const int half = (warp - 4) >> 2;   // columns [64 * half, +64) of each 128-column half
@@ -715,7 +727,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc::tc_fence_after_sync();
     tc::tmem_dealloc(tmem_base, kTmemCols);
   }
-  if (tid == 0 && ctl->abort_flag != 0u && g.status != nullptr) *g.status = 1u;
+  if (tid == 0 && ctl->abort_flag != 0u && g.status != nullptr) atomicMax(g.status, 1u);
   (void)parity;
 }
 

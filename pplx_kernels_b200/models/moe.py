@@ -106,7 +106,11 @@ class MoELayer:
 
     def check_status(self) -> None:
         self.ata.check_status()
-        if int(self.gemm_status.item()) != 0:
+        code = int(self.gemm_status.item())
+        if code == 2:
+            raise RuntimeError("pplx_kernels_b200: a grouped GEMM was told that its scales are "
+                               "powers of two and found one that is not")
+        if code != 0:
             raise RuntimeError("pplx_kernels_b200: a grouped GEMM pipeline wait ran out")
 
     def destroy(self) -> None:
@@ -226,7 +230,11 @@ class MoELayerFP8:
 
     def check_status(self) -> None:
         self.ata.check_status()
-        if int(self.gemm_status.item()) != 0:
+        code = int(self.gemm_status.item())
+        if code == 2:
+            raise RuntimeError("pplx_kernels_b200: a grouped GEMM was told that its scales are "
+                               "powers of two and found one that is not")
+        if code != 0:
             raise RuntimeError("pplx_kernels_b200: a grouped GEMM pipeline wait ran out")
 
     def destroy(self) -> None:

@@ -83,3 +83,19 @@ def test_swiglu_epilogue_quantises_its_result(E, rows, K, I, counts, pow2):
             assert ((got_s >= amax * 0.98) & (got_s <= amax * 2.05)).all()
         else:
             torch.testing.assert_close(hs[e, :m].cpu(), amax, rtol=2e-2, atol=1e-6)
+
+
+def test_hardware_scaling_reports_a_scale_that_is_not_a_power_of_two():
+    """`pow2_scales=True` is a promise; the kernel checks it while it reads the scales and
+    reports status 2 instead of silently dropping mantissa bits."""
+    xq, sa, wq, sw = _operands(1, 128, 256, 256, seed=5, pow2=False)   # amax / 448: not powers of two
+    cnt = torch.tensor([128], dtype=torch.int32, device=xq.device)
+    status = torch.zeros(1, dtype=torch.int32, device=xq.device)
+    grouped_gemm_fp8(xq, sa, wq, sw, cnt, status=status, pow2_scales=True)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 2
+    status.zero_()
+    xq, sa, wq, sw = _operands(1, 128, 256, 256, seed=5, pow2=True)
+    grouped_gemm_fp8(xq, sa, wq, sw, cnt, status=status, pow2_scales=True)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
