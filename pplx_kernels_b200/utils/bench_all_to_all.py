@@ -149,6 +149,9 @@ def main() -> None:
     ap.add_argument("--flush-l2", action="store_true")
     ap.add_argument("--dp-size", type=int, default=1,
                     help="ranks that hold the same tokens (0: all of them)")
+    ap.add_argument("--multimem-ab", action="store_true",
+                    help="run every row twice in this process: arena from CUDA IPC, then from "
+                         "driver allocations bound to an NVLink multicast object")
     ap.add_argument("--out-dir", default="data")
     args = ap.parse_args()
 
@@ -168,18 +171,22 @@ def main() -> None:
     in_dtype, out_dtype = getattr(torch, args.in_dtype), getattr(torch, args.out_dtype)
     flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev) if args.flush_l2 else None
     rows = []
-    for name in args.shapes.split(","):
-        experts, topk, hidden = shapes[name]
-        if experts % world:
-            continue
-        for tok in (int(t) for t in args.tokens.split(",")):
-            cfg = MoEConfig(experts, topk, hidden, tok, in_dtype, out_dtype)
-            row = bench_config(cfg, rank, world, dev, args.zipf, args.repeat, args.samples,
-                               args.warmup, flush, args.dp_size or world)
-            row["shape"] = name
-            rows.append(row)
-            if rank == 0:
-                print(json.dumps(row), flush=True)
+    # The arena's kind is read from the environment when an object is created.
+    modes = ("0", "1") if args.multimem_ab else (os.environ.get("PPLX_B200_MULTIMEM", "0"),)
+    for mode in modes:
+        os.environ["PPLX_B200_MULTIMEM"] = mode
+        for name in args.shapes.split(","):
+            experts, topk, hidden = shapes[name]
+            if experts % world:
+                continue
+            for tok in (int(t) for t in args.tokens.split(",")):
+                cfg = MoEConfig(experts, topk, hidden, tok, in_dtype, out_dtype)
+                row = bench_config(cfg, rank, world, dev, args.zipf, args.repeat, args.samples,
+                                   args.warmup, flush, args.dp_size or world)
+                row["shape"] = name
+                rows.append(row)
+                if rank == 0:
+                    print(json.dumps(row), flush=True)
     if rank == 0:
         out_dir = Path(args.out_dir)
         out_dir.mkdir(parents=True, exist_ok=True)
