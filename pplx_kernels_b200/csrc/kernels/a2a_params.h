@@ -93,6 +93,7 @@ struct A2AParams {
 
   uint8_t* peer[kMaxWorld];  // arena base of every rank as mapped in this process
   uint8_t* mc;  // NVLink multicast alias of the arenas (same offsets on all ranks), or nullptr
+  int mc_combine;  // non-zero: the counter-form combine multicasts rows (tokens replicated on all ranks)
 
   // rank-local state (plain device memory)
   uint32_t* iter;         // dispatch iteration counter; its parity selects the flag set

@@ -234,7 +234,7 @@ __device__ __forceinline__ void send_phase(const CombineArgs& a, const CombineSm
 
   // With the tokens replicated on all ranks and a multicast mapping of the arena, rows and
   // arrival counts are multicast instead of being sent once per rank.
-  const bool to_all = p.mc != nullptr && p.dp_size == p.world;
+  const bool to_all = p.mc != nullptr && p.mc_combine != 0;
   // Rounds: in each, every warp stores at most one part; then one fence and the
   // adds for the whole block.  All warps take part in every round's barriers.
   const uint32_t rounds = ceil_div<uint32_t>(n_units, gwarps);

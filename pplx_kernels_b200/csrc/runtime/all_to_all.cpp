@@ -149,6 +149,15 @@ AllToAll::AllToAll(const A2AConfig& cfg, std::shared_ptr<SymmetricAllocation> ar
   PPLX_CHECK(arena_->bytes() >= params_.arena_bytes, "arena too small");
   for (int r = 0; r < cfg_.world_size; ++r) params_.peer[r] = static_cast<uint8_t*>(arena_->peer(r));
   params_.mc = static_cast<uint8_t*>(arena_->multicast());
+  // Rows of replicated tokens leave once through the multicast mapping where that replaces
+  // several remote copies.  On two ranks it replaces one remote and one local copy and was
+  // measured slower (48 against 31 us at 128 tokens), so the default is four ranks or more;
+  // PPLX_B200_MULTIMEM_COMBINE=1 / 0 forces it on / off.
+  {
+    const long forced = env_long("PPLX_B200_MULTIMEM_COMBINE", -1);
+    const bool possible = params_.mc != nullptr && params_.dp_size == params_.world;
+    params_.mc_combine = possible && (forced > 0 || (forced < 0 && params_.world >= 4)) ? 1 : 0;
+  }
 
   iter_ = DeviceBuffer<uint32_t>(2);
   recv_count_ = DeviceBuffer<uint32_t>(params_.nle);
@@ -413,7 +422,7 @@ CombineArgs AllToAll::make_combine_args(const CombineCall& c) const {
   a.bound_m = c.bound_m;
   a.num_tokens = c.num_tokens;
   // Replicated tokens with a multicast mapping: the counter form, whose send multicasts rows.
-  a.ll = params_.ll != 0 && !(params_.mc != nullptr && params_.dp_size == params_.world) ? 1 : 0;
+  a.ll = params_.ll != 0 && params_.mc_combine == 0 ? 1 : 0;
   return a;
 }
 

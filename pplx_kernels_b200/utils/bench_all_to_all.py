@@ -175,6 +175,8 @@ def main() -> None:
     modes = ("0", "1") if args.multimem_ab else (os.environ.get("PPLX_B200_MULTIMEM", "0"),)
     for mode in modes:
         os.environ["PPLX_B200_MULTIMEM"] = mode
+        if args.multimem_ab:
+            os.environ["PPLX_B200_MULTIMEM_COMBINE"] = "1"  # the comparison is about this path
         for name in args.shapes.split(","):
             experts, topk, hidden = shapes[name]
             if experts % world:

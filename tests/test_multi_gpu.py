@@ -199,6 +199,7 @@ def test_vmm_arena_2_gpu(want_multicast, monkeypatch):
     _need(2)
     monkeypatch.setenv("PPLX_B200_VMM", "1")
     monkeypatch.setenv("PPLX_B200_MULTIMEM", "1" if want_multicast else "0")
+    monkeypatch.setenv("PPLX_B200_MULTIMEM_COMBINE", "1")  # on two ranks it is off by default
     monkeypatch.setenv("NCCL_NVLS_ENABLE", "0")
     parallel_launch(2, _worker_vmm, MoEConfig(16, 4, 512, 24, in_dtype=torch.bfloat16),
                     want_multicast)
