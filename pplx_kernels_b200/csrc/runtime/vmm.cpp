@@ -271,12 +271,18 @@ std::vector<int> exchange_fds(Bootstrap& bs, int my_fd, int timeout_ms) {
                "exchange_fds: bad greeting");
     send_fd(c, my_fd);
   }
-  // Collect the answers.
-  for (int r = 0; r < world; ++r) {
-    if (r != rank) out[r] = recv_fd(outgoing[r], timeout_ms);
+  // Collect the answers.  Should one of them fail, the descriptors already received are closed.
+  try {
+    for (int r = 0; r < world; ++r) {
+      if (r != rank) out[r] = recv_fd(outgoing[r], timeout_ms);
+    }
+    // Nobody closes a socket a peer may still read from.
+    bs.barrier();
+  } catch (...) {
+    for (int fd : out)
+      if (fd >= 0) ::close(fd);
+    throw;
   }
-  // Nobody closes a socket a peer may still read from.
-  bs.barrier();
   return out;
 }
 
