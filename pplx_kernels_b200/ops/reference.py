@@ -86,6 +86,40 @@ def simulate_dispatch(
     return out
 
 
+def simulate_dispatch_by_headers(
+    inputs: Sequence[RankInputs], num_experts: int, dp_size: int, max_num_tokens: int
+) -> list[ExpectedDispatch]:
+    """The decode-sized dispatch (csrc/kernels/dispatch_tiny.cu) restated step by step: every
+    sender writes, for every destination and every one of its token slots (filled or not), a
+    header ``[(k, local expert), ...]``; every receiver walks the headers in (source, token slot,
+    j) order and gives entry number n of a local expert output row n.  The result has to be the
+    very lists that ``simulate_dispatch`` builds, in the same order: the kernel's row order is
+    deterministic, unlike the general kernel's."""
+    from ..parallel.placement import EPLayout
+
+    world = len(inputs)
+    layout = EPLayout(num_experts, world, dp_size)
+    slots_per_sender = -(-max_num_tokens // dp_size)
+    # headers[dst][src][slot] -> [(k, local expert)]
+    headers = [[[[] for _ in range(slots_per_sender)] for _ in range(world)] for _ in range(world)]
+    for src in range(world):
+        idx = inputs[src].indices.cpu().to(torch.int64)
+        for o in range(slots_per_sender):
+            i = o * dp_size + src % dp_size
+            if i >= inputs[src].num_tokens:
+                continue  # the slot's headers stay empty, but they are written
+            for k in range(idx.size(1)):
+                e = int(idx[i, k])
+                headers[layout.owner(e)][src][o].append((k, layout.local_index(e)))
+    out = [ExpectedDispatch([[] for _ in range(layout.num_local_experts)]) for _ in range(world)]
+    for dst in range(world):
+        for src in range(world):
+            for o in range(slots_per_sender):
+                for k, le in headers[dst][src][o]:
+                    out[dst].rows[le].append((src, o * dp_size + src % dp_size, k))
+    return out
+
+
 def simulate_combine(
     inputs: Sequence[RankInputs],
     expert_fn,

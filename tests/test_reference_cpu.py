@@ -172,3 +172,34 @@ def test_simulated_world_invariants_over_random_shapes():
             torch.testing.assert_close(out, inputs[rank].x[:tokens].float(), rtol=1e-5, atol=1e-5)
 
     check()
+
+
+def test_the_decode_sized_protocol_yields_the_oracles_rows_in_the_oracles_order():
+    """Headers per (destination, source, token slot) and a row table derived from them in
+    (source, slot, j) order -- the algorithm of the decode-sized dispatch kernel -- give exactly
+    the per-expert row lists of the oracle, order included, for any routing, DP split, expert
+    count that does not divide, and groups with fewer tokens than slots."""
+    from pplx_kernels_b200.ops.reference import simulate_dispatch_by_headers
+
+    hypothesis = pytest.importorskip("hypothesis")
+    st = hypothesis.strategies
+
+    @hypothesis.settings(max_examples=40, deadline=None)
+    @hypothesis.given(world=st.sampled_from([1, 2, 4, 8]), dp_pow=st.integers(0, 3),
+                      experts=st.integers(1, 24), topk=st.integers(1, 4),
+                      tokens=st.integers(0, 9), slack=st.integers(0, 3),
+                      seed=st.integers(0, 10_000))
+    def check(world, dp_pow, experts, topk, tokens, slack, seed):
+        dp_size = min(world, 1 << dp_pow)
+        topk = min(topk, experts)
+        max_tokens = max(tokens, 1) + slack
+        cfg = MoEConfig(num_experts=experts, experts_per_token=topk, hidden_dim=8,
+                        max_num_tokens=max_tokens, in_dtype=torch.float32,
+                        out_dtype=torch.float32)
+        inputs = _world_inputs(cfg, world // dp_size, dp_size, seed=seed, num_tokens=tokens)
+        want = simulate_dispatch(inputs, experts, dp_size)
+        got = simulate_dispatch_by_headers(inputs, experts, dp_size, max_tokens)
+        for r in range(world):
+            assert got[r].rows == want[r].rows
+
+    check()
